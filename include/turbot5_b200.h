@@ -1,0 +1,180 @@
+/*
+ * turbot5_b200 -- C ABI of the B200 (sm_100a) T5 fused-relative-bias attention path.
+ *
+ * Every entry point takes plain pointers, sizes and element strides, launches on
+ * the CUDA stream it is given (a cudaStream_t passed as void*; NULL = the legacy
+ * default stream), allocates nothing, never synchronises, and returns a
+ * t5b_status (0 = ok).  Device pointers must belong to the current CUDA device.
+ *
+ * Each declaration names the interface of the TurboT5 reference it stands in
+ * for (path inside the reference project : line).
+ */
+#ifndef TURBOT5_B200_H_
+#define TURBOT5_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define T5B_API __attribute__((visibility("default")))
+#else
+#define T5B_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  T5B_OK = 0,
+  T5B_ERR_DTYPE = 1,          /* unknown / unsupported element type                      */
+  T5B_ERR_SHAPE = 2,          /* negative or inconsistent sizes                          */
+  T5B_ERR_ALIGN = 3,          /* pointer or stride not aligned as the kernel needs       */
+  T5B_ERR_HEAD_DIM = 4,       /* head dim not in {16, 32, 64, 128}                       */
+  T5B_ERR_ARG = 5,            /* null pointer, bad flag, bad bucket settings             */
+  T5B_ERR_LAUNCH = 6,         /* the CUDA runtime refused the launch                     */
+  T5B_ERR_DEVICE_TIMEOUT = 7, /* reported through the device status word (see below)     */
+  T5B_ERR_WORKSPACE = 8,      /* scratch buffer missing or too small                     */
+  T5B_ERR_DRIVER = 9,         /* tensor-map encode entry point unavailable / failed      */
+  T5B_ERR_UNSUPPORTED = 10    /* valid request the library has no kernel for             */
+} t5b_status;
+
+typedef enum { T5B_F32 = 0, T5B_F16 = 1, T5B_BF16 = 2 } t5b_dtype;
+
+/* Which kernel family a forward call should use.  AUTO picks the tcgen05/TMA
+ * kernel whenever dtype/shape/alignment allow (bf16 or fp16, head dim 64,
+ * 16-byte aligned rows) and the CUDA-core kernel otherwise. */
+typedef enum { T5B_KERNEL_AUTO = 0, T5B_KERNEL_TCGEN05 = 1, T5B_KERNEL_SIMT = 2 } t5b_kernel;
+
+T5B_API const char* t5b_status_string(int status);
+T5B_API int t5b_abi_version(void);
+
+/* ---- relative-position buckets ------------------------------------------------
+ * Stands in for T5Attention._relative_position_bucket
+ * (src/turbot5/model/attentions.py:78-124).  Writes bucket(delta) for every
+ * delta in [lo, hi] (delta = key position - query position) to out[hi-lo+1]
+ * on the HOST.  This is the table the kernels are driven by. */
+T5B_API int t5b_bucket_table_host(int num_buckets, int max_distance, int bidirectional,
+                          int lo, int hi, int32_t* out);
+
+/* Device check of the same mapping: out[m*N + n] = bucket(n - (q_pos_offset + m)),
+ * computed by the device-side lookup the attention kernels use.  Replaces the
+ * L x L bucket grid of T5Attention.compute_bias (attentions.py:126-137). */
+T5B_API int t5b_bucket_indices(int32_t* out_dev, int M, int N, int q_pos_offset, int bidirectional,
+                       int num_buckets, int max_distance, void* stream);
+
+/* ---- fused-bias flash attention, forward --------------------------------------
+ * Stands in for flash_attention_with_fusing_bias -> FlashAttentionBias.forward ->
+ * flash_attn_v2_fwd_bias (src/turbot5/ops/fused_bias_attention.py:876, 822-849,
+ * 23-59) and, with cu_seqlens set, for flash_attention_with_fusing_bias_varlen
+ * (src/turbot5/ops/varlen_fused_bias_attn.py:870, 802-837, 37-80).
+ *
+ *   out = softmax(sm_scale * Q K^T + table[bucket(delta), h] (+ causal mask)) V
+ *   delta = n - (q_pos_offset + m);  causal keeps delta <= 0 and selects
+ *   unidirectional buckets, exactly as `causal` does in the reference.
+ *
+ * Dense:  q (B,H,M,D), k/v (B,H,N,D), out (B,H,M,D); strides in ELEMENTS for the
+ *         batch, head and row dims; the last dim must have stride 1.
+ * Varlen: cu_seqlens_q/k are int32[B+1] device arrays; q (total_q,H,D),
+ *         k/v (total_k,H,D); stride_b is ignored, M/N are max_seqlen_q/k (upper
+ *         bounds, used only for sizing the grid); positions are relative to each
+ *         sequence and q_pos_offset is len_k - len_q per sequence.
+ * table:  [num_buckets, H] in table_dtype with element stride table_stride0
+ *         between buckets (stride 1 between heads); NULL = no bias.
+ * lse:    optional float32 (B,H,M) dense / (total_q,H) varlen, natural log.
+ * device_status: optional int32 device word; a kernel whose bounded wait ran out
+ *         stores a non-zero code there instead of hanging.
+ */
+typedef struct {
+  const void* q; const void* k; const void* v; void* out;
+  float* lse;
+  const void* table;
+  const int32_t* cu_seqlens_q; const int32_t* cu_seqlens_k;
+  int32_t* device_status;
+  int64_t q_stride_b, q_stride_h, q_stride_m;
+  int64_t k_stride_b, k_stride_h, k_stride_n;
+  int64_t v_stride_b, v_stride_h, v_stride_n;
+  int64_t o_stride_b, o_stride_h, o_stride_m;
+  int64_t table_stride0;
+  int32_t dtype;          /* t5b_dtype of q, k, v, out */
+  int32_t table_dtype;    /* t5b_dtype of table        */
+  int32_t B, H, M, N, D;
+  int32_t total_q, total_k;   /* varlen only */
+  int32_t causal;
+  int32_t num_buckets, max_distance;
+  int32_t q_pos_offset;       /* dense only; the reference's P_SEQ = N - M for cached decoding */
+  int32_t kernel;             /* t5b_kernel */
+  float sm_scale;
+} t5b_attn_args;
+
+T5B_API int t5b_attention_fwd(const t5b_attn_args* args, void* stream);
+
+/* ---- split-KV flash decoding ---------------------------------------------------
+ * Stands in for the split/merge semantics of flash_attn_v2_fwd
+ * (src/turbot5/ops/flash_decoding.py:6-55; never wired into the reference's
+ * modules) and for the cached decode step of T5Attention.forward
+ * (src/turbot5/model/attentions.py:198,229-234): q (B,H,M,D) with small M against
+ * the first kv_len keys of k/v (B,H,capacity,D).  kv_len is either the scalar N
+ * or, when seqlens_k != NULL, int32[B] on the device.  delta = n - (kv_len - M + m)
+ * unless q_pos_offset >= 0 is given explicitly (cross attention passes table=NULL).
+ * Splits are merged inside the same launch by the last block to finish; the
+ * scratch buffer must hold t5b_decode_workspace_bytes(...) bytes and its first
+ * B*H int32 counters must be zero before the first call (the kernel leaves them
+ * zero again). */
+typedef struct {
+  const void* q; const void* k; const void* v; void* out;
+  const void* table;
+  const int32_t* seqlens_k;
+  void* workspace; int64_t workspace_bytes;
+  int64_t q_stride_b, q_stride_h, q_stride_m;
+  int64_t k_stride_b, k_stride_h, k_stride_n;
+  int64_t v_stride_b, v_stride_h, v_stride_n;
+  int64_t o_stride_b, o_stride_h, o_stride_m;
+  int64_t table_stride0;
+  int32_t dtype, table_dtype;
+  int32_t B, H, M, N, D;
+  int32_t causal;              /* unidirectional buckets + causal mask */
+  int32_t num_buckets, max_distance;
+  int32_t q_pos_offset;        /* < 0: kv_len - M */
+  int32_t num_splits;          /* 0 = choose */
+  float sm_scale;
+} t5b_decode_args;
+
+T5B_API int64_t t5b_decode_workspace_bytes(int B, int H, int M, int D, int num_splits);
+T5B_API int t5b_decode_num_splits(int B, int H, int N);
+T5B_API int t5b_decode_fwd(const t5b_decode_args* args, void* stream);
+
+/* ---- T5 RMSNorm, forward -------------------------------------------------------
+ * Stands in for T5LayerNorm._forward (src/turbot5/model/modules.py:52-60) and
+ * RMSLayerNorm.forward / rms_layer_norm_fwd_fused (src/turbot5/ops/rms_norm.py:
+ * 129-152, 5-51).  y = w * round_w(x * rsqrt(mean(x^2) + eps)): float32 variance,
+ * no mean subtraction; when w is fp16/bf16 the normalised value is rounded to w's
+ * type before the multiply and y has w's type, otherwise y is float32.
+ * rstd (optional, float32[rows]) receives rsqrt(mean(x^2)+eps). */
+T5B_API int t5b_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd,
+                    int64_t rows, int32_t d, int64_t x_row_stride, int64_t y_row_stride,
+                    int32_t x_dtype, int32_t w_dtype, float eps, void* stream);
+
+/* ---- unpad / pad glue -----------------------------------------------------------
+ * Stand in for _get_unpad_data, index_first_axis and pad_input
+ * (src/turbot5/model/padding.py:79-88, 46-76, 30-44) without the host
+ * synchronisation of the reference (.item() at padding.py:82).
+ *
+ * t5b_unpad_plan: mask (B, L) of mask_dtype_bytes-wide integers (1/2/4/8; non-zero
+ *   = keep) -> seqlens int32[B], cu_seqlens int32[B+1], dest int32[B*L] (row of
+ *   each kept token in the packed layout, -1 for dropped tokens).
+ * t5b_gather_rows: packed[dest[i], :] = padded[i, :] for kept tokens.
+ * t5b_scatter_rows: padded[i, :] = dest[i] >= 0 ? packed[dest[i], :] : 0.
+ * Rows are row_bytes long (multiple of 16), row strides in bytes. */
+T5B_API int t5b_unpad_plan(const void* mask, int32_t mask_elem_bytes, int32_t B, int32_t L,
+                   int32_t* seqlens, int32_t* cu_seqlens, int32_t* dest, void* stream);
+T5B_API int t5b_gather_rows(const void* padded, int64_t padded_row_stride_bytes, void* packed,
+                    int64_t packed_row_stride_bytes, const int32_t* dest, int64_t n_rows,
+                    int32_t row_bytes, void* stream);
+T5B_API int t5b_scatter_rows(const void* packed, int64_t packed_row_stride_bytes, void* padded,
+                     int64_t padded_row_stride_bytes, const int32_t* dest, int64_t n_rows,
+                     int32_t row_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOT5_B200_H_ */

@@ -1,0 +1,255 @@
+"""Fused relative-position-bias attention: the functional surface.
+
+Same names, argument meaning and error behaviour as the TurboT5 operators they
+replace:
+
+* `flash_attention_with_fusing_bias`         src/turbot5/ops/fused_bias_attention.py:876
+* `flash_attention_with_fusing_bias_varlen`  src/turbot5/ops/varlen_fused_bias_attn.py:870
+
+plus the split-KV decoding operator the reference only sketches
+(src/turbot5/ops/flash_decoding.py) and a bucket-index check.  Forward only.
+"""
+import math
+from typing import Optional
+
+import torch
+
+from . import _native as nat
+
+_status_words = {}
+_workspaces = {}
+
+
+def device_status(device) -> torch.Tensor:
+    """Per-device int32 word the kernels write to when a bounded wait runs out."""
+    dev = torch.device(device)
+    key = (dev.type, dev.index if dev.index is not None else torch.cuda.current_device())
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _status_words[key]
+
+
+def check_device_status(device="cuda") -> None:
+    """Synchronising check of the status word (tests / debugging)."""
+    word = device_status(device)
+    code = int(word.item())
+    if code != 0:
+        word.zero_()
+        raise RuntimeError(f"turbot5_b200 kernel gave up waiting on the device (code {code})")
+
+
+def _check_qkv(q, k, v):
+    Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
+    assert Dq == Dk == Dv
+    assert Dk in {16, 32, 64, 128}
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("q, k and v must share a dtype")
+    nat.require_cuda(q, k, v)
+
+
+def _table_args(bias, H):
+    if bias is None:
+        return None, nat.F32, 0
+    nat.require_cuda(bias)
+    if bias.dim() != 2 or bias.shape[1] != H:
+        raise ValueError(f"bias table must be [NUM_BUCKETS, {H}], got {tuple(bias.shape)}")
+    if bias.stride(1) != 1:
+        bias = bias.contiguous()
+    return bias, nat.dtype_code(bias.dtype), bias.stride(0)
+
+
+def _unit_stride_last(t):
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
+                                     NUM_BUCKETS=32, MAX_DISTANCE=128, *, q_pos_offset=None,
+                                     return_lse=False, kernel="auto"):
+    """softmax(sm_scale * Q K^T + T5 bias(n - m) [+ causal mask]) V without an L x L tensor.
+
+    q (B,H,M,D), k/v (B,H,N,D), any batch/head/row strides (last dim contiguous);
+    bias is the [NUM_BUCKETS, H] relative-attention table or None.  `causal`
+    selects the mask and unidirectional buckets together, as in the reference.
+    `sm_scale=None` means 1/sqrt(D); T5 modules pass 1.0.  The query at row m sits
+    at key position `q_pos_offset + m` (default N - M, the cached-decoding
+    alignment of the reference's `basic` path; sequence parallel callers pass
+    their shard offset).  Returns a tensor with q's shape, dtype and strides.
+    """
+    _check_qkv(q, k, v)
+    B, H, M, D = q.shape
+    N = k.shape[2]
+    if k.shape[:2] != (B, H) or v.shape != k.shape:
+        raise ValueError("k/v must be (B, H, N, D) with q's batch and heads")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    q, k, v = _unit_stride_last(q), _unit_stride_last(k), _unit_stride_last(v)
+    table, tdt, ts0 = _table_args(bias, H)
+    out = torch.empty_like(q)          # preserves q's strides (BHLD view of a BLHD buffer stays free to unshape)
+    if out.stride(-1) != 1:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, M), dtype=torch.float32, device=q.device) if return_lse else None
+    a = nat.AttnArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.lse, a.table = nat.ptr(lse), nat.ptr(table)
+    a.cu_seqlens_q = a.cu_seqlens_k = None
+    a.device_status = device_status(q.device).data_ptr()
+    a.q_stride_b, a.q_stride_h, a.q_stride_m = q.stride(0), q.stride(1), q.stride(2)
+    a.k_stride_b, a.k_stride_h, a.k_stride_n = k.stride(0), k.stride(1), k.stride(2)
+    a.v_stride_b, a.v_stride_h, a.v_stride_n = v.stride(0), v.stride(1), v.stride(2)
+    a.o_stride_b, a.o_stride_h, a.o_stride_m = out.stride(0), out.stride(1), out.stride(2)
+    a.table_stride0 = ts0
+    a.dtype, a.table_dtype = nat.dtype_code(q.dtype), tdt
+    a.B, a.H, a.M, a.N, a.D = B, H, M, N, D
+    a.total_q = a.total_k = 0
+    a.causal = int(bool(causal))
+    a.num_buckets, a.max_distance = int(NUM_BUCKETS), int(MAX_DISTANCE)
+    a.q_pos_offset = (N - M) if q_pos_offset is None else int(q_pos_offset)
+    a.kernel = {"auto": nat.KERNEL_AUTO, "tcgen05": nat.KERNEL_TCGEN05, "simt": nat.KERNEL_SIMT}[kernel]
+    a.sm_scale = float(sm_scale)
+    with torch.cuda.device(q.device):
+        nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)), "flash_attention_with_fusing_bias")
+    return (out, lse) if return_lse else out
+
+
+def flash_attention_with_fusing_bias_varlen(q, k, v, bias, cu_seqlens_q, cu_seqlens_k,
+                                            max_seqlen_q, max_seqlen_k, causal=False, sm_scale=None,
+                                            NUM_BUCKETS=32, MAX_DISTANCE=128, *, return_lse=False,
+                                            kernel="auto"):
+    """Packed-sequence variant: q (Tq,H,D), k/v (Tk,H,D), int32 cu_seqlens on the device.
+
+    Positions are relative to each sequence.  Tiles are scheduled on the device
+    from cu_seqlens: no host loop, no host read of the lengths.  `max_seqlen_*`
+    are accepted for signature compatibility and are not needed.
+    """
+    _check_qkv(q, k, v)
+    Tq, H, D = q.shape
+    Tk = k.shape[0]
+    if k.shape[1:] != (H, D) or v.shape != k.shape:
+        raise ValueError("k/v must be (Tk, H, D) with q's heads")
+    nat.require_cuda(cu_seqlens_q, cu_seqlens_k)
+    if cu_seqlens_q.dtype != torch.int32 or cu_seqlens_k.dtype != torch.int32:
+        raise TypeError("cu_seqlens must be int32")
+    if cu_seqlens_q.numel() != cu_seqlens_k.numel() or cu_seqlens_q.numel() < 1:
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must both hold batch+1 entries")
+    cu_seqlens_q, cu_seqlens_k = cu_seqlens_q.contiguous(), cu_seqlens_k.contiguous()
+    nb = cu_seqlens_q.numel() - 1
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    q, k, v = _unit_stride_last(q), _unit_stride_last(k), _unit_stride_last(v)
+    table, tdt, ts0 = _table_args(bias, H)
+    out = torch.empty_like(q)
+    if out.stride(-1) != 1:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    lse = torch.zeros((Tq, H), dtype=torch.float32, device=q.device) if return_lse else None
+    a = nat.AttnArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.lse, a.table = nat.ptr(lse), nat.ptr(table)
+    a.cu_seqlens_q, a.cu_seqlens_k = cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr()
+    a.device_status = device_status(q.device).data_ptr()
+    a.q_stride_b, a.q_stride_h, a.q_stride_m = 0, q.stride(1), q.stride(0)
+    a.k_stride_b, a.k_stride_h, a.k_stride_n = 0, k.stride(1), k.stride(0)
+    a.v_stride_b, a.v_stride_h, a.v_stride_n = 0, v.stride(1), v.stride(0)
+    a.o_stride_b, a.o_stride_h, a.o_stride_m = 0, out.stride(1), out.stride(0)
+    a.table_stride0 = ts0
+    a.dtype, a.table_dtype = nat.dtype_code(q.dtype), tdt
+    a.B, a.H, a.M, a.N, a.D = nb, H, int(max_seqlen_q or 0), int(max_seqlen_k or 0), D
+    a.total_q, a.total_k = Tq, Tk
+    a.causal = int(bool(causal))
+    a.num_buckets, a.max_distance = int(NUM_BUCKETS), int(MAX_DISTANCE)
+    a.q_pos_offset = 0
+    a.kernel = {"auto": nat.KERNEL_AUTO, "tcgen05": nat.KERNEL_TCGEN05, "simt": nat.KERNEL_SIMT}[kernel]
+    a.sm_scale = float(sm_scale)
+    with torch.cuda.device(q.device):
+        nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)),
+                  "flash_attention_with_fusing_bias_varlen")
+    return (out, lse) if return_lse else out
+
+
+def _decode_workspace(device, nbytes: int) -> torch.Tensor:
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(dev).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        # counters at the front must start at zero; the kernel leaves them zero
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def flash_decoding_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32,
+                                    MAX_DISTANCE=128, *, kv_len=None, seqlens_k=None,
+                                    q_pos_offset=None, num_splits=0, workspace=None):
+    """Split-KV decoding step: q (B,H,M,D) with small M against a K/V cache (B,H,cap,D).
+
+    Only the first `kv_len` keys (default: all) -- or `seqlens_k[b]` keys per batch
+    row, an int32 device tensor -- are attended.  Query row m sits at key position
+    kv_len - M + m unless `q_pos_offset` is given; `causal` gives the decoder
+    self-attention mask and unidirectional buckets, cross attention passes
+    bias=None, causal=False.  One launch: the last block per (batch, head) merges
+    the splits.  Scratch comes from a per-stream cache unless `workspace` is given.
+    """
+    _check_qkv(q, k, v)
+    B, H, M, D = q.shape
+    cap = k.shape[2]
+    N = cap if kv_len is None else int(kv_len)
+    if N > cap or N < 0:
+        raise ValueError("kv_len exceeds the cache capacity")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(D)
+    q, k, v = _unit_stride_last(q), _unit_stride_last(k), _unit_stride_last(v)
+    table, tdt, ts0 = _table_args(bias, H)
+    out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    L = nat.lib()
+    splits = int(num_splits) if num_splits else L.t5b_decode_num_splits(B, H, N)
+    need = L.t5b_decode_workspace_bytes(B, H, M, D, splits) if splits > 1 else 0
+    if workspace is None and need:
+        workspace = _decode_workspace(q.device, need)
+    a = nat.DecodeArgs()
+    a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+    a.table = nat.ptr(table)
+    if seqlens_k is not None:
+        nat.require_cuda(seqlens_k)
+        if seqlens_k.dtype != torch.int32 or seqlens_k.numel() != B:
+            raise TypeError("seqlens_k must be int32 with one entry per batch row")
+        seqlens_k = seqlens_k.contiguous()
+    a.seqlens_k = nat.ptr(seqlens_k)
+    a.workspace = nat.ptr(workspace)
+    a.workspace_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    a.q_stride_b, a.q_stride_h, a.q_stride_m = q.stride(0), q.stride(1), q.stride(2)
+    a.k_stride_b, a.k_stride_h, a.k_stride_n = k.stride(0), k.stride(1), k.stride(2)
+    a.v_stride_b, a.v_stride_h, a.v_stride_n = v.stride(0), v.stride(1), v.stride(2)
+    a.o_stride_b, a.o_stride_h, a.o_stride_m = out.stride(0), out.stride(1), out.stride(2)
+    a.table_stride0 = ts0
+    a.dtype, a.table_dtype = nat.dtype_code(q.dtype), tdt
+    a.B, a.H, a.M, a.N, a.D = B, H, M, N, D
+    a.causal = int(bool(causal))
+    a.num_buckets, a.max_distance = int(NUM_BUCKETS), int(MAX_DISTANCE)
+    a.q_pos_offset = -1 if q_pos_offset is None else int(q_pos_offset)
+    a.num_splits = splits
+    a.sm_scale = float(sm_scale)
+    with torch.cuda.device(q.device):
+        nat.check(L.t5b_decode_fwd(a, nat.stream_ptr(q.device)), "flash_decoding_with_fusing_bias")
+    return out
+
+
+def relative_position_bucket_table(num_buckets=32, max_distance=128, bidirectional=True,
+                                   lo=None, hi=None) -> torch.Tensor:
+    """bucket(delta) for delta in [lo, hi] as an int32 CPU tensor (host table of the library)."""
+    lo = -max_distance - 1 if lo is None else int(lo)
+    hi = max_distance + 1 if hi is None else int(hi)
+    out = torch.empty(hi - lo + 1, dtype=torch.int32)
+    nat.check(nat.lib().t5b_bucket_table_host(int(num_buckets), int(max_distance), int(bool(bidirectional)),
+                                              lo, hi, out.data_ptr()), "relative_position_bucket_table")
+    return out
+
+
+def relative_position_bucket_grid(M, N, q_pos_offset=0, bidirectional=True, num_buckets=32,
+                                  max_distance=128, device="cuda") -> torch.Tensor:
+    """(M, N) int32 bucket indices computed by the device lookup the kernels use."""
+    out = torch.empty((M, N), dtype=torch.int32, device=device)
+    with torch.cuda.device(out.device):
+        nat.check(nat.lib().t5b_bucket_indices(out.data_ptr(), M, N, int(q_pos_offset), int(bool(bidirectional)),
+                                               int(num_buckets), int(max_distance), nat.stream_ptr(out.device)),
+                  "relative_position_bucket_grid")
+    return out

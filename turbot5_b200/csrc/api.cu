@@ -1,0 +1,55 @@
+// C-ABI entry point of the attention forward: validation and kernel choice.
+#include "t5b_common.cuh"
+#include "attn_params.cuh"
+
+using namespace t5b;
+
+extern "C" const char* t5b_status_string(int s) {
+  switch (s) {
+    case T5B_OK: return "ok";
+    case T5B_ERR_DTYPE: return "unsupported element type";
+    case T5B_ERR_SHAPE: return "bad shape";
+    case T5B_ERR_ALIGN: return "pointer or stride not aligned";
+    case T5B_ERR_HEAD_DIM: return "head dim must be 16, 32, 64 or 128";
+    case T5B_ERR_ARG: return "bad argument";
+    case T5B_ERR_LAUNCH: return "kernel launch failed";
+    case T5B_ERR_DEVICE_TIMEOUT: return "a device-side wait ran out";
+    case T5B_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case T5B_ERR_DRIVER: return "tensor-map encode unavailable or failed";
+    case T5B_ERR_UNSUPPORTED: return "no kernel for this request";
+  }
+  return "unknown status";
+}
+
+extern "C" int t5b_abi_version(void) { return 1; }
+
+extern "C" int t5b_attention_fwd(const t5b_attn_args* a, void* stream) {
+  if (!a) return T5B_ERR_ARG;
+  if (a->dtype != T5B_F32 && a->dtype != T5B_F16 && a->dtype != T5B_BF16) return T5B_ERR_DTYPE;
+  if (a->D != 16 && a->D != 32 && a->D != 64 && a->D != 128) return T5B_ERR_HEAD_DIM;
+  if (a->B < 0 || a->H < 0 || a->M < 0 || a->N < 0) return T5B_ERR_SHAPE;
+  const bool varlen = a->cu_seqlens_q != nullptr || a->cu_seqlens_k != nullptr;
+  if (varlen) {
+    if (!a->cu_seqlens_q || !a->cu_seqlens_k) return T5B_ERR_ARG;
+    if (a->total_q < 0 || a->total_k < 0) return T5B_ERR_SHAPE;
+    if (a->B == 0 || a->H == 0 || a->total_q == 0) return T5B_OK;
+  } else {
+    if (a->B == 0 || a->H == 0 || a->M == 0) return T5B_OK;
+  }
+  if (!a->q || !a->out) return T5B_ERR_ARG;
+  if ((!a->k || !a->v) && (varlen ? a->total_k : a->N) > 0) return T5B_ERR_ARG;
+  if (a->kernel < T5B_KERNEL_AUTO || a->kernel > T5B_KERNEL_SIMT) return T5B_ERR_ARG;
+
+  BucketSpec spec;
+  spec.n_side = 2; spec.bidirectional = 0; spec.max_distance = 1; spec.n_first = 0;
+  if (a->table) {
+    if (a->table_dtype != T5B_F32 && a->table_dtype != T5B_F16 && a->table_dtype != T5B_BF16) return T5B_ERR_DTYPE;
+    const int st = make_bucket_spec(a->num_buckets, a->max_distance, a->causal ? 0 : 1, &spec);
+    if (st != T5B_OK) return st;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool tc_ok = sm100_supports(*a) && (varlen ? a->total_k : a->N) > 0;
+  if (a->kernel == T5B_KERNEL_TCGEN05 && !tc_ok) return T5B_ERR_UNSUPPORTED;
+  if (a->kernel != T5B_KERNEL_SIMT && tc_ok) return sm100_attention_fwd(*a, spec, st);
+  return simt_attention_fwd(*a, spec, st);
+}

@@ -1,0 +1,464 @@
+// Fused relative-position-bias flash attention, forward, for sm_100a.
+//
+// One thread block owns one 128-row query tile of one (batch, head) -- or of one
+// packed sequence when cu_seqlens are given -- and walks the key/value tiles:
+//
+//   warp 4      TMA producer: Q once, then K/V tiles into a shared-memory ring
+//               (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers)
+//   warp 5      tensor-core issuer: S = Q K^T and O += P V with tcgen05.mma,
+//               accumulators in tensor memory, tcgen05.commit -> mbarriers
+//   warps 0-3   softmax: thread r owns query row r.  S is read from tensor memory
+//               (tcgen05.ld), the T5 bias is added from a shared-memory copy of
+//               delta -> table[bucket(delta), head] (no L x L tensor exists, no
+//               1/sqrt(d) unless asked), online softmax in registers with lazy
+//               rescaling of O, P written back to tensor memory as bf16/fp16
+//               (tcgen05.st) where the second MMA reads it as its A operand.
+//
+// Two blocks fit on an SM (256 TMEM columns and ~82 KB shared memory each), so one
+// block's softmax overlaps the other block's matrix products.
+//
+// Semantics follow flash_attention_with_fusing_bias
+// (src/turbot5/ops/fused_bias_attention.py:184-365) with positions as in the
+// reference's `basic` path: delta = n - (q_pos_offset + m).
+#include "t5b_common.cuh"
+#include "attn_params.cuh"
+
+#include <cuda.h>
+
+namespace t5b {
+
+namespace sm100 {
+
+constexpr int BM = 128;            // query rows per block
+constexpr int BN = 128;            // keys per tile
+constexpr int HD = 64;             // head dim
+constexpr int STAGES = 2;          // K/V ring depth
+constexpr int TILE_BYTES = BM * HD * 2;      // 16 KB, one 128B-swizzled [128][64] 16-bit tile
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 256;     // S: 128 fp32 columns, P: 64 (packed 16-bit pairs), O: 64
+constexpr int COL_S = 0, COL_P = 128, COL_O = 192;
+constexpr float RESCALE_THRESHOLD = 8.0f;    // log2 units: P stays <= 2^8 before a rescale
+
+// barrier slots
+enum {
+  BAR_Q_FULL = 0,
+  BAR_K_FULL = 1,                    // [STAGES]
+  BAR_V_FULL = BAR_K_FULL + STAGES,  // [STAGES]
+  BAR_K_EMPTY = BAR_V_FULL + STAGES, // [STAGES]
+  BAR_V_EMPTY = BAR_K_EMPTY + STAGES,
+  BAR_S_FULL = BAR_V_EMPTY + STAGES,
+  BAR_P_FULL,
+  BAR_O_DONE,
+  NUM_BARS
+};
+
+struct __align__(8) Control {
+  unsigned long long bars[NUM_BARS];
+  uint32_t tmem_base;
+  int abort_flag;
+  int work[6];   // a TileWork, broadcast from warp 0 for packed sequences
+};
+
+constexpr int SMEM_TILES = (1 + 2 * STAGES) * TILE_BYTES;
+
+__host__ __device__ inline size_t smem_bytes(int lut_entries) {
+  return 1024 /*alignment slack*/ + SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 4;
+}
+
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (kBf16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  } else {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
+                const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v,
+                const __grid_constant__ AttnParams p,
+                const __grid_constant__ BucketSpec spec) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t sQ = base;
+  const uint32_t sK = base + TILE_BYTES;
+  const uint32_t sV = sK + STAGES * TILE_BYTES;
+  Control* ctl = reinterpret_cast<Control*>(smem + SMEM_TILES);
+  float* lut = reinterpret_cast<float*>(smem + SMEM_TILES + ((sizeof(Control) + 15) / 16) * 16);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int h = blockIdx.y;
+
+  // ---------------------------------------------------------------- work item
+  // dense: blockIdx.x = query tile (heaviest causal tiles first), blockIdx.z = batch
+  // varlen: blockIdx.x indexes the concatenated per-sequence tile lists
+  TileWork* shared_work = reinterpret_cast<TileWork*>(&ctl->work[0]);
+  TileWork w;
+  if (p.cu_q == nullptr) {
+    w = dense_tile<BM>(p, (int)blockIdx.x, (int)blockIdx.z);
+  } else {
+    if (warp == 0) {
+      TileWork f = find_varlen_tile<BM>(p, (int)blockIdx.x);
+      if (lane == 0) *shared_work = f;
+    }
+    __syncthreads();
+    w = *shared_work;
+    if (w.b < 0) return;   // block beyond the last tile: uniform exit, nothing allocated yet
+  }
+  const int b = w.b, q_row0 = w.q_row0, rows_in_tile = w.rows_in_tile;
+  const int k_row0 = w.k_row0, len_k = w.len_k, qpos0 = w.qpos0;
+
+  // keys this tile can see
+  int kv_end = len_k;
+  if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
+  const int n_kv = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+
+  // ---------------------------------------------------------------- set-up
+  const uint32_t bar0 = smem_u32(&ctl->bars[0]);
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  if (tid == 0) {
+    ctl->abort_flag = 0;
+    mbar_init(bar(BAR_Q_FULL), 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar(BAR_K_FULL + s), 1);
+      mbar_init(bar(BAR_V_FULL + s), 1);
+      mbar_init(bar(BAR_K_EMPTY + s), 1);
+      mbar_init(bar(BAR_V_EMPTY + s), 1);
+    }
+    mbar_init(bar(BAR_S_FULL), 1);
+    mbar_init(bar(BAR_P_FULL), 128);
+    mbar_init(bar(BAR_O_DONE), 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  // delta -> bias (log2 domain) for this head: index = clamp(delta, -md, md) + md
+  const int md = spec.max_distance;
+  const int lut_n = 2 * md + 1;
+  if (p.table != nullptr) {
+    for (int i = tid; i < lut_n; i += NUM_THREADS) {
+      const int bucket = bucket_of_delta(spec, i - md);
+      lut[i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+  int fail_code = 0;
+
+  if (warp == 4) {
+    // ============================================================ TMA producer
+    if (lane == 0 && n_kv > 0) {
+      mbar_expect_tx(bar(BAR_Q_FULL), TILE_BYTES);
+      tma_load_4d(sQ, &tmap_q, bar(BAR_Q_FULL), 0, q_row0, h, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % STAGES;
+        const uint32_t ph = (uint32_t)((j / STAGES) & 1);
+        if (j >= STAGES && !mbar_wait_bounded(bar(BAR_K_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
+        mbar_expect_tx(bar(BAR_K_FULL + s), TILE_BYTES);
+        tma_load_4d(sK + s * TILE_BYTES, &tmap_k, bar(BAR_K_FULL + s), 0, k_row0 + j * BN, h, b);
+        if (j >= STAGES && !mbar_wait_bounded(bar(BAR_V_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
+        mbar_expect_tx(bar(BAR_V_FULL + s), TILE_BYTES);
+        tma_load_4d(sV + s * TILE_BYTES, &tmap_v, bar(BAR_V_FULL + s), 0, k_row0 + j * BN, h, b);
+      }
+    }
+  } else if (warp == 5) {
+    // ============================================================ MMA issuer
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t IDESC_QK = make_idesc_f16(kBf16, BM, BN, false, false);
+      constexpr uint32_t IDESC_PV = make_idesc_f16(kBf16, BM, HD, false, true);
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j % STAGES;
+        if (!mbar_wait_bounded(bar(BAR_K_FULL + s), (uint32_t)((j / STAGES) & 1), abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t da = make_smem_desc_sw128(sQ, 16, 1024);
+        const uint64_t db = make_smem_desc_sw128(sK + s * TILE_BYTES, 16, 1024);
+        #pragma unroll
+        for (int k = 0; k < HD / 16; ++k)   // 32 bytes of the 128-byte swizzle row per step
+          umma_ss(tmem + COL_S, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC_QK, k > 0);
+        tc_commit(bar(BAR_S_FULL));
+        tc_commit(bar(BAR_K_EMPTY + s));
+        return true;
+      };
+      bool ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0, abort_flag);
+      if (!ok) fail_code = 20;
+      if (ok && !issue_qk(0)) { ok = false; fail_code = 21; }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        if (!mbar_wait_bounded(bar(BAR_P_FULL), (uint32_t)(j & 1), abort_flag)) { fail_code = 22; break; }
+        tc_fence_after();
+        if (j + 1 < n_kv && !issue_qk(j + 1)) { fail_code = 23; break; }
+        const int s = j % STAGES;
+        if (!mbar_wait_bounded(bar(BAR_V_FULL + s), (uint32_t)((j / STAGES) & 1), abort_flag)) { fail_code = 24; break; }
+        tc_fence_after();
+        // V tile is [128 keys][64 dims], dims contiguous: an MN-major B operand.
+        // 8 keys x 128 B per swizzle group (1024 B); each K=16 step covers two groups.
+        #pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          const uint64_t dv = make_smem_desc_sw128(sV + s * TILE_BYTES + k * 2048, 16, 1024);
+          umma_ts(tmem + COL_O, tmem + COL_P + k * 8, dv, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(BAR_O_DONE));
+        tc_commit(bar(BAR_V_EMPTY + s));
+      }
+    }
+  } else {
+    // ============================================================ softmax warps
+    const int r = tid;                             // query row inside the tile
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint32_t tS = tmem + lane_base + COL_S;
+    const uint32_t tP = tmem + lane_base + COL_P;
+    const uint32_t tO = tmem + lane_base + COL_O;
+    const float scale = p.scale_log2;
+    const bool has_bias = p.table != nullptr;
+    const int qpos = qpos0 + r;
+    float m_use = -INFINITY;    // maximum the exponentials are taken against
+    float l_sum = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_kv; ++j) {
+      const int n0 = j * BN;
+      if (!mbar_wait_bounded(bar(BAR_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
+      tc_fence_after();
+
+      // tile classification (uniform over the block)
+      const bool need_mask = (n0 + BN > len_k) || (p.causal && (n0 + BN - 1 > qpos0));
+      int bias_mode = 0;            // 0 none, 1 constant, 2 per element
+      float bias_const = 0.f;
+      if (has_bias) {
+        const int dmin = n0 - (qpos0 + BM - 1), dmax = n0 + BN - 1 - qpos0;
+        if (dmin >= md) { bias_mode = 1; bias_const = lut[2 * md]; }
+        else if (dmax <= -md) { bias_mode = 1; bias_const = lut[0]; }
+        else bias_mode = 2;
+      }
+      const int idx0 = n0 - qpos + md;             // LUT index of column 0 for this row
+      const int n_valid = p.causal ? min(len_k, qpos + 1) : len_k;   // columns < n_valid are visible
+
+      auto score = [&](float s, int col) -> float {
+        float bias = bias_const;
+        if (bias_mode == 2) bias = lut[min(max(idx0 + col, 0), 2 * md)];
+        float x = fmaf(s, scale, bias);
+        if (need_mask && (n0 + col >= n_valid)) x = -INFINITY;
+        return x;
+      };
+
+      // ---- pass 1: row maximum
+      float mx = -INFINITY;
+      #pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(tS + c * 32, v);
+        tmem_ld_wait();
+        #pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, score(__uint_as_float(v[i]), c * 32 + i));
+      }
+      const float m_new = fmaxf(m_use, mx);
+
+      // PV of the previous tile must be complete before P is overwritten / O rescaled
+      if (j > 0) {
+        if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
+        tc_fence_after();
+      }
+      // lazy rescale: only when some row's maximum grew by more than the threshold
+      const bool grow = (m_new - m_use) > RESCALE_THRESHOLD;   // false for -inf - -inf (NaN)
+      if (j == 0) {
+        m_use = m_new;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        float alpha = 1.f;
+        if (grow) { alpha = fast_exp2(m_use - m_new); m_use = m_new; }
+        l_sum *= alpha;
+        #pragma unroll 1
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_x32(tO + c * 32, v);
+          tmem_ld_wait();
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_x32(tO + c * 32, v);
+        }
+      }
+      const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
+
+      // ---- pass 2: exponentials, row sum, P -> tensor memory
+      #pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(tS + c * 32, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+        #pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = fast_exp2(score(__uint_as_float(v[2 * i]), c * 32 + 2 * i) - m_safe);
+          const float p1 = fast_exp2(score(__uint_as_float(v[2 * i + 1]), c * 32 + 2 * i + 1) - m_safe);
+          l_sum += p0 + p1;
+          pk[i] = pack2<kBf16>(p0, p1);
+        }
+        tmem_st_x16(tP + c * 16, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(bar(BAR_P_FULL));
+    }
+
+    // ---- epilogue: O / l -> global
+    if (ok && n_kv > 0) {
+      if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((n_kv - 1) & 1), abort_flag)) { ok = false; fail_code = 32; }
+      tc_fence_after();
+    }
+    if (ok) {
+      const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      const bool row_ok = r < rows_in_tile;
+      const int64_t row = (int64_t)q_row0 + r;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
+                      2 * ((int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + row * p.o_stride_m);
+      #pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t v[32];
+        if (n_kv > 0) {
+          tmem_ld_x32(tO + c * 32, v);
+          tmem_ld_wait();
+        } else {
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (row_ok) {
+          #pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w;
+            w.x = pack2<kBf16>(__uint_as_float(v[8 * i + 0]) * inv_l, __uint_as_float(v[8 * i + 1]) * inv_l);
+            w.y = pack2<kBf16>(__uint_as_float(v[8 * i + 2]) * inv_l, __uint_as_float(v[8 * i + 3]) * inv_l);
+            w.z = pack2<kBf16>(__uint_as_float(v[8 * i + 4]) * inv_l, __uint_as_float(v[8 * i + 5]) * inv_l);
+            w.w = pack2<kBf16>(__uint_as_float(v[8 * i + 6]) * inv_l, __uint_as_float(v[8 * i + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c * 64 + i * 16) = w;
+          }
+        }
+      }
+      if (p.lse != nullptr && row_ok) {
+        const float lse = l_sum > 0.f ? (m_use + log2f(l_sum)) * kLn2 : -INFINITY;
+        if (p.cu_q == nullptr) p.lse[((int64_t)blockIdx.z * p.H + h) * p.M + row] = lse;
+        else p.lse[row * p.H + h] = lse;
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  if (fail_code != 0 && p.status != nullptr) atomicCAS(p.status, 0, 1000 + fail_code);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess) return nullptr;
+    if (qres != cudaDriverEntryPointSuccess) return nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// (D, rows, H, B) view with element strides; box = one [128 rows][64] tile.
+static int make_tmap(CUtensorMap* map, const void* ptr, bool bf16, int64_t rows, int H, int B,
+                     int64_t stride_row, int64_t stride_h, int64_t stride_b) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return T5B_ERR_DRIVER;
+  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)stride_row * 2, (cuuint64_t)stride_h * 2,
+                           (cuuint64_t)(B > 1 ? stride_b : (int64_t)HD) * 2};
+  // unit dims may carry any stride in the caller's tensor; give them a legal one
+  if (H == 1) strides[1] = (cuuint64_t)HD * 2;
+  if (rows == 1) strides[0] = (cuuint64_t)HD * 2;
+  cuuint32_t box[4] = {(cuuint32_t)HD, (cuuint32_t)BM, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? T5B_OK : T5B_ERR_DRIVER;
+}
+
+}  // namespace sm100
+
+// True when the tcgen05 kernel can take this problem.
+bool sm100_supports(const t5b_attn_args& a) {
+  if (a.dtype != T5B_BF16 && a.dtype != T5B_F16) return false;
+  if (a.D != sm100::HD) return false;
+  if (a.max_distance > 2048 && a.table) return false;
+  auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  if (!al16(a.q) || !al16(a.k) || !al16(a.v) || !al16(a.out)) return false;
+  const int64_t s[] = {a.q_stride_b, a.q_stride_h, a.q_stride_m, a.k_stride_b, a.k_stride_h, a.k_stride_n,
+                       a.v_stride_b, a.v_stride_h, a.v_stride_n, a.o_stride_b, a.o_stride_h, a.o_stride_m};
+  for (int64_t x : s) if (x < 0 || (x % 8) != 0) return false;   // 16-byte multiples
+  return true;
+}
+
+int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream) {
+  using namespace sm100;
+  const bool varlen = a.cu_seqlens_q != nullptr;
+  const bool bf16 = a.dtype == T5B_BF16;
+  CUtensorMap mq, mk, mv;
+  int st;
+  if (varlen) {
+    if ((st = make_tmap(&mq, a.q, bf16, a.total_q, a.H, 1, a.q_stride_m, a.q_stride_h, 0)) != T5B_OK) return st;
+    if ((st = make_tmap(&mk, a.k, bf16, a.total_k, a.H, 1, a.k_stride_n, a.k_stride_h, 0)) != T5B_OK) return st;
+    if ((st = make_tmap(&mv, a.v, bf16, a.total_k, a.H, 1, a.v_stride_n, a.v_stride_h, 0)) != T5B_OK) return st;
+  } else {
+    if ((st = make_tmap(&mq, a.q, bf16, a.M, a.H, a.B, a.q_stride_m, a.q_stride_h, a.q_stride_b)) != T5B_OK) return st;
+    if ((st = make_tmap(&mk, a.k, bf16, a.N, a.H, a.B, a.k_stride_n, a.k_stride_h, a.k_stride_b)) != T5B_OK) return st;
+    if ((st = make_tmap(&mv, a.v, bf16, a.N, a.H, a.B, a.v_stride_n, a.v_stride_h, a.v_stride_b)) != T5B_OK) return st;
+  }
+  AttnParams p = make_attn_params(a);
+  const int lut_n = a.table ? 2 * spec.max_distance + 1 : 0;
+  const size_t smem = smem_bytes(lut_n);
+  dim3 grid;
+  if (varlen) {
+    // upper bound on sum_b ceil(len_b / BM) known without reading cu_seqlens
+    const long long ub = (long long)a.total_q / BM + a.B;
+    grid = dim3((unsigned)ub, (unsigned)a.H, 1);
+  } else {
+    grid = dim3((unsigned)((a.M + BM - 1) / BM), (unsigned)a.H, (unsigned)a.B);
+  }
+  if (grid.y > 65535 || grid.z > 65535) return T5B_ERR_SHAPE;
+  auto kern = bf16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[bf16]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(2 * 2048 + 1)) != cudaSuccess) {
+      cudaGetLastError();
+      return T5B_ERR_LAUNCH;
+    }
+    attr_set[bf16] = true;
+  }
+  kern<<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, p, spec);
+  return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;
+}
+
+}  // namespace t5b

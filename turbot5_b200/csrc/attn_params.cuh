@@ -1,0 +1,117 @@
+// Kernel-side view of a forward attention call (both kernel families).
+#pragma once
+
+#include "t5b_common.cuh"
+
+namespace t5b {
+
+struct AttnParams {
+  const void* q; const void* k; const void* v; void* out;
+  float* lse;
+  const void* table;
+  const int32_t* cu_q; const int32_t* cu_k;
+  int32_t* status;
+  int64_t q_stride_b, q_stride_h, q_stride_m;
+  int64_t k_stride_b, k_stride_h, k_stride_n;
+  int64_t v_stride_b, v_stride_h, v_stride_n;
+  int64_t o_stride_b, o_stride_h, o_stride_m;
+  int64_t table_stride0;
+  int32_t table_dtype;
+  int32_t B, H, M, N, D;
+  int32_t causal;
+  int32_t q_pos_offset;
+  float scale_log2;   // sm_scale * log2(e): softmax runs in the base-2 domain
+};
+
+inline AttnParams make_attn_params(const t5b_attn_args& a) {
+  AttnParams p;
+  p.q = a.q; p.k = a.k; p.v = a.v; p.out = a.out;
+  p.lse = a.lse; p.table = a.table;
+  p.cu_q = a.cu_seqlens_q; p.cu_k = a.cu_seqlens_k;
+  p.status = a.device_status;
+  p.q_stride_b = a.q_stride_b; p.q_stride_h = a.q_stride_h; p.q_stride_m = a.q_stride_m;
+  p.k_stride_b = a.k_stride_b; p.k_stride_h = a.k_stride_h; p.k_stride_n = a.k_stride_n;
+  p.v_stride_b = a.v_stride_b; p.v_stride_h = a.v_stride_h; p.v_stride_n = a.v_stride_n;
+  p.o_stride_b = a.o_stride_b; p.o_stride_h = a.o_stride_h; p.o_stride_m = a.o_stride_m;
+  p.table_stride0 = a.table_stride0;
+  p.table_dtype = a.table_dtype;
+  p.B = a.B; p.H = a.H; p.M = a.M; p.N = a.N; p.D = a.D;
+  p.causal = a.causal;
+  p.q_pos_offset = a.q_pos_offset;
+  p.scale_log2 = a.sm_scale * kLog2e;
+  return p;
+}
+
+// Work item of one thread block: a tile of query rows of one (batch | sequence).
+struct TileWork {
+  int b;             // batch index (0 for packed tensors); -1: block has no work
+  int q_row0;        // first query row of the tile (global row for packed tensors)
+  int rows_in_tile;
+  int k_row0;        // first key row of the sequence (0 for dense)
+  int len_k;
+  int qpos0;         // key-coordinate position of the tile's first query row
+};
+
+#ifdef __CUDACC__
+// Packed sequences: block `blk` walks the concatenation of the per-sequence tile
+// lists (ceil(len_q / TILE_M) tiles each).  Called by ONE full warp; the result
+// is valid in every lane.  No host-built work list, no host synchronisation.
+template <int TILE_M>
+__device__ __forceinline__ TileWork find_varlen_tile(const AttnParams& p, int blk) {
+  const int lane = threadIdx.x & 31;
+  int found_b = -1, tile_in_seq = 0, acc = 0;
+  for (int b0 = 0; b0 < p.B && found_b < 0; b0 += 32) {
+    const int bb = b0 + lane;
+    int nt = 0;
+    if (bb < p.B) nt = (p.cu_q[bb + 1] - p.cu_q[bb] + TILE_M - 1) / TILE_M;
+    int incl = nt;
+    #pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int excl = acc + incl - nt;
+    const bool mine = blk >= excl && blk < excl + nt;
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (m) {
+      const int src = __ffs(m) - 1;
+      found_b = b0 + src;
+      tile_in_seq = blk - __shfl_sync(0xffffffffu, excl, src);
+    }
+    acc += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  TileWork w;
+  w.b = -1; w.q_row0 = 0; w.rows_in_tile = 0; w.k_row0 = 0; w.len_k = 0; w.qpos0 = 0;
+  if (found_b >= 0) {
+    const int q0 = p.cu_q[found_b], q1 = p.cu_q[found_b + 1];
+    const int k0 = p.cu_k[found_b], k1 = p.cu_k[found_b + 1];
+    w.b = 0;
+    w.q_row0 = q0 + tile_in_seq * TILE_M;
+    w.rows_in_tile = min(TILE_M, (q1 - q0) - tile_in_seq * TILE_M);
+    w.k_row0 = k0;
+    w.len_k = k1 - k0;
+    w.qpos0 = (k1 - k0) - (q1 - q0) + tile_in_seq * TILE_M;
+  }
+  return w;
+}
+
+template <int TILE_M>
+__device__ __forceinline__ TileWork dense_tile(const AttnParams& p, int blk_x, int blk_z) {
+  TileWork w;
+  const int n_tiles = (p.M + TILE_M - 1) / TILE_M;
+  const int t = n_tiles - 1 - blk_x;          // causal: longest rows first
+  w.b = blk_z;
+  w.q_row0 = t * TILE_M;
+  w.rows_in_tile = min(TILE_M, p.M - w.q_row0);
+  w.k_row0 = 0;
+  w.len_k = p.N;
+  w.qpos0 = p.q_pos_offset + w.q_row0;
+  return w;
+}
+#endif
+
+bool sm100_supports(const t5b_attn_args& a);
+int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream);
+int simt_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream);
+
+}  // namespace t5b
