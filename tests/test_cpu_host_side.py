@@ -1,0 +1,116 @@
+"""CPU-only checks of the C ABI library and the host-side logic (no kernel launches)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import load
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from turbot5_b200 import _native as nat
+    header = open(os.path.join(ROOT, "include", "turbot5_b200.h")).read()
+    declared = set(re.findall(r"T5B_API[^;(]*?\b(t5b_\w+)\s*\(", header))
+    assert declared == set(nat.SYMBOLS), declared ^ set(nat.SYMBOLS)
+    L = ctypes.CDLL(nat.LIB_PATH)
+    for name in declared:
+        assert hasattr(L, name), name
+    assert nat.lib().t5b_abi_version() == 1
+    assert nat.lib().t5b_status_string(0) == b"ok"
+
+
+def test_struct_layouts_match_header_field_order():
+    from turbot5_b200 import _native as nat
+    header = open(os.path.join(ROOT, "include", "turbot5_b200.h")).read()
+    for cname, cls in (("t5b_attn_args", nat.AttnArgs), ("t5b_decode_args", nat.DecodeArgs)):
+        end = header.index("} " + cname + ";")
+        body = header[header.rindex("typedef struct {", 0, end) + len("typedef struct {"):end]
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        names = []
+        for decl in body.split(";"):
+            decl = decl.strip()
+            if not decl:
+                continue
+            parts = decl.replace("*", " ").split(",")
+            names.append(parts[0].split()[-1])
+            names += [p.strip() for p in parts[1:]]
+        assert names == [f[0] for f in cls._fields_], cname
+
+
+def test_host_bucket_table_bit_exact_vs_reference_fixture():
+    import turbot5_b200 as t5b
+    z = load("buckets.npz")
+    for nb, md, bidir, lo, hi in z["settings"]:
+        key = f"nb{nb}_md{md}_{'bi' if bidir else 'uni'}"
+        got = t5b.relative_position_bucket_table(int(nb), int(md), bool(bidir), int(lo), int(hi)).numpy()
+        assert np.array_equal(got, z[key]), key
+
+
+def test_host_bucket_table_rejects_bad_settings():
+    import turbot5_b200 as t5b
+    for nb, md in ((2, 128), (32, 0), (32, 4), (1024, 128)):
+        with pytest.raises(RuntimeError):
+            t5b.relative_position_bucket_table(nb, md, True)
+
+
+def test_decode_split_heuristic_and_workspace_size():
+    from turbot5_b200 import _native as nat
+    L = nat.lib()
+    assert L.t5b_decode_num_splits(64, 16, 8192) >= 2
+    assert L.t5b_decode_num_splits(64, 16, 100) == 1
+    assert L.t5b_decode_num_splits(1, 1, 1 << 20) == 64
+    n = L.t5b_decode_workspace_bytes(64, 16, 1, 64, 8)
+    assert n % 256 == 0 and n >= 64 * 16 * 8 * (64 + 2) * 4
+    assert L.t5b_decode_workspace_bytes(0, 16, 1, 64, 8) == 0
+
+
+def test_cpu_tensors_are_refused_not_silently_computed():
+    import turbot5_b200 as t5b
+    q = torch.zeros((1, 1, 4, 64))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        t5b.flash_attention_with_fusing_bias(q, q, q, None)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        t5b.rms_layer_norm(torch.zeros(2, 8), torch.ones(8))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        t5b.get_unpad_plan(torch.ones((2, 3), dtype=torch.int64))
+
+
+def test_entry_points_validate_arguments_without_a_device():
+    from turbot5_b200 import _native as nat
+    L = nat.lib()
+    assert L.t5b_attention_fwd(None, None) == 5
+    a = nat.AttnArgs()
+    a.dtype, a.D, a.B, a.H, a.M, a.N = 7, 64, 1, 1, 1, 1
+    assert L.t5b_attention_fwd(a, None) == 1           # dtype
+    a.dtype, a.D = nat.BF16, 48
+    assert L.t5b_attention_fwd(a, None) == 4           # head dim
+    a.D, a.M = 64, -1
+    assert L.t5b_attention_fwd(a, None) == 2           # shape
+    a.M = 0
+    assert L.t5b_attention_fwd(a, None) == 0           # empty problem: nothing to do
+    a.M = 1
+    assert L.t5b_attention_fwd(a, None) == 5           # null pointers
+    assert L.t5b_rmsnorm_fwd(None, None, None, None, 1, 8, 8, 8, 0, 0, 1e-6, None) == 5
+    assert L.t5b_decode_fwd(None, None) == 5
+    assert L.t5b_unpad_plan(None, 1, 1, 1, None, None, None, None) == 5
+    assert L.t5b_gather_rows(None, 16, None, 16, None, 1, 16, None) == 5
+
+
+def test_registry_and_module_signature():
+    import inspect
+    import turbot5_b200 as t5b
+    assert t5b.T5ATTENTION_TYPES["flash"] is t5b.T5FlashAttention
+    sig = inspect.signature(t5b.T5FlashAttention.forward)
+    assert list(sig.parameters)[1:] == ["hidden_states", "mask", "key_value_states", "position_bias",
+                                        "past_key_value", "layer_head_mask", "query_length", "use_cache",
+                                        "output_attentions"]
+    sig = inspect.signature(t5b.flash_attention_with_fusing_bias)
+    assert list(sig.parameters)[:8] == ["q", "k", "v", "bias", "causal", "sm_scale", "NUM_BUCKETS", "MAX_DISTANCE"]
+    sig = inspect.signature(t5b.flash_attention_with_fusing_bias_varlen)
+    assert list(sig.parameters)[:12] == ["q", "k", "v", "bias", "cu_seqlens_q", "cu_seqlens_k", "max_seqlen_q",
+                                         "max_seqlen_k", "causal", "sm_scale", "NUM_BUCKETS", "MAX_DISTANCE"]
