@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Benchmark of the fused relative-position-bias attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward pass of the hot path over one batch of synthetic
+input: fused-bias attention at the 8k-token point (T5-base heads: batch 2,
+12 heads x 64, 8192 queries x 8192 keys, bf16, bidirectional buckets 32/128,
+no 1/sqrt(d) scale).  With N > 1 (launched by torchrun, one rank per GPU) every
+rank runs its own batch shard -- attention is independent per batch row, so
+there is no data-path collective -- and the value is the whole-job aggregate
+(weak scaling).  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the reference's own CPU `basic` path (the oracle port:
+bucket grid + bias lookup + einsum/softmax/einsum, all host threads) on a
+bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(name="fused-bias attention fwd, T5-base heads @8k", B=2, H=12, L=8192, D=64,
+                num_buckets=32, max_distance=128)
+L2_BYTES = 126 * 1024 * 1024
+# DRAM traffic (read + write) of one launch of the forward kernel on the workload above,
+# from the ncu capture summarised in profiles/attn_fwd_sm100_8k.md; None until captured.
+NCU_DRAM_BYTES_PER_LAUNCH = None
+
+
+def flops_per_step(w):
+    return 4.0 * w["B"] * w["H"] * w["L"] * w["L"] * w["D"]
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(tflops=float(p["bf16_tflops"]), hbm=float(p["hbm_gbs"]), source="measured (burst)")
+    return dict(tflops=1590.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the GPU is under load."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,utilization.gpu,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.06)
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 10:
+                continue
+            try:
+                clk, mx, util = float(parts[1]), float(parts[2]), float(parts[4])
+            except ValueError:
+                continue
+            smax = mx
+            if util >= 50:
+                sm.append(clk)
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                                     parts[6:10]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=smax,
+                    reasons=sorted(reasons), samples_under_load=len(sm))
+
+
+def cpu_attention_sample(w, heads, threads, rows=None):
+    """The reference's `basic` path (oracle port) on `heads` (batch, head) pairs; returns seconds."""
+    from oracle import t5_oracle as orc
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    L, D = w["L"], w["D"]
+    q = torch.randn((1, heads, L, D), generator=g).bfloat16()
+    k = torch.randn((1, heads, L, D), generator=g).bfloat16()
+    v = torch.randn((1, heads, L, D), generator=g).bfloat16()
+    table = (torch.randn((w["num_buckets"], heads), generator=g) * 0.1).bfloat16()
+    t0 = time.perf_counter()
+    orc.attention_basic(q, k, v, table, causal=False, num_buckets=w["num_buckets"],
+                        max_distance=w["max_distance"], slab=1024, rows=rows)
+    return time.perf_counter() - t0
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the CPU `basic` path on a bounded sample, rank 0 only."""
+    if rank != 0:
+        return
+    w = WORKLOAD
+    cores = os.cpu_count() or 1
+    heads = 1
+    times = []
+    for _ in range(args.warmup_ref):
+        cpu_attention_sample(w, heads, cores)
+    for _ in range(args.steps_ref):
+        times.append(cpu_attention_sample(w, heads, cores))
+    sec = sum(times) / len(times)
+    fl = 4.0 * heads * w["L"] * w["L"] * w["D"]
+    val = fl / sec / 1e12
+    sample = f"{heads} of {w['B'] * w['H']} (batch, head) pairs of the workload per step, fp32 math on bf16 values"
+    line = {
+        "impl": "reference", "metric": "fused_bias_attention_fwd_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps_ref, "warmup": args.warmup_ref, "ms_per_step": sec * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": w["name"], "B": w["B"], "H": w["H"], "M": w["L"],
+                                        "N": w["L"], "D": w["D"], "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary kernel measurements")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    # the CPU arm does far less work per second: bound its run to a few minutes
+    args.steps_ref = max(1, min(args.steps, 3))
+    args.warmup_ref = 1
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    import turbot5_b200 as t5b
+    from turbot5_b200 import _native as nat
+    nat.lib()   # fail loudly if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: turbot5_b200 has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    w = WORKLOAD
+    B, H, L, D = w["B"], w["H"], w["L"], w["D"]
+    dt = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    set_bytes = 3 * B * H * L * D * 2
+    n_sets = max(2, -(-int(1.5 * L2_BYTES) // set_bytes))        # rotating inputs exceed the L2
+
+    def make_set():
+        # (B,H,L,D) views of (B,L,H,D) buffers: the layout the attention module produces
+        return [torch.randn((B, L, H, D), generator=g, device=dev, dtype=torch.float32).to(dt).transpose(1, 2)
+                for _ in range(3)]
+    sets = [make_set() for _ in range(n_sets)]
+    table = (torch.randn((w["num_buckets"], H), generator=g, device=dev) * 0.1).to(dt)
+
+    def step(i):
+        q, k, v = sets[i % n_sets]
+        return t5b.flash_attention_with_fusing_bias(q, k, v, table, causal=False, sm_scale=1.0,
+                                                    NUM_BUCKETS=w["num_buckets"], MAX_DISTANCE=w["max_distance"])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    t5b.check_device_status(dev)
+    ms_step = ms_total / args.steps
+    fl = flops_per_step(w)
+    value = world * fl / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public API with host buffers (pinned): H2D of q/k/v, kernel, D2H of out
+    e2e_steps = max(3, min(args.steps, 20))
+    host_sets = [[t_.contiguous().cpu().pin_memory() for t_ in sets[i % n_sets]] for i in range(2)]
+    host_out = torch.empty((B, H, L, D), dtype=dt).pin_memory()
+    dev_in = [torch.empty((B, H, L, D), dtype=dt, device=dev) for _ in range(3)]
+
+    def e2e_step(i):
+        for d_, h_ in zip(dev_in, host_sets[i % 2]):
+            d_.copy_(h_, non_blocking=True)
+        o = t5b.flash_attention_with_fusing_bias(dev_in[0], dev_in[1], dev_in[2], table, causal=False, sm_scale=1.0,
+                                                 NUM_BUCKETS=w["num_buckets"], MAX_DISTANCE=w["max_distance"])
+        host_out.copy_(o, non_blocking=True)
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / e2e_steps
+    e2e_val = world * fl / (e2e_ms * 1e-3) / 1e12
+
+    secondary = None
+    if not args.no_secondary and rank == 0:
+        secondary = secondary_measurements(t5b, dev)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank == 0:
+        peaks = measured_peaks()
+        achieved = fl / (ms_step * 1e-3) / 1e12
+        line = {
+            "metric": "fused_bias_attention_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "B_per_gpu": B, "H": H, "M": L, "N": L, "D": D,
+                       "num_buckets": w["num_buckets"], "max_distance": w["max_distance"], "causal": False,
+                       "sm_scale": 1.0, "layout": "BHLD views of BLHD buffers", "parallelism": f"batch-sharded x{world}",
+                       "l2": f"inputs rotate over {n_sets} sets ({n_sets * set_bytes / 2**20:.0f} MiB > 126 MiB L2)"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["tflops"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                         "peak_source": peaks["source"], "kernel": "attn_fwd_kernel<bf16>"},
+            "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": set_bytes,
+                    "d2h_bytes_per_step": B * H * L * D * 2, "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            heads = 3
+            sec = cpu_attention_sample(w, heads, cores)
+            line["cpu_baseline"] = {
+                "value": 4.0 * heads * L * L * D / sec / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                "sample": f"{heads} of {B * H} (batch, head) pairs, all {L} rows, {sec:.1f} s of CPU work"}
+        if secondary:
+            line["secondary"] = secondary
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _time(fn, iters, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def secondary_measurements(t5b, dev):
+    """Other kernels of the path at their configured sizes (inputs larger than L2 or rotated)."""
+    out = {}
+    dt = torch.bfloat16
+    peaks = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(7)
+    # RMSNorm, 100000 x 768 bf16 rows (2 x 154 MB traffic > L2)
+    x = torch.randn((100000, 768), generator=g, device=dev).to(dt)
+    wgt = torch.rand((768,), generator=g, device=dev).to(dt)
+    ms = _time(lambda: t5b.rms_layer_norm(x, wgt, 1e-6), 50)
+    gbs = (2 * x.numel() * 2 + 768 * 2) / (ms * 1e-3) / 1e9
+    out["rmsnorm_100000x768_bf16"] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"]}
+    del x
+    # split-KV decoding, one cross-attention layer of the T5-large decode shape: B 64, H 16, N 8192
+    Bd, Hd, Nd = 64, 16, 8192
+    kc = torch.randn((Bd, Hd, Nd, 64), generator=g, device=dev, dtype=torch.float32).to(dt)
+    vc = torch.randn((Bd, Hd, Nd, 64), generator=g, device=dev, dtype=torch.float32).to(dt)
+    qd = torch.randn((Bd, Hd, 1, 64), generator=g, device=dev, dtype=torch.float32).to(dt)
+    ms = _time(lambda: t5b.flash_decoding_with_fusing_bias(qd, kc, vc, None, causal=False, sm_scale=1.0), 20)
+    gbs = (2 * kc.numel() * 2) / (ms * 1e-3) / 1e9
+    out["decode_cross_B64_H16_N8192"] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"]}
+    del kc, vc
+    # packed sequences: 32 sequences, lengths uniform in [128, 4096], T5-base heads
+    lens = torch.randint(128, 4097, (32,), generator=torch.Generator().manual_seed(0))
+    cu = torch.zeros(33, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens, 0)
+    T = int(cu[-1])
+    qkv = [torch.randn((T, 12, 64), generator=g, device=dev, dtype=torch.float32).to(dt) for _ in range(3)]
+    table = (torch.randn((32, 12), generator=g, device=dev) * 0.1).to(dt)
+    cu_d = cu.to(dev)
+    mx = int(lens.max())
+    ms = _time(lambda: t5b.flash_attention_with_fusing_bias_varlen(qkv[0], qkv[1], qkv[2], table, cu_d, cu_d, mx, mx,
+                                                                   sm_scale=1.0), 20)
+    fl = float((4 * 12 * 64 * lens.double() ** 2).sum())
+    out["varlen_32seq_128to4096"] = {"ms": ms, "TFLOP/s": fl / (ms * 1e-3) / 1e12, "tokens": T,
+                                     "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"]}
+    return out
+
+
+if __name__ == "__main__":
+    main()

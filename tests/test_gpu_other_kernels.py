@@ -16,16 +16,20 @@ def _ops():
 
 # ------------------------------------------------------------------ RMSNorm
 def _ulp_close(got, want, dtype):
-    """Equal up to one unit in the last place of `dtype` on a small fraction of elements."""
+    """Equal up to rounding flips: the reference rounds twice in the weight's type (normalised
+    value, then product), so a last-bit difference in rsqrt can move a result by one unit in
+    the last place (rarely two, when both roundings flip)."""
     got, want = got.float().cpu(), want.float()
     if dtype == torch.float32:
         assert (got - want).abs().max().item() <= 2e-6 * max(1.0, want.abs().max().item())
         return
     bits = 8 if dtype == torch.bfloat16 else 11
     ulp = torch.pow(2.0, torch.floor(torch.log2(want.abs().clamp_min(1e-30))) - (bits - 1))
-    bad = (got - want).abs() > ulp * 1.001
-    assert not bad.any(), f"{int(bad.sum())} elements differ by more than one ulp"
-    frac = ((got - want) != 0).float().mean().item()
+    err = (got - want).abs()
+    assert not (err > ulp * 2.001).any(), "an element differs by more than two ulp"
+    frac2 = (err > ulp * 1.001).float().mean().item()
+    assert frac2 < 1e-4, f"{frac2:.3%} of elements differ by two ulp"
+    frac = (err != 0).float().mean().item()
     assert frac < 0.02, f"{frac:.3%} of elements differ"
 
 

@@ -76,6 +76,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
+// kBf16: element type of Q/K/V/out (P uses the same type: tcgen05.mma kind::f16
+// takes A and B of one format; mixing fp16 P with bf16 V is an illegal instruction).
 template <bool kBf16>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -184,8 +186,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   } else if (warp == 5) {
     // ============================================================ MMA issuer
     if (lane == 0 && n_kv > 0) {
-      constexpr uint32_t IDESC_QK = make_idesc_f16(kBf16, BM, BN, false, false);
-      constexpr uint32_t IDESC_PV = make_idesc_f16(kBf16, BM, HD, false, true);
+      constexpr uint32_t IDESC_QK = make_idesc_f16(kBf16, kBf16, BM, BN, false, false);
+      constexpr uint32_t IDESC_PV = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);
       auto issue_qk = [&](int j) -> bool {
         const int s = j % STAGES;
         if (!mbar_wait_bounded(bar(BAR_K_FULL + s), (uint32_t)((j / STAGES) & 1), abort_flag)) return false;
@@ -308,8 +310,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         for (int i = 0; i < 16; ++i) {
           const float p0 = fast_exp2(score(__uint_as_float(v[2 * i]), c * 32 + 2 * i) - m_safe);
           const float p1 = fast_exp2(score(__uint_as_float(v[2 * i + 1]), c * 32 + 2 * i + 1) - m_safe);
-          l_sum += p0 + p1;
           pk[i] = pack2<kBf16>(p0, p1);
+          if (kBf16) {
+            // normalise by the sum of the ROUNDED probabilities the tensor core will
+            // use, so a row dominated by one key stays an exact convex combination
+            l_sum += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
+          } else {
+            l_sum += p0 + p1;
+          }
         }
         tmem_st_x16(tP + c * 16, pk);
       }
@@ -449,13 +457,17 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
   }
   if (grid.y > 65535 || grid.z > 65535) return T5B_ERR_SHAPE;
   auto kern = bf16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[bf16]) {
+  // opt in to > 48 KB of dynamic shared memory once per device and kernel
+  static bool attr_set[64][2] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int which = bf16 ? 1 : 0;
+  if (dev < 0 || dev >= 64 || !attr_set[dev][which]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(2 * 2048 + 1)) != cudaSuccess) {
       cudaGetLastError();
       return T5B_ERR_LAUNCH;
     }
-    attr_set[bf16] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev][which] = true;
   }
   kern<<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, p, spec);
   return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;

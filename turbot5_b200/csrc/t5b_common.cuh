@@ -219,12 +219,12 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
-// Instruction descriptor for kind::f16: fp32 accumulate, A/B both fp16 or both bf16.
-__host__ __device__ constexpr uint32_t make_idesc_f16(bool bf16, int m, int n, bool a_mn_major,
-                                                      bool b_mn_major) {
+// Instruction descriptor for kind::f16: fp32 accumulate, A and B each fp16 or bf16.
+__host__ __device__ constexpr uint32_t make_idesc_f16(bool a_bf16, bool b_bf16, int m, int n,
+                                                      bool a_mn_major, bool b_mn_major) {
   return (1u << 4)                         // D format: f32
-         | ((bf16 ? 1u : 0u) << 7)         // A format
-         | ((bf16 ? 1u : 0u) << 10)        // B format
+         | ((a_bf16 ? 1u : 0u) << 7)       // A format: 0 = f16, 1 = bf16
+         | ((b_bf16 ? 1u : 0u) << 10)      // B format
          | ((a_mn_major ? 1u : 0u) << 15)
          | ((b_mn_major ? 1u : 0u) << 16)
          | ((uint32_t)(n >> 3) << 17)
