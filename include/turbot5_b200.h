@@ -160,9 +160,11 @@ T5B_API int t5b_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd,
  * synchronisation of the reference (.item() at padding.py:82).
  *
  * t5b_unpad_plan: mask (B, L) of mask_dtype_bytes-wide integers (1/2/4/8; non-zero
- *   = keep) -> seqlens int32[B], cu_seqlens int32[B+1], dest int32[B*L] (row of
- *   each kept token in the packed layout, -1 for dropped tokens).
- * t5b_gather_rows: packed[dest[i], :] = padded[i, :] for kept tokens.
+ *   = keep) -> seqlens int32[B], cu_seqlens int32[B+1], dest int32[B*L]: the row of
+ *   each kept token in the packed layout (>= 0); a dropped token gets -2 - r with r
+ *   a distinct row of the unused tail [total_kept, B*L) of the packed buffer.
+ * t5b_gather_rows: packed[dest[i], :] = padded[i, :] for kept tokens, and the tail
+ *   row of every dropped token is zero-filled, so all B*L packed rows are defined.
  * t5b_scatter_rows: padded[i, :] = dest[i] >= 0 ? packed[dest[i], :] : 0.
  * Rows are row_bytes long (multiple of 16), row strides in bytes. */
 T5B_API int t5b_unpad_plan(const void* mask, int32_t mask_elem_bytes, int32_t B, int32_t L,

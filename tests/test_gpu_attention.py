@@ -208,7 +208,9 @@ def test_lse_matches_logsumexp():
     for kernel in KERNELS_16BIT:
         _, lse = t5b.flash_attention_with_fusing_bias(q.cuda(), k.cuda(), v.cuda(), table.cuda(), sm_scale=1.0,
                                                       return_lse=True, kernel=kernel)
-        assert (lse.cpu() - want).abs().max().item() < 2e-3
+        # the tensor-core kernel normalises by the sum of the bf16-rounded probabilities
+        # (each within 2^-9 of its value), so its LSE carries that rounding
+        assert (lse.cpu() - want).abs().max().item() < (5e-3 if kernel == "tcgen05" else 1e-3)
 
 
 def test_empty_and_argument_errors():

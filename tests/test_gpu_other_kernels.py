@@ -172,6 +172,7 @@ def test_unpad_plan_ragged_and_holes(mdt):
     assert torch.equal(packed[:idx.numel()].cpu(), x.reshape(7000, 2, 8)[idx])
     padded = t5b.pad_rows(packed, plan)
     assert torch.equal(padded.cpu(), orc.pad_rows(x.reshape(7000, 2, 8)[idx], idx, 7, 1000))
+    assert torch.count_nonzero(packed[idx.numel():]) == 0          # unused tail is defined (zero)
 
 
 # ------------------------------------------------------------------ module glue

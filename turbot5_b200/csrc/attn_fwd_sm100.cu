@@ -38,6 +38,7 @@ constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 256;     // S: 128 fp32 columns, P: 64 (packed 16-bit pairs), O: 64
 constexpr int COL_S = 0, COL_P = 128, COL_O = 192;
 constexpr float RESCALE_THRESHOLD = 8.0f;    // log2 units: P stays <= 2^8 before a rescale
+constexpr int LUT_PAD = BM + BN;             // bias table padding on each side (entries)
 
 // barrier slots
 enum {
@@ -151,12 +152,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
-  // delta -> bias (log2 domain) for this head: index = clamp(delta, -md, md) + md
+  // delta -> bias (log2 domain) for this head.  Entry i holds delta = i - md - LUT_PAD;
+  // the table is constant beyond +-md, and the padding lets a tile that straddles
+  // the +-md boundary index it without clamping.
   const int md = spec.max_distance;
-  const int lut_n = 2 * md + 1;
+  const int lut_n = 2 * md + 1 + 2 * LUT_PAD;
   if (p.table != nullptr) {
     for (int i = tid; i < lut_n; i += NUM_THREADS) {
-      const int bucket = bucket_of_delta(spec, i - md);
+      const int bucket = bucket_of_delta(spec, i - md - LUT_PAD);
       lut[i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
     }
   }
@@ -243,42 +246,56 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
       // tile classification (uniform over the block)
       const bool need_mask = (n0 + BN > len_k) || (p.causal && (n0 + BN - 1 > qpos0));
-      int bias_mode = 0;            // 0 none, 1 constant, 2 per element
+      int bias_mode = 0;            // 0 none, 1 constant over the tile, 2 per element
       float bias_const = 0.f;
       if (has_bias) {
         const int dmin = n0 - (qpos0 + BM - 1), dmax = n0 + BN - 1 - qpos0;
-        if (dmin >= md) { bias_mode = 1; bias_const = lut[2 * md]; }
-        else if (dmax <= -md) { bias_mode = 1; bias_const = lut[0]; }
+        if (dmin >= md) { bias_mode = 1; bias_const = lut[2 * md + LUT_PAD]; }
+        else if (dmax <= -md) { bias_mode = 1; bias_const = lut[LUT_PAD]; }
         else bias_mode = 2;
       }
-      const int idx0 = n0 - qpos + md;             // LUT index of column 0 for this row
-      const int n_valid = p.causal ? min(len_k, qpos + 1) : len_k;   // columns < n_valid are visible
+      // per-row window into the padded table: column c of this tile reads brow[c]
+      const float* brow = lut + (n0 - qpos + md + LUT_PAD);
+      const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0;   // columns < n_valid are visible
+      const bool fast = !need_mask && bias_mode != 2 && scale > 0.f;
 
-      auto score = [&](float s, int col) -> float {
-        float bias = bias_const;
-        if (bias_mode == 2) bias = lut[min(max(idx0 + col, 0), 2 * md)];
-        float x = fmaf(s, scale, bias);
-        if (need_mask && (n0 + col >= n_valid)) x = -INFINITY;
-        return x;
-      };
+      // Column chunks of 32 are double-buffered: the tcgen05.ld of the next chunk
+      // is in flight while the current one is processed.
+      uint32_t va[32], vb[32];
 
       // ---- pass 1: row maximum
       float mx = -INFINITY;
-      #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_x32(tS + c * 32, v);
-        tmem_ld_wait();
-        #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, score(__uint_as_float(v[i]), c * 32 + i));
-      }
+      auto max_chunk = [&](const uint32_t (&v)[32], int c) {
+        if (fast) {
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        } else if (!need_mask) {
+          #pragma unroll
+          for (int i = 0; i < 32; ++i)
+            mx = fmaxf(mx, fmaf(__uint_as_float(v[i]), scale, bias_mode == 2 ? brow[c * 32 + i] : bias_const));
+        } else {
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float bias = bias_mode == 2 ? brow[c * 32 + i] : bias_const;
+            const float x = fmaf(__uint_as_float(v[i]), scale, bias);
+            mx = fmaxf(mx, (c * 32 + i < n_valid) ? x : -INFINITY);
+          }
+        }
+      };
+      tmem_ld_x32(tS, va); tmem_ld_wait();
+      tmem_ld_x32(tS + 32, vb); max_chunk(va, 0); tmem_ld_wait();
+      tmem_ld_x32(tS + 64, va); max_chunk(vb, 1); tmem_ld_wait();
+      tmem_ld_x32(tS + 96, vb); max_chunk(va, 2); tmem_ld_wait();
+      tmem_ld_x32(tS, va);      max_chunk(vb, 3);            // first chunk of pass 2 already in flight
+      if (fast) mx = fmaf(mx, scale, bias_const);
       const float m_new = fmaxf(m_use, mx);
 
       // PV of the previous tile must be complete before P is overwritten / O rescaled
       if (j > 0) {
-        if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
+        if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; tmem_ld_wait(); break; }
         tc_fence_after();
       }
+      tmem_ld_wait();
       // lazy rescale: only when some row's maximum grew by more than the threshold
       const bool grow = (m_new - m_use) > RESCALE_THRESHOLD;   // false for -inf - -inf (NaN)
       if (j == 0) {
@@ -289,27 +306,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         l_sum *= alpha;
         #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_x32(tO + c * 32, v);
+          tmem_ld_x32(tO + c * 32, vb);
           tmem_ld_wait();
           #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_x32(tO + c * 32, v);
+          for (int i = 0; i < 32; ++i) vb[i] = __float_as_uint(__uint_as_float(vb[i]) * alpha);
+          tmem_st_x32(tO + c * 32, vb);
         }
       }
       const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
+      const float c_fast = bias_const - m_safe;
 
       // ---- pass 2: exponentials, row sum, P -> tensor memory
-      #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_x32(tS + c * 32, v);
-        tmem_ld_wait();
+      auto exp_chunk = [&](const uint32_t (&v)[32], int c) {
         uint32_t pk[16];
         #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(score(__uint_as_float(v[2 * i]), c * 32 + 2 * i) - m_safe);
-          const float p1 = fast_exp2(score(__uint_as_float(v[2 * i + 1]), c * 32 + 2 * i + 1) - m_safe);
+          float x0, x1;
+          if (fast) {
+            x0 = fmaf(__uint_as_float(v[2 * i]), scale, c_fast);
+            x1 = fmaf(__uint_as_float(v[2 * i + 1]), scale, c_fast);
+          } else {
+            const float b0 = (bias_mode == 2 ? brow[c * 32 + 2 * i] : bias_const) - m_safe;
+            const float b1 = (bias_mode == 2 ? brow[c * 32 + 2 * i + 1] : bias_const) - m_safe;
+            x0 = fmaf(__uint_as_float(v[2 * i]), scale, b0);
+            x1 = fmaf(__uint_as_float(v[2 * i + 1]), scale, b1);
+            if (need_mask) {
+              if (c * 32 + 2 * i >= n_valid) x0 = -INFINITY;
+              if (c * 32 + 2 * i + 1 >= n_valid) x1 = -INFINITY;
+            }
+          }
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
           pk[i] = pack2<kBf16>(p0, p1);
           if (kBf16) {
             // normalise by the sum of the ROUNDED probabilities the tensor core will
@@ -320,7 +346,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           }
         }
         tmem_st_x16(tP + c * 16, pk);
-      }
+      };
+      tmem_ld_x32(tS + 32, vb); exp_chunk(va, 0); tmem_ld_wait();
+      tmem_ld_x32(tS + 64, va); exp_chunk(vb, 1); tmem_ld_wait();
+      tmem_ld_x32(tS + 96, vb); exp_chunk(va, 2); tmem_ld_wait();
+      exp_chunk(vb, 3);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL));
@@ -445,7 +475,7 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
     if ((st = make_tmap(&mv, a.v, bf16, a.N, a.H, a.B, a.v_stride_n, a.v_stride_h, a.v_stride_b)) != T5B_OK) return st;
   }
   AttnParams p = make_attn_params(a);
-  const int lut_n = a.table ? 2 * spec.max_distance + 1 : 0;
+  const int lut_n = a.table ? 2 * spec.max_distance + 1 + 2 * LUT_PAD : 0;
   const size_t smem = smem_bytes(lut_n);
   dim3 grid;
   if (varlen) {
@@ -463,7 +493,7 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
   cudaGetDevice(&dev);
   const int which = bf16 ? 1 : 0;
   if (dev < 0 || dev >= 64 || !attr_set[dev][which]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(2 * 2048 + 1)) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(2 * 2048 + 1 + 2 * LUT_PAD)) != cudaSuccess) {
       cudaGetLastError();
       return T5B_ERR_LAUNCH;
     }

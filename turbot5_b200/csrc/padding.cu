@@ -42,15 +42,24 @@ __global__ void count_kernel(const void* mask, int eb, int L, int32_t* seqlens) 
   if (threadIdx.x == 0) seqlens[b] = total;
 }
 
-// one block per batch row: cumulative lengths and destination rows
+// one block per batch row: cumulative lengths and destination rows.  Kept token ->
+// its packed row (>= 0).  Dropped token -> -2 - r, where r is a distinct row of the
+// unused tail of the worst-case-sized packed buffer: the gather zero-fills that row,
+// so the whole packed buffer is defined (a tile that runs past the last sequence
+// must never multiply a zero probability with uninitialised memory).
 __global__ void plan_kernel(const void* mask, int eb, int B, int L, const int32_t* seqlens,
                             int32_t* cu, int32_t* dest) {
   __shared__ int scratch[32];
   __shared__ int warp_base[32];
   const int b = blockIdx.x;
-  int before = 0;
-  for (int i = threadIdx.x; i < b; i += blockDim.x) before += seqlens[i];
+  int before = 0, all = 0;
+  for (int i = threadIdx.x; i < B; i += blockDim.x) {
+    const int n = seqlens[i];
+    all += n;
+    if (i < b) before += n;
+  }
   before = block_sum(before, scratch);
+  all = block_sum(all, scratch);
   if (threadIdx.x == 0) {
     cu[b] = before;
     if (b == B - 1) cu[B] = before + seqlens[b];
@@ -69,7 +78,11 @@ __global__ void plan_kernel(const void* mask, int eb, int B, int L, const int32_
       if (w2 < warp) base += warp_base[w2];
       total += warp_base[w2];
     }
-    if (i < L) dest[(int64_t)b * L + i] = keep ? base + __popc(bal & ((1u << lane) - 1)) : -1;
+    if (i < L) {
+      const int kept_before = base + __popc(bal & ((1u << lane) - 1));   // kept tokens before this one, all rows
+      const int flat = b * L + i;
+      dest[(int64_t)flat] = keep ? kept_before : -2 - (all + (flat - kept_before));
+    }
     run += total;
   }
 }
@@ -82,6 +95,7 @@ __global__ void gather_kernel(const uint4* __restrict__ padded, int64_t ps16, ui
     const int64_t r = i / v16; const int c = (int)(i % v16);
     const int d = dest[r];
     if (d >= 0) packed[(int64_t)d * ks16 + c] = padded[r * ps16 + c];
+    else packed[(int64_t)(-2 - d) * ks16 + c] = make_uint4(0, 0, 0, 0);
   }
 }
 

@@ -16,7 +16,7 @@ from . import _native as nat
 class UnpadPlan(NamedTuple):
     seqlens: torch.Tensor      # int32 (B,)
     cu_seqlens: torch.Tensor   # int32 (B+1,)
-    dest: torch.Tensor         # int32 (B*L,): packed row of each token, -1 for padding
+    dest: torch.Tensor         # int32 (B*L,): packed row of each kept token, negative for padding
     batch: int
     seqlen: int
 
@@ -53,7 +53,7 @@ def _rows(t: torch.Tensor, n_rows: int):
 
 
 def unpad_rows(x: torch.Tensor, plan: UnpadPlan) -> torch.Tensor:
-    """(B, L, ...) -> packed (B*L, ...): kept tokens first, in order; the tail is unspecified."""
+    """(B, L, ...) -> packed (B*L, ...): kept tokens first, in order; the unused tail is zero."""
     nat.require_cuda(x)
     n = plan.batch * plan.seqlen
     src = _rows(x, n)
