@@ -143,6 +143,21 @@ T5B_API int64_t t5b_decode_workspace_bytes(int B, int H, int M, int D, int num_s
 T5B_API int t5b_decode_num_splits(int B, int H, int N);
 T5B_API int t5b_decode_fwd(const t5b_decode_args* args, void* stream);
 
+/* Same decoding step for callers that cannot allocate device memory where they
+ * decode (inside a stream capture, under a frozen memory budget, or from C code
+ * that owns nothing but the input and output buffers).  No counterpart in the
+ * reference.  args->workspace and args->workspace_bytes are ignored: the split
+ * scratch is a fixed 4 MiB array inside the library (held by every GPU that loads
+ * it, until the process exits; t5b_decode_static_scratch_bytes() returns the
+ * size).  Problems whose scratch need (t5b_decode_workspace_bytes) exceeds it are
+ * refused with T5B_ERR_WORKSPACE.  The call allocates nothing and frees nothing.
+ * The first call on each device looks up the array's device address; make it
+ * before any stream capture begins.  All calls share the array: the counters are
+ * cleared on `stream` before each launch, and calls whose kernels overlap on the
+ * GPU (issued on different streams) race on it -- issue them on one stream. */
+T5B_API int64_t t5b_decode_static_scratch_bytes(void);
+T5B_API int t5b_decode_fwd_static_scratch(const t5b_decode_args* args, void* stream);
+
 /* ---- T5 RMSNorm, forward -------------------------------------------------------
  * Stands in for T5LayerNorm._forward (src/turbot5/model/modules.py:52-60) and
  * RMSLayerNorm.forward / rms_layer_norm_fwd_fused (src/turbot5/ops/rms_norm.py:

@@ -391,3 +391,72 @@ extern "C" int t5b_decode_fwd(const t5b_decode_args* a, void* stream) {
   }
   return T5B_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------
+// Decoding without any allocation by the caller or by this library.
+//
+// Some hosts of this kernel cannot call cudaMalloc (or torch's allocator) at the
+// point where they decode: code running while a CUDA stream is being captured,
+// serving loops with a frozen memory budget, or plain C callers that were handed
+// only the input and output buffers.  For them the split-KV scratch lives in a
+// fixed array inside the library image; every GPU that loads the library holds
+// these bytes until the process exits.
+//
+// The array's name is a host-side handle, not a device address, so its address
+// is obtained with cudaGetSymbolAddress once per device (with that device
+// current) on the first call made on that device; make that first call before
+// starting any stream capture.  All calls share the one array: the split counters
+// at its front are cleared on the stream before every launch, and two calls
+// whose kernels overlap on the GPU (different streams) would race on it.
+constexpr long long kStaticScratchBytes = 4ll << 20;   // 4 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+#include <mutex>
+
+static void* static_scratch_address(int* status) {
+  static std::mutex mu;
+  static void* cached[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *status = T5B_ERR_LAUNCH; return nullptr; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress((void**)&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      *status = T5B_ERR_LAUNCH;
+      return nullptr;
+    }
+    cached[dev] = ptr;
+  }
+  *status = T5B_OK;
+  return cached[dev];
+}
+
+extern "C" int64_t t5b_decode_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int t5b_decode_fwd_static_scratch(const t5b_decode_args* a, void* stream) {
+  if (!a) return T5B_ERR_ARG;
+  if (a->B < 0 || a->H < 0 || a->M < 0 || a->N < 0) return T5B_ERR_SHAPE;
+  int splits = a->num_splits > 0 ? a->num_splits : t5b_decode_num_splits(a->B, a->H, a->N);
+  if (a->N == 0) splits = 1;
+  t5b_decode_args b = *a;
+  b.num_splits = splits;
+  b.workspace = nullptr;
+  b.workspace_bytes = 0;
+  if (splits > 1) {
+    const int64_t need = t5b_decode_workspace_bytes(a->B, a->H, a->M, a->D, splits);
+    if (need > kStaticScratchBytes) return T5B_ERR_WORKSPACE;   // beyond the built-in scratch: use t5b_decode_fwd
+    int st = T5B_OK;
+    void* ptr = static_scratch_address(&st);
+    if (st != T5B_OK) return st;
+    // the array keeps whatever the previous call left: the counters must start at zero
+    const int64_t counter_bytes = decode::align256((int64_t)a->B * a->H * 4);
+    if (cudaMemsetAsync(ptr, 0, (size_t)counter_bytes, (cudaStream_t)stream) != cudaSuccess) {
+      cudaGetLastError();
+      return T5B_ERR_LAUNCH;
+    }
+    b.workspace = ptr;
+    b.workspace_bytes = kStaticScratchBytes;
+  }
+  return t5b_decode_fwd(&b, stream);
+}
