@@ -144,8 +144,9 @@ T5B_API int t5b_decode_num_splits(int B, int H, int N);
 T5B_API int t5b_decode_fwd(const t5b_decode_args* args, void* stream);
 
 /* Same decoding step for callers that cannot allocate device memory where they
- * decode (inside a stream capture, under a frozen memory budget, or from C code
- * that owns nothing but the input and output buffers).  No counterpart in the
+ * decode (a serving loop under a frozen memory budget, a latency-critical thread
+ * where an allocation could block, or C code that owns nothing but the input and
+ * output buffers).  No counterpart in the
  * reference.  args->workspace and args->workspace_bytes are ignored: the split
  * scratch is a fixed 4 MiB array inside the library (held by every GPU that loads
  * it, until the process exits; t5b_decode_static_scratch_bytes() returns the

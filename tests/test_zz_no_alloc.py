@@ -1,8 +1,8 @@
 """The allocation-free decoding entry point against the ordinary one.
 
 Some callers cannot allocate device memory at the point where they decode (a
-stream capture in progress, a serving loop with a frozen memory budget, C code
-that was given only inputs and outputs).  `t5b_decode_fwd_static_scratch` keeps
+serving loop with a frozen memory budget, a latency-critical thread where an
+allocation could block, C code that was given only inputs and outputs).  `t5b_decode_fwd_static_scratch` keeps
 the split-KV scratch in a fixed array inside the library instead.  This test
 drives it through the C ABI with caller-owned input and output buffers and
 checks it against `t5b_decode_fwd` on two consecutive calls (the second call

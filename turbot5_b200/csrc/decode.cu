@@ -396,9 +396,9 @@ extern "C" int t5b_decode_fwd(const t5b_decode_args* a, void* stream) {
 // Decoding without any allocation by the caller or by this library.
 //
 // Some hosts of this kernel cannot call cudaMalloc (or torch's allocator) at the
-// point where they decode: code running while a CUDA stream is being captured,
-// serving loops with a frozen memory budget, or plain C callers that were handed
-// only the input and output buffers.  For them the split-KV scratch lives in a
+// point where they decode: serving loops with a frozen memory budget, latency-
+// critical threads where an allocation could block, or plain C callers that were
+// handed only the input and output buffers.  For them the split-KV scratch lives in a
 // fixed array inside the library image; every GPU that loads the library holds
 // these bytes until the process exits.
 //
