@@ -3,18 +3,24 @@
 // One thread block owns one 128-row query tile of one (batch, head) -- or of one
 // packed sequence when cu_seqlens are given -- and walks the key/value tiles:
 //
-//   warp 4      TMA producer: Q once, then K/V tiles into a shared-memory ring
+//   warp 8      TMA producer: Q once, then K/V tiles into a shared-memory ring
 //               (cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers)
-//   warp 5      tensor-core issuer: S = Q K^T and O += P V with tcgen05.mma,
+//   warp 9      tensor-core issuer: S = Q K^T and O += P V with tcgen05.mma,
 //               accumulators in tensor memory, tcgen05.commit -> mbarriers
-//   warps 0-3   softmax: thread r owns query row r.  S is read from tensor memory
-//               (tcgen05.ld), the T5 bias is added from a shared-memory copy of
-//               delta -> table[bucket(delta), head] (no L x L tensor exists, no
-//               1/sqrt(d) unless asked), online softmax in registers with lazy
-//               rescaling of O, P written back to tensor memory as bf16/fp16
-//               (tcgen05.st) where the second MMA reads it as its A operand.
+//   warps 0-7   softmax: two threads share a query row (warp w and warp w+4 see the
+//               same 32 TMEM lanes; one takes key columns 0-63, the other 64-127 and
+//               the matching half of the O columns).  A thread copies its 64 scores
+//               from tensor memory to registers at once (tcgen05.ld) and the S buffer
+//               is handed back immediately, so the next QK^T runs while this tile's
+//               softmax is computed.  The T5 bias is added from a shared-memory copy
+//               of delta -> table[bucket(delta), head] (no L x L tensor exists, no
+//               1/sqrt(d) unless asked); the two halves of a row exchange their
+//               maxima through shared memory; lazy rescaling of O; P is written
+//               back to tensor memory as bf16/fp16 (tcgen05.st) where the second MMA
+//               reads it as its A operand.
+//   warps 8,9   TMA producer and MMA issuer (one elected lane each).
 //
-// Two blocks fit on an SM (256 TMEM columns and ~82 KB shared memory each), so one
+// Two blocks fit on an SM (256 TMEM columns and ~85 KB shared memory each), so one
 // block's softmax overlaps the other block's matrix products.
 //
 // Semantics follow flash_attention_with_fusing_bias
@@ -34,7 +40,9 @@ constexpr int BN = 128;            // keys per tile
 constexpr int HD = 64;             // head dim
 constexpr int STAGES = 2;          // K/V ring depth
 constexpr int TILE_BYTES = BM * HD * 2;      // 16 KB, one 128B-swizzled [128][64] 16-bit tile
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;
+constexpr int SOFTMAX_THREADS = 256;
+constexpr int WARP_TMA = 8, WARP_MMA = 9;
 constexpr int TMEM_COLS = 256;     // S: 128 fp32 columns, P: 64 (packed 16-bit pairs), O: 64
 constexpr int COL_S = 0, COL_P = 128, COL_O = 192;
 constexpr float RESCALE_THRESHOLD = 8.0f;    // log2 units: P stays <= 2^8 before a rescale
@@ -48,6 +56,7 @@ enum {
   BAR_K_EMPTY = BAR_V_FULL + STAGES, // [STAGES]
   BAR_V_EMPTY = BAR_K_EMPTY + STAGES,
   BAR_S_FULL = BAR_V_EMPTY + STAGES,
+  BAR_S_FREE,
   BAR_P_FULL,
   BAR_O_DONE,
   NUM_BARS
@@ -58,6 +67,7 @@ struct __align__(8) Control {
   uint32_t tmem_base;
   int abort_flag;
   int work[6];   // a TileWork, broadcast from warp 0 for packed sequences
+  float xchg[2][2][BM];   // [tile parity][column half][row]: row maxima; at the end: row sums
 };
 
 constexpr int SMEM_TILES = (1 + 2 * STAGES) * TILE_BYTES;
@@ -138,17 +148,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       mbar_init(bar(BAR_V_EMPTY + s), 1);
     }
     mbar_init(bar(BAR_S_FULL), 1);
-    mbar_init(bar(BAR_P_FULL), 128);
+    mbar_init(bar(BAR_S_FREE), SOFTMAX_THREADS);
+    mbar_init(bar(BAR_P_FULL), SOFTMAX_THREADS);
     mbar_init(bar(BAR_O_DONE), 1);
     fence_barrier_init();
     fence_proxy_async();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == WARP_TMA && lane == 0) {
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
   }
-  if (warp == 5) {
+  if (warp == WARP_MMA) {
     tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
     tmem_relinquish();
   }
@@ -170,7 +181,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   volatile int* abort_flag = &ctl->abort_flag;
   int fail_code = 0;
 
-  if (warp == 4) {
+  if (warp == WARP_TMA) {
     // ============================================================ TMA producer
     if (lane == 0 && n_kv > 0) {
       mbar_expect_tx(bar(BAR_Q_FULL), TILE_BYTES);
@@ -186,7 +197,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tma_load_4d(sV + s * TILE_BYTES, &tmap_v, bar(BAR_V_FULL + s), 0, k_row0 + j * BN, h, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == WARP_MMA) {
     // ============================================================ MMA issuer
     if (lane == 0 && n_kv > 0) {
       constexpr uint32_t IDESC_QK = make_idesc_f16(kBf16, kBf16, BM, BN, false, false);
@@ -208,9 +219,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (!ok) fail_code = 20;
       if (ok && !issue_qk(0)) { ok = false; fail_code = 21; }
       for (int j = 0; ok && j < n_kv; ++j) {
+        if (j + 1 < n_kv) {
+          // S has been copied to registers: the next QK^T overlaps this tile's softmax
+          if (!mbar_wait_bounded(bar(BAR_S_FREE), (uint32_t)(j & 1), abort_flag)) { fail_code = 25; break; }
+          tc_fence_after();
+          if (!issue_qk(j + 1)) { fail_code = 23; break; }
+        }
         if (!mbar_wait_bounded(bar(BAR_P_FULL), (uint32_t)(j & 1), abort_flag)) { fail_code = 22; break; }
         tc_fence_after();
-        if (j + 1 < n_kv && !issue_qk(j + 1)) { fail_code = 23; break; }
         const int s = j % STAGES;
         if (!mbar_wait_bounded(bar(BAR_V_FULL + s), (uint32_t)((j / STAGES) & 1), abort_flag)) { fail_code = 24; break; }
         tc_fence_after();
@@ -225,24 +241,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tc_commit(bar(BAR_V_EMPTY + s));
       }
     }
-  } else {
+  } else if (warp < 8) {
     // ============================================================ softmax warps
-    const int r = tid;                             // query row inside the tile
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const uint32_t tS = tmem + lane_base + COL_S;
-    const uint32_t tP = tmem + lane_base + COL_P;
-    const uint32_t tO = tmem + lane_base + COL_O;
+    const int quarter = warp & 3;                  // TMEM lane quarter this warp may touch
+    const int half = warp >> 2;                    // which 64 key columns / 32 output columns
+    const int r = quarter * 32 + lane;             // query row inside the tile
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + lane_base + COL_S + half * 64;
+    const uint32_t tP = tmem + lane_base + COL_P + half * 32;
+    const uint32_t tO = tmem + lane_base + COL_O + half * 32;
     const float scale = p.scale_log2;
     const bool has_bias = p.table != nullptr;
     const int qpos = qpos0 + r;
+    const int pair_bar = 1 + quarter;              // named barrier shared by warps w and w+4
     float m_use = -INFINITY;    // maximum the exponentials are taken against
-    float l_sum = 0.f;
+    float l_sum = 0.f;          // this thread's half of the row sum
     bool ok = true;
 
     for (int j = 0; j < n_kv; ++j) {
-      const int n0 = j * BN;
+      const int n0 = j * BN;                       // first key of the tile
+      const int c0 = half * 64;                    // first column of this thread inside the tile
       if (!mbar_wait_bounded(bar(BAR_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
+
+      // this thread's 64 scores -> registers, then give the S buffer back to the MMA warp
+      uint32_t sv[2][32];
+      tmem_ld_x32(tS, sv[0]);
+      tmem_ld_x32(tS + 32, sv[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(bar(BAR_S_FREE));
 
       // tile classification (uniform over the block)
       const bool need_mask = (n0 + BN > len_k) || (p.causal && (n0 + BN - 1 > qpos0));
@@ -254,49 +282,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         else if (dmax <= -md) { bias_mode = 1; bias_const = lut[LUT_PAD]; }
         else bias_mode = 2;
       }
-      // per-row window into the padded table: column c of this tile reads brow[c]
-      const float* brow = lut + (n0 - qpos + md + LUT_PAD);
-      const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0;   // columns < n_valid are visible
       const bool fast = !need_mask && bias_mode != 2 && scale > 0.f;
 
-      // Column chunks of 32 are double-buffered: the tcgen05.ld of the next chunk
-      // is in flight while the current one is processed.
-      uint32_t va[32], vb[32];
-
-      // ---- pass 1: row maximum
+      // ---- row maximum.  Fast tiles (no mask, constant bias): max of the raw scores,
+      // transformed once.  Other tiles: x = s*scale + bias(delta) (+ mask) in place first.
       float mx = -INFINITY;
-      auto max_chunk = [&](const uint32_t (&v)[32], int c) {
-        if (fast) {
+      if (fast) {
+        #pragma unroll
+        for (int c = 0; c < 2; ++c)
           #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
-        } else if (!need_mask) {
-          #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            mx = fmaxf(mx, fmaf(__uint_as_float(v[i]), scale, bias_mode == 2 ? brow[c * 32 + i] : bias_const));
-        } else {
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
+        mx = fmaf(mx, scale, bias_const);
+      } else {
+        // per-row window into the padded table: column c of this tile reads brow[c]
+        const float* brow = lut + (n0 + c0 - qpos + md + LUT_PAD);
+        const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;   // columns < n_valid are visible
+        #pragma unroll
+        for (int c = 0; c < 2; ++c) {
           #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float bias = bias_mode == 2 ? brow[c * 32 + i] : bias_const;
-            const float x = fmaf(__uint_as_float(v[i]), scale, bias);
-            mx = fmaxf(mx, (c * 32 + i < n_valid) ? x : -INFINITY);
+            float x = fmaf(__uint_as_float(sv[c][i]), scale, bias);
+            if (need_mask && (c * 32 + i >= n_valid)) x = -INFINITY;
+            sv[c][i] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
           }
+          asm volatile("" ::: "memory");   // keep the table reads of one chunk from piling up in registers
         }
-      };
-      tmem_ld_x32(tS, va); tmem_ld_wait();
-      tmem_ld_x32(tS + 32, vb); max_chunk(va, 0); tmem_ld_wait();
-      tmem_ld_x32(tS + 64, va); max_chunk(vb, 1); tmem_ld_wait();
-      tmem_ld_x32(tS + 96, vb); max_chunk(va, 2); tmem_ld_wait();
-      tmem_ld_x32(tS, va);      max_chunk(vb, 3);            // first chunk of pass 2 already in flight
-      if (fast) mx = fmaf(mx, scale, bias_const);
+      }
+      // combine with the other half of the row
+      ctl->xchg[j & 1][half][r] = mx;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      mx = fmaxf(mx, ctl->xchg[j & 1][half ^ 1][r]);
       const float m_new = fmaxf(m_use, mx);
 
       // PV of the previous tile must be complete before P is overwritten / O rescaled
       if (j > 0) {
-        if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; tmem_ld_wait(); break; }
+        if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
         tc_fence_after();
       }
-      tmem_ld_wait();
       // lazy rescale: only when some row's maximum grew by more than the threshold
+      // (both threads of a row see the same m_new and m_use, hence decide alike)
       const bool grow = (m_new - m_use) > RESCALE_THRESHOLD;   // false for -inf - -inf (NaN)
       if (j == 0) {
         m_use = m_new;
@@ -305,37 +331,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (grow) { alpha = fast_exp2(m_use - m_new); m_use = m_new; }
         l_sum *= alpha;
         #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
-          tmem_ld_x32(tO + c * 32, vb);
+        for (int c = 0; c < 2; ++c) {            // this thread's 32 columns of O
+          uint32_t ov[16];
+          tmem_ld_x16(tO + c * 16, ov);
           tmem_ld_wait();
           #pragma unroll
-          for (int i = 0; i < 32; ++i) vb[i] = __float_as_uint(__uint_as_float(vb[i]) * alpha);
-          tmem_st_x32(tO + c * 32, vb);
+          for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st_x16(tO + c * 16, ov);
         }
       }
       const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
-      const float c_fast = bias_const - m_safe;
+      // fast tiles: p = 2^(s*scale + (bias - m)); others: p = 2^(x - m) = 2^(x*1 + (-m))
+      const float e_mul = fast ? scale : 1.f;
+      const float e_add = fast ? bias_const - m_safe : -m_safe;
 
-      // ---- pass 2: exponentials, row sum, P -> tensor memory
-      auto exp_chunk = [&](const uint32_t (&v)[32], int c) {
+      // ---- exponentials, row sum, P -> tensor memory (32 columns at a time)
+      #pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t pk[16];
         #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float x0, x1;
-          if (fast) {
-            x0 = fmaf(__uint_as_float(v[2 * i]), scale, c_fast);
-            x1 = fmaf(__uint_as_float(v[2 * i + 1]), scale, c_fast);
-          } else {
-            const float b0 = (bias_mode == 2 ? brow[c * 32 + 2 * i] : bias_const) - m_safe;
-            const float b1 = (bias_mode == 2 ? brow[c * 32 + 2 * i + 1] : bias_const) - m_safe;
-            x0 = fmaf(__uint_as_float(v[2 * i]), scale, b0);
-            x1 = fmaf(__uint_as_float(v[2 * i + 1]), scale, b1);
-            if (need_mask) {
-              if (c * 32 + 2 * i >= n_valid) x0 = -INFINITY;
-              if (c * 32 + 2 * i + 1 >= n_valid) x1 = -INFINITY;
-            }
-          }
-          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i]), e_mul, e_add));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i + 1]), e_mul, e_add));
           pk[i] = pack2<kBf16>(p0, p1);
           if (kBf16) {
             // normalise by the sum of the ROUNDED probabilities the tensor core will
@@ -346,50 +363,48 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           }
         }
         tmem_st_x16(tP + c * 16, pk);
-      };
-      tmem_ld_x32(tS + 32, vb); exp_chunk(va, 0); tmem_ld_wait();
-      tmem_ld_x32(tS + 64, va); exp_chunk(vb, 1); tmem_ld_wait();
-      tmem_ld_x32(tS + 96, vb); exp_chunk(va, 2); tmem_ld_wait();
-      exp_chunk(vb, 3);
+      }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL));
     }
 
-    // ---- epilogue: O / l -> global
+    // ---- epilogue: O / l -> global (each thread its 32 output columns)
     if (ok && n_kv > 0) {
       if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((n_kv - 1) & 1), abort_flag)) { ok = false; fail_code = 32; }
       tc_fence_after();
     }
+    // total row sum = this half + the other half (slot parity distinct from the last tile's maxima)
+    const int slot = n_kv & 1;
+    ctl->xchg[slot][half][r] = l_sum;
+    asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+    l_sum += ctl->xchg[slot][half ^ 1][r];
     if (ok) {
       const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
       const bool row_ok = r < rows_in_tile;
       const int64_t row = (int64_t)q_row0 + r;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + half * 64 +
                       2 * ((int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + row * p.o_stride_m);
-      #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t v[32];
-        if (n_kv > 0) {
-          tmem_ld_x32(tO + c * 32, v);
-          tmem_ld_wait();
-        } else {
-          #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0u;
-        }
-        if (row_ok) {
-          #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 w;
-            w.x = pack2<kBf16>(__uint_as_float(v[8 * i + 0]) * inv_l, __uint_as_float(v[8 * i + 1]) * inv_l);
-            w.y = pack2<kBf16>(__uint_as_float(v[8 * i + 2]) * inv_l, __uint_as_float(v[8 * i + 3]) * inv_l);
-            w.z = pack2<kBf16>(__uint_as_float(v[8 * i + 4]) * inv_l, __uint_as_float(v[8 * i + 5]) * inv_l);
-            w.w = pack2<kBf16>(__uint_as_float(v[8 * i + 6]) * inv_l, __uint_as_float(v[8 * i + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c * 64 + i * 16) = w;
-          }
+      uint32_t v[32];
+      if (n_kv > 0) {
+        tmem_ld_x32(tO, v);
+        tmem_ld_wait();
+      } else {
+        #pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      if (row_ok) {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 w;
+          w.x = pack2<kBf16>(__uint_as_float(v[8 * i + 0]) * inv_l, __uint_as_float(v[8 * i + 1]) * inv_l);
+          w.y = pack2<kBf16>(__uint_as_float(v[8 * i + 2]) * inv_l, __uint_as_float(v[8 * i + 3]) * inv_l);
+          w.z = pack2<kBf16>(__uint_as_float(v[8 * i + 4]) * inv_l, __uint_as_float(v[8 * i + 5]) * inv_l);
+          w.w = pack2<kBf16>(__uint_as_float(v[8 * i + 6]) * inv_l, __uint_as_float(v[8 * i + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(orow + i * 16) = w;
         }
       }
-      if (p.lse != nullptr && row_ok) {
+      if (p.lse != nullptr && row_ok && half == 0) {
         const float lse = l_sum > 0.f ? (m_use + log2f(l_sum)) * kLn2 : -INFINITY;
         if (p.cu_q == nullptr) p.lse[((int64_t)blockIdx.z * p.H + h) * p.M + row] = lse;
         else p.lse[row * p.H + h] = lse;
@@ -401,7 +416,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   if (fail_code != 0 && p.status != nullptr) atomicCAS(p.status, 0, 1000 + fail_code);
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
