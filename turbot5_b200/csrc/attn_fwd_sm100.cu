@@ -45,7 +45,6 @@ constexpr int SOFTMAX_THREADS = 256;
 constexpr int WARP_TMA = 8, WARP_MMA = 9;
 constexpr int TMEM_COLS = 256;     // S: 128 fp32 columns, P: 64 (packed 16-bit pairs), O: 64
 constexpr int COL_S = 0, COL_P = 128, COL_O = 192;
-constexpr float RESCALE_THRESHOLD = 8.0f;    // log2 units: P stays <= 2^8 before a rescale
 constexpr int LUT_PAD = BM + BN;             // bias table padding on each side (entries)
 
 // barrier slots
@@ -76,6 +75,16 @@ __host__ __device__ inline size_t smem_bytes(int lut_entries) {
   return 1024 /*alignment slack*/ + SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 4;
 }
 
+// named barrier over the two warps that share a TMEM lane quarter (64 threads)
+__device__ __forceinline__ void pair_sync(int id) {
+  switch (id) {
+    case 1: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+    case 3: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+    default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+  }
+}
+
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   if (kBf16) {
@@ -89,6 +98,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 // kBf16: element type of Q/K/V/out (P uses the same type: tcgen05.mma kind::f16
 // takes A and B of one format; mixing fp16 P with bf16 V is an illegal instruction).
+// Exponentials are taken against the row maximum seen up to the previous tile; O and
+// the row sum are rescaled only when the maximum grows by more than this many
+// powers of two.  P then stays below 2^threshold times the tile's own spread: far
+// inside bf16's range (an fp32 exponent) with 32, and inside fp16's 65504 with 12.
+template <bool kBf16> struct Rescale { static constexpr float kThreshold = kBf16 ? 32.f : 12.f; };
+
 template <bool kBf16>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
@@ -284,90 +299,125 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       const bool fast = !need_mask && bias_mode != 2 && scale > 0.f;
 
-      // ---- row maximum.  Fast tiles (no mask, constant bias): max of the raw scores,
-      // transformed once.  Other tiles: x = s*scale + bias(delta) (+ mask) in place first.
+      // Maximum of this thread's half row, four independent chains.  Fast tiles (no
+      // mask, constant bias): over the raw scores, transformed once.  Other tiles:
+      // x = s*scale + bias(delta) (+ mask) is computed in place first.
       float mx = -INFINITY;
-      if (fast) {
-        #pragma unroll
-        for (int c = 0; c < 2; ++c)
+      const bool track_in_pass = fast && j > 0;   // fast tiles after the first: maximum taken inside the exp pass
+      if (!track_in_pass) {
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+        if (fast) {
           #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[c][i]));
-        mx = fmaf(mx, scale, bias_const);
-      } else {
-        // per-row window into the padded table: column c of this tile reads brow[c]
-        const float* brow = lut + (n0 + c0 - qpos + md + LUT_PAD);
-        const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;   // columns < n_valid are visible
-        #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < 2; ++c)
+            #pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              m0 = max3(m0, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+              m1 = max3(m1, __uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3]));
+              m2 = max3(m2, __uint_as_float(sv[c][i + 4]), __uint_as_float(sv[c][i + 5]));
+              m3 = max3(m3, __uint_as_float(sv[c][i + 6]), __uint_as_float(sv[c][i + 7]));
+            }
+          mx = fmaf(max3(fmaxf(m0, m1), m2, m3), scale, bias_const);
+        } else {
+          // per-row window into the padded table: column c of this tile reads brow[c]
+          const float* brow = lut + (n0 + c0 - qpos + md + LUT_PAD);
+          const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;   // columns < n_valid are visible
           #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float bias = bias_mode == 2 ? brow[c * 32 + i] : bias_const;
-            float x = fmaf(__uint_as_float(sv[c][i]), scale, bias);
-            if (need_mask && (c * 32 + i >= n_valid)) x = -INFINITY;
-            sv[c][i] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
+          for (int c = 0; c < 2; ++c) {
+            #pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float bias = bias_mode == 2 ? brow[c * 32 + i] : bias_const;
+              float x = fmaf(__uint_as_float(sv[c][i]), scale, bias);
+              if (need_mask && (c * 32 + i >= n_valid)) x = -INFINITY;
+              sv[c][i] = __float_as_uint(x);
+              if ((i & 3) == 0) m0 = fmaxf(m0, x); else if ((i & 3) == 1) m1 = fmaxf(m1, x);
+              else if ((i & 3) == 2) m2 = fmaxf(m2, x); else m3 = fmaxf(m3, x);
+            }
+            asm volatile("" ::: "memory");   // keep the table reads of one chunk from piling up in registers
           }
-          asm volatile("" ::: "memory");   // keep the table reads of one chunk from piling up in registers
+          mx = max3(fmaxf(m0, m1), m2, m3);
         }
       }
-      // combine with the other half of the row
-      ctl->xchg[j & 1][half][r] = mx;
-      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      mx = fmaxf(mx, ctl->xchg[j & 1][half ^ 1][r]);
-      const float m_new = fmaxf(m_use, mx);
-
-      // PV of the previous tile must be complete before P is overwritten / O rescaled
-      if (j > 0) {
+      // The first tile needs the true row maximum before any exponential.  Later tiles
+      // take their exponentials against the maximum seen so far and only check
+      // afterwards whether the row maximum grew past the rescale threshold (rare).
+      if (j == 0) {
+        ctl->xchg[0][half][r] = mx;
+        pair_sync(pair_bar);
+        m_use = fmaxf(mx, ctl->xchg[0][half ^ 1][r]);
+      } else {
+        // PV of the previous tile must be complete before P is overwritten / O rescaled
         if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
         tc_fence_after();
       }
-      // lazy rescale: only when some row's maximum grew by more than the threshold
-      // (both threads of a row see the same m_new and m_use, hence decide alike)
-      const bool grow = (m_new - m_use) > RESCALE_THRESHOLD;   // false for -inf - -inf (NaN)
-      if (j == 0) {
-        m_use = m_new;
-      } else if (__any_sync(0xffffffffu, grow)) {
-        float alpha = 1.f;
-        if (grow) { alpha = fast_exp2(m_use - m_new); m_use = m_new; }
-        l_sum *= alpha;
-        #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {            // this thread's 32 columns of O
-          uint32_t ov[16];
-          tmem_ld_x16(tO + c * 16, ov);
-          tmem_ld_wait();
-          #pragma unroll
-          for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          tmem_st_x16(tO + c * 16, ov);
-        }
-      }
-      const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
-      // fast tiles: p = 2^(s*scale + (bias - m)); others: p = 2^(x - m) = 2^(x*1 + (-m))
-      const float e_mul = fast ? scale : 1.f;
-      const float e_add = fast ? bias_const - m_safe : -m_safe;
 
-      // ---- exponentials, row sum, P -> tensor memory (32 columns at a time)
-      #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[16];
+      #pragma unroll 1
+      for (int attempt = 0; attempt < 2; ++attempt) {
+        const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
+        // fast tiles: p = 2^(s*scale + (bias - m)); others: p = 2^(x - m) = 2^(x*1 + (-m))
+        const float e_mul = fast ? scale : 1.f;
+        const float e_add = fast ? bias_const - m_safe : -m_safe;
+        float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;   // this tile's share of the row sum
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+
+        // ---- exponentials, row sum, P -> tensor memory (32 columns at a time)
         #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i]), e_mul, e_add));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i + 1]), e_mul, e_add));
-          pk[i] = pack2<kBf16>(p0, p1);
-          if (kBf16) {
-            // normalise by the sum of the ROUNDED probabilities the tensor core will
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[16];
+          #pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float s0 = __uint_as_float(sv[c][2 * i]), s1 = __uint_as_float(sv[c][2 * i + 1]);
+            if (track_in_pass) {
+              if ((i & 3) == 0) m0 = max3(m0, s0, s1); else if ((i & 3) == 1) m1 = max3(m1, s0, s1);
+              else if ((i & 3) == 2) m2 = max3(m2, s0, s1); else m3 = max3(m3, s0, s1);
+            }
+            float x0, x1;
+            fma2(x0, x1, s0, s1, e_mul, e_add);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            pk[i] = pack2<kBf16>(p0, p1);
+            // bf16: normalise by the sum of the ROUNDED probabilities the tensor core will
             // use, so a row dominated by one key stays an exact convex combination
-            l_sum += __uint_as_float(pk[i] << 16) + __uint_as_float(pk[i] & 0xffff0000u);
-          } else {
-            l_sum += p0 + p1;
+            const float q0 = kBf16 ? __uint_as_float(pk[i] << 16) : p0;
+            const float q1 = kBf16 ? __uint_as_float(pk[i] & 0xffff0000u) : p1;
+            if (i & 1) add2(t2, t3, q0, q1); else add2(t0, t1, q0, q1);
+          }
+          tmem_st_x16(tP + c * 16, pk);
+        }
+        const float l_tile = (t0 + t1) + (t2 + t3);
+        if (j == 0) { l_sum = l_tile; break; }
+
+        // did the row maximum grow past the threshold?  (both halves of a row see the
+        // same values here, hence decide alike; the decision is uniform per warp pair)
+        bool redo = false;
+        if (attempt == 0) {
+          if (track_in_pass) mx = fmaf(max3(fmaxf(m0, m1), m2, m3), scale, bias_const);
+          ctl->xchg[j & 1][half][r] = mx;
+          pair_sync(pair_bar);
+          const float m_new = fmaxf(m_use, fmaxf(mx, ctl->xchg[j & 1][half ^ 1][r]));
+          const bool grow = (m_new - m_use) > Rescale<kBf16>::kThreshold;   // false for -inf - -inf (NaN)
+          redo = __any_sync(0xffffffffu, grow);
+          if (redo) {
+            float alpha = 1.f;
+            if (grow) { alpha = fast_exp2(m_use - m_new); m_use = m_new; }
+            l_sum *= alpha;
+            #pragma unroll 1
+            for (int c = 0; c < 2; ++c) {            // this thread's 32 columns of O
+              uint32_t ov[16];
+              tmem_ld_x16(tO + c * 16, ov);
+              tmem_ld_wait();
+              #pragma unroll
+              for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+              tmem_st_x16(tO + c * 16, ov);
+            }
+            tmem_st_wait();     // P of the first attempt must have landed before it is rewritten
           }
         }
-        tmem_st_x16(tP + c * 16, pk);
+        if (!redo) { l_sum += l_tile; break; }
       }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL));
     }
+
 
     // ---- epilogue: O / l -> global (each thread its 32 output columns)
     if (ok && n_kv > 0) {
@@ -377,7 +427,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // total row sum = this half + the other half (slot parity distinct from the last tile's maxima)
     const int slot = n_kv & 1;
     ctl->xchg[slot][half][r] = l_sum;
-    asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+    pair_sync(pair_bar);
     l_sum += ctl->xchg[slot][half ^ 1][r];
     if (ok) {
       const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;

@@ -222,6 +222,27 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 3-input maximum and packed 2 x fp32 arithmetic (one issue slot for two elements).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// (d0, d1) = (a0, a1) * (b, b) + (c, c)
+__device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, float b, float c) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+// (acc0, acc1) += (x0, x1)
+__device__ __forceinline__ void add2(float& acc0, float& acc1, float x0, float x1) {
+  asm("{\n\t.reg .b64 ra, rx;\n\t"
+      "mov.b64 ra, {%0, %1};\n\tmov.b64 rx, {%2, %3};\n\t"
+      "add.rn.f32x2 ra, ra, rx;\n\tmov.b64 {%0, %1}, ra;\n\t}"
+      : "+f"(acc0), "+f"(acc1) : "f"(x0), "f"(x1));
+}
+
 // Shared-memory matrix descriptor for tcgen05.mma (128-byte swizzle, version 1).
 // start address, leading/stride byte offsets are encoded >> 4.
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
