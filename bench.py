@@ -249,6 +249,9 @@ def main():
     e2e_val = world * fl / (e2e_ms * 1e-3) / 1e12
 
     secondary = None
+    sp_line = None
+    if not args.no_secondary:
+        sp_line = sequence_parallel_measurement(t5b, dev, rank, world, dist)
     if not args.no_secondary and rank == 0:
         secondary = secondary_measurements(t5b, dev)
     clocks = sampler.stop() if rank == 0 else None
@@ -281,6 +284,8 @@ def main():
                 "sample": f"{heads} of {B * H} (batch, head) pairs, all {L} rows, {sec:.1f} s of CPU work"}
         if secondary:
             line["secondary"] = secondary
+        if sp_line:
+            line["sequence_parallel"] = sp_line
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -297,6 +302,39 @@ def _time(fn, iters, warm=3):
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / iters
+
+
+def sequence_parallel_measurement(t5b, dev, rank, world, dist):
+    """One fused-bias attention layer over a single 100 000-token sequence (T5-base heads),
+    query rows sharded over the ranks, K/V all-gathered with NCCL (strong scaling)."""
+    from turbot5_b200.sequence_parallel import sequence_parallel_attention, shard_size
+    L, H, D = 100000, 12, 64
+    dt = torch.bfloat16
+    S = shard_size(L, world)
+    g = torch.Generator(device=dev).manual_seed(99 + rank)
+    q, k, v = (torch.randn((1, S, H, D), generator=g, device=dev, dtype=torch.float32).to(dt) for _ in range(3))
+    table = (torch.randn((32, H), generator=torch.Generator(device=dev).manual_seed(5), device=dev) * 0.1).to(dt)
+    run = lambda: sequence_parallel_attention(q, k, v, table, L, causal=False, sm_scale=1.0)
+    iters = 3
+    run()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    fl = 4.0 * H * float(L) * float(L) * D
+    return {"workload": "one attention layer, 1 x 100000 tokens, H12 D64 bf16, query-block sharded, K/V all-gather",
+            "scaling": "strong", "ms_per_layer": ms, "tokens_per_s": L / (ms * 1e-3),
+            "TFLOP/s_aggregate": fl / (ms * 1e-3) / 1e12,
+            "all_gather_bytes_per_rank": 0 if world == 1 else 2 * S * world * H * D * 2}
 
 
 def secondary_measurements(t5b, dev):

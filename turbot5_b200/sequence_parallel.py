@@ -1,0 +1,82 @@
+"""Query-block sequence parallelism for one long sequence on one multi-GPU node.
+
+Rank r owns the token shard [r*S, (r+1)*S) (S = ceil(L / world)) for every
+token-wise operation.  For attention each rank keeps its own query rows,
+all-gathers the key and value shards of all ranks into a buffer in its OWN
+memory (NCCL over NVLink; `torch.distributed.all_gather_into_tensor`) and runs
+the fused-bias kernel on `q_local x all keys` with `q_pos_offset = r*S`, the
+position of its first query row.  Every rank holds complete softmax rows, so no
+reduction follows.  Remote keys are always read from local memory by the
+kernel's ordinary per-block TMA loads.
+
+The reference has no multi-GPU path; this is the partitioning of its single-GPU
+call (src/turbot5/model/attentions.py:486-490) whose bias depends only on
+absolute positions (src/turbot5/model/attentions.py:126-141).
+"""
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_size(seq_len: int, world: int) -> int:
+    """Tokens per rank (the last rank may own fewer real tokens; shards are padded to this size)."""
+    return -(-seq_len // world)
+
+
+def shard_bounds(seq_len: int, world: int, rank: int) -> Tuple[int, int]:
+    """[start, stop) of the real tokens owned by `rank`."""
+    s = shard_size(seq_len, world)
+    return min(rank * s, seq_len), min((rank + 1) * s, seq_len)
+
+
+def all_gather_sequence(x_local: torch.Tensor, group=None) -> torch.Tensor:
+    """(B, S, H, D) shard per rank -> (B, world*S, H, D) in this rank's memory.
+
+    One collective per batch row, each into a contiguous slice of the output, so
+    that the gathered buffer is directly addressable as (B, H, L, D) by strides.
+    """
+    world = dist.get_world_size(group)
+    B, S = x_local.shape[:2]
+    x_local = x_local.contiguous()
+    out = torch.empty((B, world * S) + tuple(x_local.shape[2:]), dtype=x_local.dtype, device=x_local.device)
+    if world == 1:
+        out.copy_(x_local)
+        return out
+    for b in range(B):
+        dist.all_gather_into_tensor(out[b], x_local[b], group=group)
+    return out
+
+
+def sequence_parallel_attention(q_local: torch.Tensor, k_local: torch.Tensor, v_local: torch.Tensor,
+                                bias: Optional[torch.Tensor], seq_len: int, causal: bool = False,
+                                sm_scale: Optional[float] = None, NUM_BUCKETS: int = 32,
+                                MAX_DISTANCE: int = 128, group=None,
+                                attention_fn: Optional[Callable] = None) -> torch.Tensor:
+    """Attention of this rank's query rows against the whole sequence.
+
+    q_local, k_local, v_local: (B, S, H, D) token-major shards, S = shard_size(seq_len, world);
+    rows of the last shard beyond `seq_len` are padding (their outputs are unspecified and
+    their keys are never attended).  Returns (B, S, H, D).  `attention_fn` defaults to
+    `flash_attention_with_fusing_bias`; tests on CPU ranks pass a reference implementation
+    with the same signature.
+    """
+    if attention_fn is None:
+        from .attention import flash_attention_with_fusing_bias as attention_fn
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    S = q_local.shape[1]
+    if S != shard_size(seq_len, world):
+        raise ValueError(f"shard length {S} does not match ceil({seq_len} / {world})")
+    if world > 1:
+        k_all = all_gather_sequence(k_local, group)
+        v_all = all_gather_sequence(v_local, group)
+    else:
+        k_all, v_all = k_local, v_local
+    # (B, H, rows, D) views of the token-major buffers; only the real keys are attended
+    q = q_local.transpose(1, 2)
+    k = k_all[:, :seq_len].transpose(1, 2)
+    v = v_all[:, :seq_len].transpose(1, 2)
+    out = attention_fn(q, k, v, bias, causal=causal, sm_scale=sm_scale, NUM_BUCKETS=NUM_BUCKETS,
+                       MAX_DISTANCE=MAX_DISTANCE, q_pos_offset=rank * S)
+    return out.transpose(1, 2)
