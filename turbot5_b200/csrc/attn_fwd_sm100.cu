@@ -58,7 +58,8 @@ enum {
   BAR_S_FREE,
   BAR_P_FULL,
   BAR_O_DONE,
-  NUM_BARS
+  BAR_PAIR,                          // [4]: the two warps sharing a TMEM lane quarter (64 arrivals)
+  NUM_BARS = BAR_PAIR + 4
 };
 
 struct __align__(8) Control {
@@ -75,15 +76,6 @@ __host__ __device__ inline size_t smem_bytes(int lut_entries) {
   return 1024 /*alignment slack*/ + SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 4;
 }
 
-// named barrier over the two warps that share a TMEM lane quarter (64 threads)
-__device__ __forceinline__ void pair_sync(int id) {
-  switch (id) {
-    case 1: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
-    case 2: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
-    case 3: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
-    default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
-  }
-}
 
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -166,6 +158,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     mbar_init(bar(BAR_S_FREE), SOFTMAX_THREADS);
     mbar_init(bar(BAR_P_FULL), SOFTMAX_THREADS);
     mbar_init(bar(BAR_O_DONE), 1);
+    for (int qd = 0; qd < 4; ++qd) mbar_init(bar(BAR_PAIR + qd), 64);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -268,7 +261,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const float scale = p.scale_log2;
     const bool has_bias = p.table != nullptr;
     const int qpos = qpos0 + r;
-    const int pair_bar = 1 + quarter;              // named barrier shared by warps w and w+4
+    // Rendezvous of the two warps that share this lane quarter: an mbarrier with a bounded
+    // wait, so that a partner that gave up can never leave this warp waiting for ever.
+    const uint32_t pair_bar = bar(BAR_PAIR + quarter);
+    uint32_t pair_uses = 0;
+    auto pair_sync = [&]() -> bool {
+      mbar_arrive(pair_bar);
+      const bool done = mbar_wait_bounded(pair_bar, pair_uses & 1u, abort_flag);
+      ++pair_uses;
+      return done;
+    };
     float m_use = -INFINITY;    // maximum the exponentials are taken against
     float l_sum = 0.f;          // this thread's half of the row sum
     bool ok = true;
@@ -342,7 +344,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // afterwards whether the row maximum grew past the rescale threshold (rare).
       if (j == 0) {
         ctl->xchg[0][half][r] = mx;
-        pair_sync(pair_bar);
+        if (!pair_sync()) { ok = false; fail_code = 33; break; }
         m_use = fmaxf(mx, ctl->xchg[0][half ^ 1][r]);
       } else {
         // PV of the previous tile must be complete before P is overwritten / O rescaled
@@ -391,7 +393,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (attempt == 0) {
           if (track_in_pass) mx = fmaf(max3(fmaxf(m0, m1), m2, m3), scale, bias_const);
           ctl->xchg[j & 1][half][r] = mx;
-          pair_sync(pair_bar);
+          if (!pair_sync()) { ok = false; fail_code = 33; break; }
           const float m_new = fmaxf(m_use, fmaxf(mx, ctl->xchg[j & 1][half ^ 1][r]));
           const bool grow = (m_new - m_use) > Rescale<kBf16>::kThreshold;   // false for -inf - -inf (NaN)
           redo = __any_sync(0xffffffffu, grow);
@@ -413,6 +415,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         }
         if (!redo) { l_sum += l_tile; break; }
       }
+      if (!ok) break;
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL));
@@ -427,7 +430,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // total row sum = this half + the other half (slot parity distinct from the last tile's maxima)
     const int slot = n_kv & 1;
     ctl->xchg[slot][half][r] = l_sum;
-    pair_sync(pair_bar);
+    if (ok && !pair_sync()) { ok = false; fail_code = 33; }
     l_sum += ctl->xchg[slot][half ^ 1][r];
     if (ok) {
       const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
