@@ -373,6 +373,18 @@ def secondary_measurements(t5b, dev):
     fl = float((4 * 12 * 64 * lens.double() ** 2).sum())
     out["varlen_32seq_128to4096"] = {"ms": ms, "TFLOP/s": fl / (ms * 1e-3) / 1e12, "tokens": T,
                                      "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"]}
+    del qkv
+    # T5-base encoder (12 layers, d_model 768, 12 x 64 heads, gated-GELU d_ff 2048, random init, bf16):
+    # tokens/s of a forward pass at 2 x 8192 tokens and at 16 x 1024 tokens
+    from turbot5_b200.t5 import T5Stack, T5StackConfig
+    cfg = T5StackConfig()
+    torch.manual_seed(0)
+    enc = T5Stack(cfg, torch.nn.Embedding(cfg.vocab_size, cfg.d_model), is_decoder=False).to(dev).to(dt).eval()
+    for Bt, Lt in ((2, 8192), (16, 1024)):
+        ids = torch.randint(0, cfg.vocab_size, (Bt, Lt), generator=g, device=dev)
+        with torch.no_grad():
+            ms = _time(lambda: enc(ids), 5, warm=2)
+        out[f"t5_base_encoder_fwd_{Bt}x{Lt}"] = {"ms": ms, "tokens_per_s": Bt * Lt / (ms * 1e-3)}
     return out
 
 

@@ -283,3 +283,57 @@ def t5_attention_layer(hidden: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor,
     o = naive_attention_with_bias(qh, kh, vh, bias)
     o = o.transpose(1, 2).contiguous().view(B, -1, n_heads * d_kv)
     return o @ wo.t(), (kh, vh)
+
+
+# --------------------------------------------------------------------------- #
+# next row: the encoder / decoder stack around the attention path
+# --------------------------------------------------------------------------- #
+def _ffn(w, prefix, x, gated=True):
+    """T5LayerFF (src/turbot5/model/modeling.py:63-128): pre-norm, gated-GELU (tanh) or ReLU, residual."""
+    h = t5_layer_norm(x, w[prefix + "layer_norm.weight"])
+    if gated:
+        a = torch.nn.functional.gelu(h @ w[prefix + "DenseReluDense.wi_0.weight"].t(), approximate="tanh")
+        h = (a * (h @ w[prefix + "DenseReluDense.wi_1.weight"].t())) @ w[prefix + "DenseReluDense.wo.weight"].t()
+    else:
+        h = torch.relu(h @ w[prefix + "DenseReluDense.wi.weight"].t()) @ w[prefix + "DenseReluDense.wo.weight"].t()
+    return x + h
+
+
+def t5_stack_forward(w, cfg, input_ids, is_decoder=False, mask=None, encoder_hidden=None, encoder_mask=None):
+    """`T5Stack.forward` without a cache (src/turbot5/model/modeling.py:421-632) on a dict of
+    weights with the Hugging Face parameter names.  `cfg`: dict with num_heads, d_kv, the bucket
+    settings and the layer counts."""
+    side = "decoder" if is_decoder else "encoder"
+    n_layers = cfg["num_decoder_layers"] if is_decoder else cfg["num_layers"]
+    H, D = cfg["num_heads"], cfg["d_kv"]
+    nb, md = cfg["relative_attention_num_buckets"], cfg["relative_attention_max_distance"]
+    x = w["shared.weight"][input_ids]
+    table = w[f"{side}.block.0.layer.0.SelfAttention.relative_attention_bias.weight"]
+    for i in range(n_layers):
+        pre = f"{side}.block.{i}.layer.0."
+        a = pre + "SelfAttention."
+        h = t5_layer_norm(x, w[pre + "layer_norm.weight"])
+        o, _ = t5_attention_layer(h, w[a + "q.weight"], w[a + "k.weight"], w[a + "v.weight"], w[a + "o.weight"],
+                                  table, H, D, is_decoder=is_decoder, num_buckets=nb, max_distance=md,
+                                  key_padding_mask=None if is_decoder else mask)
+        x = x + o
+        if is_decoder:
+            pre = f"{side}.block.{i}.layer.1."
+            a = pre + "EncDecAttention."
+            h = t5_layer_norm(x, w[pre + "layer_norm.weight"])
+            o, _ = t5_attention_layer(h, w[a + "q.weight"], w[a + "k.weight"], w[a + "v.weight"], w[a + "o.weight"],
+                                      None, H, D, is_decoder=True, key_value_states=encoder_hidden,
+                                      key_padding_mask=encoder_mask, causal=False)
+            x = x + o
+        ff = f"{side}.block.{i}.layer.{2 if is_decoder else 1}."
+        x = _ffn(w, ff, x, gated=(ff + "DenseReluDense.wi_0.weight") in w)
+    return t5_layer_norm(x, w[f"{side}.final_layer_norm.weight"])
+
+
+def t5_model_logits(w, cfg, input_ids, decoder_input_ids, mask=None, tie_word_embeddings=False):
+    """Encoder + decoder + LM head (src/turbot5/heads/t5_heads.py:132-260)."""
+    enc = t5_stack_forward(w, cfg, input_ids, mask=mask)
+    dec = t5_stack_forward(w, cfg, decoder_input_ids, is_decoder=True, encoder_hidden=enc, encoder_mask=mask)
+    if tie_word_embeddings:
+        dec = dec * (w["shared.weight"].shape[1] ** -0.5)
+    return enc, dec @ w["lm_head.weight"].t()

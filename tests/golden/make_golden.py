@@ -24,6 +24,9 @@ Fixtures written:
                    from the seed by the test).
   rmsnorm.npz      `T5LayerNorm._forward` for float32 / bfloat16 weights.
   padding.npz      `_get_unpad_data` + `pad_input` on a ragged mask.
+  stack.npz        the reference's whole encoder-decoder model (tiny shape, 'basic' attention,
+                   weights seeded by parameter name): encoder output, logits, masked variants and
+                   four greedy decoding steps through its K/V cache.
 """
 import math
 import os
@@ -209,6 +212,48 @@ def main(ref_root: str):
     np.savez_compressed(os.path.join(here, "padding.npz"), mask=mask.numpy(), indices=idx.numpy(),
                         cu_seqlens=cu.numpy(), max_seqlen=np.asarray(mx), values=vals.numpy(),
                         padded=padded.numpy())
+    # ------------------------------------------------------------ tiny enc-dec stack
+    # the reference's full model ('basic' attention on CPU) with name-seeded weights: encoder
+    # output, teacher-forced logits and four greedy steps through its tuple K/V cache
+    sys.path.insert(0, os.path.dirname(os.path.dirname(here)))
+    from tests.helpers import TINY_T5, seed_named_parameters, tiny_t5_inputs
+    from transformers.modeling_utils import PreTrainedModel
+    from turbot5 import T5ForConditionalGeneration
+    from turbot5.model import modeling
+    _orig = PreTrainedModel.get_extended_attention_mask
+
+    def _gem(self, attention_mask, input_shape, device=None, dtype=None):
+        if isinstance(device, torch.dtype):
+            dtype, device = device, None
+        return _orig(self, attention_mask, input_shape, dtype=dtype)
+    modeling.T5PreTrainedModel.get_extended_attention_mask = _gem
+    modeling.T5PreTrainedModel.get_head_mask = lambda self, hm, n, *a: [None] * n
+    cfg = T5Config(feed_forward_proj="gated-gelu", attention_type="basic", use_triton=False, dropout_rate=0.0,
+                   tie_word_embeddings=False, **TINY_T5)
+    model = T5ForConditionalGeneration(cfg).eval()
+    model.encoder.config.attention_type = "full"      # broadcastable mask handling in the encoder stack
+    seed_named_parameters(model, 0)
+    ids, dec = tiny_t5_inputs()
+    mask = torch.ones_like(ids)
+    mask[1, 29:] = 0
+    with torch.no_grad():
+        enc = model.encoder(input_ids=ids)
+        logits = model(input_ids=ids, decoder_input_ids=dec).logits
+        enc_m = model.encoder(input_ids=ids, attention_mask=mask)
+        logits_m = model(input_ids=ids, attention_mask=mask, decoder_input_ids=dec).logits
+        cur = torch.zeros((2, 1), dtype=torch.long)
+        pkv, toks, step_logits = None, [], []
+        for _ in range(4):
+            o = model(encoder_outputs=enc, decoder_input_ids=cur, past_key_values=pkv, use_cache=True)
+            pkv = o.past_key_values
+            step_logits.append(o.logits[:, -1])
+            cur = o.logits[:, -1:].argmax(-1)
+            toks.append(cur)
+    np.savez_compressed(os.path.join(here, "stack.npz"), encoder=enc.last_hidden_state.numpy(),
+                        logits=logits.numpy(), encoder_masked=enc_m.last_hidden_state.numpy(),
+                        logits_masked=logits_m.numpy(), mask=mask.numpy(),
+                        greedy_tokens=torch.cat(toks, 1).numpy(), greedy_logits=torch.stack(step_logits, 1).numpy(),
+                        param_names=np.asarray(sorted(n for n, _ in model.named_parameters())))
     print("golden fixtures written to", here)
 
 

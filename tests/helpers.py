@@ -43,3 +43,35 @@ def check_close(got, want, dtype, what=""):
 def seeded(shape, seed, std=1.0, dtype=torch.float32):
     g = torch.Generator().manual_seed(seed)
     return (torch.randn(shape, generator=g, dtype=torch.float32) * std).to(dtype)
+
+
+TINY_T5 = dict(vocab_size=128, d_model=32, d_kv=64, num_heads=2, d_ff=64, num_layers=2, num_decoder_layers=2,
+               relative_attention_num_buckets=32, relative_attention_max_distance=128)
+
+
+def seed_named_parameters(model, seed=0):
+    """Deterministic weights keyed by parameter name (the same names exist in the reference's
+    T5ForConditionalGeneration and in turbot5_b200.t5), so both models get identical values
+    without storing them."""
+    import zlib
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            g = torch.Generator().manual_seed((zlib.crc32(name.encode()) ^ seed) & 0x7fffffff)
+            v = torch.randn(p.shape, generator=g)
+            if name.endswith("layer_norm.weight"):
+                v = 1.0 + 0.1 * v
+            elif "relative_attention_bias" in name:
+                v = 0.5 * v
+            elif name in ("shared.weight",):
+                v = 1.0 * v
+            else:
+                v = 0.08 * v
+            p.copy_(v.to(p.dtype))
+    return model
+
+
+def tiny_t5_inputs():
+    g = torch.Generator().manual_seed(123)
+    ids = torch.randint(0, TINY_T5["vocab_size"], (2, 40), generator=g)
+    dec = torch.randint(0, TINY_T5["vocab_size"], (2, 5), generator=g)
+    return ids, dec

@@ -258,3 +258,62 @@ def test_full_size_8k_properties():
     rows = slice(8100, 8192)
     want = orc.attention_basic(q[1:, 10:].cpu(), k[1:, 10:].cpu(), v[1:, 10:].cpu(), table[:, 10:].cpu(), rows=rows)
     check_close(out[1:, 10:, rows], want, dt, "8k rows 8100:8192")
+
+
+# ------------------------------------------------------------------ configured full sizes
+def test_config3_varlen_full_size_spot_sequences():
+    # 32 sequences with lengths uniform in [128, 4096] (seed 0), T5-base heads, bf16: every
+    # sequence is compared on a band of rows; the shortest and two others in full.
+    t5b = _ops()
+    dt = torch.bfloat16
+    lens = torch.randint(128, 4097, (32,), generator=torch.Generator().manual_seed(0))
+    cu = torch.zeros(33, dtype=torch.int32)
+    cu[1:] = torch.cumsum(lens, 0)
+    T, H = int(cu[-1]), 12
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q, k, v = (torch.randn((T, H, 64), generator=g, device="cuda", dtype=torch.float32).to(dt) for _ in range(3))
+    table = (torch.randn((32, H), generator=g, device="cuda") * 0.1).to(dt)
+    out = t5b.flash_attention_with_fusing_bias_varlen(q, k, v, table, cu.cuda(), cu.cuda(), int(lens.max()),
+                                                      int(lens.max()), sm_scale=1.0)
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    order = torch.argsort(lens)
+    full = {int(order[0]), int(order[1]), 7}
+    for b in range(32):
+        a, e = int(cu[b]), int(cu[b + 1])
+        n = e - a
+        rows = slice(0, n) if b in full else slice(max(0, n - 96), n)
+        heads = slice(0, 12) if b in full else slice(3, 5)
+        qs = q[a:e, heads].transpose(0, 1)[None].cpu()
+        ks = k[a:e, heads].transpose(0, 1)[None].cpu()
+        vs = v[a:e, heads].transpose(0, 1)[None].cpu()
+        want = orc.attention_basic(qs, ks, vs, table[:, heads].cpu(), rows=rows)
+        got = out[a:e, heads].transpose(0, 1)[None][:, :, rows]
+        check_close(got, want, dt, f"sequence {b} (len {n})")
+
+
+def test_config4_long_sequence_spot_rows():
+    # one sequence of 100 000 tokens, T5-base heads: query slabs at the start, across the
+    # middle and at the end against all keys (the oracle never builds L x L)
+    t5b = _ops()
+    dt = torch.bfloat16
+    L, H = 100000, 12
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q, k, v = (torch.randn((1, L, H, 64), generator=g, device="cuda", dtype=torch.float32).to(dt).transpose(1, 2)
+               for _ in range(3))
+    table = (torch.randn((32, H), generator=g, device="cuda") * 0.1).to(dt)
+    out = t5b.flash_attention_with_fusing_bias(q, k, v, table, sm_scale=1.0)
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    heads = slice(4, 6)
+    kc, vc, tc = k[:, heads].cpu(), v[:, heads].cpu(), table[:, heads].cpu()
+    for rows in (slice(0, 64), slice(49990, 50054), slice(99936, 100000)):
+        want = orc.attention_basic(q[:, heads].cpu(), kc, vc, tc, rows=rows, slab=64)
+        check_close(out[:, heads, rows], want, dt, f"rows {rows.start}:{rows.stop}")
+    # a sequence-parallel shard (rows 87500.. of 8 ranks) gives the same rows as the whole.  Not
+    # bit for bit: the shard's rows sit in other tiles/warps, so the running maxima that the
+    # probabilities are rounded against may differ; both are within tolerance of the oracle.
+    lo = 7 * 12500
+    shard = t5b.flash_attention_with_fusing_bias(q[:, :, lo:lo + 12500], k, v, table, sm_scale=1.0, q_pos_offset=lo)
+    diff = (shard.float() - out[:, :, lo:lo + 12500].float()).abs()
+    assert diff.max().item() <= 2e-2 and diff.mean().item() <= 5e-4

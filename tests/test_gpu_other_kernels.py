@@ -285,3 +285,25 @@ def test_state_dict_keys_match_hf_t5_names():
     assert set(mod.state_dict().keys()) == {"q.weight", "k.weight", "v.weight", "o.weight",
                                             "relative_attention_bias.weight"}
     assert set(t5b.T5LayerNorm(8).state_dict().keys()) == {"weight"}
+
+
+def test_config5_decode_full_size_spot_heads():
+    # T5-large decoding shape: batch 64, 16 heads, encoder memory 8192 (cross attention,
+    # no bias) and a 128-token self-attention cache with unidirectional bias
+    t5b = _ops()
+    dt = torch.bfloat16
+    B, H, N = 64, 16, 8192
+    g = torch.Generator(device="cuda").manual_seed(0)
+    k = torch.randn((B, H, N, 64), generator=g, device="cuda", dtype=torch.float32).to(dt)
+    v = torch.randn((B, H, N, 64), generator=g, device="cuda", dtype=torch.float32).to(dt)
+    q = torch.randn((B, H, 1, 64), generator=g, device="cuda", dtype=torch.float32).to(dt)
+    out = t5b.flash_decoding_with_fusing_bias(q, k, v, None, causal=False, sm_scale=1.0)
+    for b, h in ((0, 0), (17, 5), (63, 15)):
+        want = orc.attention_basic(q[b:b + 1, h:h + 1].cpu(), k[b:b + 1, h:h + 1].cpu(), v[b:b + 1, h:h + 1].cpu(), None)
+        check_close(out[b:b + 1, h:h + 1], want, dt, f"cross (b,h)=({b},{h})")
+    table = (torch.randn((32, H), generator=g, device="cuda") * 0.1).to(dt)
+    ks, vs = k[:, :, :128].contiguous(), v[:, :, :128].contiguous()
+    for t_step in (1, 77, 128):
+        out = t5b.flash_decoding_with_fusing_bias(q, ks, vs, table, causal=True, sm_scale=1.0, kv_len=t_step)
+        want = orc.attention_basic(q[:3].cpu(), ks[:3, :, :t_step].cpu(), vs[:3, :, :t_step].cpu(), table.cpu(), causal=True)
+        check_close(out[:3], want, dt, f"self step {t_step}")

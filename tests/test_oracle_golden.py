@@ -126,3 +126,35 @@ def test_varlen_matches_dense_per_sequence():
     one = orc.attention_basic(q[sl].transpose(0, 1)[None], k[sl].transpose(0, 1)[None],
                               v[sl].transpose(0, 1)[None], table)
     assert torch.equal(out[sl], one[0].transpose(0, 1))
+
+
+def _tiny_reference_weights():
+    """The name-seeded weights of the tiny fixture model, as a dict (built on the product's own
+    module tree only to enumerate names and shapes; no kernel is involved)."""
+    from tests.helpers import TINY_T5, seed_named_parameters
+    from turbot5_b200.t5 import T5ForConditionalGeneration, T5StackConfig
+    model = seed_named_parameters(T5ForConditionalGeneration(T5StackConfig(**TINY_T5)), 0)
+    return {k: v.detach().clone() for k, v in model.state_dict().items()}, model
+
+
+def test_stack_oracle_matches_reference_model_fixture():
+    from tests.helpers import TINY_T5, tiny_t5_inputs
+    z = load("stack.npz")
+    w, model = _tiny_reference_weights()
+    assert sorted(n for n, _ in model.named_parameters()) == [str(x) for x in z["param_names"]]
+    ids, dec = tiny_t5_inputs()
+    enc, logits = orc.t5_model_logits(w, TINY_T5, ids, dec)
+    assert (enc - torch.from_numpy(z["encoder"])).abs().max() < 2e-5
+    assert (logits - torch.from_numpy(z["logits"])).abs().max() < 2e-5
+    mask = torch.from_numpy(z["mask"])
+    enc_m, logits_m = orc.t5_model_logits(w, TINY_T5, ids, dec, mask=mask)
+    valid = mask.bool()
+    assert (enc_m - torch.from_numpy(z["encoder_masked"]))[valid].abs().max() < 2e-5
+    assert (logits_m - torch.from_numpy(z["logits_masked"])).abs().max() < 2e-5
+    # greedy decoding (recomputed without a cache) reproduces the reference's cached steps
+    cur = torch.zeros((2, 1), dtype=torch.long)
+    for step in range(4):
+        _, lg = orc.t5_model_logits(w, TINY_T5, ids, cur)
+        assert (lg[:, -1] - torch.from_numpy(z["greedy_logits"][:, step])).abs().max() < 2e-5
+        cur = torch.cat([cur, lg[:, -1:].argmax(-1)], dim=1)
+    assert torch.equal(cur[:, 1:], torch.from_numpy(z["greedy_tokens"]))

@@ -1,0 +1,237 @@
+"""A thin T5 encoder / decoder stack around the fused-bias kernels.
+
+Only what is needed to drive the attention path end to end (and to measure
+encoder tokens/s): embeddings, pre-norm blocks (RMSNorm -> attention -> residual,
+RMSNorm -> feed-forward -> residual), final norm, LM head.  Linear layers are
+plain `nn.Linear` (cuBLAS); attention, RMSNorm and decoding go through the
+library.  Module and parameter names follow the Hugging Face / TurboT5 layout
+(`shared`, `encoder.block.N.layer.0.SelfAttention.q`, `...layer.1.DenseReluDense.wi_0`,
+`decoder.block.N.layer.1.EncDecAttention.k`, `lm_head`), so a T5 state dict
+loads with `load_state_dict`.
+
+Restates the control flow of `T5Stack` / `T5Block` / `T5LayerSelfAttention` /
+`T5LayerCrossAttention` / `T5LayerFF` (src/turbot5/model/modeling.py:63-342,
+352-632) and the LM head of `T5ForConditionalGeneration`
+(src/turbot5/heads/t5_heads.py:132-260).  Differences: the decoder uses the
+flash module too (the reference hard-wires its `basic` attention there,
+modeling.py:134-135,170) and generation keeps a preallocated K/V cache that the
+split-KV decoding kernel reads in place, instead of `torch.cat` per step
+(src/turbot5/model/attentions.py:198).
+"""
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+from torch import nn
+
+from .attention import flash_attention_with_fusing_bias, flash_decoding_with_fusing_bias
+from .modules import T5FlashAttention, T5LayerNorm
+
+
+@dataclass
+class T5StackConfig:
+    vocab_size: int = 32128
+    d_model: int = 768
+    d_kv: int = 64
+    d_ff: int = 2048
+    num_layers: int = 12
+    num_decoder_layers: int = 12
+    num_heads: int = 12
+    relative_attention_num_buckets: int = 32
+    relative_attention_max_distance: int = 128
+    dropout_rate: float = 0.0
+    layer_norm_epsilon: float = 1e-6
+    feed_forward_proj: str = "gated-gelu"      # or "relu"
+    tie_word_embeddings: bool = False
+    is_decoder: bool = False
+    decoder_start_token_id: int = 0
+
+
+class T5DenseGatedActDense(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.wi_0 = nn.Linear(cfg.d_model, cfg.d_ff, bias=False)
+        self.wi_1 = nn.Linear(cfg.d_model, cfg.d_ff, bias=False)
+        self.wo = nn.Linear(cfg.d_ff, cfg.d_model, bias=False)
+
+    def forward(self, x):
+        return self.wo(nn.functional.gelu(self.wi_0(x), approximate="tanh") * self.wi_1(x))
+
+
+class T5DenseActDense(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.wi = nn.Linear(cfg.d_model, cfg.d_ff, bias=False)
+        self.wo = nn.Linear(cfg.d_ff, cfg.d_model, bias=False)
+
+    def forward(self, x):
+        return self.wo(torch.relu(self.wi(x)))
+
+
+class T5LayerFF(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        gated = cfg.feed_forward_proj.startswith("gated")
+        self.DenseReluDense = T5DenseGatedActDense(cfg) if gated else T5DenseActDense(cfg)
+        self.layer_norm = T5LayerNorm(cfg.d_model, eps=cfg.layer_norm_epsilon)
+
+    def forward(self, hidden):
+        return hidden + self.DenseReluDense(self.layer_norm(hidden).to(hidden.dtype))
+
+
+class T5LayerSelfAttention(nn.Module):
+    def __init__(self, cfg, has_relative_attention_bias):
+        super().__init__()
+        self.SelfAttention = T5FlashAttention(cfg, has_relative_attention_bias=has_relative_attention_bias)
+        self.layer_norm = T5LayerNorm(cfg.d_model, eps=cfg.layer_norm_epsilon)
+
+
+class T5LayerCrossAttention(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.EncDecAttention = T5FlashAttention(cfg, cross_attention=True, has_relative_attention_bias=False)
+        self.layer_norm = T5LayerNorm(cfg.d_model, eps=cfg.layer_norm_epsilon)
+
+
+class T5Block(nn.Module):
+    def __init__(self, cfg, has_relative_attention_bias):
+        super().__init__()
+        layers = [T5LayerSelfAttention(cfg, has_relative_attention_bias)]
+        if cfg.is_decoder:
+            layers.append(T5LayerCrossAttention(cfg))
+        layers.append(T5LayerFF(cfg))
+        self.layer = nn.ModuleList(layers)
+
+
+class DecoderCache:
+    """Preallocated K/V cache of one generation: self-attention keys/values grow in place,
+    cross-attention keys/values are projected once from the encoder output."""
+
+    def __init__(self, n_layers, batch, heads, d_kv, max_len, dtype, device):
+        self.self_k = [torch.empty((batch, heads, max_len, d_kv), dtype=dtype, device=device) for _ in range(n_layers)]
+        self.self_v = [torch.empty((batch, heads, max_len, d_kv), dtype=dtype, device=device) for _ in range(n_layers)]
+        self.cross_k: List[Optional[torch.Tensor]] = [None] * n_layers
+        self.cross_v: List[Optional[torch.Tensor]] = [None] * n_layers
+        self.length = 0
+        self.max_len = max_len
+
+
+class T5Stack(nn.Module):
+    def __init__(self, cfg: T5StackConfig, embed_tokens: nn.Embedding, is_decoder: bool):
+        super().__init__()
+        cfg = T5StackConfig(**{**cfg.__dict__, "is_decoder": is_decoder})
+        self.cfg = cfg
+        self.is_decoder = is_decoder
+        self.embed_tokens = embed_tokens
+        n = cfg.num_decoder_layers if is_decoder else cfg.num_layers
+        self.block = nn.ModuleList([T5Block(cfg, has_relative_attention_bias=(i == 0)) for i in range(n)])
+        self.final_layer_norm = T5LayerNorm(cfg.d_model, eps=cfg.layer_norm_epsilon)
+
+    def _table(self):
+        return self.block[0].layer[0].SelfAttention.relative_attention_bias.weight
+
+    def forward(self, input_ids=None, attention_mask=None, inputs_embeds=None, encoder_hidden_states=None,
+                encoder_attention_mask=None):
+        """Full (uncached) pass.  `attention_mask` is the raw 0/1 (B, L) mask or None."""
+        hidden = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+        table = self._table()
+        for blk in self.block:
+            sa = blk.layer[0]
+            normed = sa.layer_norm(hidden).to(hidden.dtype)
+            hidden = hidden + sa.SelfAttention(normed, mask=None if self.is_decoder else attention_mask,
+                                               position_bias=table)[0]
+            if self.is_decoder:
+                ca = blk.layer[1]
+                normed = ca.layer_norm(hidden).to(hidden.dtype)
+                hidden = hidden + ca.EncDecAttention(normed, mask=encoder_attention_mask,
+                                                     key_value_states=encoder_hidden_states)[0]
+            hidden = blk.layer[-1](hidden)
+        return self.final_layer_norm(hidden).to(hidden.dtype)
+
+    # ---- generation with a preallocated cache (decoder only)
+    def new_cache(self, encoder_hidden_states, max_len) -> DecoderCache:
+        cfg = self.cfg
+        B = encoder_hidden_states.shape[0]
+        cache = DecoderCache(len(self.block), B, cfg.num_heads, cfg.d_kv, max_len, encoder_hidden_states.dtype,
+                             encoder_hidden_states.device)
+        for i, blk in enumerate(self.block):
+            att = blk.layer[1].EncDecAttention
+            shape = lambda x: x.view(B, -1, cfg.num_heads, cfg.d_kv).transpose(1, 2)
+            cache.cross_k[i] = shape(att.k(encoder_hidden_states))
+            cache.cross_v[i] = shape(att.v(encoder_hidden_states))
+        return cache
+
+    def decode_step(self, input_ids, cache: DecoderCache, encoder_seqlens=None):
+        """One cached step for `input_ids` (B, M) (M new tokens, usually 1); returns (B, M, d_model)."""
+        cfg = self.cfg
+        B, M = input_ids.shape
+        H, D = cfg.num_heads, cfg.d_kv
+        t0 = cache.length
+        if t0 + M > cache.max_len:
+            raise ValueError("decoder cache is full")
+        hidden = self.embed_tokens(input_ids)
+        table = self._table()
+        shape = lambda x: x.view(B, M, H, D).transpose(1, 2)
+        for i, blk in enumerate(self.block):
+            sa, ca = blk.layer[0], blk.layer[1]
+            att = sa.SelfAttention
+            normed = sa.layer_norm(hidden).to(hidden.dtype)
+            q = shape(att.q(normed))
+            cache.self_k[i][:, :, t0:t0 + M] = shape(att.k(normed))
+            cache.self_v[i][:, :, t0:t0 + M] = shape(att.v(normed))
+            if M <= att.decode_max_rows:
+                o = flash_decoding_with_fusing_bias(q, cache.self_k[i], cache.self_v[i], table, causal=True,
+                                                    sm_scale=1.0, NUM_BUCKETS=cfg.relative_attention_num_buckets,
+                                                    MAX_DISTANCE=cfg.relative_attention_max_distance, kv_len=t0 + M)
+            else:
+                o = flash_attention_with_fusing_bias(q, cache.self_k[i][:, :, :t0 + M], cache.self_v[i][:, :, :t0 + M],
+                                                     table, causal=True, sm_scale=1.0,
+                                                     NUM_BUCKETS=cfg.relative_attention_num_buckets,
+                                                     MAX_DISTANCE=cfg.relative_attention_max_distance)
+            hidden = hidden + att.o(o.transpose(1, 2).reshape(B, M, H * D))
+            catt = ca.EncDecAttention
+            normed = ca.layer_norm(hidden).to(hidden.dtype)
+            q = shape(catt.q(normed))
+            if M <= catt.decode_max_rows:
+                o = flash_decoding_with_fusing_bias(q, cache.cross_k[i], cache.cross_v[i], None, causal=False,
+                                                    sm_scale=1.0, seqlens_k=encoder_seqlens, q_pos_offset=0)
+            else:
+                o = flash_attention_with_fusing_bias(q, cache.cross_k[i], cache.cross_v[i], None, causal=False,
+                                                     sm_scale=1.0, q_pos_offset=0)
+            hidden = hidden + catt.o(o.transpose(1, 2).reshape(B, M, H * D))
+            hidden = blk.layer[-1](hidden)
+        cache.length = t0 + M
+        return self.final_layer_norm(hidden).to(hidden.dtype)
+
+
+class T5ForConditionalGeneration(nn.Module):
+    def __init__(self, cfg: T5StackConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.shared = nn.Embedding(cfg.vocab_size, cfg.d_model)
+        self.encoder = T5Stack(cfg, self.shared, is_decoder=False)
+        self.decoder = T5Stack(cfg, self.shared, is_decoder=True)
+        self.lm_head = nn.Linear(cfg.d_model, cfg.vocab_size, bias=False)
+
+    def logits(self, decoder_hidden):
+        if self.cfg.tie_word_embeddings:
+            decoder_hidden = decoder_hidden * (self.cfg.d_model ** -0.5)
+        return self.lm_head(decoder_hidden)
+
+    def forward(self, input_ids, decoder_input_ids, attention_mask=None):
+        enc = self.encoder(input_ids, attention_mask=attention_mask)
+        dec = self.decoder(decoder_input_ids, encoder_hidden_states=enc, encoder_attention_mask=attention_mask)
+        return self.logits(dec)
+
+    @torch.no_grad()
+    def greedy_decode(self, encoder_hidden_states, steps, encoder_seqlens=None):
+        """Greedy generation from `decoder_start_token_id` with the preallocated cache."""
+        B = encoder_hidden_states.shape[0]
+        cache = self.decoder.new_cache(encoder_hidden_states, steps)
+        cur = torch.full((B, 1), self.cfg.decoder_start_token_id, dtype=torch.long, device=encoder_hidden_states.device)
+        tokens, last_logits = [], None
+        for _ in range(steps):
+            last_logits = self.logits(self.decoder.decode_step(cur, cache, encoder_seqlens))
+            cur = last_logits[:, -1:].argmax(-1)
+            tokens.append(cur)
+        return torch.cat(tokens, dim=1), last_logits
