@@ -104,9 +104,19 @@ typedef struct {
   int32_t q_pos_offset;       /* dense only; the reference's P_SEQ = N - M for cached decoding */
   int32_t kernel;             /* t5b_kernel */
   float sm_scale;
+  /* Optional scratch (may be NULL): lets the tensor-core kernel split the key range of the
+   * query tiles of the last, partially filled wave of blocks over several blocks and merge
+   * the partial results in the same launch.  Size from t5b_attention_workspace_bytes();
+   * 256-byte aligned; must be zero before its first use (the kernel leaves its counters at
+   * zero); one buffer per stream in flight. */
+  void* workspace;
+  int64_t workspace_bytes;
 } t5b_attn_args;
 
 T5B_API int t5b_attention_fwd(const t5b_attn_args* args, void* stream);
+/* Bytes of scratch that would let t5b_attention_fwd balance its last wave on the current
+ * device for these arguments (0 if splitting would not help or does not apply). */
+T5B_API int64_t t5b_attention_workspace_bytes(const t5b_attn_args* args);
 
 /* ---- split-KV flash decoding ---------------------------------------------------
  * Stands in for the split/merge semantics of flash_attn_v2_fwd

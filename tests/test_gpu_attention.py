@@ -317,3 +317,25 @@ def test_config4_long_sequence_spot_rows():
     shard = t5b.flash_attention_with_fusing_bias(q[:, :, lo:lo + 12500], k, v, table, sm_scale=1.0, q_pos_offset=lo)
     diff = (shard.float() - out[:, :, lo:lo + 12500].float()).abs()
     assert diff.max().item() <= 2e-2 and diff.mean().item() <= 5e-4
+
+
+@pytest.mark.parametrize("B,H,M,N", [(1, 2, 2048, 2048), (1, 3, 300, 4096), (2, 2, 1000, 1500)])
+def test_last_wave_split_matches_unsplit_and_oracle(B, H, M, N):
+    # few query tiles: the key range of every tile is split over several blocks and merged in
+    # the same launch; results and LSE must agree with the unsplit launch and the oracle
+    t5b = _ops()
+    dt = torch.bfloat16
+    q, k, v = seeded((B, H, M, 64), 1, dtype=dt), seeded((B, H, N, 64), 2, dtype=dt), seeded((B, H, N, 64), 3, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    args = (q.cuda(), k.cuda(), v.cuda(), table.cuda())
+    for _ in range(2):      # second call reuses the scratch: its counters were left at zero
+        split, lse_s = t5b.flash_attention_with_fusing_bias(*args, sm_scale=1.0, q_pos_offset=0, return_lse=True,
+                                                            kernel="tcgen05")
+    plain, lse_p = t5b.flash_attention_with_fusing_bias(*args, sm_scale=1.0, q_pos_offset=0, return_lse=True,
+                                                        kernel="tcgen05", balance_last_wave=False)
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    want = orc.attention_basic(q, k, v, table, q_pos_offset=0)
+    check_close(split, want, dt, "split")
+    check_close(plain, want, dt, "unsplit")
+    assert (lse_s - lse_p).abs().max().item() < 1e-2      # each carries the bf16 rounding of its row sums

@@ -64,7 +64,7 @@ def _unit_stride_last(t):
 
 def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
                                      NUM_BUCKETS=32, MAX_DISTANCE=128, *, q_pos_offset=None,
-                                     return_lse=False, kernel="auto"):
+                                     return_lse=False, kernel="auto", balance_last_wave=True):
     """softmax(sm_scale * Q K^T + T5 bias(n - m) [+ causal mask]) V without an L x L tensor.
 
     q (B,H,M,D), k/v (B,H,N,D), any batch/head/row strides (last dim contiguous);
@@ -74,6 +74,8 @@ def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
     at key position `q_pos_offset + m` (default N - M, the cached-decoding
     alignment of the reference's `basic` path; sequence parallel callers pass
     their shard offset).  Returns a tensor with q's shape, dtype and strides.
+    `balance_last_wave` lets the kernel split the key range of the query tiles of a partially
+    filled last wave of blocks (scratch comes from a per-stream cache).
     """
     _check_qkv(q, k, v)
     B, H, M, D = q.shape
@@ -106,7 +108,13 @@ def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
     a.q_pos_offset = (N - M) if q_pos_offset is None else int(q_pos_offset)
     a.kernel = {"auto": nat.KERNEL_AUTO, "tcgen05": nat.KERNEL_TCGEN05, "simt": nat.KERNEL_SIMT}[kernel]
     a.sm_scale = float(sm_scale)
+    a.workspace, a.workspace_bytes = None, 0
     with torch.cuda.device(q.device):
+        if balance_last_wave:
+            need = nat.lib().t5b_attention_workspace_bytes(a)
+            if need > 0:
+                ws = _scratch(q.device, "attn", need)
+                a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)), "flash_attention_with_fusing_bias")
     return (out, lse) if return_lse else out
 
@@ -159,22 +167,28 @@ def flash_attention_with_fusing_bias_varlen(q, k, v, bias, cu_seqlens_q, cu_seql
     a.q_pos_offset = 0
     a.kernel = {"auto": nat.KERNEL_AUTO, "tcgen05": nat.KERNEL_TCGEN05, "simt": nat.KERNEL_SIMT}[kernel]
     a.sm_scale = float(sm_scale)
+    a.workspace, a.workspace_bytes = None, 0
     with torch.cuda.device(q.device):
         nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)),
                   "flash_attention_with_fusing_bias_varlen")
     return (out, lse) if return_lse else out
 
 
-def _decode_workspace(device, nbytes: int) -> torch.Tensor:
+def _scratch(device, kind: str, nbytes: int) -> torch.Tensor:
+    """Zero-initialised scratch, one buffer per (device, stream, kernel kind).  The counters at
+    its front must start at zero; the kernels leave them zero."""
     dev = torch.device(device)
-    key = (dev.index if dev.index is not None else torch.cuda.current_device(),
+    key = (kind, dev.index if dev.index is not None else torch.cuda.current_device(),
            torch.cuda.current_stream(dev).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        # counters at the front must start at zero; the kernel leaves them zero
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
         _workspaces[key] = ws
     return ws
+
+
+def _decode_workspace(device, nbytes: int) -> torch.Tensor:
+    return _scratch(device, "decode", nbytes)
 
 
 def flash_decoding_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32,

@@ -53,3 +53,10 @@ extern "C" int t5b_attention_fwd(const t5b_attn_args* a, void* stream) {
   if (a->kernel != T5B_KERNEL_SIMT && tc_ok) return sm100_attention_fwd(*a, spec, st);
   return simt_attention_fwd(*a, spec, st);
 }
+
+extern "C" int64_t t5b_attention_workspace_bytes(const t5b_attn_args* a) {
+  if (!a || a->B <= 0 || a->H <= 0 || a->M <= 0 || a->N <= 0) return 0;
+  if (a->kernel == T5B_KERNEL_SIMT || !sm100_supports(*a)) return 0;
+  const TailPlan plan = sm100_tail_plan(*a);
+  return plan.parts > 1 ? plan.bytes() : 0;
+}

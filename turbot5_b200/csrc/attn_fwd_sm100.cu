@@ -116,16 +116,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int h = blockIdx.y;
 
   // ---------------------------------------------------------------- work item
-  // dense: blockIdx.x = query tile (heaviest causal tiles first), blockIdx.z = batch
-  // varlen: blockIdx.x indexes the concatenated per-sequence tile lists
+  // dense: 1-D grid over (query tile, head, batch), heaviest causal tiles first; blocks at or
+  //        beyond p.tail_first share a tile `parts` ways along the keys (last-wave balancing)
+  // varlen: blockIdx.x indexes the concatenated per-sequence tile lists, blockIdx.y = head
   TileWork* shared_work = reinterpret_cast<TileWork*>(&ctl->work[0]);
   TileWork w;
+  int h, batch_idx = 0, part = 0, parts = 1, tail_slot = 0;
   if (p.cu_q == nullptr) {
-    w = dense_tile<BM>(p, (int)blockIdx.x, (int)blockIdx.z);
+    int tile_lin = (int)blockIdx.x;
+    if (tile_lin >= p.tail_first) {
+      const int e = tile_lin - p.tail_first;
+      parts = p.tail_parts;
+      tail_slot = e / parts;
+      part = e - tail_slot * parts;
+      tile_lin = p.tail_first + tail_slot;
+    }
+    const int tx = tile_lin % p.tiles_x;
+    const int hb = tile_lin / p.tiles_x;
+    h = hb % p.H;
+    batch_idx = hb / p.H;
+    w = dense_tile<BM>(p, tx, batch_idx);
   } else {
+    h = blockIdx.y;
     if (warp == 0) {
       TileWork f = find_varlen_tile<BM>(p, (int)blockIdx.x);
       if (lane == 0) *shared_work = f;
@@ -140,7 +154,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // keys this tile can see
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
-  const int n_kv = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+  const int n_kv_all = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+  // this block's share of the key tiles: [kv_first, kv_first + n_kv)
+  const int kv_per = (n_kv_all + parts - 1) / parts;
+  const int kv_first = min(part * kv_per, n_kv_all);
+  const int n_kv = min(n_kv_all, kv_first + kv_per) - kv_first;
 
   // ---------------------------------------------------------------- set-up
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
@@ -199,10 +217,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const uint32_t ph = (uint32_t)((j / STAGES) & 1);
         if (j >= STAGES && !mbar_wait_bounded(bar(BAR_K_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
         mbar_expect_tx(bar(BAR_K_FULL + s), TILE_BYTES);
-        tma_load_4d(sK + s * TILE_BYTES, &tmap_k, bar(BAR_K_FULL + s), 0, k_row0 + j * BN, h, b);
+        tma_load_4d(sK + s * TILE_BYTES, &tmap_k, bar(BAR_K_FULL + s), 0, k_row0 + (kv_first + j) * BN, h, b);
         if (j >= STAGES && !mbar_wait_bounded(bar(BAR_V_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
         mbar_expect_tx(bar(BAR_V_FULL + s), TILE_BYTES);
-        tma_load_4d(sV + s * TILE_BYTES, &tmap_v, bar(BAR_V_FULL + s), 0, k_row0 + j * BN, h, b);
+        tma_load_4d(sV + s * TILE_BYTES, &tmap_v, bar(BAR_V_FULL + s), 0, k_row0 + (kv_first + j) * BN, h, b);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -276,7 +294,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     bool ok = true;
 
     for (int j = 0; j < n_kv; ++j) {
-      const int n0 = j * BN;                       // first key of the tile
+      const int n0 = (kv_first + j) * BN;          // first key of the tile
       const int c0 = half * 64;                    // first column of this thread inside the tile
       if (!mbar_wait_bounded(bar(BAR_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
@@ -433,34 +451,82 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (ok && !pair_sync()) { ok = false; fail_code = 33; }
     l_sum += ctl->xchg[slot][half ^ 1][r];
     if (ok) {
-      const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
       const bool row_ok = r < rows_in_tile;
       const int64_t row = (int64_t)q_row0 + r;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + half * 64 +
                       2 * ((int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + row * p.o_stride_m);
-      uint32_t v[32];
-      if (n_kv > 0) {
-        tmem_ld_x32(tO, v);
-        tmem_ld_wait();
-      } else {
+      float o[32];
+      {
+        uint32_t v[32];
+        if (n_kv > 0) {
+          tmem_ld_x32(tO, v);
+          tmem_ld_wait();
+        } else {
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
         #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0u;
+        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]);
       }
-      if (row_ok) {
+      bool write_out = row_ok;
+      if (parts > 1 && row_ok) {
+        // This block saw only part of the keys.  Publish (max, sum, unnormalised O) for this
+        // row half; the last of the `parts` blocks to arrive merges them (no waiting).
+        const int64_t slot = (int64_t)tail_slot * parts + part;
+        float* my_o = p.ws_o + (slot * BM + r) * HD + half * 32;
         #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 w;
-          w.x = pack2<kBf16>(__uint_as_float(v[8 * i + 0]) * inv_l, __uint_as_float(v[8 * i + 1]) * inv_l);
-          w.y = pack2<kBf16>(__uint_as_float(v[8 * i + 2]) * inv_l, __uint_as_float(v[8 * i + 3]) * inv_l);
-          w.z = pack2<kBf16>(__uint_as_float(v[8 * i + 4]) * inv_l, __uint_as_float(v[8 * i + 5]) * inv_l);
-          w.w = pack2<kBf16>(__uint_as_float(v[8 * i + 6]) * inv_l, __uint_as_float(v[8 * i + 7]) * inv_l);
-          *reinterpret_cast<uint4*>(orow + i * 16) = w;
+        for (int i = 0; i < 8; ++i)
+          reinterpret_cast<float4*>(my_o)[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        float* my_ml = p.ws_ml + ((slot * BM + r) * 2 + half) * 2;
+        my_ml[0] = m_use;
+        my_ml[1] = l_sum;
+        __threadfence();
+        int* counter = p.ws_counters + ((int64_t)tail_slot * BM + r) * 2 + half;
+        const int arrived = atomicAdd(counter, 1);
+        write_out = (arrived == parts - 1);
+        if (write_out) {
+          __threadfence();
+          float m_all = -INFINITY;
+          for (int s2 = 0; s2 < parts; ++s2)
+            m_all = fmaxf(m_all, __ldcg(p.ws_ml + ((((int64_t)tail_slot * parts + s2) * BM + r) * 2 + half) * 2));
+          const float m_ref = (m_all == -INFINITY) ? 0.f : m_all;
+          float l_all = 0.f;
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+          for (int s2 = 0; s2 < parts; ++s2) {
+            const int64_t sl = (int64_t)tail_slot * parts + s2;
+            const float* ml = p.ws_ml + ((sl * BM + r) * 2 + half) * 2;
+            const float sc = fast_exp2(__ldcg(ml) - m_ref);
+            l_all = fmaf(__ldcg(ml + 1), sc, l_all);
+            const float4* po = reinterpret_cast<const float4*>(p.ws_o + (sl * BM + r) * HD + half * 32);
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 t4 = __ldcg(po + i);
+              o[4 * i] = fmaf(t4.x, sc, o[4 * i]);         o[4 * i + 1] = fmaf(t4.y, sc, o[4 * i + 1]);
+              o[4 * i + 2] = fmaf(t4.z, sc, o[4 * i + 2]); o[4 * i + 3] = fmaf(t4.w, sc, o[4 * i + 3]);
+            }
+          }
+          m_use = m_all;
+          l_sum = l_all;
+          *counter = 0;     // leave the scratch ready for the next launch
         }
       }
-      if (p.lse != nullptr && row_ok && half == 0) {
-        const float lse = l_sum > 0.f ? (m_use + log2f(l_sum)) * kLn2 : -INFINITY;
-        if (p.cu_q == nullptr) p.lse[((int64_t)blockIdx.z * p.H + h) * p.M + row] = lse;
-        else p.lse[row * p.H + h] = lse;
+      if (write_out) {
+        const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 w4;
+          w4.x = pack2<kBf16>(o[8 * i + 0] * inv_l, o[8 * i + 1] * inv_l);
+          w4.y = pack2<kBf16>(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
+          w4.z = pack2<kBf16>(o[8 * i + 4] * inv_l, o[8 * i + 5] * inv_l);
+          w4.w = pack2<kBf16>(o[8 * i + 6] * inv_l, o[8 * i + 7] * inv_l);
+          *reinterpret_cast<uint4*>(orow + i * 16) = w4;
+        }
+        if (p.lse != nullptr && half == 0) {
+          const float lse = l_sum > 0.f ? (m_use + log2f(l_sum)) * kLn2 : -INFINITY;
+          if (p.cu_q == nullptr) p.lse[((int64_t)batch_idx * p.H + h) * p.M + row] = lse;
+          else p.lse[row * p.H + h] = lse;
+        }
       }
     }
   }
@@ -527,6 +593,44 @@ bool sm100_supports(const t5b_attn_args& a) {
   return true;
 }
 
+// Last-wave balancing for dense, non-causal launches: with two blocks per SM the grid runs in
+// waves of 2 x SMs equal-sized blocks; the tiles of a partially filled last wave are split along
+// the keys so that the wave finishes in a fraction of a block time.
+TailPlan sm100_tail_plan(const t5b_attn_args& a) {
+  using namespace sm100;
+  TailPlan t;
+  t.tiles_x = (a.M + BM - 1) / BM;
+  const long long n_total = (long long)t.tiles_x * a.H * a.B;
+  t.n_total = (int)(n_total > 0x7fffffffLL ? 0x7fffffff : n_total);
+  t.tail_first = t.n_total;
+  t.parts = 1;
+  t.counters_bytes = t.ml_bytes = t.o_bytes = 0;
+  if (a.cu_seqlens_q != nullptr || a.causal || n_total > 0x3fffffffLL) return t;
+  static int sms[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return t; }
+  if (sms[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { cudaGetLastError(); return t; }
+    sms[dev] = n;
+  }
+  const int slots = 2 * sms[dev];
+  const int rem = (int)(n_total % slots);
+  const int n_kv = (a.N + BN - 1) / BN;
+  if (rem == 0) return t;
+  int parts = slots / rem;
+  if (parts > n_kv / 4) parts = n_kv / 4;     // at least four key tiles per part
+  if (parts > 8) parts = 8;
+  if (parts < 2) return t;
+  t.parts = parts;
+  t.tail_first = t.n_total - rem;
+  auto al = [](int64_t x) { return (x + 255) / 256 * 256; };
+  t.counters_bytes = al((int64_t)rem * BM * 2 * 4);
+  t.ml_bytes = al((int64_t)rem * parts * BM * 2 * 2 * 4);
+  t.o_bytes = al((int64_t)rem * parts * BM * HD * 4);
+  return t;
+}
+
 int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream) {
   using namespace sm100;
   const bool varlen = a.cu_seqlens_q != nullptr;
@@ -551,7 +655,22 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
     const long long ub = (long long)a.total_q / BM + a.B;
     grid = dim3((unsigned)ub, (unsigned)a.H, 1);
   } else {
-    grid = dim3((unsigned)((a.M + BM - 1) / BM), (unsigned)a.H, (unsigned)a.B);
+    TailPlan plan = sm100_tail_plan(a);
+    p.tiles_x = plan.tiles_x;
+    p.tail_first = plan.n_total;
+    long long blocks = plan.n_total;
+    if (plan.parts > 1 && a.workspace != nullptr && a.workspace_bytes >= plan.bytes() &&
+        ((uintptr_t)a.workspace & 255) == 0) {
+      char* ws = (char*)a.workspace;
+      p.ws_counters = (int32_t*)ws;
+      p.ws_ml = (float*)(ws + plan.counters_bytes);
+      p.ws_o = (float*)(ws + plan.counters_bytes + plan.ml_bytes);
+      p.tail_first = plan.tail_first;
+      p.tail_parts = plan.parts;
+      blocks = plan.tail_first + (long long)(plan.n_total - plan.tail_first) * plan.parts;
+    }
+    if (blocks > 0x7fffffffLL) return T5B_ERR_SHAPE;
+    grid = dim3((unsigned)blocks, 1, 1);
   }
   if (grid.y > 65535 || grid.z > 65535) return T5B_ERR_SHAPE;
   auto kern = bf16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;

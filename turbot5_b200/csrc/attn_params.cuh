@@ -21,7 +21,22 @@ struct AttnParams {
   int32_t causal;
   int32_t q_pos_offset;
   float scale_log2;   // sm_scale * log2(e): softmax runs in the base-2 domain
+  // Dense tensor-core launches use a 1-D grid over (query tile, head, batch).  Blocks at or
+  // beyond `tail_first` share a query tile `tail_parts` ways along the keys and merge through
+  // the scratch arrays (tail_first = number of tiles when nothing is split).
+  int32_t tiles_x, tail_first, tail_parts;
+  int32_t* ws_counters;   // [tail tiles][128 rows][2 halves]
+  float* ws_ml;           // [tail tiles * parts][128][2][2]  (max, sum) per row half
+  float* ws_o;            // [tail tiles * parts][128][64]    unnormalised O
 };
+
+// How the last wave of a dense launch is split (host side).
+struct TailPlan {
+  int tiles_x, n_total, tail_first, parts;
+  int64_t counters_bytes, ml_bytes, o_bytes;
+  int64_t bytes() const { return counters_bytes + ml_bytes + o_bytes; }
+};
+TailPlan sm100_tail_plan(const t5b_attn_args& a);
 
 inline AttnParams make_attn_params(const t5b_attn_args& a) {
   AttnParams p;
@@ -39,6 +54,8 @@ inline AttnParams make_attn_params(const t5b_attn_args& a) {
   p.causal = a.causal;
   p.q_pos_offset = a.q_pos_offset;
   p.scale_log2 = a.sm_scale * kLog2e;
+  p.tiles_x = 0; p.tail_first = 0x7fffffff; p.tail_parts = 1;
+  p.ws_counters = nullptr; p.ws_ml = nullptr; p.ws_o = nullptr;
   return p;
 }
 

@@ -1,7 +1,8 @@
 // T5 RMSNorm forward: y = w * round_w(x * rsqrt(mean(x^2) + eps)), float32
 // statistics, no mean subtraction, no bias.  HBM-bound: every element is read
-// once and written once; a warp owns a row and keeps it in registers between
-// the reduction and the scaling (rows up to 8 x 512 bytes), 16-byte accesses.
+// once and written once; a warp owns two rows at a time and keeps them in registers
+// between the reduction and the scaling (rows up to 8 x 512 bytes), 16-byte streaming
+// accesses, grid-stride over the rows.
 //
 // Rounding points follow T5LayerNorm._forward (src/turbot5/model/modules.py:
 // 52-60): with a half-precision weight the normalised value is first rounded to
@@ -13,7 +14,6 @@ namespace t5b {
 namespace rms {
 
 constexpr int WARPS = 4;
-constexpr int MAXV = 8;   // 16-byte vectors cached per lane
 
 template <typename T> struct VecOf { static constexpr int N = 16 / sizeof(T); };
 
@@ -24,70 +24,90 @@ __device__ __forceinline__ TY scale_one(float x, float rstd, TW w) {
   return from_float<TY>(to_float<TW>(w) * xn);
 }
 
-template <typename TX, typename TW, typename TY, bool VECTOR>
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_stream16(void* p, const uint4& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Vector path: a warp owns ROWS rows at a time and keeps them in registers (VPL 16-byte
+// vectors per lane and row) between the sum of squares and the scaling, so every element is
+// read once and written once.  All loads of the ROWS rows are issued before the first
+// reduction, and warps walk the rows with a grid stride (no tail wave).
+template <typename TX, typename TW, typename TY, int VPL, int ROWS>
 __global__ void __launch_bounds__(WARPS * 32)
-rmsnorm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y,
-               float* __restrict__ rstd_out, int64_t rows, int d, int64_t xs, int64_t ys, float eps) {
+rmsnorm_vec_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y,
+                   float* __restrict__ rstd_out, int64_t rows, int d, int64_t xs, int64_t ys, float eps) {
+  constexpr int VX = VecOf<TX>::N;
+  constexpr int OUT16 = (int)(VX * sizeof(TY) / 16);   // 16-byte stores per input vector (1 or 2)
+  const int lane = threadIdx.x & 31;
+  const int nvec = d / VX;
+  const int64_t warp_id = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
+  const int64_t n_warps = (int64_t)gridDim.x * WARPS;
+  const float inv_d = 1.f / (float)d;
+  for (int64_t row0 = warp_id * ROWS; row0 < rows; row0 += n_warps * ROWS) {
+    uint4 cache[ROWS][VPL];
+    #pragma unroll
+    for (int r = 0; r < ROWS; ++r)
+      #pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = lane + i * 32;
+        cache[r][i] = make_uint4(0, 0, 0, 0);
+        if (row0 + r < rows && v < nvec) cache[r][i] = ld_stream16(x + (row0 + r) * xs + v * VX);
+      }
+    #pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      if (row0 + r >= rows) break;
+      float ss = 0.f;
+      #pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const TX* e = reinterpret_cast<const TX*>(&cache[r][i]);
+        #pragma unroll
+        for (int k = 0; k < VX; ++k) { const float f = to_float<TX>(e[k]); ss = fmaf(f, f, ss); }
+      }
+      #pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float rstd = rsqrtf(ss * inv_d + eps);
+      if (rstd_out && lane == 0) rstd_out[row0 + r] = rstd;
+      TY* yr = y + (row0 + r) * ys;
+      #pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = lane + i * 32;
+        if (v < nvec) {
+          const TX* e = reinterpret_cast<const TX*>(&cache[r][i]);
+          TY outv[VX];
+          #pragma unroll
+          for (int k = 0; k < VX; ++k) outv[k] = scale_one<TX, TW, TY>(to_float<TX>(e[k]), rstd, w[v * VX + k]);
+          const uint4* src = reinterpret_cast<const uint4*>(outv);
+          #pragma unroll
+          for (int k = 0; k < OUT16; ++k) st_stream16(yr + v * VX + k * (16 / (int)sizeof(TY)), src[k]);
+        }
+      }
+    }
+  }
+}
+
+// Generic path: any d, any alignment; the row is read twice (the second read hits L1/L2).
+template <typename TX, typename TW, typename TY>
+__global__ void __launch_bounds__(WARPS * 32)
+rmsnorm_generic_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y,
+                       float* __restrict__ rstd_out, int64_t rows, int d, int64_t xs, int64_t ys, float eps) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5);
   if (row >= rows) return;
   const TX* xr = x + row * xs;
   TY* yr = y + row * ys;
   float ss = 0.f;
-  if (VECTOR) {
-    constexpr int VX = VecOf<TX>::N;
-    const int nvec = d / VX;
-    uint4 cache[MAXV];
-    #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-      const int v = lane + i * 32;
-      if (v < nvec) {
-        cache[i] = *reinterpret_cast<const uint4*>(xr + v * VX);
-        const TX* e = reinterpret_cast<const TX*>(&cache[i]);
-        #pragma unroll
-        for (int k = 0; k < VX; ++k) { const float f = to_float<TX>(e[k]); ss = fmaf(f, f, ss); }
-      }
-    }
-    for (int v = lane + MAXV * 32; v < nvec; v += 32) {
-      const uint4 u = *reinterpret_cast<const uint4*>(xr + v * VX);
-      const TX* e = reinterpret_cast<const TX*>(&u);
-      #pragma unroll
-      for (int k = 0; k < VX; ++k) { const float f = to_float<TX>(e[k]); ss = fmaf(f, f, ss); }
-    }
-    #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float rstd = rsqrtf(ss / (float)d + eps);
-    if (rstd_out && lane == 0) rstd_out[row] = rstd;
-    auto emit = [&](const uint4& u, int v) {
-      const TX* e = reinterpret_cast<const TX*>(&u);
-      TY outv[VX];
-      #pragma unroll
-      for (int k = 0; k < VX; ++k) outv[k] = scale_one<TX, TW, TY>(to_float<TX>(e[k]), rstd, w[v * VX + k]);
-      constexpr int OUT16 = (int)(VX * sizeof(TY) / 16);
-      const uint4* src = reinterpret_cast<const uint4*>(outv);
-      uint4* dst = reinterpret_cast<uint4*>(yr + v * VX);
-      #pragma unroll
-      for (int k = 0; k < OUT16; ++k) dst[k] = src[k];
-      if (OUT16 == 0) {   // 8-byte case cannot happen for the supported type pairs
-        #pragma unroll
-        for (int k = 0; k < VX; ++k) yr[v * VX + k] = outv[k];
-      }
-    };
-    #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-      const int v = lane + i * 32;
-      if (v < nvec) emit(cache[i], v);
-    }
-    for (int v = lane + MAXV * 32; v < nvec; v += 32)
-      emit(*reinterpret_cast<const uint4*>(xr + v * VX), v);
-  } else {
-    for (int i = lane; i < d; i += 32) { const float f = to_float<TX>(xr[i]); ss = fmaf(f, f, ss); }
-    #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float rstd = rsqrtf(ss / (float)d + eps);
-    if (rstd_out && lane == 0) rstd_out[row] = rstd;
-    for (int i = lane; i < d; i += 32) yr[i] = scale_one<TX, TW, TY>(to_float<TX>(xr[i]), rstd, w[i]);
-  }
+  for (int i = lane; i < d; i += 32) { const float f = to_float<TX>(xr[i]); ss = fmaf(f, f, ss); }
+  #pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float rstd = rsqrtf(ss / (float)d + eps);
+  if (rstd_out && lane == 0) rstd_out[row] = rstd;
+  for (int i = lane; i < d; i += 32) yr[i] = scale_one<TX, TW, TY>(to_float<TX>(xr[i]), rstd, w[i]);
 }
 
 template <typename TX, typename TW, typename TY>
@@ -96,15 +116,28 @@ static int launch(const void* x, const void* w, void* y, float* rstd, int64_t ro
   constexpr int VX = VecOf<TX>::N;
   const bool vec = d % VX == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
                    (xs * sizeof(TX)) % 16 == 0 && (ys * sizeof(TY)) % 16 == 0 &&
-                   (VX * sizeof(TY)) % 16 == 0;
-  const int64_t blocks = (rows + WARPS - 1) / WARPS;
-  if (blocks > 0x7fffffffLL) return T5B_ERR_SHAPE;
-  if (vec)
-    rmsnorm_kernel<TX, TW, TY, true><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
-        (const TX*)x, (const TW*)w, (TY*)y, rstd, rows, d, xs, ys, eps);
-  else
-    rmsnorm_kernel<TX, TW, TY, false><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
-        (const TX*)x, (const TW*)w, (TY*)y, rstd, rows, d, xs, ys, eps);
+                   (VX * sizeof(TY)) % 16 == 0 && d / VX <= 32 * 8;
+  const TX* xp = (const TX*)x; const TW* wp = (const TW*)w; TY* yp = (TY*)y;
+  if (vec) {
+    const int vpl = (d / VX + 31) / 32;
+    constexpr int ROWS = 2;
+    int64_t blocks = (rows + WARPS * ROWS - 1) / (WARPS * ROWS);
+    const int64_t cap = 148 * 16;          // grid-stride over the rows beyond a few waves
+    if (blocks > cap) blocks = cap;
+#define T5B_RMS_LAUNCH(V) rmsnorm_vec_kernel<TX, TW, TY, V, ROWS><<<(unsigned)blocks, WARPS * 32, 0, stream>>>( \
+        xp, wp, yp, rstd, rows, d, xs, ys, eps)
+    if (vpl <= 1) T5B_RMS_LAUNCH(1);
+    else if (vpl == 2) T5B_RMS_LAUNCH(2);
+    else if (vpl == 3) T5B_RMS_LAUNCH(3);
+    else if (vpl == 4) T5B_RMS_LAUNCH(4);
+    else if (vpl <= 6) T5B_RMS_LAUNCH(6);
+    else T5B_RMS_LAUNCH(8);
+#undef T5B_RMS_LAUNCH
+  } else {
+    const int64_t blocks = (rows + WARPS - 1) / WARPS;
+    if (blocks > 0x7fffffffLL) return T5B_ERR_SHAPE;
+    rmsnorm_generic_kernel<TX, TW, TY><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(xp, wp, yp, rstd, rows, d, xs, ys, eps);
+  }
   return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;
 }
 

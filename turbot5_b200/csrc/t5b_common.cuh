@@ -84,6 +84,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// Same, but the hardware may keep the thread suspended for up to `hint_ns` before it
+// reports "not yet" (it still wakes as soon as the phase completes): far fewer polling
+// instructions competing with the working warps for issue slots.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -99,13 +111,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   long long limit_cycles = 2000000000LL) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  int spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255) == 0) {
-      if (*abort_flag != 0) return false;
-      if (clock64() - t0 > limit_cycles) { *abort_flag = 1; return false; }
-    }
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;   // sleeps up to 20 us per attempt
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > limit_cycles) { *abort_flag = 1; return false; }
   }
 }
 
