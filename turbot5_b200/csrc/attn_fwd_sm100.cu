@@ -625,7 +625,9 @@ TailPlan sm100_tail_plan(const t5b_attn_args& a) {
   t.parts = parts;
   t.tail_first = t.n_total - rem;
   auto al = [](int64_t x) { return (x + 255) / 256 * 256; };
-  t.counters_bytes = al((int64_t)rem * BM * 2 * 4);
+  // the counter area has one fixed size per device, so that launches with different splits
+  // sharing a scratch buffer never see each other's partial results as counters
+  t.counters_bytes = al((int64_t)slots * BM * 2 * 4);
   t.ml_bytes = al((int64_t)rem * parts * BM * 2 * 2 * 4);
   t.o_bytes = al((int64_t)rem * parts * BM * HD * 4);
   return t;
