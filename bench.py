@@ -33,8 +33,8 @@ WORKLOAD = dict(name="fused-bias attention fwd, T5-base heads @8k", B=2, H=12, L
                 num_buckets=32, max_distance=128)
 L2_BYTES = 126 * 1024 * 1024
 # DRAM traffic (read + write) of one launch of the forward kernel on the workload above,
-# from the ncu capture summarised in profiles/attn_fwd_sm100_8k.md; None until captured.
-NCU_DRAM_BYTES_PER_LAUNCH = None
+# from the ncu capture summarised in profiles/attn_fwd_sm100_8k.md (dram__bytes_read + dram__bytes_write).
+NCU_DRAM_BYTES_PER_LAUNCH = 75.6e6 + 12.4e6
 
 
 def flops_per_step(w):
