@@ -396,9 +396,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             pk[i] = pack2<kBf16>(p0, p1);
             // bf16: normalise by the sum of the ROUNDED probabilities the tensor core will
             // use, so a row dominated by one key stays an exact convex combination
-            const float q0 = kBf16 ? __uint_as_float(pk[i] << 16) : p0;
-            const float q1 = kBf16 ? __uint_as_float(pk[i] & 0xffff0000u) : p1;
-            if (i & 1) add2(t2, t3, q0, q1); else add2(t0, t1, q0, q1);
+            if (kBf16) {
+              if (i & 1) add_bf16x2(t2, t3, pk[i]); else add_bf16x2(t0, t1, pk[i]);
+            } else {
+              if (i & 1) add2(t2, t3, p0, p1); else add2(t0, t1, p0, p1);
+            }
           }
           tmem_st_x16(tP + c * 16, pk);
         }

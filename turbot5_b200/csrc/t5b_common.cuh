@@ -252,6 +252,14 @@ __device__ __forceinline__ void add2(float& acc0, float& acc1, float x0, float x
       : "+f"(acc0), "+f"(acc1) : "f"(x0), "f"(x1));
 }
 
+// (acc0, acc1) += the two bf16 halves of `packed`, exactly (mixed-precision add: the bf16
+// operand is widened inside the instruction, no shift/mask to unpack it first).
+__device__ __forceinline__ void add_bf16x2(float& acc0, float& acc1, uint32_t packed) {
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\t"
+      "add.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %1, hi, %1;\n\t}"
+      : "+f"(acc0), "+f"(acc1) : "r"(packed));
+}
+
 // Shared-memory matrix descriptor for tcgen05.mma (128-byte swizzle, version 1).
 // start address, leading/stride byte offsets are encoded >> 4.
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
