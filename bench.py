@@ -222,24 +222,49 @@ def main():
     fl = flops_per_step(w)
     value = world * fl / (ms_step * 1e-3) / 1e12
 
-    # ---- end to end through the public API with host buffers (pinned): H2D of q/k/v, kernel, D2H of out
+    # ---- end to end through the public API with host buffers (pinned): every step copies its
+    # q/k/v from the host, runs the attention call and copies the result back.  The copies run
+    # on their own streams with two buffer slots, so that the upload of step i+1 and the
+    # download of step i-1 overlap the kernel of step i (as a serving loop would do it).
     e2e_steps = max(3, min(args.steps, 20))
     host_sets = [[t_.contiguous().cpu().pin_memory() for t_ in sets[i % n_sets]] for i in range(2)]
-    host_out = torch.empty((B, H, L, D), dtype=dt).pin_memory()
-    dev_in = [torch.empty((B, H, L, D), dtype=dt, device=dev) for _ in range(3)]
+    host_out = [torch.empty((B, H, L, D), dtype=dt).pin_memory() for _ in range(2)]
+    dev_in = [[torch.empty((B, H, L, D), dtype=dt, device=dev) for _ in range(3)] for _ in range(2)]
+    main = torch.cuda.current_stream(dev)
+    up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
 
     def e2e_step(i):
-        for d_, h_ in zip(dev_in, host_sets[i % 2]):
-            d_.copy_(h_, non_blocking=True)
-        o = t5b.flash_attention_with_fusing_bias(dev_in[0], dev_in[1], dev_in[2], table, causal=False, sm_scale=1.0,
-                                                 NUM_BUCKETS=w["num_buckets"], MAX_DISTANCE=w["max_distance"])
-        host_out.copy_(o, non_blocking=True)
-    for i in range(3):
+        s_ = i % 2
+        with torch.cuda.stream(up):
+            up.wait_event(ev_done[s_])            # the kernel that last read this slot has finished
+            for d_, h_ in zip(dev_in[s_], host_sets[s_]):
+                d_.copy_(h_, non_blocking=True)
+            ev_in[s_].record(up)
+        main.wait_event(ev_in[s_])
+        o = t5b.flash_attention_with_fusing_bias(dev_in[s_][0], dev_in[s_][1], dev_in[s_][2], table, causal=False,
+                                                 sm_scale=1.0, NUM_BUCKETS=w["num_buckets"],
+                                                 MAX_DISTANCE=w["max_distance"])
+        ev_done[s_].record(main)
+        with torch.cuda.stream(down):
+            down.wait_event(ev_done[s_])
+            host_out[s_].copy_(o, non_blocking=True)
+            o.record_stream(down)
+            ev_out[s_].record(down)
+
+    def e2e_drain():
+        for e_ in ev_out:
+            main.wait_event(e_)
+    for i in range(4):
         e2e_step(i)
+    e2e_drain()
     barrier()
     e0.record()
     for i in range(e2e_steps):
         e2e_step(i)
+    e2e_drain()
     e1.record()
     barrier()
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)

@@ -114,3 +114,36 @@ def test_registry_and_module_signature():
     sig = inspect.signature(t5b.flash_attention_with_fusing_bias_varlen)
     assert list(sig.parameters)[:12] == ["q", "k", "v", "bias", "cu_seqlens_q", "cu_seqlens_k", "max_seqlen_q",
                                          "max_seqlen_k", "causal", "sm_scale", "NUM_BUCKETS", "MAX_DISTANCE"]
+
+
+def test_host_bucket_table_matches_oracle_on_random_settings():
+    # property test over (num_buckets, max_distance, direction): the library's host table (glibc
+    # logf, float32 chain) and the oracle (the reference's torch expression) agree bit for bit
+    from hypothesis import given, settings, strategies as st
+    import turbot5_b200 as t5b
+    from oracle import t5_oracle as orc
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.sampled_from([4, 6, 8, 12, 16, 24, 32, 40, 64, 96, 128, 256]), st.integers(2, 2048), st.booleans())
+    def check(nb, md, bidir):
+        n_side = nb // 2 if bidir else nb
+        if n_side < 2 or md <= n_side // 2:
+            with pytest.raises(RuntimeError):
+                t5b.relative_position_bucket_table(nb, md, bidir)
+            return
+        got = t5b.relative_position_bucket_table(nb, md, bidir, -md - 3, md + 3).numpy()
+        want = orc.bucket_of_delta(range(-md - 3, md + 4), bidir, nb, md)
+        assert np.array_equal(got, want), (nb, md, bidir)
+        # monotone in distance on each side and saturating at max_distance
+        neg = got[:md + 4][::-1]
+        assert np.all(np.diff(neg) >= 0) and neg[md] == neg[-1]
+    check()
+
+
+def test_attention_workspace_query_is_zero_without_a_device_or_when_not_applicable():
+    from turbot5_b200 import _native as nat
+    L = nat.lib()
+    a = nat.AttnArgs()
+    assert L.t5b_attention_workspace_bytes(None) == 0
+    a.dtype, a.D, a.B, a.H, a.M, a.N = nat.F32, 64, 1, 1, 4096, 4096
+    assert L.t5b_attention_workspace_bytes(a) == 0        # float32 never takes the tensor-core kernel
