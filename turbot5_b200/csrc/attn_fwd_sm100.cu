@@ -90,11 +90,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 // kBf16: element type of Q/K/V/out (P uses the same type: tcgen05.mma kind::f16
 // takes A and B of one format; mixing fp16 P with bf16 V is an illegal instruction).
-// Exponentials are taken against the row maximum seen up to the previous tile; O and
-// the row sum are rescaled only when the maximum grows by more than this many
-// powers of two.  P then stays below 2^threshold times the tile's own spread: far
-// inside bf16's range (an fp32 exponent) with 32, and inside fp16's 65504 with 12.
-template <bool kBf16> struct Rescale { static constexpr float kThreshold = kBf16 ? 32.f : 12.f; };
+// O and the row sum are rescaled only when a row maximum grows by more than this many powers
+// of two; P then stays <= 2^8, far inside the range of bf16 and fp16.
+constexpr float kRescaleThreshold = 8.f;
 
 template <bool kBf16>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
@@ -319,12 +317,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       const bool fast = !need_mask && bias_mode != 2 && scale > 0.f;
 
-      // Maximum of this thread's half row, four independent chains.  Fast tiles (no
-      // mask, constant bias): over the raw scores, transformed once.  Other tiles:
+      // ---- pass 1: maximum of this thread's half row, four independent chains.  Fast tiles
+      // (no mask, constant bias): over the raw scores, transformed once.  Other tiles:
       // x = s*scale + bias(delta) (+ mask) is computed in place first.
-      float mx = -INFINITY;
-      const bool track_in_pass = fast && j > 0;   // fast tiles after the first: maximum taken inside the exp pass
-      if (!track_in_pass) {
+      float mx;
+      {
         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
         if (fast) {
           #pragma unroll
@@ -357,90 +354,73 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           mx = max3(fmaxf(m0, m1), m2, m3);
         }
       }
-      // The first tile needs the true row maximum before any exponential.  Later tiles
-      // take their exponentials against the maximum seen so far and only check
-      // afterwards whether the row maximum grew past the rescale threshold (rare).
+      // combine with the other half of the row (both see the same values afterwards, hence
+      // take the same decisions)
+      ctl->xchg[j & 1][half][r] = mx;
+      if (!pair_sync()) { ok = false; fail_code = 33; break; }
+      const float m_new = fmaxf(m_use, fmaxf(mx, ctl->xchg[j & 1][half ^ 1][r]));
+
+      // lazy rescale: only when some row's maximum grew by more than the threshold (rare
+      // after the first tiles); needs the previous PV to be complete
+      const bool grow = (m_new - m_use) > kRescaleThreshold;   // false for -inf - -inf (NaN)
+      bool o_done_seen = (j == 0);
       if (j == 0) {
-        ctl->xchg[0][half][r] = mx;
-        if (!pair_sync()) { ok = false; fail_code = 33; break; }
-        m_use = fmaxf(mx, ctl->xchg[0][half ^ 1][r]);
-      } else {
-        // PV of the previous tile must be complete before P is overwritten / O rescaled
+        m_use = m_new;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
+        tc_fence_after();
+        o_done_seen = true;
+        float alpha = 1.f;
+        if (grow) { alpha = fast_exp2(m_use - m_new); m_use = m_new; }
+        l_sum *= alpha;
+        #pragma unroll 1
+        for (int c = 0; c < 2; ++c) {            // this thread's 32 columns of O
+          uint32_t ov[16];
+          tmem_ld_x16(tO + c * 16, ov);
+          tmem_ld_wait();
+          #pragma unroll
+          for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st_x16(tO + c * 16, ov);
+        }
+      }
+      const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
+      // fast tiles: p = 2^(s*scale + (bias - m)); others: p = 2^(x - m) = 2^(x*1 + (-m))
+      const float e_mul = fast ? scale : 1.f;
+      const float e_add = fast ? bias_const - m_safe : -m_safe;
+
+      // ---- pass 2: all exponentials of the tile into registers (packed P) and the row sum.
+      // The scores die as they are consumed.  Only then wait for the previous tile's PV (it
+      // still reads the P buffer): its latency hides behind the exponentials.
+      uint32_t pk[2][16];
+      float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
+      #pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        #pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float x0, x1;
+          fma2(x0, x1, __uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]), e_mul, e_add);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          pk[c][i] = pack2<kBf16>(p0, p1);
+          // bf16: normalise by the sum of the ROUNDED probabilities the tensor core will
+          // use, so a row dominated by one key stays an exact convex combination
+          if (kBf16) {
+            if (i & 1) add_bf16x2(t2, t3, pk[c][i]); else add_bf16x2(t0, t1, pk[c][i]);
+          } else {
+            if (i & 1) add2(t2, t3, p0, p1); else add2(t0, t1, p0, p1);
+          }
+        }
+      }
+      l_sum += (t0 + t1) + (t2 + t3);
+      if (!o_done_seen) {
         if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
         tc_fence_after();
       }
-
-      #pragma unroll 1
-      for (int attempt = 0; attempt < 2; ++attempt) {
-        const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
-        // fast tiles: p = 2^(s*scale + (bias - m)); others: p = 2^(x - m) = 2^(x*1 + (-m))
-        const float e_mul = fast ? scale : 1.f;
-        const float e_add = fast ? bias_const - m_safe : -m_safe;
-        float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;   // this tile's share of the row sum
-        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
-
-        // ---- exponentials, row sum, P -> tensor memory (32 columns at a time)
-        #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t pk[16];
-          #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float s0 = __uint_as_float(sv[c][2 * i]), s1 = __uint_as_float(sv[c][2 * i + 1]);
-            if (track_in_pass) {
-              if ((i & 3) == 0) m0 = max3(m0, s0, s1); else if ((i & 3) == 1) m1 = max3(m1, s0, s1);
-              else if ((i & 3) == 2) m2 = max3(m2, s0, s1); else m3 = max3(m3, s0, s1);
-            }
-            float x0, x1;
-            fma2(x0, x1, s0, s1, e_mul, e_add);
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-            pk[i] = pack2<kBf16>(p0, p1);
-            // bf16: normalise by the sum of the ROUNDED probabilities the tensor core will
-            // use, so a row dominated by one key stays an exact convex combination
-            if (kBf16) {
-              if (i & 1) add_bf16x2(t2, t3, pk[i]); else add_bf16x2(t0, t1, pk[i]);
-            } else {
-              if (i & 1) add2(t2, t3, p0, p1); else add2(t0, t1, p0, p1);
-            }
-          }
-          tmem_st_x16(tP + c * 16, pk);
-        }
-        const float l_tile = (t0 + t1) + (t2 + t3);
-        if (j == 0) { l_sum = l_tile; break; }
-
-        // did the row maximum grow past the threshold?  (both halves of a row see the
-        // same values here, hence decide alike; the decision is uniform per warp pair)
-        bool redo = false;
-        if (attempt == 0) {
-          if (track_in_pass) mx = fmaf(max3(fmaxf(m0, m1), m2, m3), scale, bias_const);
-          ctl->xchg[j & 1][half][r] = mx;
-          if (!pair_sync()) { ok = false; fail_code = 33; break; }
-          const float m_new = fmaxf(m_use, fmaxf(mx, ctl->xchg[j & 1][half ^ 1][r]));
-          const bool grow = (m_new - m_use) > Rescale<kBf16>::kThreshold;   // false for -inf - -inf (NaN)
-          redo = __any_sync(0xffffffffu, grow);
-          if (redo) {
-            float alpha = 1.f;
-            if (grow) { alpha = fast_exp2(m_use - m_new); m_use = m_new; }
-            l_sum *= alpha;
-            #pragma unroll 1
-            for (int c = 0; c < 2; ++c) {            // this thread's 32 columns of O
-              uint32_t ov[16];
-              tmem_ld_x16(tO + c * 16, ov);
-              tmem_ld_wait();
-              #pragma unroll
-              for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-              tmem_st_x16(tO + c * 16, ov);
-            }
-            tmem_st_wait();     // P of the first attempt must have landed before it is rewritten
-          }
-        }
-        if (!redo) { l_sum += l_tile; break; }
-      }
-      if (!ok) break;
+      tmem_st_x16(tP, pk[0]);
+      tmem_st_x16(tP + 16, pk[1]);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL));
     }
-
 
     // ---- epilogue: O / l -> global (each thread its 32 output columns)
     if (ok && n_kv > 0) {
