@@ -410,6 +410,40 @@ def secondary_measurements(t5b, dev):
         with torch.no_grad():
             ms = _time(lambda: enc(ids), 5, warm=2)
         out[f"t5_base_encoder_fwd_{Bt}x{Lt}"] = {"ms": ms, "tokens_per_s": Bt * Lt / (ms * 1e-3)}
+    del enc
+    # T5-large-shaped greedy decoding (24 decoder layers, d_model 1024, 16 x 64 heads, d_ff 4096 ReLU as in
+    # the original T5-large; random init, bf16): batch 64 against an encoder memory of 8192 states.  Every
+    # step streams the cross-attention K/V of all layers (51.5 GB) through the split-KV kernel.
+    try:
+        from turbot5_b200.t5 import T5ForConditionalGeneration
+        free, _ = torch.cuda.mem_get_info(dev)
+        if free > 90e9:
+            cfg5 = T5StackConfig(d_model=1024, d_kv=64, d_ff=4096, num_layers=0, num_decoder_layers=24, num_heads=16,
+                                 feed_forward_proj="relu")
+            model = T5ForConditionalGeneration(cfg5).to(dev).to(dt).eval()
+            enc_states = torch.randn((64, 8192, 1024), generator=g, device=dev, dtype=torch.float32).to(dt)
+            with torch.no_grad():
+                cache = model.decoder.new_cache(enc_states, 40)
+                cur = torch.zeros((64, 1), dtype=torch.long, device=dev)
+                for _ in range(4):                      # warm-up steps
+                    cur = model.logits(model.decoder.decode_step(cur, cache))[:, -1:].argmax(-1)
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                steps = 32
+                e0.record()
+                for _ in range(steps):
+                    cur = model.logits(model.decoder.decode_step(cur, cache))[:, -1:].argmax(-1)
+                e1.record()
+                torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            kv_bytes = 24 * 2 * 64 * 16 * 8192 * 64 * 2
+            out["t5_large_decode_B64_enc8192"] = {"ms_per_step": ms, "tokens_per_s": 64 / (ms * 1e-3),
+                                                  "cross_kv_GB_per_step": kv_bytes / 1e9,
+                                                  "GB/s_cross_kv_only": kv_bytes / (ms * 1e-3) / 1e9,
+                                                  "frac_of_hbm_peak": kv_bytes / (ms * 1e-3) / 1e9 / peaks["hbm"]}
+            del model, cache, enc_states
+    except torch.cuda.OutOfMemoryError:
+        out["t5_large_decode_B64_enc8192"] = {"skipped": "not enough free device memory"}
     return out
 
 
