@@ -76,3 +76,15 @@ def test_state_dict_names_follow_hf_layout():
     z = load("stack.npz")
     model = T5ForConditionalGeneration(T5StackConfig(**TINY_T5))
     assert sorted(n for n, _ in model.named_parameters()) == [str(x) for x in z["param_names"]]
+
+
+def test_cuda_graph_decoding_equals_eager_decoding():
+    model = _model(torch.bfloat16, d_model=128, num_heads=4, d_ff=256)
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 128, (3, 300), generator=g).cuda()
+    with torch.no_grad():
+        enc = model.encoder(ids)
+        eager_tokens, eager_last = model.greedy_decode(enc, 7)
+        graph_tokens, graph_last = model.greedy_decode(enc, 7, use_cuda_graph=True)
+    assert torch.equal(eager_tokens, graph_tokens)
+    assert (eager_last.float() - graph_last.float()).abs().max().item() < 1e-2

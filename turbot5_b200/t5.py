@@ -161,6 +161,41 @@ class T5Stack(nn.Module):
             cache.cross_v[i] = shape(att.v(encoder_hidden_states))
         return cache
 
+    def decode_step_static(self, input_ids, cache: DecoderCache, pos, seqlens, encoder_seqlens=None):
+        """One cached single-token step whose position lives on the device.
+
+        `pos` (int64, shape (1,)) is the slot of the new token in the cache and `seqlens` (int32,
+        shape (B,)) the number of cached keys including it; nothing in the launch sequence
+        depends on their values, so the step can be captured once in a CUDA graph and replayed
+        (the caller advances both tensors between replays).  Returns (B, 1, d_model).
+        """
+        cfg = self.cfg
+        B = input_ids.shape[0]
+        H, D = cfg.num_heads, cfg.d_kv
+        hidden = self.embed_tokens(input_ids)
+        table = self._table()
+        shape = lambda x: x.view(B, 1, H, D).transpose(1, 2)
+        for i, blk in enumerate(self.block):
+            sa, ca = blk.layer[0], blk.layer[1]
+            att = sa.SelfAttention
+            normed = sa.layer_norm(hidden).to(hidden.dtype)
+            q = shape(att.q(normed))
+            cache.self_k[i].index_copy_(2, pos, shape(att.k(normed)))
+            cache.self_v[i].index_copy_(2, pos, shape(att.v(normed)))
+            o = flash_decoding_with_fusing_bias(q, cache.self_k[i], cache.self_v[i], table, causal=True, sm_scale=1.0,
+                                                NUM_BUCKETS=cfg.relative_attention_num_buckets,
+                                                MAX_DISTANCE=cfg.relative_attention_max_distance, seqlens_k=seqlens,
+                                                num_splits=1)
+            hidden = hidden + att.o(o.transpose(1, 2).reshape(B, 1, H * D))
+            catt = ca.EncDecAttention
+            normed = ca.layer_norm(hidden).to(hidden.dtype)
+            q = shape(catt.q(normed))
+            o = flash_decoding_with_fusing_bias(q, cache.cross_k[i], cache.cross_v[i], None, causal=False,
+                                                sm_scale=1.0, seqlens_k=encoder_seqlens, q_pos_offset=0)
+            hidden = hidden + catt.o(o.transpose(1, 2).reshape(B, 1, H * D))
+            hidden = blk.layer[-1](hidden)
+        return self.final_layer_norm(hidden).to(hidden.dtype)
+
     def decode_step(self, input_ids, cache: DecoderCache, encoder_seqlens=None):
         """One cached step for `input_ids` (B, M) (M new tokens, usually 1); returns (B, M, d_model)."""
         cfg = self.cfg
@@ -204,6 +239,64 @@ class T5Stack(nn.Module):
         return self.final_layer_norm(hidden).to(hidden.dtype)
 
 
+class GraphedDecoding:
+    """Greedy generation whose single-token step is one CUDA graph.
+
+    The step (all decoder layers, LM head, argmax, token write-back, position update) is run
+    once eagerly on a side stream (so scratch buffers and library workspaces exist), rewound,
+    captured, and rewound again; `step()` then replays it.  The token position and the cached
+    length live in device tensors that the graph itself advances, so no launch argument
+    changes between replays.
+    """
+
+    def __init__(self, model, encoder_hidden_states, max_len, encoder_seqlens=None):
+        B = encoder_hidden_states.shape[0]
+        dev = encoder_hidden_states.device
+        self.model = model
+        self.max_len = max_len
+        self.cache = model.decoder.new_cache(encoder_hidden_states, max_len)
+        self.cur = torch.empty((B, 1), dtype=torch.long, device=dev)
+        self.pos = torch.empty(1, dtype=torch.long, device=dev)
+        self.seqlens = torch.empty(B, dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros((B, max_len), dtype=torch.long, device=dev)
+        self.encoder_seqlens = encoder_seqlens
+        self.steps_done = 0
+        self.rewind()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side), torch.no_grad():
+            self._step()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.rewind()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.last_logits = self._step()
+        self.rewind()
+
+    def rewind(self):
+        self.cur.fill_(self.model.cfg.decoder_start_token_id)
+        self.pos.zero_()
+        self.seqlens.fill_(1)
+        self.steps_done = 0
+
+    def _step(self):
+        m = self.model
+        logits = m.logits(m.decoder.decode_step_static(self.cur, self.cache, self.pos, self.seqlens,
+                                                       self.encoder_seqlens))
+        nxt = logits[:, -1:].argmax(-1)
+        self.tokens.index_copy_(1, self.pos, nxt)
+        self.cur.copy_(nxt)
+        self.pos.add_(1)
+        self.seqlens.add_(1)
+        return logits
+
+    def step(self):
+        if self.steps_done >= self.max_len:
+            raise RuntimeError("the cache is full: %d steps" % self.max_len)
+        self.graph.replay()
+        self.steps_done += 1
+
+
 class T5ForConditionalGeneration(nn.Module):
     def __init__(self, cfg: T5StackConfig):
         super().__init__()
@@ -224,14 +317,26 @@ class T5ForConditionalGeneration(nn.Module):
         return self.logits(dec)
 
     @torch.no_grad()
-    def greedy_decode(self, encoder_hidden_states, steps, encoder_seqlens=None):
-        """Greedy generation from `decoder_start_token_id` with the preallocated cache."""
+    def greedy_decode(self, encoder_hidden_states, steps, encoder_seqlens=None, use_cuda_graph=False):
+        """Greedy generation from `decoder_start_token_id` with the preallocated cache.
+
+        With `use_cuda_graph` the whole single-token step (all layers, LM head, argmax, position
+        update) is captured once after a warm-up step and replayed: one graph launch per token
+        instead of a few hundred kernel launches issued from Python.
+        """
         B = encoder_hidden_states.shape[0]
+        dev = encoder_hidden_states.device
         cache = self.decoder.new_cache(encoder_hidden_states, steps)
-        cur = torch.full((B, 1), self.cfg.decoder_start_token_id, dtype=torch.long, device=encoder_hidden_states.device)
-        tokens, last_logits = [], None
+        cur = torch.full((B, 1), self.cfg.decoder_start_token_id, dtype=torch.long, device=dev)
+        if not use_cuda_graph:
+            tokens, last_logits = [], None
+            for _ in range(steps):
+                last_logits = self.logits(self.decoder.decode_step(cur, cache, encoder_seqlens))
+                cur = last_logits[:, -1:].argmax(-1)
+                tokens.append(cur)
+            return torch.cat(tokens, dim=1), last_logits
+
+        session = GraphedDecoding(self, encoder_hidden_states, steps, encoder_seqlens)
         for _ in range(steps):
-            last_logits = self.logits(self.decoder.decode_step(cur, cache, encoder_seqlens))
-            cur = last_logits[:, -1:].argmax(-1)
-            tokens.append(cur)
-        return torch.cat(tokens, dim=1), last_logits
+            session.step()
+        return session.tokens, session.last_logits
