@@ -339,3 +339,49 @@ def test_last_wave_split_matches_unsplit_and_oracle(B, H, M, N):
     check_close(split, want, dt, "split")
     check_close(plain, want, dt, "unsplit")
     assert (lse_s - lse_p).abs().max().item() < 1e-2      # each carries the bf16 rounding of its row sums
+
+
+# ---- head dim 128 on the tensor-core kernel (64-key tiles, two 64-dim sub-tiles per row)
+CASES_D128 = [
+    (2, 3, 1024, 1024, False, None),
+    (1, 2, 777, 777, True, None),
+    (2, 2, 128, 1024, False, 0),
+    (1, 2, 200, 555, True, None),
+    (1, 2, 300, 300, False, 4000),
+    (1, 1, 1, 300, True, None),
+    (1, 2, 640, 130, True, None),
+    (1, 3, 300, 4096, False, 0),        # few query tiles: keys split over several blocks and merged
+]
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,M,N,causal,off", CASES_D128)
+def test_head_dim_128_tensor_core_vs_oracle(B, H, M, N, causal, off, dt):
+    q = seeded((B, H, M, 128), 1, dtype=dt)
+    k = seeded((B, H, N, 128), 2, dtype=dt)
+    v = seeded((B, H, N, 128), 3, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    want = orc.attention_basic(q, k, v, table, causal=causal, q_pos_offset=off, sm_scale=0.5)
+    out = _run_dense(q, k, v, table, dt, "tcgen05", causal=causal, q_pos_offset=off, sm_scale=0.5)
+    check_close(out, want, dt, f"d128 {(B, H, M, N, causal, off)}")
+
+
+def test_head_dim_128_golden_and_varlen():
+    t5b = _ops()
+    c = attention_case(load("attention.npz"), "enc_d128")
+    out = _run_dense(c["q"], c["k"], c["v"], c["table"], torch.bfloat16, "tcgen05", nb=c["nb"], md=c["md"])
+    check_close(out, c["out"], torch.bfloat16, "enc_d128")
+    dt = torch.bfloat16
+    lens = [5, 128, 0, 129, 300, 1, 257, 64]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    T, H = int(cu[-1]), 3
+    q, k, v = seeded((T, H, 128), 1, 0.5, dtype=dt), seeded((T, H, 128), 2, 0.5, dtype=dt), seeded((T, H, 128), 3, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    for causal in (False, True):
+        want = orc.attention_basic_varlen(q, k, v, table, cu, cu, causal=causal)
+        got = t5b.flash_attention_with_fusing_bias_varlen(
+            q.cuda(), k.cuda(), v.cuda(), table.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens),
+            causal=causal, sm_scale=1.0, kernel="tcgen05")
+        torch.cuda.synchronize()
+        t5b.check_device_status()
+        check_close(got, want, dt, f"varlen d128 causal={causal}")

@@ -36,16 +36,33 @@ namespace t5b {
 namespace sm100 {
 
 constexpr int BM = 128;            // query rows per block
-constexpr int BN = 128;            // keys per tile
-constexpr int HD = 64;             // head dim
 constexpr int STAGES = 2;          // K/V ring depth
-constexpr int TILE_BYTES = BM * HD * 2;      // 16 KB, one 128B-swizzled [128][64] 16-bit tile
 constexpr int NUM_THREADS = 320;
 constexpr int SOFTMAX_THREADS = 256;
 constexpr int WARP_TMA = 8, WARP_MMA = 9;
-constexpr int TMEM_COLS = 256;     // S: 128 fp32 columns, P: 64 (packed 16-bit pairs), O: 64
-constexpr int COL_S = 0, COL_P = 128, COL_O = 192;
-constexpr int LUT_PAD = BM + BN;             // bias table padding on each side (entries)
+constexpr int TMEM_COLS = 256;
+
+// Tile geometry per head dim.  Head dim 64: 128 keys per tile.  Head dim 128: 64 keys per tile,
+// so that two blocks still fit on an SM (96 KB of tiles, 224 TMEM columns each).  A tile row of
+// 128 dims is two 128-byte-swizzled sub-tiles of 64 dims, loaded by two TMA boxes.
+template <int HD_>
+struct Geo {
+  static constexpr int HD = HD_;
+  static constexpr int BN = HD_ == 64 ? 128 : 64;     // keys per tile
+  static constexpr int NSUB = HD_ / 64;                 // 64-dim sub-tiles per row
+  static constexpr int SUB_Q = BM * 128;                // bytes of one Q sub-tile  [128 rows][64 dims]
+  static constexpr int SUB_KV = BN * 128;               // bytes of one K/V sub-tile [BN rows][64 dims]
+  static constexpr int Q_BYTES = NSUB * SUB_Q;
+  static constexpr int KV_BYTES = NSUB * SUB_KV;
+  static constexpr int SMEM_TILES = Q_BYTES + 2 * STAGES * KV_BYTES;
+  // tensor memory: S = BN fp32 columns, P = BN/2 (packed 16-bit pairs), O = HD fp32 columns
+  static constexpr int COL_S = 0, COL_P = BN, COL_O = BN + BN / 2;
+  static constexpr int NH = BN / 2;                     // score columns per softmax thread
+  static constexpr int NCH = NH / 32;                   // ... in chunks of 32
+  static constexpr int OH = HD_ / 2;                    // output columns per softmax thread
+  static constexpr int LUT_PAD = BM + BN;               // bias table padding on each side (entries)
+  static_assert(COL_O + HD_ <= TMEM_COLS, "tensor memory layout");
+};
 
 // barrier slots
 enum {
@@ -70,10 +87,9 @@ struct __align__(8) Control {
   float xchg[2][2][BM];   // [tile parity][column half][row]: row maxima; at the end: row sums
 };
 
-constexpr int SMEM_TILES = (1 + 2 * STAGES) * TILE_BYTES;
-
+template <int HD>
 __host__ __device__ inline size_t smem_bytes(int lut_entries) {
-  return 1024 /*alignment slack*/ + SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 4;
+  return 1024 /*alignment slack*/ + Geo<HD>::SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 4;
 }
 
 
@@ -94,20 +110,25 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // of two; P then stays <= 2^8, far inside the range of bf16 and fp16.
 constexpr float kRescaleThreshold = 8.f;
 
-template <bool kBf16>
+template <bool kBf16, int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v,
                 const __grid_constant__ AttnParams p,
                 const __grid_constant__ BucketSpec spec) {
+  using G = Geo<HD>;
+  constexpr int BN = G::BN, NSUB = G::NSUB, SUB_Q = G::SUB_Q, SUB_KV = G::SUB_KV;
+  constexpr int Q_BYTES = G::Q_BYTES, KV_BYTES = G::KV_BYTES, SMEM_TILES = G::SMEM_TILES;
+  constexpr int COL_S = G::COL_S, COL_P = G::COL_P, COL_O = G::COL_O;
+  constexpr int NH = G::NH, NCH = G::NCH, OH = G::OH, LUT_PAD = G::LUT_PAD;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
   const uint32_t sQ = base;
-  const uint32_t sK = base + TILE_BYTES;
-  const uint32_t sV = sK + STAGES * TILE_BYTES;
+  const uint32_t sK = base + Q_BYTES;
+  const uint32_t sV = sK + STAGES * KV_BYTES;
   Control* ctl = reinterpret_cast<Control*>(smem + SMEM_TILES);
   float* lut = reinterpret_cast<float*>(smem + SMEM_TILES + ((sizeof(Control) + 15) / 16) * 16);
 
@@ -208,17 +229,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   if (warp == WARP_TMA) {
     // ============================================================ TMA producer
     if (lane == 0 && n_kv > 0) {
-      mbar_expect_tx(bar(BAR_Q_FULL), TILE_BYTES);
-      tma_load_4d(sQ, &tmap_q, bar(BAR_Q_FULL), 0, q_row0, h, b);
+      mbar_expect_tx(bar(BAR_Q_FULL), Q_BYTES);
+      #pragma unroll
+      for (int u = 0; u < NSUB; ++u) tma_load_4d(sQ + u * SUB_Q, &tmap_q, bar(BAR_Q_FULL), 64 * u, q_row0, h, b);
       for (int j = 0; j < n_kv; ++j) {
         const int s = j % STAGES;
         const uint32_t ph = (uint32_t)((j / STAGES) & 1);
         if (j >= STAGES && !mbar_wait_bounded(bar(BAR_K_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
-        mbar_expect_tx(bar(BAR_K_FULL + s), TILE_BYTES);
-        tma_load_4d(sK + s * TILE_BYTES, &tmap_k, bar(BAR_K_FULL + s), 0, k_row0 + (kv_first + j) * BN, h, b);
+        mbar_expect_tx(bar(BAR_K_FULL + s), KV_BYTES);
+        #pragma unroll
+        for (int u = 0; u < NSUB; ++u)
+          tma_load_4d(sK + s * KV_BYTES + u * SUB_KV, &tmap_k, bar(BAR_K_FULL + s), 64 * u, k_row0 + (kv_first + j) * BN, h, b);
         if (j >= STAGES && !mbar_wait_bounded(bar(BAR_V_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
-        mbar_expect_tx(bar(BAR_V_FULL + s), TILE_BYTES);
-        tma_load_4d(sV + s * TILE_BYTES, &tmap_v, bar(BAR_V_FULL + s), 0, k_row0 + (kv_first + j) * BN, h, b);
+        mbar_expect_tx(bar(BAR_V_FULL + s), KV_BYTES);
+        #pragma unroll
+        for (int u = 0; u < NSUB; ++u)
+          tma_load_4d(sV + s * KV_BYTES + u * SUB_KV, &tmap_v, bar(BAR_V_FULL + s), 64 * u, k_row0 + (kv_first + j) * BN, h, b);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -230,11 +256,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const int s = j % STAGES;
         if (!mbar_wait_bounded(bar(BAR_K_FULL + s), (uint32_t)((j / STAGES) & 1), abort_flag)) return false;
         tc_fence_after();
-        const uint64_t da = make_smem_desc_sw128(sQ, 16, 1024);
-        const uint64_t db = make_smem_desc_sw128(sK + s * TILE_BYTES, 16, 1024);
         #pragma unroll
-        for (int k = 0; k < HD / 16; ++k)   // 32 bytes of the 128-byte swizzle row per step
-          umma_ss(tmem + COL_S, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC_QK, k > 0);
+        for (int u = 0; u < NSUB; ++u) {
+          const uint64_t da = make_smem_desc_sw128(sQ + u * SUB_Q, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sK + s * KV_BYTES + u * SUB_KV, 16, 1024);
+          #pragma unroll
+          for (int k = 0; k < 4; ++k)   // 32 bytes of the 128-byte swizzle row per step
+            umma_ss(tmem + COL_S, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC_QK, (u | k) > 0);
+        }
         tc_commit(bar(BAR_S_FULL));
         tc_commit(bar(BAR_K_EMPTY + s));
         return true;
@@ -254,11 +283,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const int s = j % STAGES;
         if (!mbar_wait_bounded(bar(BAR_V_FULL + s), (uint32_t)((j / STAGES) & 1), abort_flag)) { fail_code = 24; break; }
         tc_fence_after();
-        // V tile is [128 keys][64 dims], dims contiguous: an MN-major B operand.
-        // 8 keys x 128 B per swizzle group (1024 B); each K=16 step covers two groups.
+        // V tile is [BN keys][HD dims], dims contiguous: an MN-major B operand.  8 keys x 128 B
+        // per swizzle group (1024 B, the stride byte offset); each K=16 step covers two groups;
+        // dims 64-127 live in the second sub-tile, SUB_KV bytes on (the leading byte offset).
         #pragma unroll
         for (int k = 0; k < BN / 16; ++k) {
-          const uint64_t dv = make_smem_desc_sw128(sV + s * TILE_BYTES + k * 2048, 16, 1024);
+          const uint64_t dv = make_smem_desc_sw128(sV + s * KV_BYTES + k * 2048, NSUB > 1 ? SUB_KV : 16, 1024);
           umma_ts(tmem + COL_O, tmem + COL_P + k * 8, dv, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar(BAR_O_DONE));
@@ -271,9 +301,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const int half = warp >> 2;                    // which 64 key columns / 32 output columns
     const int r = quarter * 32 + lane;             // query row inside the tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tS = tmem + lane_base + COL_S + half * 64;
-    const uint32_t tP = tmem + lane_base + COL_P + half * 32;
-    const uint32_t tO = tmem + lane_base + COL_O + half * 32;
+    const uint32_t tS = tmem + lane_base + COL_S + half * NH;
+    const uint32_t tP = tmem + lane_base + COL_P + half * (NH / 2);
+    const uint32_t tO = tmem + lane_base + COL_O + half * OH;
     const float scale = p.scale_log2;
     const bool has_bias = p.table != nullptr;
     const int qpos = qpos0 + r;
@@ -293,14 +323,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     for (int j = 0; j < n_kv; ++j) {
       const int n0 = (kv_first + j) * BN;          // first key of the tile
-      const int c0 = half * 64;                    // first column of this thread inside the tile
+      const int c0 = half * NH;                    // first column of this thread inside the tile
       if (!mbar_wait_bounded(bar(BAR_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
 
-      // this thread's 64 scores -> registers, then give the S buffer back to the MMA warp
-      uint32_t sv[2][32];
-      tmem_ld_x32(tS, sv[0]);
-      tmem_ld_x32(tS + 32, sv[1]);
+      // this thread's scores -> registers, then give the S buffer back to the MMA warp
+      uint32_t sv[NCH][32];
+      #pragma unroll
+      for (int c = 0; c < NCH; ++c) tmem_ld_x32(tS + 32 * c, sv[c]);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(bar(BAR_S_FREE));
@@ -325,7 +355,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
         if (fast) {
           #pragma unroll
-          for (int c = 0; c < 2; ++c)
+          for (int c = 0; c < NCH; ++c)
             #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               m0 = max3(m0, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
@@ -339,7 +369,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           const float* brow = lut + (n0 + c0 - qpos + md + LUT_PAD);
           const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;   // columns < n_valid are visible
           #pragma unroll
-          for (int c = 0; c < 2; ++c) {
+          for (int c = 0; c < NCH; ++c) {
             #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float bias = bias_mode == 2 ? brow[c * 32 + i] : bias_const;
@@ -374,7 +404,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (grow) { alpha = fast_exp2(m_use - m_new); m_use = m_new; }
         l_sum *= alpha;
         #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {            // this thread's 32 columns of O
+        for (int c = 0; c < OH / 16; ++c) {      // this thread's columns of O
           uint32_t ov[16];
           tmem_ld_x16(tO + c * 16, ov);
           tmem_ld_wait();
@@ -391,10 +421,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // ---- pass 2: all exponentials of the tile into registers (packed P) and the row sum.
       // The scores die as they are consumed.  Only then wait for the previous tile's PV (it
       // still reads the P buffer): its latency hides behind the exponentials.
-      uint32_t pk[2][16];
+      uint32_t pk[NCH][16];
       float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
       #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < NCH; ++c) {
         #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float x0, x1;
@@ -415,8 +445,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
         tc_fence_after();
       }
-      tmem_st_x16(tP, pk[0]);
-      tmem_st_x16(tP + 16, pk[1]);
+      #pragma unroll
+      for (int c = 0; c < NCH; ++c) tmem_st_x16(tP + 16 * c, pk[c]);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL));
@@ -435,29 +465,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (ok) {
       const bool row_ok = r < rows_in_tile;
       const int64_t row = (int64_t)q_row0 + r;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + half * 64 +
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + half * OH * 2 +
                       2 * ((int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + row * p.o_stride_m);
-      float o[32];
-      {
+      float o[OH];
+      #pragma unroll
+      for (int c = 0; c < OH / 32; ++c) {
         uint32_t v[32];
         if (n_kv > 0) {
-          tmem_ld_x32(tO, v);
+          tmem_ld_x32(tO + 32 * c, v);
           tmem_ld_wait();
         } else {
           #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0u;
         }
         #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) o[32 * c + i] = __uint_as_float(v[i]);
       }
       bool write_out = row_ok;
       if (parts > 1 && row_ok) {
         // This block saw only part of the keys.  Publish (max, sum, unnormalised O) for this
         // row half; the last of the `parts` blocks to arrive merges them (no waiting).
         const int64_t slot = (int64_t)tail_slot * parts + part;
-        float* my_o = p.ws_o + (slot * BM + r) * HD + half * 32;
+        float* my_o = p.ws_o + (slot * BM + r) * HD + half * OH;
         #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < OH / 4; ++i)
           reinterpret_cast<float4*>(my_o)[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
         float* my_ml = p.ws_ml + ((slot * BM + r) * 2 + half) * 2;
         my_ml[0] = m_use;
@@ -474,15 +505,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           const float m_ref = (m_all == -INFINITY) ? 0.f : m_all;
           float l_all = 0.f;
           #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0.f;
+          for (int i = 0; i < OH; ++i) o[i] = 0.f;
           for (int s2 = 0; s2 < parts; ++s2) {
             const int64_t sl = (int64_t)tail_slot * parts + s2;
             const float* ml = p.ws_ml + ((sl * BM + r) * 2 + half) * 2;
             const float sc = fast_exp2(__ldcg(ml) - m_ref);
             l_all = fmaf(__ldcg(ml + 1), sc, l_all);
-            const float4* po = reinterpret_cast<const float4*>(p.ws_o + (sl * BM + r) * HD + half * 32);
+            const float4* po = reinterpret_cast<const float4*>(p.ws_o + (sl * BM + r) * HD + half * OH);
             #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < OH / 4; ++i) {
               const float4 t4 = __ldcg(po + i);
               o[4 * i] = fmaf(t4.x, sc, o[4 * i]);         o[4 * i + 1] = fmaf(t4.y, sc, o[4 * i + 1]);
               o[4 * i + 2] = fmaf(t4.z, sc, o[4 * i + 2]); o[4 * i + 3] = fmaf(t4.w, sc, o[4 * i + 3]);
@@ -496,7 +527,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (write_out) {
         const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
         #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < OH / 8; ++i) {
           uint4 w4;
           w4.x = pack2<kBf16>(o[8 * i + 0] * inv_l, o[8 * i + 1] * inv_l);
           w4.y = pack2<kBf16>(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
@@ -540,8 +571,8 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// (D, rows, H, B) view with element strides; box = one [128 rows][64] tile.
-static int make_tmap(CUtensorMap* map, const void* ptr, bool bf16, int64_t rows, int H, int B,
+// (D, rows, H, B) view with element strides; box = one [box_rows][64 dims] sub-tile.
+static int make_tmap(CUtensorMap* map, const void* ptr, bool bf16, int HD, int box_rows, int64_t rows, int H, int B,
                      int64_t stride_row, int64_t stride_h, int64_t stride_b) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return T5B_ERR_DRIVER;
@@ -551,7 +582,7 @@ static int make_tmap(CUtensorMap* map, const void* ptr, bool bf16, int64_t rows,
   // unit dims may carry any stride in the caller's tensor; give them a legal one
   if (H == 1) strides[1] = (cuuint64_t)HD * 2;
   if (rows == 1) strides[0] = (cuuint64_t)HD * 2;
-  cuuint32_t box[4] = {(cuuint32_t)HD, (cuuint32_t)BM, 1, 1};
+  cuuint32_t box[4] = {64u, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -565,7 +596,7 @@ static int make_tmap(CUtensorMap* map, const void* ptr, bool bf16, int64_t rows,
 // True when the tcgen05 kernel can take this problem.
 bool sm100_supports(const t5b_attn_args& a) {
   if (a.dtype != T5B_BF16 && a.dtype != T5B_F16) return false;
-  if (a.D != sm100::HD) return false;
+  if (a.D != 64 && a.D != 128) return false;
   if (a.max_distance > 2048 && a.table) return false;
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   if (!al16(a.q) || !al16(a.k) || !al16(a.v) || !al16(a.out)) return false;
@@ -580,6 +611,7 @@ bool sm100_supports(const t5b_attn_args& a) {
 // the keys so that the wave finishes in a fraction of a block time.
 TailPlan sm100_tail_plan(const t5b_attn_args& a) {
   using namespace sm100;
+  const int HD = a.D, BN = a.D == 64 ? Geo<64>::BN : Geo<128>::BN;
   TailPlan t;
   t.tiles_x = (a.M + BM - 1) / BM;
   const long long n_total = (long long)t.tiles_x * a.H * a.B;
@@ -619,20 +651,23 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
   using namespace sm100;
   const bool varlen = a.cu_seqlens_q != nullptr;
   const bool bf16 = a.dtype == T5B_BF16;
+  const int HD = a.D;
+  const int BN = HD == 64 ? Geo<64>::BN : Geo<128>::BN;
+  const int LUT_PAD = BM + BN;
   CUtensorMap mq, mk, mv;
   int st;
   if (varlen) {
-    if ((st = make_tmap(&mq, a.q, bf16, a.total_q, a.H, 1, a.q_stride_m, a.q_stride_h, 0)) != T5B_OK) return st;
-    if ((st = make_tmap(&mk, a.k, bf16, a.total_k, a.H, 1, a.k_stride_n, a.k_stride_h, 0)) != T5B_OK) return st;
-    if ((st = make_tmap(&mv, a.v, bf16, a.total_k, a.H, 1, a.v_stride_n, a.v_stride_h, 0)) != T5B_OK) return st;
+    if ((st = make_tmap(&mq, a.q, bf16, HD, BM, a.total_q, a.H, 1, a.q_stride_m, a.q_stride_h, 0)) != T5B_OK) return st;
+    if ((st = make_tmap(&mk, a.k, bf16, HD, BN, a.total_k, a.H, 1, a.k_stride_n, a.k_stride_h, 0)) != T5B_OK) return st;
+    if ((st = make_tmap(&mv, a.v, bf16, HD, BN, a.total_k, a.H, 1, a.v_stride_n, a.v_stride_h, 0)) != T5B_OK) return st;
   } else {
-    if ((st = make_tmap(&mq, a.q, bf16, a.M, a.H, a.B, a.q_stride_m, a.q_stride_h, a.q_stride_b)) != T5B_OK) return st;
-    if ((st = make_tmap(&mk, a.k, bf16, a.N, a.H, a.B, a.k_stride_n, a.k_stride_h, a.k_stride_b)) != T5B_OK) return st;
-    if ((st = make_tmap(&mv, a.v, bf16, a.N, a.H, a.B, a.v_stride_n, a.v_stride_h, a.v_stride_b)) != T5B_OK) return st;
+    if ((st = make_tmap(&mq, a.q, bf16, HD, BM, a.M, a.H, a.B, a.q_stride_m, a.q_stride_h, a.q_stride_b)) != T5B_OK) return st;
+    if ((st = make_tmap(&mk, a.k, bf16, HD, BN, a.N, a.H, a.B, a.k_stride_n, a.k_stride_h, a.k_stride_b)) != T5B_OK) return st;
+    if ((st = make_tmap(&mv, a.v, bf16, HD, BN, a.N, a.H, a.B, a.v_stride_n, a.v_stride_h, a.v_stride_b)) != T5B_OK) return st;
   }
   AttnParams p = make_attn_params(a);
   const int lut_n = a.table ? 2 * spec.max_distance + 1 + 2 * LUT_PAD : 0;
-  const size_t smem = smem_bytes(lut_n);
+  const size_t smem = HD == 64 ? smem_bytes<64>(lut_n) : smem_bytes<128>(lut_n);
   dim3 grid;
   if (varlen) {
     // upper bound on sum_b ceil(len_b / BM) known without reading cu_seqlens
@@ -657,14 +692,16 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
     grid = dim3((unsigned)blocks, 1, 1);
   }
   if (grid.y > 65535 || grid.z > 65535) return T5B_ERR_SHAPE;
-  auto kern = bf16 ? attn_fwd_kernel<true> : attn_fwd_kernel<false>;
+  auto kern = HD == 64 ? (bf16 ? attn_fwd_kernel<true, 64> : attn_fwd_kernel<false, 64>)
+                       : (bf16 ? attn_fwd_kernel<true, 128> : attn_fwd_kernel<false, 128>);
   // opt in to > 48 KB of dynamic shared memory once per device and kernel
-  static bool attr_set[64][2] = {};
+  static bool attr_set[64][4] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  const int which = bf16 ? 1 : 0;
+  const int which = (bf16 ? 1 : 0) + (HD == 64 ? 0 : 2);
+  const size_t smem_max = HD == 64 ? smem_bytes<64>(2 * 2048 + 1 + 2 * LUT_PAD) : smem_bytes<128>(2 * 2048 + 1 + 2 * LUT_PAD);
   if (dev < 0 || dev >= 64 || !attr_set[dev][which]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(2 * 2048 + 1 + 2 * LUT_PAD)) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max) != cudaSuccess) {
       cudaGetLastError();
       return T5B_ERR_LAUNCH;
     }
