@@ -107,8 +107,10 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 // kBf16: element type of Q/K/V/out (P uses the same type: tcgen05.mma kind::f16
 // takes A and B of one format; mixing fp16 P with bf16 V is an illegal instruction).
 // O and the row sum are rescaled only when a row maximum grows by more than this many powers
-// of two; P then stays <= 2^8, far inside the range of bf16 and fp16.
-constexpr float kRescaleThreshold = 8.f;
+// of two over the value the exponentials are taken against.  Until then P may exceed 1: bf16
+// has the exponent range of fp32, so P <= 2^40 (and O, l <= 2^40 x keys x |v|) is harmless and
+// rounding stays relative; fp16 P must stay below 65504, hence 2^10.
+template <bool kBf16> constexpr float kRescaleThreshold = kBf16 ? 40.f : 10.f;
 
 template <bool kBf16, int HD>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
@@ -350,7 +352,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // ---- pass 1: maximum of this thread's half row, four independent chains.  Fast tiles
       // (no mask, constant bias): over the raw scores, transformed once.  Other tiles:
       // x = s*scale + bias(delta) (+ mask) is computed in place first.
-      float mx;
+      float mx, top_raw;     // top_raw: the largest value pass 2 will exponentiate (before e_mul, e_add)
       {
         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
         if (fast) {
@@ -363,7 +365,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
               m2 = max3(m2, __uint_as_float(sv[c][i + 4]), __uint_as_float(sv[c][i + 5]));
               m3 = max3(m3, __uint_as_float(sv[c][i + 6]), __uint_as_float(sv[c][i + 7]));
             }
-          mx = fmaf(max3(fmaxf(m0, m1), m2, m3), scale, bias_const);
+          top_raw = max3(fmaxf(m0, m1), m2, m3);
+          mx = fmaf(top_raw, scale, bias_const);
         } else {
           // per-row window into the padded table: column c of this tile reads brow[c]
           const float* brow = lut + (n0 + c0 - qpos + md + LUT_PAD);
@@ -382,6 +385,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
             asm volatile("" ::: "memory");   // keep the table reads of one chunk from piling up in registers
           }
           mx = max3(fmaxf(m0, m1), m2, m3);
+          top_raw = mx;
         }
       }
       // combine with the other half of the row (both see the same values afterwards, hence
@@ -392,7 +396,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
       // lazy rescale: only when some row's maximum grew by more than the threshold (rare
       // after the first tiles); needs the previous PV to be complete
-      const bool grow = (m_new - m_use) > kRescaleThreshold;   // false for -inf - -inf (NaN)
+      const bool grow = (m_new - m_use) > kRescaleThreshold<kBf16>;   // false for -inf - -inf (NaN)
       bool o_done_seen = (j == 0);
       if (j == 0) {
         m_use = m_new;
@@ -431,16 +435,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           fma2(x0, x1, __uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]), e_mul, e_add);
           const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
           pk[c][i] = pack2<kBf16>(p0, p1);
-          // bf16: normalise by the sum of the ROUNDED probabilities the tensor core will
-          // use, so a row dominated by one key stays an exact convex combination
-          if (kBf16) {
-            if (i & 1) add_bf16x2(t2, t3, pk[c][i]); else add_bf16x2(t0, t1, pk[c][i]);
-          } else {
-            if (i & 1) add2(t2, t3, p0, p1); else add2(t0, t1, p0, p1);
-          }
+          if (i & 1) add2(t2, t3, p0, p1); else add2(t0, t1, p0, p1);
         }
       }
       l_sum += (t0 + t1) + (t2 + t3);
+      if (kBf16) {
+        // The tensor core multiplies V by the ROUNDED probabilities.  With lazy rescaling the
+        // largest one is not exactly 1, so when one key dominates a row its rounding error
+        // (up to 2^-9 relative) would pass straight into the output.  Count that element in
+        // the row sum as the tensor core sees it: same arithmetic as pass 2, then rounded.
+        const float p_top = fast_exp2(fmaf(top_raw, e_mul, e_add));
+        l_sum += __bfloat162float(__float2bfloat16_rn(p_top)) - p_top;
+      }
       if (!o_done_seen) {
         if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
         tc_fence_after();
