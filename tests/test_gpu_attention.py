@@ -385,3 +385,26 @@ def test_head_dim_128_golden_and_varlen():
         torch.cuda.synchronize()
         t5b.check_device_status()
         check_close(got, want, dt, f"varlen d128 causal={causal}")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("dt,step", [(torch.bfloat16, 30.0), (torch.bfloat16, -30.0), (torch.float16, 9.0)])
+def test_scores_that_keep_growing_take_the_rescale_path(dt, step, D):
+    # The scores climb (or fall) by `step` every 37 keys, so the running maximum outgrows the
+    # lazy-rescale threshold inside nearly every tile, by a different whole number of powers
+    # of two in the two halves of a row and in different rows: O, l and the packed P are
+    # rescaled.  The result is dominated by the top block of keys, whose weights differ by a
+    # few units of noise.
+    B, H, M, N = 1, 2, 300, 1000
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn((B, H, M, D), generator=g) * 0.05
+    k = torch.randn((B, H, N, D), generator=g) * 0.05
+    q[..., 0] = 1.0 + 0.5 * torch.rand((B, H, M), generator=g)
+    k[..., 0] = step * torch.floor(torch.arange(N) / 37.0) + 2.0 * torch.randn((B, H, N), generator=g)
+    v = torch.randn((B, H, N, D), generator=g)
+    q, k, v = q.to(dt), k.to(dt), v.to(dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    want = orc.attention_basic(q, k, v, table, q_pos_offset=0)
+    for kernel in ("tcgen05",):
+        out = _run_dense(q, k, v, table, dt, kernel, q_pos_offset=0)
+        check_close(out, want, dt, f"growing scores {dt} {step} d{D}")

@@ -104,6 +104,27 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   }
 }
 
+// 2^-k for a non-negative whole number k held in a float (0 once it leaves the normal range).
+__device__ __forceinline__ float pow2_neg(float k) {
+  return k >= 127.f ? 0.f : __int_as_float((127 - (int)k) << 23);
+}
+
+// Both halves of a packed pair times a power of two (exact unless the result leaves the
+// normal range, where it no longer matters).
+template <bool kBf16>
+__device__ __forceinline__ uint32_t scale_packed(uint32_t v, float beta) {
+  float lo, hi;
+  if (kBf16) {
+    lo = __uint_as_float(v << 16);
+    hi = __uint_as_float(v & 0xffff0000u);
+  } else {
+    const __half2 h = *reinterpret_cast<const __half2*>(&v);
+    lo = __low2float(h);
+    hi = __high2float(h);
+  }
+  return pack2<kBf16>(lo * beta, hi * beta);
+}
+
 // kBf16: element type of Q/K/V/out (P uses the same type: tcgen05.mma kind::f16
 // takes A and B of one format; mixing fp16 P with bf16 V is an illegal instruction).
 // O and the row sum are rescaled only when a row maximum grows by more than this many powers
@@ -388,43 +409,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           top_raw = mx;
         }
       }
-      // combine with the other half of the row (both see the same values afterwards, hence
-      // take the same decisions)
-      ctl->xchg[j & 1][half][r] = mx;
-      if (!pair_sync()) { ok = false; fail_code = 33; break; }
-      const float m_new = fmaxf(m_use, fmaxf(mx, ctl->xchg[j & 1][half ^ 1][r]));
-
-      // lazy rescale: only when some row's maximum grew by more than the threshold (rare
-      // after the first tiles); needs the previous PV to be complete
-      const bool grow = (m_new - m_use) > kRescaleThreshold<kBf16>;   // false for -inf - -inf (NaN)
-      bool o_done_seen = (j == 0);
+      // The maximum the exponentials are taken against, m_use, is the same in both threads of a
+      // row.  First tile: the two halves exchange their maxima and wait for each other.  Later
+      // tiles: m_use only moves when a half grew past the threshold, and then by a whole number
+      // of powers of two, k.  Each thread publishes its k (almost always 0), computes its
+      // exponentials against m_use + k without waiting, and reads the partner's k afterwards;
+      // if the two differ, the smaller side rescales its packed P by 2^-(difference), which is
+      // exact.  The rendezvous latency so hides behind the exponentials.
+      float k_me = 0.f;
       if (j == 0) {
-        m_use = m_new;
-      } else if (__any_sync(0xffffffffu, grow)) {
-        if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
-        tc_fence_after();
-        o_done_seen = true;
-        float alpha = 1.f;
-        if (grow) { alpha = fast_exp2(m_use - m_new); m_use = m_new; }
-        l_sum *= alpha;
-        #pragma unroll 1
-        for (int c = 0; c < OH / 16; ++c) {      // this thread's columns of O
-          uint32_t ov[16];
-          tmem_ld_x16(tO + c * 16, ov);
-          tmem_ld_wait();
-          #pragma unroll
-          for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          tmem_st_x16(tO + c * 16, ov);
-        }
+        ctl->xchg[0][half][r] = mx;
+        if (!pair_sync()) { ok = false; fail_code = 33; break; }
+        const float m0 = fmaxf(mx, ctl->xchg[0][half ^ 1][r]);
+        m_use = (m0 == -INFINITY) ? 0.f : m0;     // finite from here on; a row without keys keeps l = 0
+      } else {
+        const float g = mx - m_use;
+        if (g > kRescaleThreshold<kBf16>) k_me = fminf(ceilf(g), 1.0e6f);
+        ctl->xchg[j & 1][half][r] = k_me;
+        mbar_arrive(pair_bar);
       }
-      const float m_safe = (m_use == -INFINITY) ? 0.f : m_use;
+      const float m_prov = m_use + k_me;
       // fast tiles: p = 2^(s*scale + (bias - m)); others: p = 2^(x - m) = 2^(x*1 + (-m))
       const float e_mul = fast ? scale : 1.f;
-      const float e_add = fast ? bias_const - m_safe : -m_safe;
+      const float e_add = fast ? bias_const - m_prov : -m_prov;
 
       // ---- pass 2: all exponentials of the tile into registers (packed P) and the row sum.
-      // The scores die as they are consumed.  Only then wait for the previous tile's PV (it
-      // still reads the P buffer): its latency hides behind the exponentials.
+      // The scores die as they are consumed.
       uint32_t pk[NCH][16];
       float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
       #pragma unroll
@@ -438,15 +448,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           if (i & 1) add2(t2, t3, p0, p1); else add2(t0, t1, p0, p1);
         }
       }
-      l_sum += (t0 + t1) + (t2 + t3);
+      float t_sum = (t0 + t1) + (t2 + t3);
       if (kBf16) {
         // The tensor core multiplies V by the ROUNDED probabilities.  With lazy rescaling the
         // largest one is not exactly 1, so when one key dominates a row its rounding error
         // (up to 2^-9 relative) would pass straight into the output.  Count that element in
         // the row sum as the tensor core sees it: same arithmetic as pass 2, then rounded.
         const float p_top = fast_exp2(fmaf(top_raw, e_mul, e_add));
-        l_sum += __bfloat162float(__float2bfloat16_rn(p_top)) - p_top;
+        t_sum += __bfloat162float(__float2bfloat16_rn(p_top)) - p_top;
       }
+
+      // ---- partner's step; rescale O, l and (if the steps differ) this tile's P.  Rare.
+      bool o_done_seen = (j == 0);
+      if (j > 0) {
+        const bool met = mbar_wait_bounded(pair_bar, pair_uses & 1u, abort_flag);
+        ++pair_uses;
+        if (!met) { ok = false; fail_code = 33; break; }
+        const float k_max = fmaxf(k_me, ctl->xchg[j & 1][half ^ 1][r]);
+        if (__any_sync(0xffffffffu, k_max > 0.f)) {
+          if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
+          tc_fence_after();
+          o_done_seen = true;
+          const float alpha = pow2_neg(k_max);
+          l_sum *= alpha;
+          m_use += k_max;
+          #pragma unroll 1
+          for (int c = 0; c < OH / 16; ++c) {      // this thread's columns of O
+            uint32_t ov[16];
+            tmem_ld_x16(tO + c * 16, ov);
+            tmem_ld_wait();
+            #pragma unroll
+            for (int i = 0; i < 16; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st_x16(tO + c * 16, ov);
+          }
+          if (k_max > k_me) {
+            const float beta = pow2_neg(k_max - k_me);
+            t_sum *= beta;
+            #pragma unroll
+            for (int c = 0; c < NCH; ++c)
+              #pragma unroll
+              for (int i = 0; i < 16; ++i) pk[c][i] = scale_packed<kBf16>(pk[c][i], beta);
+          }
+        }
+      }
+      l_sum += t_sum;
       if (!o_done_seen) {
         if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
         tc_fence_after();
@@ -497,7 +542,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         for (int i = 0; i < OH / 4; ++i)
           reinterpret_cast<float4*>(my_o)[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
         float* my_ml = p.ws_ml + ((slot * BM + r) * 2 + half) * 2;
-        my_ml[0] = m_use;
+        my_ml[0] = l_sum > 0.f ? m_use : -INFINITY;
         my_ml[1] = l_sum;
         __threadfence();
         int* counter = p.ws_counters + ((int64_t)tail_slot * BM + r) * 2 + half;
