@@ -399,6 +399,21 @@ def secondary_measurements(t5b, dev):
     out["varlen_32seq_128to4096"] = {"ms": ms, "TFLOP/s": fl / (ms * 1e-3) / 1e12, "tokens": T,
                                      "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"]}
     del qkv
+    # head dim 128 (the T5-3B / 11B head size): same sequence length, 3 rotating input sets
+    # (3 x 151 MB > L2), T5 bias, bf16
+    sets = [[(torch.randn((2, 8192, 12, 128), generator=g, device=dev, dtype=torch.float32) * 0.5).to(dt).transpose(1, 2)
+             for _ in range(3)] for _ in range(3)]
+    turn = [0]
+
+    def d128_step():
+        q_, k_, v_ = sets[turn[0] % 3]
+        turn[0] += 1
+        return t5b.flash_attention_with_fusing_bias(q_, k_, v_, table, sm_scale=1.0)
+    ms = _time(d128_step, 15)
+    fl = 4.0 * 2 * 12 * 8192 * 8192 * 128
+    out["attention_d128_B2_H12_L8192"] = {"ms": ms, "TFLOP/s": fl / (ms * 1e-3) / 1e12,
+                                          "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"]}
+    del sets
     # T5-base encoder (12 layers, d_model 768, 12 x 64 heads, gated-GELU d_ff 2048, random init, bf16):
     # tokens/s of a forward pass at 2 x 8192 tokens and at 16 x 1024 tokens
     from turbot5_b200.t5 import T5Stack, T5StackConfig

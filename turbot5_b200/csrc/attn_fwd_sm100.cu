@@ -8,20 +8,26 @@
 //   warp 9      tensor-core issuer: S = Q K^T and O += P V with tcgen05.mma,
 //               accumulators in tensor memory, tcgen05.commit -> mbarriers
 //   warps 0-7   softmax: two threads share a query row (warp w and warp w+4 see the
-//               same 32 TMEM lanes; one takes key columns 0-63, the other 64-127 and
-//               the matching half of the O columns).  A thread copies its 64 scores
-//               from tensor memory to registers at once (tcgen05.ld) and the S buffer
-//               is handed back immediately, so the next QK^T runs while this tile's
-//               softmax is computed.  The T5 bias is added from a shared-memory copy
-//               of delta -> table[bucket(delta), head] (no L x L tensor exists, no
-//               1/sqrt(d) unless asked); the two halves of a row exchange their
-//               maxima through shared memory; lazy rescaling of O; P is written
-//               back to tensor memory as bf16/fp16 (tcgen05.st) where the second MMA
-//               reads it as its A operand.
-//   warps 8,9   TMA producer and MMA issuer (one elected lane each).
+//               same 32 TMEM lanes; one takes the first half of the tile's key columns,
+//               the other the second half, and the matching half of the O columns).  A
+//               thread copies its scores from tensor memory to registers at once
+//               (tcgen05.ld) and the S buffer is handed back immediately, so the next
+//               QK^T runs while this tile's softmax is computed.  The T5 bias is added
+//               from a shared-memory copy of delta -> table[bucket(delta), head] (no
+//               L x L tensor exists, no 1/sqrt(d) unless asked).  Two passes over the
+//               registers: maximum, then all exponentials (packed to bf16/fp16) and the
+//               row sum; P goes back to tensor memory (tcgen05.st) where the second MMA
+//               reads it as its A operand.  O and the row sum are rescaled lazily: the
+//               value the exponentials are taken against moves only when a maximum has
+//               outgrown it by 2^40 (bf16; 2^10 for fp16), and then by a whole number of
+//               powers of two, which lets the two threads of a row agree after the
+//               exponentials instead of before them (see the loop).
 //
-// Two blocks fit on an SM (256 TMEM columns and ~85 KB shared memory each), so one
-// block's softmax overlaps the other block's matrix products.
+// Head dim 64 uses 128-key tiles, head dim 128 uses 64-key tiles whose rows are two
+// 128-byte-swizzled sub-tiles; either way two blocks fit on an SM (<= 256 TMEM columns and
+// 80-96 KB of tiles each), so one block's softmax overlaps the other block's matrix products.
+// The exponential unit (16 ex2 per clock per SM) is the scarcest resource at head dim 64: it
+// needs twice the time of the tensor core for the same tile.
 //
 // Semantics follow flash_attention_with_fusing_bias
 // (src/turbot5/ops/fused_bias_attention.py:184-365) with positions as in the
@@ -75,7 +81,7 @@ enum {
   BAR_S_FREE,
   BAR_P_FULL,
   BAR_O_DONE,
-  BAR_PAIR,                          // [4]: the two warps sharing a TMEM lane quarter (64 arrivals)
+  BAR_PAIR,                          // [4]: the two warps sharing a TMEM lane quarter (one arrival each)
   NUM_BARS = BAR_PAIR + 4
 };
 
@@ -215,10 +221,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       mbar_init(bar(BAR_V_EMPTY + s), 1);
     }
     mbar_init(bar(BAR_S_FULL), 1);
-    mbar_init(bar(BAR_S_FREE), SOFTMAX_THREADS);
-    mbar_init(bar(BAR_P_FULL), SOFTMAX_THREADS);
+    // one arrival per softmax warp (lane 0, after the warp has converged): 32 lanes arriving
+    // on one barrier word are 32 serialised shared-memory atomics
+    mbar_init(bar(BAR_S_FREE), SOFTMAX_THREADS / 32);
+    mbar_init(bar(BAR_P_FULL), SOFTMAX_THREADS / 32);
     mbar_init(bar(BAR_O_DONE), 1);
-    for (int qd = 0; qd < 4; ++qd) mbar_init(bar(BAR_PAIR + qd), 64);
+    for (int qd = 0; qd < 4; ++qd) mbar_init(bar(BAR_PAIR + qd), 2);
     fence_barrier_init();
     fence_proxy_async();
   }
@@ -335,7 +343,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t pair_bar = bar(BAR_PAIR + quarter);
     uint32_t pair_uses = 0;
     auto pair_sync = [&]() -> bool {
-      mbar_arrive(pair_bar);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pair_bar);
       const bool done = mbar_wait_bounded(pair_bar, pair_uses & 1u, abort_flag);
       ++pair_uses;
       return done;
@@ -356,7 +365,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       for (int c = 0; c < NCH; ++c) tmem_ld_x32(tS + 32 * c, sv[c]);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(bar(BAR_S_FREE));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_S_FREE));
 
       // tile classification (uniform over the block)
       const bool need_mask = (n0 + BN > len_k) || (p.causal && (n0 + BN - 1 > qpos0));
@@ -426,7 +436,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         const float g = mx - m_use;
         if (g > kRescaleThreshold<kBf16>) k_me = fminf(ceilf(g), 1.0e6f);
         ctl->xchg[j & 1][half][r] = k_me;
-        mbar_arrive(pair_bar);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pair_bar);
       }
       const float m_prov = m_use + k_me;
       // fast tiles: p = 2^(s*scale + (bias - m)); others: p = 2^(x - m) = 2^(x*1 + (-m))
@@ -500,7 +511,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       for (int c = 0; c < NCH; ++c) tmem_st_x16(tP + 16 * c, pk[c]);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar(BAR_P_FULL));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_P_FULL));
     }
 
     // ---- epilogue: O / l -> global (each thread its 32 output columns)
