@@ -34,7 +34,7 @@ WORKLOAD = dict(name="fused-bias attention fwd, T5-base heads @8k", B=2, H=12, L
 L2_BYTES = 126 * 1024 * 1024
 # DRAM traffic (read + write) of one launch of the forward kernel on the workload above,
 # from the ncu capture summarised in profiles/attn_fwd_sm100_8k.md (dram__bytes_read + dram__bytes_write).
-NCU_DRAM_BYTES_PER_LAUNCH = 75.6e6 + 12.4e6
+NCU_DRAM_BYTES_PER_LAUNCH = 75.6e6 + 13.8e6
 
 
 def flops_per_step(w):
@@ -152,6 +152,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary kernel measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128],
+                    help="64: the headline workload; 128: the same workload at the T5-3B/11B head size "
+                         "(a second tile geometry of the kernel; used for its profile)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     # the CPU arm does far less work per second: bound its run to a few minutes
@@ -176,7 +179,9 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    w = WORKLOAD
+    w = dict(WORKLOAD)
+    if args.head_dim != w["D"]:
+        w.update(D=args.head_dim, name=f"fused-bias attention fwd, 12 heads of dim {args.head_dim} @8k")
     B, H, L, D = w["B"], w["H"], w["L"], w["D"]
     dt = torch.bfloat16
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
@@ -293,7 +298,8 @@ def main():
                        "sm_scale": 1.0, "layout": "BHLD views of BLHD buffers", "parallelism": f"batch-sharded x{world}",
                        "l2": f"inputs rotate over {n_sets} sets ({n_sets * set_bytes / 2**20:.0f} MiB > 126 MiB L2)"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["tflops"], "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                         "frac": achieved / peaks["tflops"],
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH if D == WORKLOAD["D"] else None,
                          "peak_source": peaks["source"], "kernel": "attn_fwd_kernel<bf16>"},
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": set_bytes,
                     "d2h_bytes_per_step": B * H * L * D * 2, "ms_per_step": e2e_ms, "steps": e2e_steps},
