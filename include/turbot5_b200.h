@@ -118,6 +118,33 @@ T5B_API int t5b_attention_fwd(const t5b_attn_args* args, void* stream);
  * device for these arguments (0 if splitting would not help or does not apply). */
 T5B_API int64_t t5b_attention_workspace_bytes(const t5b_attn_args* args);
 
+/* ------------------------------------------------------------------------ *
+ * Backward of the fused-bias attention: replaces FlashAttentionBias.backward ->
+ * flash_attn_v2_bwd_bias (src/turbot5/ops/fused_bias_attention.py:852-873, 62-147:
+ * _bwd_preprocess :398-437, _bwd_kv_bias_kernel :440-632, _bwd_q_kernel_with_bias_calculation
+ * :635-820) and the varlen counterpart (src/turbot5/ops/varlen_fused_bias_attn.py).
+ *
+ *   fwd     the forward call whose gradient is taken: same pointers, strides, sizes and
+ *           flags; fwd.out and fwd.lse hold its results (lse is required here).
+ *   dout    gradient of out, dtype of out, element strides do_stride_*, last dim contiguous.
+ *   dq, dk, dv   written; dtype and strides of q, k, v.
+ *   dtable  float32 [num_buckets, H], contiguous; the gradient of the bias table is ADDED to
+ *           it (the caller zeroes it); NULL when fwd.table is NULL.
+ *   delta   float32 scratch of the shape of lse.
+ * Tensor-core path only: bf16/fp16, head dim 64, 16-byte aligned rows (T5B_ERR_UNSUPPORTED
+ * otherwise), N > 0.
+ */
+typedef struct {
+  t5b_attn_args fwd;
+  const void* dout;
+  int64_t do_stride_b, do_stride_h, do_stride_m;
+  void* dq; void* dk; void* dv;
+  float* dtable;
+  float* delta;
+} t5b_attn_bwd_args;
+
+T5B_API int t5b_attention_bwd(const t5b_attn_bwd_args* args, void* stream);
+
 /* ---- split-KV flash decoding ---------------------------------------------------
  * Stands in for the split/merge semantics of flash_attn_v2_fwd
  * (src/turbot5/ops/flash_decoding.py:6-55; never wired into the reference's

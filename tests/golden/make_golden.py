@@ -14,6 +14,7 @@ Fixtures written:
   buckets.npz      bucket index for every delta in [-2*md-3, 2*md+3] for a spread
                    of (num_buckets, max_distance, bidirectional) settings, from
                    `T5Attention._relative_position_bucket`.
+  attention_grad.npz  the same two functions under autograd: gradients of q, k, v and the table
   attention.npz    small seeded q/k/v/table cases through `compute_bias` +
                    `naive_torch_attention_with_bias` (float32 math on bf16-representable
                    inputs, stored as bf16 bit patterns), incl. cached
@@ -183,6 +184,41 @@ def main(ref_root: str):
     np.savez_compressed(os.path.join(here, "layer.npz"), **layer)
 
     # ---------------------------------------------------------------- rmsnorm
+    # ------------------------------------------------- attention gradients
+    # the same two reference functions under autograd: d(sum(out * dout)) / d(q, k, v, table)
+    grads = {}
+    gspecs = [
+        # name, B, H, M, N, D, unidirectional, nb, md, seed
+        ("g_enc", 1, 2, 150, 150, 64, False, 32, 128, 11),
+        ("g_cross", 2, 2, 70, 200, 64, False, 32, 128, 12),
+        ("g_long", 1, 1, 400, 400, 64, False, 32, 128, 13),
+        ("g_uni", 1, 2, 90, 90, 64, True, 32, 128, 14),      # unidirectional buckets, no mask
+    ]
+    for name, B, H, M, N, D, dec, nb, md, seed in gspecs:
+        att = make_att(dec, H, nb, md)
+        table = seeded((nb, H), 100 + seed, 0.1).bfloat16().float()
+        with torch.no_grad():
+            att.relative_attention_bias.weight.copy_(table)
+        q = (seeded((B, H, M, D), 200 + seed) * 0.5).bfloat16().float().requires_grad_(True)
+        k = (seeded((B, H, N, D), 300 + seed) * 0.5).bfloat16().float().requires_grad_(True)
+        v = seeded((B, H, N, D), 400 + seed).bfloat16().float().requires_grad_(True)
+        dout = seeded((B, H, M, D), 500 + seed).bfloat16().float()
+        bias = att.compute_bias(M, N) if M != N else att.compute_bias(N, N)
+        o, _ = naive_torch_attention_with_bias(q, k, v, bias.clone())
+        (o * dout).sum().backward()
+        grads[name + "_q"] = bf16_bits(q.detach())
+        grads[name + "_k"] = bf16_bits(k.detach())
+        grads[name + "_v"] = bf16_bits(v.detach())
+        grads[name + "_table"] = bf16_bits(table)
+        grads[name + "_dout"] = bf16_bits(dout)
+        grads[name + "_dq"] = q.grad.numpy()
+        grads[name + "_dk"] = k.grad.numpy()
+        grads[name + "_dv"] = v.grad.numpy()
+        grads[name + "_dtable"] = att.relative_attention_bias.weight.grad.numpy()
+        grads[name + "_meta"] = np.asarray([B, H, M, N, D, int(dec), nb, md], dtype=np.int64)
+    grads["names"] = np.asarray([s[0] for s in gspecs])
+    np.savez_compressed(os.path.join(here, "attention_grad.npz"), **grads)
+
     rn = {}
     for tag, xdt, wdt in (("f32", torch.float32, torch.float32),
                           ("bf16", torch.bfloat16, torch.bfloat16),

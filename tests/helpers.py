@@ -75,3 +75,17 @@ def tiny_t5_inputs():
     ids = torch.randint(0, TINY_T5["vocab_size"], (2, 40), generator=g)
     dec = torch.randint(0, TINY_T5["vocab_size"], (2, 5), generator=g)
     return ids, dec
+
+
+def check_grad_close(got, want, what="", rel=2e-2, floor=1e-6):
+    """Gradients from 16-bit kernels against float32 autograd: the error of every element is
+    bounded relative to the largest magnitude of the tensor (gradients span decades, and each
+    is a sum of products of rounded factors), and the mean error by a tenth of that.  `floor`
+    is the smallest magnitude taken as that scale: a bias-table gradient is a sum of thousands
+    of terms of order 1e-2..1 that can cancel to exactly zero (all keys in one bucket)."""
+    got, want = got.float().cpu(), want.float().cpu()
+    scale = max(want.abs().max().item(), floor)
+    diff = (got - want).abs()
+    mx, mean = diff.max().item() / scale, diff.mean().item() / scale
+    assert mx <= rel and mean <= rel / 10, f"{what}: max error {mx:.3e}, mean error {mean:.3e} of max |grad| {scale:.3e}"
+    return mx, mean

@@ -27,7 +27,8 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header_field_order():
     from turbot5_b200 import _native as nat
     header = open(os.path.join(ROOT, "include", "turbot5_b200.h")).read()
-    for cname, cls in (("t5b_attn_args", nat.AttnArgs), ("t5b_decode_args", nat.DecodeArgs)):
+    for cname, cls in (("t5b_attn_args", nat.AttnArgs), ("t5b_decode_args", nat.DecodeArgs),
+                       ("t5b_attn_bwd_args", nat.AttnBwdArgs)):
         end = header.index("} " + cname + ";")
         body = header[header.rindex("typedef struct {", 0, end) + len("typedef struct {"):end]
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)

@@ -1,0 +1,126 @@
+"""Backward of the fused-bias attention (through the C ABI and torch.autograd) against the
+CPU oracle under autograd and the gradient fixtures generated from the reference."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import t5_oracle as orc
+from tests.helpers import check_close, check_grad_close, from_bf16_bits, load, seeded
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    import turbot5_b200 as t5b
+    return t5b
+
+
+def _cuda_grads(q, k, v, table, dout, dt, **kw):
+    t5b = _ops()
+    qc, kc, vc = (t.to("cuda", dt).requires_grad_(True) for t in (q, k, v))
+    tc = None if table is None else table.to("cuda", dt).requires_grad_(True)
+    out = t5b.flash_attention_with_fusing_bias(qc, kc, vc, tc, sm_scale=kw.pop("sm_scale", 1.0), **kw)
+    out.backward(dout.to("cuda", dt))
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    return out.detach(), qc.grad, kc.grad, vc.grad, (None if tc is None else tc.grad)
+
+
+def _oracle_grads(q, k, v, table, dout, **kw):
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    tf = None if table is None else table.float().requires_grad_(True)
+    out = orc.attention_basic(qf, kf, vf, tf, **kw)
+    (out * dout.float()).sum().backward()
+    return out.detach(), qf.grad, kf.grad, vf.grad, (None if tf is None else tf.grad)
+
+
+@pytest.mark.parametrize("name", ["g_enc", "g_cross", "g_long"])
+def test_gradients_match_reference_fixture(name):
+    z = load("attention_grad.npz")
+    B, H, M, N, D, dec, nb, md = [int(x) for x in z[name + "_meta"]]
+    q, k, v, table, dout = (from_bf16_bits(z[name + s]) for s in ("_q", "_k", "_v", "_table", "_dout"))
+    _, dq, dk, dv, dt_ = _cuda_grads(q, k, v, table, dout, torch.bfloat16, q_pos_offset=0, NUM_BUCKETS=nb,
+                                     MAX_DISTANCE=md)
+    check_grad_close(dq, torch.from_numpy(z[name + "_dq"]), name + " dq")
+    check_grad_close(dk, torch.from_numpy(z[name + "_dk"]), name + " dk")
+    check_grad_close(dv, torch.from_numpy(z[name + "_dv"]), name + " dv")
+    check_grad_close(dt_, torch.from_numpy(z[name + "_dtable"]), name + " dtable")
+
+
+CASES = [
+    # B, H, M, N, causal, q_pos_offset
+    (2, 3, 512, 512, False, None),
+    (1, 2, 777, 777, False, None),
+    (1, 2, 777, 777, True, None),
+    (2, 2, 128, 1024, False, 0),        # cross-attention shape
+    (1, 2, 200, 555, True, None),       # cached prefill: queries aligned to the end
+    (1, 2, 300, 300, False, 4000),      # far from the diagonal: one bucket only
+    (1, 1, 1, 300, True, None),
+    (1, 2, 1000, 70, False, 0),
+]
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,M,N,causal,off", CASES)
+def test_seeded_gradients_vs_oracle(B, H, M, N, causal, off, dt):
+    q = seeded((B, H, M, 64), 1, 0.5, dtype=dt)
+    k = seeded((B, H, N, 64), 2, 0.5, dtype=dt)
+    v = seeded((B, H, N, 64), 3, dtype=dt)
+    dout = seeded((B, H, M, 64), 5, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    want = _oracle_grads(q, k, v, table, dout, causal=causal, q_pos_offset=off)
+    got = _cuda_grads(q, k, v, table, dout, dt, causal=causal, q_pos_offset=off)
+    what = f"{(B, H, M, N, causal, off)}"
+    check_close(got[0], want[0], dt, what + " out")
+    for g, w, nm in zip(got[1:], want[1:], ("dq", "dk", "dv", "dtable")):
+        check_grad_close(g, w, what + " " + nm, floor=2.0 if nm == "dtable" else 1e-6)
+
+
+def test_no_bias_scale_and_strided_views():
+    # BHLD views of BLHD buffers, sm_scale != 1, no table: gradients keep the inputs' layout
+    t5b = _ops()
+    dt = torch.bfloat16
+    B, H, L, D = 2, 3, 300, 64
+    base = [seeded((B, L, H, D), s, 0.7, dtype=dt) for s in (1, 2, 3)]
+    dout = seeded((B, H, L, D), 5, dtype=dt)
+    want = _oracle_grads(*(t.transpose(1, 2) for t in base), None, dout, sm_scale=0.25)
+    leaves = [t.cuda().requires_grad_(True) for t in base]
+    out = t5b.flash_attention_with_fusing_bias(*(t.transpose(1, 2) for t in leaves), None, sm_scale=0.25)
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    for leaf, w, nm in zip(leaves, want[1:4], ("dq", "dk", "dv")):
+        check_grad_close(leaf.grad.transpose(1, 2), w, nm)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_varlen_gradients_vs_oracle(causal):
+    t5b = _ops()
+    dt = torch.bfloat16
+    lens = [5, 128, 0, 129, 300, 1, 257, 64]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    T, H = int(cu[-1]), 3
+    q, k, v = seeded((T, H, 64), 1, 0.5, dtype=dt), seeded((T, H, 64), 2, 0.5, dtype=dt), seeded((T, H, 64), 3, dtype=dt)
+    dout = seeded((T, H, 64), 5, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    qf, kf, vf, tf = (t.float().requires_grad_(True) for t in (q, k, v, table))
+    want = orc.attention_basic_varlen(qf, kf, vf, tf, cu, cu, causal=causal)
+    (want * dout.float()).sum().backward()
+    qc, kc, vc, tc = (t.cuda().requires_grad_(True) for t in (q, k, v, table))
+    out = t5b.flash_attention_with_fusing_bias_varlen(qc, kc, vc, tc, cu.cuda(), cu.cuda(), max(lens), max(lens),
+                                                      causal=causal, sm_scale=1.0)
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    check_close(out.detach(), want.detach(), dt, "varlen out")
+    for g, w, nm in ((qc.grad, qf.grad, "dq"), (kc.grad, kf.grad, "dk"), (vc.grad, vf.grad, "dv"),
+                     (tc.grad, tf.grad, "dtable")):
+        check_grad_close(g, w, f"varlen causal={causal} {nm}")
+
+
+def test_backward_of_unsupported_shapes_is_refused():
+    t5b = _ops()
+    q = torch.randn(1, 2, 64, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    out = t5b.flash_attention_with_fusing_bias(q, q.detach(), q.detach(), None, sm_scale=1.0)
+    with pytest.raises(NotImplementedError):
+        out.sum().backward()

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import t5_oracle as orc
-from tests.helpers import attention_case, load, seeded
+from tests.helpers import attention_case, from_bf16_bits, load, seeded
 
 
 def test_bucket_tables_bit_exact():
@@ -158,3 +158,21 @@ def test_stack_oracle_matches_reference_model_fixture():
         assert (lg[:, -1] - torch.from_numpy(z["greedy_logits"][:, step])).abs().max() < 2e-5
         cur = torch.cat([cur, lg[:, -1:].argmax(-1)], dim=1)
     assert torch.equal(cur[:, 1:], torch.from_numpy(z["greedy_tokens"]))
+
+
+@pytest.mark.parametrize("name", ["g_enc", "g_cross", "g_long", "g_uni"])
+def test_attention_gradients_under_autograd(name):
+    # the oracle restatement under torch autograd against the reference's functions under autograd
+    z = load("attention_grad.npz")
+    B, H, M, N, D, dec, nb, md = [int(x) for x in z[name + "_meta"]]
+    q = from_bf16_bits(z[name + "_q"]).requires_grad_(True)
+    k = from_bf16_bits(z[name + "_k"]).requires_grad_(True)
+    v = from_bf16_bits(z[name + "_v"]).requires_grad_(True)
+    table = from_bf16_bits(z[name + "_table"]).requires_grad_(True)
+    dout = from_bf16_bits(z[name + "_dout"])
+    bias = orc.compute_bias(table, M, N, not dec, nb, md, q_pos_offset=0)
+    out = orc.naive_attention_with_bias(q, k, v, bias)
+    (out * dout).sum().backward()
+    for got, key in ((q.grad, "_dq"), (k.grad, "_dk"), (v.grad, "_dv"), (table.grad, "_dtable")):
+        want = torch.from_numpy(z[name + key])
+        assert (got - want).abs().max().item() <= 1e-4 * max(1.0, want.abs().max().item()), (name, key)

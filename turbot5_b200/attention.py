@@ -7,7 +7,10 @@ replace:
 * `flash_attention_with_fusing_bias_varlen`  src/turbot5/ops/varlen_fused_bias_attn.py:870
 
 plus the split-KV decoding operator the reference only sketches
-(src/turbot5/ops/flash_decoding.py) and a bucket-index check.  Forward only.
+(src/turbot5/ops/flash_decoding.py) and a bucket-index check.  Both attention
+operators are differentiable (q, k, v and the bias table) through
+`torch.autograd.Function`s that mirror `FlashAttentionBias`
+(src/turbot5/ops/fused_bias_attention.py:822-873).
 """
 import math
 from typing import Optional
@@ -65,6 +68,17 @@ def _unit_stride_last(t):
 def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
                                      NUM_BUCKETS=32, MAX_DISTANCE=128, *, q_pos_offset=None,
                                      return_lse=False, kernel="auto", balance_last_wave=True):
+    """See `_dense_forward`; differentiable when an input requires grad (bf16/fp16, head dim 64)."""
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
+        out, lse = _DenseAttention.apply(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset,
+                                         kernel, balance_last_wave)
+        return (out, lse) if return_lse else out
+    return _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset=q_pos_offset,
+                          return_lse=return_lse, kernel=kernel, balance_last_wave=balance_last_wave)
+
+
+def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *,
+                   q_pos_offset=None, return_lse=False, kernel="auto", balance_last_wave=True, _keep=None):
     """softmax(sm_scale * Q K^T + T5 bias(n - m) [+ causal mask]) V without an L x L tensor.
 
     q (B,H,M,D), k/v (B,H,N,D), any batch/head/row strides (last dim contiguous);
@@ -116,6 +130,8 @@ def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
                 ws = _scratch(q.device, "attn", need)
                 a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)), "flash_attention_with_fusing_bias")
+    if _keep is not None:
+        _keep.update(args=a, q=q, k=k, v=v, table=table)
     return (out, lse) if return_lse else out
 
 
@@ -123,6 +139,17 @@ def flash_attention_with_fusing_bias_varlen(q, k, v, bias, cu_seqlens_q, cu_seql
                                             max_seqlen_q, max_seqlen_k, causal=False, sm_scale=None,
                                             NUM_BUCKETS=32, MAX_DISTANCE=128, *, return_lse=False,
                                             kernel="auto"):
+    """See `_varlen_forward`; differentiable when an input requires grad (bf16/fp16, head dim 64)."""
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
+        out, lse = _VarlenAttention.apply(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                                          causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, kernel)
+        return (out, lse) if return_lse else out
+    return _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, sm_scale,
+                           NUM_BUCKETS, MAX_DISTANCE, return_lse=return_lse, kernel=kernel)
+
+
+def _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=False,
+                    sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *, return_lse=False, kernel="auto", _keep=None):
     """Packed-sequence variant: q (Tq,H,D), k/v (Tk,H,D), int32 cu_seqlens on the device.
 
     Positions are relative to each sequence.  Tiles are scheduled on the device
@@ -171,7 +198,97 @@ def flash_attention_with_fusing_bias_varlen(q, k, v, bias, cu_seqlens_q, cu_seql
     with torch.cuda.device(q.device):
         nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)),
                   "flash_attention_with_fusing_bias_varlen")
+    if _keep is not None:
+        _keep.update(args=a, q=q, k=k, v=v, table=table, cu_q=cu_seqlens_q, cu_k=cu_seqlens_k)
     return (out, lse) if return_lse else out
+
+
+def _attention_backward(keep, out, lse, dout, varlen):
+    """dq, dk, dv, dtable for the forward call recorded in `keep` (its argument block and the
+    tensors it points to).  Mirrors flash_attn_v2_bwd_bias
+    (src/turbot5/ops/fused_bias_attention.py:62-147): delta, then the k/v and q kernels."""
+    q, k, v, table = keep["q"], keep["k"], keep["v"], keep["table"]
+    row_dim = 0 if varlen else 2
+    if dout.dtype != out.dtype:
+        dout = dout.to(out.dtype)
+    if dout.stride(-1) != 1 or dout.data_ptr() % 16 or any(s % 8 for s in dout.stride()[:-1]):
+        dout = dout.contiguous()
+    dq = torch.empty_strided(q.shape, q.stride(), dtype=q.dtype, device=q.device)
+    dk = torch.empty_strided(k.shape, k.stride(), dtype=k.dtype, device=k.device)
+    dv = torch.empty_strided(v.shape, v.stride(), dtype=v.dtype, device=v.device)
+    n_keys = k.shape[row_dim]
+    if n_keys == 0 or q.shape[row_dim] == 0:
+        dtab = None if table is None else torch.zeros_like(table)
+        return dq.zero_(), dk.zero_(), dv.zero_(), dtab
+    H = q.shape[1]
+    g = nat.AttnBwdArgs()
+    g.fwd = keep["args"]
+    g.fwd.out, g.fwd.lse = out.data_ptr(), lse.data_ptr()
+    g.fwd.o_stride_h = out.stride(1)
+    g.fwd.o_stride_b, g.fwd.o_stride_m = (0, out.stride(0)) if varlen else (out.stride(0), out.stride(2))
+    g.fwd.workspace, g.fwd.workspace_bytes = None, 0
+    g.fwd.device_status = device_status(q.device).data_ptr()
+    g.dout = dout.data_ptr()
+    g.do_stride_h = dout.stride(1)
+    g.do_stride_b, g.do_stride_m = (0, dout.stride(0)) if varlen else (dout.stride(0), dout.stride(2))
+    g.dq, g.dk, g.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    dtable = None
+    if table is not None:
+        dtable = torch.zeros((g.fwd.num_buckets, H), dtype=torch.float32, device=q.device)
+    delta = torch.empty_like(lse)
+    g.dtable, g.delta = nat.ptr(dtable), delta.data_ptr()
+    with torch.cuda.device(q.device):
+        st = nat.lib().t5b_attention_bwd(g, nat.stream_ptr(q.device))
+    if st == nat.ERR_UNSUPPORTED:
+        raise NotImplementedError("the attention backward runs on the tensor-core path only: bf16/fp16, "
+                                  "head dim 64, 16-byte aligned rows")
+    nat.check(st, "flash_attention_with_fusing_bias (backward)")
+    if dtable is not None:
+        dtable = dtable[: table.shape[0]].to(table.dtype)
+    return dq, dk, dv, dtable
+
+
+class _DenseAttention(torch.autograd.Function):
+    """Autograd wrapper of the dense operator, as FlashAttentionBias
+    (src/turbot5/ops/fused_bias_attention.py:822-873)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset, kernel, balance):
+        keep = {}
+        out, lse = _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE,
+                                  q_pos_offset=q_pos_offset, return_lse=True, kernel=kernel,
+                                  balance_last_wave=balance, _keep=keep)
+        ctx.keep = keep
+        ctx.save_for_backward(out, lse)
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        out, lse = ctx.saved_tensors
+        dq, dk, dv, dtable = _attention_backward(ctx.keep, out, lse, dout, varlen=False)
+        return dq, dk, dv, dtable, None, None, None, None, None, None, None
+
+
+class _VarlenAttention(torch.autograd.Function):
+    """Autograd wrapper of the packed-sequence operator
+    (src/turbot5/ops/varlen_fused_bias_attn.py: FlashAttentionBias of that file)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, bias, cu_q, cu_k, max_q, max_k, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, kernel):
+        keep = {}
+        out, lse = _varlen_forward(q, k, v, bias, cu_q, cu_k, max_q, max_k, causal, sm_scale, NUM_BUCKETS,
+                                   MAX_DISTANCE, return_lse=True, kernel=kernel, _keep=keep)
+        ctx.keep = keep
+        ctx.save_for_backward(out, lse)
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        out, lse = ctx.saved_tensors
+        dq, dk, dv, dtable = _attention_backward(ctx.keep, out, lse, dout, varlen=True)
+        return dq, dk, dv, dtable, None, None, None, None, None, None, None, None, None
 
 
 def _scratch(device, kind: str, nbytes: int) -> torch.Tensor:

@@ -54,6 +54,35 @@ extern "C" int t5b_attention_fwd(const t5b_attn_args* a, void* stream) {
   return simt_attention_fwd(*a, spec, st);
 }
 
+extern "C" int t5b_attention_bwd(const t5b_attn_bwd_args* g, void* stream) {
+  if (!g) return T5B_ERR_ARG;
+  const t5b_attn_args* a = &g->fwd;
+  if (a->dtype != T5B_F32 && a->dtype != T5B_F16 && a->dtype != T5B_BF16) return T5B_ERR_DTYPE;
+  if (a->D != 16 && a->D != 32 && a->D != 64 && a->D != 128) return T5B_ERR_HEAD_DIM;
+  if (a->B < 0 || a->H < 0 || a->M < 0 || a->N < 0) return T5B_ERR_SHAPE;
+  const bool varlen = a->cu_seqlens_q != nullptr || a->cu_seqlens_k != nullptr;
+  if (varlen) {
+    if (!a->cu_seqlens_q || !a->cu_seqlens_k) return T5B_ERR_ARG;
+    if (a->total_q < 0 || a->total_k < 0) return T5B_ERR_SHAPE;
+    if (a->B == 0 || a->H == 0 || (a->total_q == 0 && a->total_k == 0)) return T5B_OK;
+  } else {
+    if (a->B == 0 || a->H == 0 || (a->M == 0 && a->N == 0)) return T5B_OK;
+  }
+  if (!a->q || !a->k || !a->v || !a->out || !a->lse) return T5B_ERR_ARG;
+  if (!g->dout || !g->dq || !g->dk || !g->dv || !g->delta) return T5B_ERR_ARG;
+  if (a->table && !g->dtable) return T5B_ERR_ARG;
+  if ((varlen ? a->total_k : a->N) == 0 || (varlen ? a->total_q : a->M) == 0) return T5B_ERR_UNSUPPORTED;
+  BucketSpec spec;
+  spec.n_side = 2; spec.bidirectional = 0; spec.max_distance = 1; spec.n_first = 0;
+  if (a->table) {
+    if (a->table_dtype != T5B_F32 && a->table_dtype != T5B_F16 && a->table_dtype != T5B_BF16) return T5B_ERR_DTYPE;
+    const int st = make_bucket_spec(a->num_buckets, a->max_distance, a->causal ? 0 : 1, &spec);
+    if (st != T5B_OK) return st;
+  }
+  if (!sm100_bwd_supports(*g)) return T5B_ERR_UNSUPPORTED;
+  return sm100_attention_bwd(*g, spec, (cudaStream_t)stream);
+}
+
 extern "C" int64_t t5b_attention_workspace_bytes(const t5b_attn_args* a) {
   if (!a || a->B <= 0 || a->H <= 0 || a->M <= 0 || a->N <= 0) return 0;
   if (a->kernel == T5B_KERNEL_SIMT || !sm100_supports(*a)) return 0;

@@ -1,0 +1,844 @@
+// Backward of the fused relative-position-bias attention for sm_100a (bf16/fp16, head dim 64).
+//
+// Three launches, as the reference's backward (src/turbot5/ops/fused_bias_attention.py:62-147):
+//
+//   bwd_delta_kernel      delta[row] = sum_d dO[row,d] * O[row,d]           (:398-437)
+//   attn_bwd_dq_kernel    one block per 128-row query tile, streaming 64-key tiles:
+//                           S = Q K^T, dP = dO V^T           (tcgen05.mma, both operands in shared memory)
+//                           P = exp2(S*scale + bias - lse),  dS = P o (dP - delta)   (softmax warps)
+//                           dQ += dS K                       (dS from tensor memory, K as MN-major operand)
+//                         and the gradient of the bias table: dtable[bucket(delta), h] += dS   (:635-820)
+//   attn_bwd_dkv_kernel   one block per 128-key tile, streaming 64-query tiles, everything transposed
+//                         so that the keys are the rows (TMEM lanes):
+//                           S^T = K Q^T, dP^T = V dO^T
+//                           P^T, dS^T written over S^T, dP^T in place (16-bit)
+//                           dV += P^T dO,  dK += dS^T Q                                  (:440-632)
+//
+// S and dP are recomputed in both kernels (7 matrix products per tile pair instead of 5): no
+// atomics on dQ, every output tile has one owner, results are deterministic except the few
+// atomics on the small bias-table gradient.  Warp roles, barriers, bounded waits and the
+// shared-memory bias table are those of the forward kernel (attn_fwd_sm100.cu); the saved
+// log-sum-exp replaces the running maximum, so the softmax warps have no rendezvous at all.
+#include "t5b_common.cuh"
+#include "attn_params.cuh"
+#include "attn_sm100_util.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+
+namespace t5b {
+namespace sm100b {
+
+using sm100::make_tmap;
+using sm100::pack2;
+
+constexpr int BM = 128;            // rows of the tile a block owns (MMA M)
+constexpr int BT = 64;             // rows of a streamed tile
+constexpr int HD = 64;
+constexpr int STAGES = 2;
+constexpr int BIG_BYTES = BM * 128;     // [128 rows][64 dims] 16-bit, 128-byte swizzle
+constexpr int SMALL_BYTES = BT * 128;   // [64 rows][64 dims]
+constexpr int NUM_THREADS = 320;
+constexpr int WARP_TMA = 8, WARP_MMA = 9;
+constexpr int TMEM_COLS = 256;
+constexpr int LUT_PAD = BM + BT;
+constexpr int MAX_BUCKETS = 2 * kMaxBucketsPerSide;
+constexpr int SMEM_TILES = 2 * BIG_BYTES + 2 * STAGES * SMALL_BYTES;   // 64 KB in both kernels
+
+struct BwdExtra {
+  const void* dout;
+  int64_t do_stride_b, do_stride_h, do_stride_m;
+  void* dq; void* dk; void* dv;
+  float* dtable;
+  float* delta;
+  float sm_scale;
+};
+
+struct __align__(16) Control {
+  unsigned long long bars[24];
+  uint32_t tmem_base;
+  int abort_flag;
+  int work[6];
+  float vec[STAGES][2][BT];     // dkv kernel: lse (log2 domain) and delta of the streamed query tile
+  float hist[MAX_BUCKETS];      // dq kernel: bias-table gradient of this block
+};
+
+__host__ __device__ inline size_t smem_bytes(int lut_entries) {
+  // float bias per delta, float gradient per delta, int16 bucket per delta
+  return 1024 + SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 10;
+}
+
+// ---------------------------------------------------------------- delta = rowsum(dO o O)
+template <typename T>
+__global__ void bwd_delta_kernel(const AttnParams p, const BwdExtra e, long long n_rows) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long i = warp0; i < n_rows; i += n_warps) {
+    int64_t o_off, do_off;
+    if (p.cu_q == nullptr) {
+      const int m = (int)(i % p.M);
+      const long long bh = i / p.M;
+      const int h = (int)(bh % p.H), b = (int)(bh / p.H);
+      o_off = (int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + (int64_t)m * p.o_stride_m;
+      do_off = (int64_t)b * e.do_stride_b + (int64_t)h * e.do_stride_h + (int64_t)m * e.do_stride_m;
+    } else {
+      const int h = (int)(i % p.H);
+      const long long row = i / p.H;
+      o_off = (int64_t)h * p.o_stride_h + row * p.o_stride_m;
+      do_off = (int64_t)h * e.do_stride_h + row * e.do_stride_m;
+    }
+    const T* o = reinterpret_cast<const T*>(p.out) + o_off;
+    const T* d = reinterpret_cast<const T*>(e.dout) + do_off;
+    float s = to_float(o[lane]) * to_float(d[lane]) + to_float(o[lane + 32]) * to_float(d[lane + 32]);
+    #pragma unroll
+    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (lane == 0) e.delta[i] = s;      // same indexing as lse: (b,h,m) dense, (row,h) packed
+  }
+}
+
+// Sequence and tile of block `blk` in the concatenated per-sequence tile lists of `cu`
+// (ceil(len / tile) tiles each).  Called by one full warp; result valid in every lane.
+__device__ __forceinline__ bool find_seq_tile(const int32_t* cu, int B, int tile, int blk, int& seq, int& tile_in_seq) {
+  const int lane = threadIdx.x & 31;
+  int acc = 0;
+  for (int b0 = 0; b0 < B; b0 += 32) {
+    const int bb = b0 + lane;
+    int nt = 0;
+    if (bb < B) nt = (cu[bb + 1] - cu[bb] + tile - 1) / tile;
+    int incl = nt;
+    #pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int excl = acc + incl - nt;
+    const bool mine = blk >= excl && blk < excl + nt;
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (m) {
+      const int src = __ffs(m) - 1;
+      seq = b0 + src;
+      tile_in_seq = blk - __shfl_sync(0xffffffffu, excl, src);
+      return true;
+    }
+    acc += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  return false;
+}
+
+// lse (natural log) -> log2 domain; rows that saw no key (-inf) or lie outside the tensor
+// get +inf, so that their probabilities come out as exactly 0
+__device__ __forceinline__ float lse_to_log2(float lse, bool valid) {
+  return (valid && lse > -INFINITY) ? lse * kLog2e : INFINITY;
+}
+
+enum {
+  B_RES_FULL = 0,                    // the block's resident tiles (Q,dO | K,V)
+  B_A_FULL = 1,                      // [STAGES] streamed tile A (K | Q)
+  B_B_FULL = B_A_FULL + STAGES,      // [STAGES] streamed tile B (V | dO)
+  B_A_EMPTY = B_B_FULL + STAGES,
+  B_B_EMPTY = B_A_EMPTY + STAGES,
+  B_S_FULL = B_B_EMPTY + STAGES,
+  B_S_FREE,
+  B_P_FULL,
+  B_O_DONE,
+  B_NUM
+};
+static_assert(B_NUM <= 24, "barrier slots");
+
+// ======================================================================== dQ and dtable
+template <bool kBf16>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                   const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                   const __grid_constant__ AttnParams p, const __grid_constant__ BwdExtra e,
+                   const __grid_constant__ BucketSpec spec) {
+  constexpr int COL_S = 0, COL_DP = 64, COL_DS = 128, COL_DQ = 160;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t sQ = base, sDO = base + BIG_BYTES;
+  const uint32_t sK = base + 2 * BIG_BYTES, sV = sK + STAGES * SMALL_BYTES;
+  Control* ctl = reinterpret_cast<Control*>(smem + SMEM_TILES);
+  float* lut = reinterpret_cast<float*>(smem + SMEM_TILES + ((sizeof(Control) + 15) / 16) * 16);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- work item: as the forward kernel (query tile of a (batch, head) or packed sequence)
+  TileWork* shared_work = reinterpret_cast<TileWork*>(&ctl->work[0]);
+  TileWork w;
+  int h, batch_idx = 0;
+  if (p.cu_q == nullptr) {
+    const int tile_lin = (int)blockIdx.x;
+    const int tx = tile_lin % p.tiles_x;
+    const int hb = tile_lin / p.tiles_x;
+    h = hb % p.H;
+    batch_idx = hb / p.H;
+    w = dense_tile<BM>(p, tx, batch_idx);
+  } else {
+    h = blockIdx.y;
+    if (warp == 0) {
+      TileWork f = find_varlen_tile<BM>(p, (int)blockIdx.x);
+      if (lane == 0) *shared_work = f;
+    }
+    __syncthreads();
+    w = *shared_work;
+    if (w.b < 0) return;
+  }
+  const int b = w.b, q_row0 = w.q_row0, rows_in_tile = w.rows_in_tile;
+  const int k_row0 = w.k_row0, len_k = w.len_k, qpos0 = w.qpos0;
+  int kv_end = len_k;
+  if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
+  const int n_kv = kv_end > 0 ? (kv_end + BT - 1) / BT : 0;
+
+  const uint32_t bar0 = smem_u32(&ctl->bars[0]);
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  if (tid == 0) {
+    ctl->abort_flag = 0;
+    mbar_init(bar(B_RES_FULL), 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar(B_A_FULL + s), 1);
+      mbar_init(bar(B_B_FULL + s), 1);
+      mbar_init(bar(B_A_EMPTY + s), 1);
+      mbar_init(bar(B_B_EMPTY + s), 1);
+    }
+    mbar_init(bar(B_S_FULL), 1);
+    mbar_init(bar(B_S_FREE), 8);
+    mbar_init(bar(B_P_FULL), 8);
+    mbar_init(bar(B_O_DONE), 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == WARP_TMA && lane == 0) {
+    tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == WARP_MMA) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  // delta -> bias (log2 domain) and delta -> bucket for this head
+  const int md = spec.max_distance;
+  const int lut_n = 2 * md + 1 + 2 * LUT_PAD;
+  // gradient per delta: element (row r, column c) of a tile adds to entry (c - r + const), so
+  // the 32 lanes of a warp instruction hit 32 consecutive words: conflict-free shared atomics.
+  // Folded into buckets once, at the end of the block.
+  float* dlut = lut + lut_n;
+  int16_t* lutb = reinterpret_cast<int16_t*>(dlut + lut_n);
+  const bool has_bias = p.table != nullptr;
+  if (has_bias) {
+    for (int i = tid; i < lut_n; i += NUM_THREADS) {
+      const int bucket = bucket_of_delta(spec, i - md - LUT_PAD);
+      lut[i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
+      dlut[i] = 0.f;
+      lutb[i] = (int16_t)bucket;
+    }
+    for (int i = tid; i < MAX_BUCKETS; i += NUM_THREADS) ctl->hist[i] = 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+  int fail_code = 0;
+
+  if (warp == WARP_TMA) {
+    if (lane == 0 && n_kv > 0) {
+      mbar_expect_tx(bar(B_RES_FULL), 2 * BIG_BYTES);
+      tma_load_4d(sQ, &tmap_q, bar(B_RES_FULL), 0, q_row0, h, b);
+      tma_load_4d(sDO, &tmap_do, bar(B_RES_FULL), 0, q_row0, h, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int s = j % STAGES;
+        const uint32_t ph = (uint32_t)((j / STAGES) & 1);
+        if (j >= STAGES && !mbar_wait_bounded(bar(B_A_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
+        mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
+        tma_load_4d(sK + s * SMALL_BYTES, &tmap_k, bar(B_A_FULL + s), 0, k_row0 + j * BT, h, b);
+        if (j >= STAGES && !mbar_wait_bounded(bar(B_B_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
+        mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
+        tma_load_4d(sV + s * SMALL_BYTES, &tmap_v, bar(B_B_FULL + s), 0, k_row0 + j * BT, h, b);
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t IDESC_SS = make_idesc_f16(kBf16, kBf16, BM, BT, false, false);   // 128 x 64 keys
+      constexpr uint32_t IDESC_DQ = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);    // K as MN-major B
+      const uint64_t dq_ = make_smem_desc_sw128(sQ, 16, 1024);
+      const uint64_t ddo = make_smem_desc_sw128(sDO, 16, 1024);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j % STAGES;
+        const uint32_t ph = (uint32_t)((j / STAGES) & 1);
+        if (!mbar_wait_bounded(bar(B_A_FULL + s), ph, abort_flag)) return false;
+        if (!mbar_wait_bounded(bar(B_B_FULL + s), ph, abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t dk = make_smem_desc_sw128(sK + s * SMALL_BYTES, 16, 1024);
+        const uint64_t dv = make_smem_desc_sw128(sV + s * SMALL_BYTES, 16, 1024);
+        #pragma unroll
+        for (int k = 0; k < HD / 16; ++k) umma_ss(tmem + COL_S, dq_ + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), IDESC_SS, k > 0);
+        #pragma unroll
+        for (int k = 0; k < HD / 16; ++k) umma_ss(tmem + COL_DP, ddo + (uint64_t)(2 * k), dv + (uint64_t)(2 * k), IDESC_SS, k > 0);
+        tc_commit(bar(B_S_FULL));
+        tc_commit(bar(B_B_EMPTY + s));      // V is not needed again
+        return true;
+      };
+      bool ok = mbar_wait_bounded(bar(B_RES_FULL), 0, abort_flag);
+      if (!ok) fail_code = 20;
+      if (ok && !issue_s(0)) { ok = false; fail_code = 21; }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        if (j + 1 < n_kv) {
+          if (!mbar_wait_bounded(bar(B_S_FREE), (uint32_t)(j & 1), abort_flag)) { fail_code = 25; break; }
+          tc_fence_after();
+          if (!issue_s(j + 1)) { fail_code = 23; break; }
+        }
+        if (!mbar_wait_bounded(bar(B_P_FULL), (uint32_t)(j & 1), abort_flag)) { fail_code = 22; break; }
+        tc_fence_after();
+        const int s = j % STAGES;
+        // dQ += dS K: the K tile [64 keys][64 dims] read as an MN-major B operand
+        #pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          const uint64_t dkm = make_smem_desc_sw128(sK + s * SMALL_BYTES + k * 2048, 16, 1024);
+          umma_ts(tmem + COL_DQ, tmem + COL_DS + k * 8, dkm, IDESC_DQ, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(B_O_DONE));
+        tc_commit(bar(B_A_EMPTY + s));
+      }
+    }
+  } else if (warp < 8) {
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + lane_base + COL_S + half * 32;
+    const uint32_t tDP = tmem + lane_base + COL_DP + half * 32;
+    const uint32_t tDS = tmem + lane_base + COL_DS + half * 16;
+    const uint32_t tDQ = tmem + lane_base + COL_DQ + half * 32;
+    const float scale = p.scale_log2;
+    const int qpos = qpos0 + r;
+    const bool row_ok = r < rows_in_tile;
+    const int64_t row = (int64_t)q_row0 + r;
+    const int64_t stat_idx = p.cu_q == nullptr ? ((int64_t)batch_idx * p.H + h) * p.M + row : row * p.H + h;
+    const float lse2 = lse_to_log2(row_ok ? p.lse[stat_idx] : 0.f, row_ok);
+    const float delta_r = row_ok ? e.delta[stat_idx] : 0.f;
+    // bias-table gradient of tiles that lie entirely beyond +-max_distance: one bucket each
+    float far_neg = 0.f, far_pos = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_kv; ++j) {
+      const int n0 = j * BT;
+      const int c0 = half * 32;
+      if (!mbar_wait_bounded_warp(bar(B_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
+      tc_fence_after();
+      uint32_t sv[32], dp[32];
+      tmem_ld_x32(tS, sv);
+      tmem_ld_x32(tDP, dp);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_S_FREE));
+
+      const bool need_mask = (n0 + BT > len_k) || (p.causal && (n0 + BT - 1 > qpos0));
+      int bias_mode = 0;
+      float bias_const = 0.f;
+      if (has_bias) {
+        const int dmin = n0 - (qpos0 + BM - 1), dmax = n0 + BT - 1 - qpos0;
+        if (dmin >= md) { bias_mode = 1; bias_const = lut[2 * md + LUT_PAD]; }
+        else if (dmax <= -md) { bias_mode = 3; bias_const = lut[LUT_PAD]; }
+        else bias_mode = 2;
+      }
+      const int lut0 = n0 + c0 - qpos + md + LUT_PAD;      // table index of column 0 of this thread
+      const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;
+      uint32_t pk[16];
+      float ds_sum = 0.f;
+      #pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float dsv[2];
+        #pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int c = 2 * i + u;
+          const float bias = bias_mode == 2 ? lut[lut0 + c] : bias_const;
+          float x = fmaf(__uint_as_float(sv[c]), scale, bias) - lse2;
+          if (need_mask && c >= n_valid) x = -INFINITY;
+          const float pr = fast_exp2(x);
+          const float d = pr * (__uint_as_float(dp[c]) - delta_r);
+          dsv[u] = d;
+          if (bias_mode == 2) atomicAdd(&dlut[lut0 + c], d);
+          else ds_sum += d;
+        }
+        pk[i] = pack2<kBf16>(dsv[0], dsv[1]);
+      }
+      if (bias_mode == 1) far_pos += ds_sum;
+      if (bias_mode == 3) far_neg += ds_sum;
+      if (j > 0) {
+        if (!mbar_wait_bounded_warp(bar(B_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
+        tc_fence_after();
+      }
+      tmem_st_x16(tDS, pk);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_P_FULL));
+    }
+
+    if (ok && n_kv > 0) {
+      if (!mbar_wait_bounded_warp(bar(B_O_DONE), (uint32_t)((n_kv - 1) & 1), abort_flag)) { ok = false; fail_code = 32; }
+      tc_fence_after();
+    }
+    if (ok) {          // warp-uniform: tcgen05.ld is a whole-warp instruction; only the stores depend on the row
+      uint32_t v[32];
+      if (n_kv > 0) {
+        tmem_ld_x32(tDQ, v);
+        tmem_ld_wait();
+      } else {
+        #pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      uint8_t* drow = reinterpret_cast<uint8_t*>(e.dq) + half * 64 +
+                      2 * ((int64_t)b * p.q_stride_b + (int64_t)h * p.q_stride_h + row * p.q_stride_m);
+      const float sc = e.sm_scale;
+      #pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 w4;
+        w4.x = pack2<kBf16>(__uint_as_float(v[8 * i + 0]) * sc, __uint_as_float(v[8 * i + 1]) * sc);
+        w4.y = pack2<kBf16>(__uint_as_float(v[8 * i + 2]) * sc, __uint_as_float(v[8 * i + 3]) * sc);
+        w4.z = pack2<kBf16>(__uint_as_float(v[8 * i + 4]) * sc, __uint_as_float(v[8 * i + 5]) * sc);
+        w4.w = pack2<kBf16>(__uint_as_float(v[8 * i + 6]) * sc, __uint_as_float(v[8 * i + 7]) * sc);
+        if (row_ok) *reinterpret_cast<uint4*>(drow + i * 16) = w4;
+      }
+    }
+    if (has_bias) {
+      #pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        far_pos += __shfl_xor_sync(0xffffffffu, far_pos, off);
+        far_neg += __shfl_xor_sync(0xffffffffu, far_neg, off);
+      }
+      if (lane == 0) {
+        if (far_pos != 0.f) atomicAdd(&ctl->hist[lutb[2 * md + LUT_PAD]], far_pos);
+        if (far_neg != 0.f) atomicAdd(&ctl->hist[lutb[LUT_PAD]], far_neg);
+      }
+    }
+  }
+
+  if (fail_code != 0 && p.status != nullptr) atomicCAS(p.status, 0, 2000 + fail_code);
+  tc_fence_before();
+  __syncthreads();
+  if (has_bias && e.dtable != nullptr) {
+    for (int i = tid; i < lut_n; i += NUM_THREADS) {
+      const float g = dlut[i];
+      if (g != 0.f) atomicAdd(&ctl->hist[lutb[i]], g);
+    }
+    __syncthreads();
+    const int nb = spec.bidirectional ? 2 * spec.n_side : spec.n_side;
+    for (int i = tid; i < nb; i += NUM_THREADS) {
+      const float g = ctl->hist[i];
+      if (g != 0.f) atomicAdd(&e.dtable[(int64_t)i * p.H + h], g);
+    }
+  }
+  if (warp == WARP_MMA) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ======================================================================== dK and dV
+template <bool kBf16>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                    const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                    const __grid_constant__ AttnParams p, const __grid_constant__ BwdExtra e,
+                    const __grid_constant__ BucketSpec spec) {
+  // tensor memory: S^T and dP^T (64 fp32 columns each, keys in the lanes); P^T and dS^T are
+  // written over them in place: the 32 query columns of row half q sit, packed, in the first
+  // 16 columns of that half's own 32 (a K=16 step of the second MMA takes any column address)
+  constexpr int COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 192;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t sK = base, sV = base + BIG_BYTES;
+  const uint32_t sQ = base + 2 * BIG_BYTES, sDO = sQ + STAGES * SMALL_BYTES;
+  Control* ctl = reinterpret_cast<Control*>(smem + SMEM_TILES);
+  float* lut = reinterpret_cast<float*>(smem + SMEM_TILES + ((sizeof(Control) + 15) / 16) * 16);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- work item: a 128-key tile of one (batch, head) or packed sequence
+  int h, b = 0, batch_idx = 0;
+  int key0;            // first key of the tile inside its sequence
+  int k_row0 = 0, len_k, q_row0 = 0, len_q, q_off;
+  if (p.cu_k == nullptr) {
+    const int tiles_k = (p.N + BM - 1) / BM;
+    const int tile_lin = (int)blockIdx.x;
+    const int tx = tile_lin % tiles_k;
+    const int hb = tile_lin / tiles_k;
+    h = hb % p.H;
+    batch_idx = b = hb / p.H;
+    key0 = tx * BM;
+    len_k = p.N; len_q = p.M; q_off = p.q_pos_offset;
+  } else {
+    h = blockIdx.y;
+    if (warp == 0) {
+      int seq = -1, t = 0;
+      const bool found = find_seq_tile(p.cu_k, p.B, BM, (int)blockIdx.x, seq, t);
+      if (lane == 0) { ctl->work[0] = found ? seq : -1; ctl->work[1] = t; }
+    }
+    __syncthreads();
+    const int seq = ctl->work[0];
+    if (seq < 0) return;
+    key0 = ctl->work[1] * BM;
+    k_row0 = p.cu_k[seq]; len_k = p.cu_k[seq + 1] - k_row0;
+    q_row0 = p.cu_q[seq]; len_q = p.cu_q[seq + 1] - q_row0;
+    q_off = len_k - len_q;
+  }
+  const int keys_in_tile = min(BM, len_k - key0);
+  // query tiles that can see a key of this tile: causal keeps q_off + m >= key
+  int i_first = 0;
+  if (p.causal) i_first = max(0, key0 - q_off) / BT;
+  const int n_qt_all = (len_q + BT - 1) / BT;
+  const int n_qt = max(0, n_qt_all - i_first);
+
+  const uint32_t bar0 = smem_u32(&ctl->bars[0]);
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  if (tid == 0) {
+    ctl->abort_flag = 0;
+    mbar_init(bar(B_RES_FULL), 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar(B_A_FULL + s), 2);       // TMA transaction + the lse/delta vectors written by the producer warp
+      mbar_init(bar(B_B_FULL + s), 1);
+      mbar_init(bar(B_A_EMPTY + s), 1);
+      mbar_init(bar(B_B_EMPTY + s), 1);
+    }
+    mbar_init(bar(B_S_FULL), 1);
+    mbar_init(bar(B_P_FULL), 8);
+    mbar_init(bar(B_O_DONE), 1);
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == WARP_TMA && lane == 0) {
+    tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == WARP_MMA) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  const int md = spec.max_distance;
+  const int lut_n = 2 * md + 1 + 2 * LUT_PAD;
+  const bool has_bias = p.table != nullptr;
+  if (has_bias) {
+    for (int i = tid; i < lut_n; i += NUM_THREADS) {
+      const int bucket = bucket_of_delta(spec, i - md - LUT_PAD);
+      lut[i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+  int fail_code = 0;
+
+  if (warp == WARP_TMA) {
+    // whole warp: lane 0 drives the TMA, all lanes fetch the lse / delta of the query tile
+    if (n_qt > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(bar(B_RES_FULL), 2 * BIG_BYTES);
+        tma_load_4d(sK, &tmap_k, bar(B_RES_FULL), 0, k_row0 + key0, h, b);
+        tma_load_4d(sV, &tmap_v, bar(B_RES_FULL), 0, k_row0 + key0, h, b);
+      }
+      bool okp = true;
+      for (int i = 0; i < n_qt; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)((i / STAGES) & 1);
+        const int m0 = (i_first + i) * BT;
+        if (i >= STAGES) {
+          // every lane waits: the vectors of this stage are rewritten below
+          if (!mbar_wait_bounded(bar(B_A_EMPTY + s), ph ^ 1u, abort_flag)) { okp = false; }
+          if (okp && !mbar_wait_bounded(bar(B_B_EMPTY + s), ph ^ 1u, abort_flag)) { okp = false; }
+          if (!__all_sync(0xffffffffu, okp)) { fail_code = 10; break; }
+        }
+        if (lane == 0) {
+          mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
+          tma_load_4d(sQ + s * SMALL_BYTES, &tmap_q, bar(B_A_FULL + s), 0, q_row0 + m0, h, b);
+          mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
+          tma_load_4d(sDO + s * SMALL_BYTES, &tmap_do, bar(B_B_FULL + s), 0, q_row0 + m0, h, b);
+        }
+        #pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int c = lane + 32 * u;
+          const int m = m0 + c;
+          const bool valid = m < len_q;
+          const int64_t idx = p.cu_q == nullptr ? ((int64_t)batch_idx * p.H + h) * p.M + m
+                                                : ((int64_t)q_row0 + m) * p.H + h;
+          ctl->vec[s][0][c] = lse_to_log2(valid ? p.lse[idx] : 0.f, valid);
+          ctl->vec[s][1][c] = valid ? e.delta[idx] : 0.f;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_A_FULL + s));
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    if (lane == 0 && n_qt > 0) {
+      constexpr uint32_t IDESC_SS = make_idesc_f16(kBf16, kBf16, BM, BT, false, false);   // 128 keys x 64 queries
+      constexpr uint32_t IDESC_TS = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);    // dO / Q as MN-major B
+      const uint64_t dk = make_smem_desc_sw128(sK, 16, 1024);
+      const uint64_t dv = make_smem_desc_sw128(sV, 16, 1024);
+      auto issue_s = [&](int i) -> bool {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)((i / STAGES) & 1);
+        if (!mbar_wait_bounded(bar(B_A_FULL + s), ph, abort_flag)) return false;
+        if (!mbar_wait_bounded(bar(B_B_FULL + s), ph, abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t dq_ = make_smem_desc_sw128(sQ + s * SMALL_BYTES, 16, 1024);
+        const uint64_t ddo = make_smem_desc_sw128(sDO + s * SMALL_BYTES, 16, 1024);
+        #pragma unroll
+        for (int k = 0; k < HD / 16; ++k) umma_ss(tmem + COL_ST, dk + (uint64_t)(2 * k), dq_ + (uint64_t)(2 * k), IDESC_SS, k > 0);
+        #pragma unroll
+        for (int k = 0; k < HD / 16; ++k) umma_ss(tmem + COL_DPT, dv + (uint64_t)(2 * k), ddo + (uint64_t)(2 * k), IDESC_SS, k > 0);
+        tc_commit(bar(B_S_FULL));
+        return true;
+      };
+      bool ok = mbar_wait_bounded(bar(B_RES_FULL), 0, abort_flag);
+      if (!ok) fail_code = 20;
+      if (ok && !issue_s(0)) { ok = false; fail_code = 21; }
+      for (int i = 0; ok && i < n_qt; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait_bounded(bar(B_P_FULL), (uint32_t)(i & 1), abort_flag)) { fail_code = 22; break; }
+        tc_fence_after();
+        #pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {       // 16 queries per step
+          const uint32_t a_off = (uint32_t)(k < 2 ? 8 * k : 32 + 8 * (k - 2));
+          const uint64_t ddo = make_smem_desc_sw128(sDO + s * SMALL_BYTES + k * 2048, 16, 1024);
+          umma_ts(tmem + COL_DV, tmem + COL_ST + a_off, ddo, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(B_B_EMPTY + s));
+        #pragma unroll
+        for (int k = 0; k < BT / 16; ++k) {
+          const uint32_t a_off = (uint32_t)(k < 2 ? 8 * k : 32 + 8 * (k - 2));
+          const uint64_t dq_ = make_smem_desc_sw128(sQ + s * SMALL_BYTES + k * 2048, 16, 1024);
+          umma_ts(tmem + COL_DK, tmem + COL_DPT + a_off, dq_, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(B_A_EMPTY + s));
+        if (i + 1 < n_qt) {
+          // the tensor core runs MMAs in issue order: S^T / dP^T may be overwritten once the
+          // products that read P^T / dS^T from the same columns are queued
+          if (!issue_s(i + 1)) { fail_code = 23; break; }
+        } else {
+          tc_commit(bar(B_O_DONE));
+        }
+      }
+    }
+  } else if (warp < 8) {
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;               // key row inside the tile
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tST = tmem + lane_base + COL_ST + half * 32;
+    const uint32_t tDPT = tmem + lane_base + COL_DPT + half * 32;
+    const float scale = p.scale_log2;
+    const int key = key0 + r;
+    const bool key_ok = r < keys_in_tile;
+    bool ok = true;
+
+    for (int i = 0; i < n_qt; ++i) {
+      const int s = i % STAGES;
+      const int m0 = (i_first + i) * BT + half * 32;     // first query of this thread's columns
+      if (!mbar_wait_bounded_warp(bar(B_S_FULL), (uint32_t)(i & 1), abort_flag)) { ok = false; fail_code = 30; break; }
+      tc_fence_after();
+      uint32_t sv[32], dp[32];
+      tmem_ld_x32(tST, sv);
+      tmem_ld_x32(tDPT, dp);
+      // the lse / delta vectors of this stage were published on the same barrier as the Q tile
+      // (long complete: the matrix products above needed it); observing it here orders the reads
+      if (!mbar_wait_bounded_warp(bar(B_A_FULL + s), (uint32_t)((i / STAGES) & 1), abort_flag)) { ok = false; fail_code = 33; break; }
+      tmem_ld_wait();
+
+      const int qp0 = q_off + m0;                        // key-coordinate position of column 0
+      // column c has delta = key - (qp0 + c): table index falls as c grows
+      const int lut0 = key - qp0 + md + LUT_PAD;
+      int bias_mode = 0;
+      float bias_const = 0.f;
+      if (has_bias) {
+        const int dmin = key0 - (q_off + (i_first + i) * BT + BT - 1), dmax = key0 + BM - 1 - (q_off + (i_first + i) * BT);
+        if (dmin >= md) { bias_mode = 1; bias_const = lut[2 * md + LUT_PAD]; }
+        else if (dmax <= -md) { bias_mode = 1; bias_const = lut[LUT_PAD]; }
+        else bias_mode = 2;
+      }
+      const float* vl = &ctl->vec[s][0][half * 32];
+      const float* vd = &ctl->vec[s][1][half * 32];
+      uint32_t pp[16], pd[16];
+      #pragma unroll
+      for (int ii = 0; ii < 16; ++ii) {
+        float pv[2], dv2[2];
+        #pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int c = 2 * ii + u;
+          const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
+          float x = fmaf(__uint_as_float(sv[c]), scale, bias) - vl[c];
+          // masked: key outside the sequence, or (causal) after the query
+          if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
+          const float pr = fast_exp2(x);
+          pv[u] = pr;
+          dv2[u] = pr * (__uint_as_float(dp[c]) - vd[c]);
+        }
+        pp[ii] = pack2<kBf16>(pv[0], pv[1]);
+        pd[ii] = pack2<kBf16>(dv2[0], dv2[1]);
+      }
+      tmem_st_x16(tST, pp);
+      tmem_st_x16(tDPT, pd);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_P_FULL));
+    }
+
+    if (ok && n_qt > 0) {
+      if (!mbar_wait_bounded_warp(bar(B_O_DONE), 0, abort_flag)) { ok = false; fail_code = 32; }
+      tc_fence_after();
+    }
+    if (ok) {          // warp-uniform (see the dQ kernel); only the stores depend on the key row
+      const int64_t krow = (int64_t)k_row0 + key;
+      uint8_t* dvrow = reinterpret_cast<uint8_t*>(e.dv) + half * 64 +
+                       2 * ((int64_t)b * p.v_stride_b + (int64_t)h * p.v_stride_h + krow * p.v_stride_n);
+      uint8_t* dkrow = reinterpret_cast<uint8_t*>(e.dk) + half * 64 +
+                       2 * ((int64_t)b * p.k_stride_b + (int64_t)h * p.k_stride_h + krow * p.k_stride_n);
+      #pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        uint32_t v[32];
+        if (n_qt > 0) {
+          tmem_ld_x32(tmem + lane_base + (t == 0 ? COL_DV : COL_DK) + half * 32, v);
+          tmem_ld_wait();
+        } else {
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        const float sc = t == 0 ? 1.f : e.sm_scale;
+        uint8_t* dst = t == 0 ? dvrow : dkrow;
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 w4;
+          w4.x = pack2<kBf16>(__uint_as_float(v[8 * i + 0]) * sc, __uint_as_float(v[8 * i + 1]) * sc);
+          w4.y = pack2<kBf16>(__uint_as_float(v[8 * i + 2]) * sc, __uint_as_float(v[8 * i + 3]) * sc);
+          w4.z = pack2<kBf16>(__uint_as_float(v[8 * i + 4]) * sc, __uint_as_float(v[8 * i + 5]) * sc);
+          w4.w = pack2<kBf16>(__uint_as_float(v[8 * i + 6]) * sc, __uint_as_float(v[8 * i + 7]) * sc);
+          if (key_ok) *reinterpret_cast<uint4*>(dst + i * 16) = w4;
+        }
+      }
+    }
+  }
+
+  if (fail_code != 0 && p.status != nullptr) atomicCAS(p.status, 0, 3000 + fail_code);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+}  // namespace sm100b
+
+// True when the tensor-core backward can take this problem.
+bool sm100_bwd_supports(const t5b_attn_bwd_args& g) {
+  const t5b_attn_args& a = g.fwd;
+  if (!sm100_supports(a) || a.D != 64) return false;
+  auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  if (!al16(g.dout) || !al16(g.dq) || !al16(g.dk) || !al16(g.dv)) return false;
+  const int64_t s[] = {g.do_stride_b, g.do_stride_h, g.do_stride_m};
+  for (int64_t x : s) if (x < 0 || (x % 8) != 0) return false;
+  return true;
+}
+
+int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cudaStream_t stream) {
+  using namespace sm100b;
+  const t5b_attn_args& a = g.fwd;
+  const bool varlen = a.cu_seqlens_q != nullptr;
+  const bool bf16 = a.dtype == T5B_BF16;
+  AttnParams p = make_attn_params(a);
+  p.tiles_x = (a.M + BM - 1) / BM;
+  BwdExtra e;
+  e.dout = g.dout;
+  e.do_stride_b = g.do_stride_b; e.do_stride_h = g.do_stride_h; e.do_stride_m = g.do_stride_m;
+  e.dq = g.dq; e.dk = g.dk; e.dv = g.dv;
+  e.dtable = g.dtable; e.delta = g.delta; e.sm_scale = a.sm_scale;
+
+  const long long rows_q = varlen ? (long long)a.total_q : (long long)a.B * a.M;
+  const long long rows_k = varlen ? (long long)a.total_k : (long long)a.B * a.N;
+  // 1. delta
+  {
+    const long long n_rows = rows_q * a.H;
+    long long blocks = (n_rows + 7) / 8;
+    if (blocks > 148LL * 16) blocks = 148LL * 16;
+    if (blocks > 0) {
+      if (bf16) bwd_delta_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(p, e, n_rows);
+      else bwd_delta_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(p, e, n_rows);
+      if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
+    }
+  }
+  const bool dbg = getenv("T5B_BWD_DEBUG") != nullptr;
+  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
+  if (dbg) { for (auto& x : ev) cudaEventCreate(&x); cudaEventRecord(ev[0], stream); }
+  (void)rows_k;   // > 0: checked by the caller
+  int st;
+  CUtensorMap q128, do128, k64, v64, k128, v128, q64, do64;
+  const int64_t Mr = varlen ? a.total_q : a.M, Nr = varlen ? a.total_k : a.N;
+  const int Bm = varlen ? 1 : a.B;
+  const int64_t qsb = varlen ? 0 : a.q_stride_b, ksb = varlen ? 0 : a.k_stride_b, vsb = varlen ? 0 : a.v_stride_b;
+  const int64_t dsb = varlen ? 0 : g.do_stride_b;
+  if ((st = make_tmap(&q128, a.q, bf16, HD, BM, Mr, a.H, Bm, a.q_stride_m, a.q_stride_h, qsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&do128, g.dout, bf16, HD, BM, Mr, a.H, Bm, g.do_stride_m, g.do_stride_h, dsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&k64, a.k, bf16, HD, BT, Nr, a.H, Bm, a.k_stride_n, a.k_stride_h, ksb)) != T5B_OK) return st;
+  if ((st = make_tmap(&v64, a.v, bf16, HD, BT, Nr, a.H, Bm, a.v_stride_n, a.v_stride_h, vsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&k128, a.k, bf16, HD, BM, Nr, a.H, Bm, a.k_stride_n, a.k_stride_h, ksb)) != T5B_OK) return st;
+  if ((st = make_tmap(&v128, a.v, bf16, HD, BM, Nr, a.H, Bm, a.v_stride_n, a.v_stride_h, vsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&q64, a.q, bf16, HD, BT, Mr, a.H, Bm, a.q_stride_m, a.q_stride_h, qsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&do64, g.dout, bf16, HD, BT, Mr, a.H, Bm, g.do_stride_m, g.do_stride_h, dsb)) != T5B_OK) return st;
+
+  const int lut_n = a.table ? 2 * spec.max_distance + 1 + 2 * LUT_PAD : 0;
+  const size_t smem = smem_bytes(lut_n);
+  auto kq = bf16 ? attn_bwd_dq_kernel<true> : attn_bwd_dq_kernel<false>;
+  auto kkv = bf16 ? attn_bwd_dkv_kernel<true> : attn_bwd_dkv_kernel<false>;
+  static bool attr_set[64][2] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int which = bf16 ? 1 : 0;
+  if (dev < 0 || dev >= 64 || !attr_set[dev][which]) {
+    const int smem_max = (int)smem_bytes(2 * 2048 + 1 + 2 * LUT_PAD);
+    if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) != cudaSuccess ||
+        cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) != cudaSuccess) {
+      cudaGetLastError();
+      return T5B_ERR_LAUNCH;
+    }
+    if (dev >= 0 && dev < 64) attr_set[dev][which] = true;
+  }
+  dim3 gq, gk;
+  if (varlen) {
+    gq = dim3((unsigned)((long long)a.total_q / BM + a.B), (unsigned)a.H, 1);
+    gk = dim3((unsigned)((long long)a.total_k / BM + a.B), (unsigned)a.H, 1);
+  } else {
+    const long long nq = (long long)p.tiles_x * a.H * a.B;
+    const long long nk = (long long)((a.N + BM - 1) / BM) * a.H * a.B;
+    if (nq > 0x7fffffffLL || nk > 0x7fffffffLL) return T5B_ERR_SHAPE;
+    gq = dim3((unsigned)nq, 1, 1);
+    gk = dim3((unsigned)nk, 1, 1);
+  }
+  if (gq.y > 65535 || gk.y > 65535) return T5B_ERR_SHAPE;
+  if (gq.x > 0) {
+    kq<<<gq, NUM_THREADS, smem, stream>>>(q128, do128, k64, v64, p, e, spec);
+    if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
+    if (dbg) cudaEventRecord(ev[1], stream);
+  }
+  if (gk.x > 0) {
+    kkv<<<gk, NUM_THREADS, smem, stream>>>(k128, v128, q64, do64, p, e, spec);
+    if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
+    if (dbg) {
+      cudaEventRecord(ev[2], stream);
+      cudaEventSynchronize(ev[2]);
+      float t_dq = 0.f, t_dkv = 0.f;
+      cudaEventElapsedTime(&t_dq, ev[0], ev[1]);
+      cudaEventElapsedTime(&t_dkv, ev[1], ev[2]);
+      fprintf(stderr, "[bwd] dq %.3f ms, dkv %.3f ms\n", t_dq, t_dkv);
+      for (auto& x : ev) cudaEventDestroy(x);
+    }
+  }
+  return T5B_OK;
+}
+
+}  // namespace t5b

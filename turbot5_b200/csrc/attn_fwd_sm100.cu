@@ -34,8 +34,7 @@
 // reference's `basic` path: delta = n - (q_pos_offset + m).
 #include "t5b_common.cuh"
 #include "attn_params.cuh"
-
-#include <cuda.h>
+#include "attn_sm100_util.cuh"
 
 namespace t5b {
 
@@ -98,17 +97,6 @@ __host__ __device__ inline size_t smem_bytes(int lut_entries) {
   return 1024 /*alignment slack*/ + Geo<HD>::SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 4;
 }
 
-
-template <bool kBf16>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  if (kBf16) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-  } else {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-}
 
 // 2^-k for a non-negative whole number k held in a float (0 once it leaves the normal range).
 __device__ __forceinline__ float pow2_neg(float k) {
@@ -345,7 +333,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     auto pair_sync = [&]() -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(pair_bar);
-      const bool done = mbar_wait_bounded(pair_bar, pair_uses & 1u, abort_flag);
+      const bool done = mbar_wait_bounded_warp(pair_bar, pair_uses & 1u, abort_flag);
       ++pair_uses;
       return done;
     };
@@ -356,7 +344,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (int j = 0; j < n_kv; ++j) {
       const int n0 = (kv_first + j) * BN;          // first key of the tile
       const int c0 = half * NH;                    // first column of this thread inside the tile
-      if (!mbar_wait_bounded(bar(BAR_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
+      if (!mbar_wait_bounded_warp(bar(BAR_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
 
       // this thread's scores -> registers, then give the S buffer back to the MMA warp
@@ -472,12 +460,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // ---- partner's step; rescale O, l and (if the steps differ) this tile's P.  Rare.
       bool o_done_seen = (j == 0);
       if (j > 0) {
-        const bool met = mbar_wait_bounded(pair_bar, pair_uses & 1u, abort_flag);
+        const bool met = mbar_wait_bounded_warp(pair_bar, pair_uses & 1u, abort_flag);
         ++pair_uses;
         if (!met) { ok = false; fail_code = 33; break; }
         const float k_max = fmaxf(k_me, ctl->xchg[j & 1][half ^ 1][r]);
         if (__any_sync(0xffffffffu, k_max > 0.f)) {
-          if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
+          if (!mbar_wait_bounded_warp(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
           tc_fence_after();
           o_done_seen = true;
           const float alpha = pow2_neg(k_max);
@@ -504,7 +492,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       l_sum += t_sum;
       if (!o_done_seen) {
-        if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
+        if (!mbar_wait_bounded_warp(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
         tc_fence_after();
       }
       #pragma unroll
@@ -517,7 +505,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
     // ---- epilogue: O / l -> global (each thread its 32 output columns)
     if (ok && n_kv > 0) {
-      if (!mbar_wait_bounded(bar(BAR_O_DONE), (uint32_t)((n_kv - 1) & 1), abort_flag)) { ok = false; fail_code = 32; }
+      if (!mbar_wait_bounded_warp(bar(BAR_O_DONE), (uint32_t)((n_kv - 1) & 1), abort_flag)) { ok = false; fail_code = 32; }
       tc_fence_after();
     }
     // total row sum = this half + the other half (slot parity distinct from the last tile's maxima)
@@ -618,42 +606,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess) return nullptr;
-    if (qres != cudaDriverEntryPointSuccess) return nullptr;
-    return (EncodeTiledFn)p;
-  }();
-  return fn;
-}
-
-// (D, rows, H, B) view with element strides; box = one [box_rows][64 dims] sub-tile.
-static int make_tmap(CUtensorMap* map, const void* ptr, bool bf16, int HD, int box_rows, int64_t rows, int H, int B,
-                     int64_t stride_row, int64_t stride_h, int64_t stride_b) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return T5B_ERR_DRIVER;
-  cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)rows, (cuuint64_t)H, (cuuint64_t)B};
-  cuuint64_t strides[3] = {(cuuint64_t)stride_row * 2, (cuuint64_t)stride_h * 2,
-                           (cuuint64_t)(B > 1 ? stride_b : (int64_t)HD) * 2};
-  // unit dims may carry any stride in the caller's tensor; give them a legal one
-  if (H == 1) strides[1] = (cuuint64_t)HD * 2;
-  if (rows == 1) strides[0] = (cuuint64_t)HD * 2;
-  cuuint32_t box[4] = {64u, (cuuint32_t)box_rows, 1, 1};
-  cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                   const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? T5B_OK : T5B_ERR_DRIVER;
-}
-
 }  // namespace sm100
 
 // True when the tcgen05 kernel can take this problem.

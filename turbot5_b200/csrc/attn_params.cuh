@@ -130,5 +130,7 @@ __device__ __forceinline__ TileWork dense_tile(const AttnParams& p, int blk_x, i
 bool sm100_supports(const t5b_attn_args& a);
 int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream);
 int simt_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream);
+bool sm100_bwd_supports(const t5b_attn_bwd_args& g);
+int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cudaStream_t stream);
 
 }  // namespace t5b

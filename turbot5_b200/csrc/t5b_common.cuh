@@ -118,6 +118,14 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// The same for a whole converged warp: every lane gets the same answer, so a warp that gives up
+// leaves its loop together (a later __syncwarp or warp vote must never wait for lanes that
+// already left).
+__device__ __forceinline__ bool mbar_wait_bounded_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  const bool done = mbar_wait_bounded(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, done);
+}
+
 // 4-D tiled TMA load, global -> shared, completion on an mbarrier (no multicast).
 __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
