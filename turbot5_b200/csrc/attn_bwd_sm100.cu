@@ -35,7 +35,7 @@ using sm100::pack2;
 constexpr int BM = 128;            // rows of the tile a block owns (MMA M)
 constexpr int BT = 64;             // rows of a streamed tile
 constexpr int HD = 64;
-constexpr int STAGES = 2;
+constexpr int STAGES = 3;            // the streamed tiles stay resident until the LAST product of their step
 constexpr int BIG_BYTES = BM * 128;     // [128 rows][64 dims] 16-bit, 128-byte swizzle
 constexpr int SMALL_BYTES = BT * 128;   // [64 rows][64 dims]
 constexpr int NUM_THREADS = 320;
@@ -43,7 +43,7 @@ constexpr int WARP_TMA = 8, WARP_MMA = 9;
 constexpr int TMEM_COLS = 256;
 constexpr int LUT_PAD = BM + BT;
 constexpr int MAX_BUCKETS = 2 * kMaxBucketsPerSide;
-constexpr int SMEM_TILES = 2 * BIG_BYTES + 2 * STAGES * SMALL_BYTES;   // 64 KB in both kernels
+constexpr int SMEM_TILES = 2 * BIG_BYTES + 2 * STAGES * SMALL_BYTES;   // 80 KB in both kernels
 
 struct BwdExtra {
   const void* dout;
@@ -348,22 +348,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;
       uint32_t pk[16];
       float ds_sum = 0.f;
-      #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float dsv[2];
+      if (!need_mask && bias_mode != 2) {
+        // whole tile visible, one bias value: two elements per instruction
+        const float add = bias_const - lse2, nd = -delta_r;
+        float a0 = 0.f, a1 = 0.f;
         #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int c = 2 * i + u;
-          const float bias = bias_mode == 2 ? lut[lut0 + c] : bias_const;
-          float x = fmaf(__uint_as_float(sv[c]), scale, bias) - lse2;
-          if (need_mask && c >= n_valid) x = -INFINITY;
-          const float pr = fast_exp2(x);
-          const float d = pr * (__uint_as_float(dp[c]) - delta_r);
-          dsv[u] = d;
-          if (bias_mode == 2) atomicAdd(&dlut[lut0 + c], d);
-          else ds_sum += d;
+        for (int i = 0; i < 16; ++i) {
+          float x0, x1, g0, g1, d0, d1;
+          fma2(x0, x1, __uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1]), scale, add);
+          fma2(g0, g1, __uint_as_float(dp[2 * i]), __uint_as_float(dp[2 * i + 1]), 1.f, nd);
+          mul2(d0, d1, fast_exp2(x0), fast_exp2(x1), g0, g1);
+          add2(a0, a1, d0, d1);
+          pk[i] = pack2<kBf16>(d0, d1);
         }
-        pk[i] = pack2<kBf16>(dsv[0], dsv[1]);
+        ds_sum = a0 + a1;
+      } else {
+        #pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float dsv[2];
+          #pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int c = 2 * i + u;
+            const float bias = bias_mode == 2 ? lut[lut0 + c] : bias_const;
+            float x = fmaf(__uint_as_float(sv[c]), scale, bias) - lse2;
+            if (need_mask && c >= n_valid) x = -INFINITY;
+            const float pr = fast_exp2(x);
+            const float d = pr * (__uint_as_float(dp[c]) - delta_r);
+            dsv[u] = d;
+            if (bias_mode == 2) atomicAdd(&dlut[lut0 + c], d);
+            else ds_sum += d;
+          }
+          pk[i] = pack2<kBf16>(dsv[0], dsv[1]);
+        }
       }
       if (bias_mode == 1) far_pos += ds_sum;
       if (bias_mode == 3) far_neg += ds_sum;
@@ -664,22 +680,42 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       const float* vl = &ctl->vec[s][0][half * 32];
       const float* vd = &ctl->vec[s][1][half * 32];
       uint32_t pp[16], pd[16];
-      #pragma unroll
-      for (int ii = 0; ii < 16; ++ii) {
-        float pv[2], dv2[2];
+      // fast path (uniform over the block): every key of the tile is inside the sequence, no
+      // causal boundary crosses the tile, one bias value
+      const int q_lo = q_off + (i_first + i) * BT;      // position of the tile's first query
+      const bool tile_masked = (key0 + BM > len_k) || (p.causal && key0 + BM - 1 > q_lo);
+      if (!tile_masked && bias_mode != 2) {
         #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int c = 2 * ii + u;
-          const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
-          float x = fmaf(__uint_as_float(sv[c]), scale, bias) - vl[c];
-          // masked: key outside the sequence, or (causal) after the query
-          if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
-          const float pr = fast_exp2(x);
-          pv[u] = pr;
-          dv2[u] = pr * (__uint_as_float(dp[c]) - vd[c]);
+        for (int ii = 0; ii < 16; ++ii) {
+          const float2 l2 = *reinterpret_cast<const float2*>(vl + 2 * ii);
+          const float2 d2 = *reinterpret_cast<const float2*>(vd + 2 * ii);
+          float x0, x1, g0, g1, e0, e1;
+          fma2(x0, x1, __uint_as_float(sv[2 * ii]), __uint_as_float(sv[2 * ii + 1]), scale, bias_const);
+          x0 -= l2.x; x1 -= l2.y;
+          g0 = __uint_as_float(dp[2 * ii]) - d2.x; g1 = __uint_as_float(dp[2 * ii + 1]) - d2.y;
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          mul2(e0, e1, p0, p1, g0, g1);
+          pp[ii] = pack2<kBf16>(p0, p1);
+          pd[ii] = pack2<kBf16>(e0, e1);
         }
-        pp[ii] = pack2<kBf16>(pv[0], pv[1]);
-        pd[ii] = pack2<kBf16>(dv2[0], dv2[1]);
+      } else {
+        #pragma unroll
+        for (int ii = 0; ii < 16; ++ii) {
+          float pv[2], dv2[2];
+          #pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int c = 2 * ii + u;
+            const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
+            float x = fmaf(__uint_as_float(sv[c]), scale, bias) - vl[c];
+            // masked: key outside the sequence, or (causal) after the query
+            if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
+            const float pr = fast_exp2(x);
+            pv[u] = pr;
+            dv2[u] = pr * (__uint_as_float(dp[c]) - vd[c]);
+          }
+          pp[ii] = pack2<kBf16>(pv[0], pv[1]);
+          pd[ii] = pack2<kBf16>(dv2[0], dv2[1]);
+        }
       }
       tmem_st_x16(tST, pp);
       tmem_st_x16(tDPT, pd);

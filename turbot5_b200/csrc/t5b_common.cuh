@@ -252,6 +252,13 @@ __device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, f
       "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
       : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
 }
+// (d0, d1) = (a0, a1) * (b0, b1)
+__device__ __forceinline__ void mul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
 // (acc0, acc1) += (x0, x1)
 __device__ __forceinline__ void add2(float& acc0, float& acc1, float x0, float x1) {
   asm("{\n\t.reg .b64 ra, rx;\n\t"
