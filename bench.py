@@ -405,6 +405,39 @@ def secondary_measurements(t5b, dev):
     out["varlen_32seq_128to4096"] = {"ms": ms, "TFLOP/s": fl / (ms * 1e-3) / 1e12, "tokens": T,
                                      "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"]}
     del qkv
+    # training step of the attention core at the headline shape: forward + backward (dQ, dK, dV and the
+    # bias-table gradient).  FLOPs counted as the 5 matrix products a backward needs (2.5 x forward) plus
+    # the forward; the two backward kernels recompute S and dP (7 products executed).
+    qg, kg, vg = [torch.randn((2, 8192, 12, 64), generator=g, device=dev, dtype=torch.float32).to(dt)
+                  .transpose(1, 2).requires_grad_(True) for _ in range(3)]
+    tg = table.detach().clone().requires_grad_(True)
+    dout = torch.randn((2, 12, 8192, 64), generator=g, device=dev, dtype=torch.float32).to(dt)
+
+    def train_step():
+        o_ = t5b.flash_attention_with_fusing_bias(qg, kg, vg, tg, sm_scale=1.0)
+        o_.backward(dout)
+    ms = _time(train_step, 10)
+    with torch.no_grad():
+        ms_f = _time(lambda: t5b.flash_attention_with_fusing_bias(qg, kg, vg, tg, sm_scale=1.0), 10)
+    fl = 4.0 * 2 * 12 * 8192 * 8192 * 64
+    out["attention_fwd_bwd_B2_H12_L8192"] = {"ms_fwd_bwd": ms, "ms_fwd": ms_f, "ms_bwd": ms - ms_f,
+                                             "TFLOP/s_fwd_bwd": 3.5 * fl / (ms * 1e-3) / 1e12,
+                                             "TFLOP/s_bwd": 2.5 * fl / ((ms - ms_f) * 1e-3) / 1e12,
+                                             "frac_of_bf16_peak_bwd": 2.5 * fl / ((ms - ms_f) * 1e-3) / 1e12 / peaks["tflops"]}
+    del qg, kg, vg, tg, dout
+    # RMSNorm backward, 100000 x 768 bf16: reads x and dy, writes dx (3 x 154 MB) + the weight gradient
+    xg = torch.randn((100000, 768), generator=g, device=dev).to(dt).requires_grad_(True)
+    wg = torch.rand((768,), generator=g, device=dev).to(dt).requires_grad_(True)
+    dyg = torch.randn((100000, 768), generator=g, device=dev).to(dt)
+
+    def norm_step():
+        t5b.rms_layer_norm(xg, wg, 1e-6).backward(dyg)
+    ms = _time(norm_step, 20)
+    with torch.no_grad():
+        ms_f = _time(lambda: t5b.rms_layer_norm(xg, wg, 1e-6), 20)
+    gbs = 3 * xg.numel() * 2 / ((ms - ms_f) * 1e-3) / 1e9
+    out["rmsnorm_bwd_100000x768_bf16"] = {"ms_bwd": ms - ms_f, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"]}
+    del xg, wg, dyg
     # head dim 128 (the T5-3B / 11B head size): same sequence length, 3 rotating input sets
     # (3 x 151 MB > L2), T5 bias, bf16
     sets = [[(torch.randn((2, 8192, 12, 128), generator=g, device=dev, dtype=torch.float32) * 0.5).to(dt).transpose(1, 2)

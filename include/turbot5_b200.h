@@ -207,6 +207,17 @@ T5B_API int t5b_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd,
                     int64_t rows, int32_t d, int64_t x_row_stride, int64_t y_row_stride,
                     int32_t x_dtype, int32_t w_dtype, float eps, void* stream);
 
+/* ---- T5 RMSNorm, backward ------------------------------------------------------
+ * Stands in for RMSLayerNorm.backward -> rms_layer_norm_bwd_dx_fused and the weight-gradient
+ * reduction (src/turbot5/ops/rms_norm.py:53-124, 154-185) and for autograd through
+ * T5LayerNorm._forward (src/turbot5/model/modules.py:52-60).  dy has the type of the
+ * forward's output (w's type when w is fp16/bf16, float32 otherwise); dx has x's type; the
+ * weight gradient is ADDED to dw, float32[d] (the caller zeroes it). */
+T5B_API int t5b_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw,
+                            int64_t rows, int32_t d, int64_t x_row_stride, int64_t dy_row_stride,
+                            int64_t dx_row_stride, int32_t x_dtype, int32_t w_dtype, float eps,
+                            void* stream);
+
 /* ---- unpad / pad glue -----------------------------------------------------------
  * Stand in for _get_unpad_data, index_first_axis and pad_input
  * (src/turbot5/model/padding.py:79-88, 46-76, 30-44) without the host

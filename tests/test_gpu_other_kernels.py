@@ -307,3 +307,64 @@ def test_config5_decode_full_size_spot_heads():
         out = t5b.flash_decoding_with_fusing_bias(q, ks, vs, table, causal=True, sm_scale=1.0, kv_len=t_step)
         want = orc.attention_basic(q[:3].cpu(), ks[:3, :, :t_step].cpu(), vs[:3, :, :t_step].cpu(), table.cpu(), causal=True)
         check_close(out[:3], want, dt, f"self step {t_step}")
+
+
+@pytest.mark.parametrize("xdt,wdt", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32),
+                                     (torch.bfloat16, torch.float32), (torch.float16, torch.float16)])
+@pytest.mark.parametrize("rows,d", [(37, 768), (300, 512), (5, 1000)])
+def test_rmsnorm_backward_vs_oracle_autograd(rows, d, xdt, wdt):
+    import turbot5_b200 as t5b
+    from tests.helpers import check_grad_close
+    x = seeded((rows, d), 1, dtype=xdt)
+    w = (1.0 + 0.2 * seeded((d,), 2)).to(wdt)
+    xf, wf = x.float().clone().requires_grad_(True), w.float().clone().requires_grad_(True)
+    # the same function on float32 copies under autograd; the reference's two roundings do not
+    # change the derivative it propagates (the casts pass gradients through)
+    y_ref = orc.t5_layer_norm(xf, wf)
+    dy = seeded((rows, d), 3, dtype=y_ref.dtype)
+    (y_ref * dy).sum().backward()
+    xc, wc = x.detach().cuda().requires_grad_(True), w.detach().cuda().requires_grad_(True)
+    y = t5b.rms_layer_norm(xc, wc, 1e-6)
+    y.backward(dy.cuda().to(y.dtype))
+    torch.cuda.synchronize()
+    check_grad_close(xc.grad, xf.grad, "dx", rel=1e-4 if xdt == torch.float32 else 2e-2)
+    check_grad_close(wc.grad, wf.grad, "dw", rel=1e-4 if (xdt == torch.float32 and wdt == torch.float32) else 2e-2)
+
+
+def test_module_training_step_gradients_vs_oracle_layer():
+    # one attention layer, encoder (with a padding mask: the packed-sequence kernels) and decoder
+    # self-attention: gradients of every weight and of the input against the oracle layer under autograd
+    from tests.helpers import check_grad_close
+    dt = torch.bfloat16
+    for is_decoder, mask_lens in ((False, None), (False, [200, 37, 129]), (True, None)):
+        cfg = _Cfg(is_decoder=is_decoder)
+        mod = _make_module(cfg, dt, 11).train()
+        hidden = seeded((3, 200, 128), 12, dtype=dt)
+        dout = seeded((3, 200, 128), 13, dtype=dt)
+        mask = None
+        if mask_lens is not None:
+            mask = torch.zeros((3, 200), dtype=torch.int64)
+            for b, n in enumerate(mask_lens):
+                mask[b, :n] = 1
+            dout = dout * mask[:, :, None].to(dt)        # padded rows carry no loss
+        hc = hidden.cuda().requires_grad_(True)
+        out = mod(hc, mask=None if mask is None else mask.cuda())[0]
+        out.backward(dout.cuda())
+        torch.cuda.synchronize()
+        # oracle: float32 copies of the same parameters under autograd
+        names = ["q", "k", "v", "o"]
+        ws = {n: getattr(mod, n).weight.detach().float().cpu().requires_grad_(True) for n in names}
+        table = mod.relative_attention_bias.weight.detach().float().cpu().requires_grad_(True)
+        hf = hidden.float().requires_grad_(True)
+        want, _ = orc.t5_attention_layer(hf, ws["q"], ws["k"], ws["v"], ws["o"], table, mod.n_heads,
+                                         mod.key_value_proj_dim, is_decoder=is_decoder, key_padding_mask=mask)
+        (want * dout.float()).sum().backward()
+        tag = f"decoder={is_decoder} mask={mask_lens}"
+        for n in names:
+            check_grad_close(getattr(mod, n).weight.grad, ws[n].grad, f"{tag} d{n}.weight", rel=3e-2)
+        check_grad_close(mod.relative_attention_bias.weight.grad, table.grad, f"{tag} dtable", rel=3e-2, floor=1.0)
+        if mask is None:
+            check_grad_close(hc.grad, hf.grad, f"{tag} dhidden", rel=3e-2)
+        else:
+            for b, n in enumerate(mask_lens):
+                check_grad_close(hc.grad[b, :n], hf.grad[b, :n], f"{tag} dhidden row {b}", rel=3e-2)

@@ -88,3 +88,24 @@ def test_cuda_graph_decoding_equals_eager_decoding():
         graph_tokens, graph_last = model.greedy_decode(enc, 7, use_cuda_graph=True)
     assert torch.equal(eager_tokens, graph_tokens)
     assert (eager_last.float() - graph_last.float()).abs().max().item() < 1e-2
+
+
+def test_training_step_through_the_stack_gives_finite_gradients_everywhere():
+    # encoder-decoder forward with a padding mask, cross-entropy loss, backward: every parameter
+    # gets a finite, non-zero gradient through the CUDA attention, RMSNorm and unpad/pad kernels
+    model = _model(torch.bfloat16, d_model=128, num_heads=2, d_ff=256).train()
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, 128, (2, 150), generator=g).cuda()
+    dec = torch.randint(0, 128, (2, 40), generator=g).cuda()
+    mask = torch.ones((2, 150), dtype=torch.int64)
+    mask[1, 90:] = 0
+    enc = model.encoder(ids, attention_mask=mask.cuda())
+    hid = model.decoder(dec, encoder_hidden_states=enc, encoder_attention_mask=mask.cuda())
+    logits = model.logits(hid)
+    loss = torch.nn.functional.cross_entropy(logits.float().view(-1, logits.shape[-1]), dec.view(-1))
+    loss.backward()
+    torch.cuda.synchronize()
+    for name, prm in model.named_parameters():
+        assert prm.grad is not None, name
+        assert torch.isfinite(prm.grad.float()).all(), name
+        assert prm.grad.float().abs().sum().item() > 0, name

@@ -22,7 +22,7 @@ _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 SYMBOLS = ("t5b_status_string", "t5b_abi_version", "t5b_bucket_table_host", "t5b_bucket_indices",
            "t5b_attention_fwd", "t5b_attention_workspace_bytes", "t5b_attention_bwd", "t5b_decode_workspace_bytes", "t5b_decode_num_splits",
            "t5b_decode_fwd", "t5b_decode_static_scratch_bytes", "t5b_decode_fwd_static_scratch",
-           "t5b_rmsnorm_fwd", "t5b_unpad_plan", "t5b_gather_rows",
+           "t5b_rmsnorm_fwd", "t5b_rmsnorm_bwd", "t5b_unpad_plan", "t5b_gather_rows",
            "t5b_scatter_rows")
 
 
@@ -110,6 +110,9 @@ def lib():
     L.t5b_rmsnorm_fwd.restype = C.c_int
     L.t5b_rmsnorm_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                   C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]
+    L.t5b_rmsnorm_bwd.restype = C.c_int
+    L.t5b_rmsnorm_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
+                                  C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_float, C.c_void_p]
     L.t5b_unpad_plan.restype = C.c_int
     L.t5b_unpad_plan.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.c_void_p]

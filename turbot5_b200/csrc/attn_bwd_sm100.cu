@@ -23,9 +23,6 @@
 #include "attn_params.cuh"
 #include "attn_sm100_util.cuh"
 
-#include <cstdio>
-#include <cstdlib>
-
 namespace t5b {
 namespace sm100b {
 
@@ -808,9 +805,6 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
       if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
     }
   }
-  const bool dbg = getenv("T5B_BWD_DEBUG") != nullptr;
-  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};
-  if (dbg) { for (auto& x : ev) cudaEventCreate(&x); cudaEventRecord(ev[0], stream); }
   (void)rows_k;   // > 0: checked by the caller
   int st;
   CUtensorMap q128, do128, k64, v64, k128, v128, q64, do64;
@@ -859,20 +853,10 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
   if (gq.x > 0) {
     kq<<<gq, NUM_THREADS, smem, stream>>>(q128, do128, k64, v64, p, e, spec);
     if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
-    if (dbg) cudaEventRecord(ev[1], stream);
   }
   if (gk.x > 0) {
     kkv<<<gk, NUM_THREADS, smem, stream>>>(k128, v128, q64, do64, p, e, spec);
     if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
-    if (dbg) {
-      cudaEventRecord(ev[2], stream);
-      cudaEventSynchronize(ev[2]);
-      float t_dq = 0.f, t_dkv = 0.f;
-      cudaEventElapsedTime(&t_dq, ev[0], ev[1]);
-      cudaEventElapsedTime(&t_dkv, ev[1], ev[2]);
-      fprintf(stderr, "[bwd] dq %.3f ms, dkv %.3f ms\n", t_dq, t_dkv);
-      for (auto& x : ev) cudaEventDestroy(x);
-    }
   }
   return T5B_OK;
 }

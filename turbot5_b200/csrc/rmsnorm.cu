@@ -146,6 +146,103 @@ static int launch(const void* x, const void* w, void* y, float* rstd, int64_t ro
 
 using namespace t5b;
 
+namespace t5b {
+namespace rms {
+
+// Backward of y = w * round_w(x * rstd), rstd = rsqrt(mean(x^2) + eps)
+// (rms_layer_norm_bwd_dx_fused + the weight-gradient reduction, src/turbot5/ops/rms_norm.py:53-124):
+//   g = w * dy;  dx = rstd * g - x * rstd^3 * mean(g * x);  dw += dy * round_w(x * rstd).
+// A warp owns a row (grid-stride); the row is read twice, the second time from L1/L2.  The
+// weight gradient is summed per block in shared memory (lanes hit consecutive words) and
+// added to the float32 result with one atomic per column and block.
+template <typename TX, typename TW, typename TDY>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const TDY* __restrict__ dy,
+                   TX* __restrict__ dx, float* __restrict__ dw, int64_t rows, int d,
+                   int64_t x_stride, int64_t dy_stride, int64_t dx_stride, float eps) {
+  extern __shared__ float s_dw[];
+  for (int c = threadIdx.x; c < d; c += blockDim.x) s_dw[c] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const float inv_d = 1.f / (float)d;
+  for (int64_t r = warp0; r < rows; r += n_warps) {
+    const TX* xr = x + r * x_stride;
+    const TDY* gr = dy + r * dy_stride;
+    TX* dxr = dx + r * dx_stride;
+    float ss = 0.f, sg = 0.f;
+    for (int c = lane; c < d; c += 32) {
+      const float xv = to_float(xr[c]);
+      ss = fmaf(xv, xv, ss);
+      sg = fmaf(to_float(w[c]) * to_float(gr[c]), xv, sg);
+    }
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      sg += __shfl_xor_sync(0xffffffffu, sg, o);
+    }
+    const float rstd = rsqrtf(ss * inv_d + eps);
+    const float k = rstd * rstd * rstd * sg * inv_d;
+    for (int c = lane; c < d; c += 32) {
+      const float xv = to_float(xr[c]);
+      const float gv = to_float(gr[c]);
+      dxr[c] = from_float<TX>(rstd * to_float(w[c]) * gv - xv * k);
+      const float xhat = to_float(from_float<TW>(xv * rstd));     // as the forward rounds it
+      atomicAdd(&s_dw[c], gv * xhat);
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    const float g = s_dw[c];
+    if (g != 0.f) atomicAdd(&dw[c], g);
+  }
+}
+
+template <typename TX, typename TW, typename TDY>
+int launch_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, int64_t rows, int d,
+               int64_t xs, int64_t dys, int64_t dxs, float eps, cudaStream_t st) {
+  const size_t smem = (size_t)d * sizeof(float);
+  if (smem > 200 * 1024) return T5B_ERR_SHAPE;
+  auto kern = rmsnorm_bwd_kernel<TX, TW, TDY>;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    cudaGetLastError();
+    return T5B_ERR_LAUNCH;
+  }
+  int64_t blocks = (rows + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  kern<<<(unsigned)blocks, 256, smem, st>>>((const TX*)x, (const TW*)w, (const TDY*)dy, (TX*)dx, dw, rows, d,
+                                            xs, dys, dxs, eps);
+  return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;
+}
+
+}  // namespace rms
+}  // namespace t5b
+
+extern "C" int t5b_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw,
+                               int64_t rows, int32_t d, int64_t x_row_stride, int64_t dy_row_stride,
+                               int64_t dx_row_stride, int32_t x_dtype, int32_t w_dtype, float eps, void* stream) {
+  using namespace t5b;
+  if (!x || !w || !dy || !dx || !dw) return T5B_ERR_ARG;
+  if (rows < 0 || d <= 0) return T5B_ERR_SHAPE;
+  if (rows == 0) return T5B_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  // dy has the type of the forward's output: w's type when w is 16-bit, float32 otherwise
+#define T5B_RMSB(TXE, TX, TWE, TW, TDY)                                                       \
+  if (x_dtype == TXE && w_dtype == TWE)                                                      \
+    return rms::launch_bwd<TX, TW, TDY>(x, w, dy, dx, dw, rows, d, x_row_stride, dy_row_stride, dx_row_stride, eps, st);
+  T5B_RMSB(T5B_BF16, __nv_bfloat16, T5B_BF16, __nv_bfloat16, __nv_bfloat16)
+  T5B_RMSB(T5B_BF16, __nv_bfloat16, T5B_F32, float, float)
+  T5B_RMSB(T5B_F16, __half, T5B_F16, __half, __half)
+  T5B_RMSB(T5B_F16, __half, T5B_F32, float, float)
+  T5B_RMSB(T5B_F32, float, T5B_F32, float, float)
+  T5B_RMSB(T5B_F32, float, T5B_BF16, __nv_bfloat16, __nv_bfloat16)
+  T5B_RMSB(T5B_F32, float, T5B_F16, __half, __half)
+#undef T5B_RMSB
+  return T5B_ERR_DTYPE;
+}
+
 extern "C" int t5b_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int64_t rows,
                                int32_t d, int64_t x_row_stride, int64_t y_row_stride,
                                int32_t x_dtype, int32_t w_dtype, float eps, void* stream) {

@@ -16,7 +16,43 @@ from .padding import get_unpad_plan, pad_rows, unpad_rows
 
 
 def rms_layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, return_rstd: bool = False):
-    """T5 RMSNorm forward on the device (replaces RMSLayerNorm.apply, src/turbot5/ops/rms_norm.py:129)."""
+    """T5 RMSNorm on the device (replaces RMSLayerNorm.apply, src/turbot5/ops/rms_norm.py:129-185);
+    differentiable in x and weight."""
+    if not return_rstd and torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
+        return _RMSNormFn.apply(x, weight, eps)
+    return _rms_layer_norm_fwd(x, weight, eps, return_rstd)
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        ctx.save_for_backward(x, weight)
+        ctx.eps = eps
+        return _rms_layer_norm_fwd(x, weight, eps)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        d = x.shape[-1]
+        x2 = x.reshape(-1, d)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        out_dtype = weight.dtype if weight.dtype in (torch.float16, torch.bfloat16) else torch.float32
+        dy2 = dy.reshape(-1, d).to(out_dtype)
+        if dy2.stride(-1) != 1:
+            dy2 = dy2.contiguous()
+        dx = torch.empty((x2.shape[0], d), dtype=x.dtype, device=x.device)
+        dw = torch.zeros((d,), dtype=torch.float32, device=x.device)
+        w = weight.contiguous()
+        with torch.cuda.device(x.device):
+            nat.check(nat.lib().t5b_rmsnorm_bwd(x2.data_ptr(), w.data_ptr(), dy2.data_ptr(), dx.data_ptr(),
+                                                dw.data_ptr(), x2.shape[0], d, x2.stride(0), dy2.stride(0),
+                                                dx.stride(0), nat.dtype_code(x.dtype), nat.dtype_code(w.dtype),
+                                                float(ctx.eps), nat.stream_ptr(x.device)), "rms_layer_norm (backward)")
+        return dx.view(x.shape), dw.to(weight.dtype), None
+
+
+def _rms_layer_norm_fwd(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, return_rstd: bool = False):
     nat.require_cuda(x, weight)
     d = x.shape[-1]
     if weight.shape != (d,):
@@ -38,7 +74,7 @@ def rms_layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, ret
 
 
 class RMSLayerNorm:
-    """`RMSLayerNorm.apply(x, weight, eps)` call shape of the reference (forward only)."""
+    """`RMSLayerNorm.apply(x, weight, eps)` call shape of the reference."""
 
     @staticmethod
     def apply(x, weight, eps):

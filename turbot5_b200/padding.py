@@ -53,7 +53,50 @@ def _rows(t: torch.Tensor, n_rows: int):
 
 
 def unpad_rows(x: torch.Tensor, plan: UnpadPlan) -> torch.Tensor:
-    """(B, L, ...) -> packed (B*L, ...): kept tokens first, in order; the unused tail is zero."""
+    """(B, L, ...) -> packed (B*L, ...): kept tokens first, in order; the unused tail is zero.
+    Differentiable: the gradient is the scatter back (`pad_rows`)."""
+    if torch.is_grad_enabled() and x.requires_grad:
+        return _Unpad.apply(x, plan)
+    return _unpad_rows(x, plan)
+
+
+def pad_rows(packed: torch.Tensor, plan: UnpadPlan) -> torch.Tensor:
+    """packed (>= total kept rows, ...) -> (B, L, ...) with zeros at padded positions.
+    Differentiable: the gradient is the gather (`unpad_rows`)."""
+    if torch.is_grad_enabled() and packed.requires_grad:
+        return _Pad.apply(packed, plan)
+    return _pad_rows(packed, plan)
+
+
+class _Unpad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, plan):
+        ctx.plan = plan
+        return _unpad_rows(x, plan)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _pad_rows(g, ctx.plan), None
+
+
+class _Pad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, packed, plan):
+        ctx.plan, ctx.rows = plan, packed.shape[0]
+        return _pad_rows(packed, plan)
+
+    @staticmethod
+    def backward(ctx, g):
+        gp = _unpad_rows(g, ctx.plan)            # B*L rows, kept tokens first, zero tail
+        if gp.shape[0] != ctx.rows:
+            if gp.shape[0] > ctx.rows:
+                gp = gp[: ctx.rows]
+            else:
+                gp = torch.cat([gp, gp.new_zeros((ctx.rows - gp.shape[0],) + tuple(gp.shape[1:]))])
+        return gp, None
+
+
+def _unpad_rows(x: torch.Tensor, plan: UnpadPlan) -> torch.Tensor:
     nat.require_cuda(x)
     n = plan.batch * plan.seqlen
     src = _rows(x, n)
@@ -68,8 +111,7 @@ def unpad_rows(x: torch.Tensor, plan: UnpadPlan) -> torch.Tensor:
     return out.view(n, *x.shape[2:])
 
 
-def pad_rows(packed: torch.Tensor, plan: UnpadPlan) -> torch.Tensor:
-    """packed (>= total kept rows, ...) -> (B, L, ...) with zeros at padded positions."""
+def _pad_rows(packed: torch.Tensor, plan: UnpadPlan) -> torch.Tensor:
     nat.require_cuda(packed)
     n = plan.batch * plan.seqlen
     src = _rows(packed, packed.shape[0])
