@@ -10,6 +10,8 @@
 // result stays float32.
 #include "t5b_common.cuh"
 
+#include <type_traits>
+
 namespace t5b {
 namespace rms {
 
@@ -199,9 +201,92 @@ rmsnorm_bwd_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const TDY
   }
 }
 
+// d = 256 * NT, 16-bit x and dy, 16-byte aligned rows: a lane owns 8 consecutive columns of every
+// 256-column group, reads them with one 16-byte load, keeps the row in registers between the two
+// reductions and the outputs, and carries its share of the weight gradient in registers over all
+// the rows of its warp (one shared-memory add per column and warp at the end).
+template <typename TX, typename TW, int NT>
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_vec_kernel(const TX* __restrict__ x, const TW* __restrict__ w, const TX* __restrict__ dy,
+                       TX* __restrict__ dx, float* __restrict__ dw, int64_t rows,
+                       int64_t x_stride, int64_t dy_stride, int64_t dx_stride, float eps) {
+  constexpr int D = 256 * NT;
+  __shared__ float s_dw[D];
+  for (int c = threadIdx.x; c < D; c += blockDim.x) s_dw[c] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  float wv[NT][8], acc[NT][8];
+  #pragma unroll
+  for (int t = 0; t < NT; ++t)
+    #pragma unroll
+    for (int k = 0; k < 8; ++k) { wv[t][k] = to_float(w[t * 256 + lane * 8 + k]); acc[t][k] = 0.f; }
+  for (int64_t r = warp0; r < rows; r += n_warps) {
+    float xv[NT][8], gv[NT][8];
+    float ss = 0.f, sg = 0.f;
+    #pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      const uint4 xa = ld_stream16(x + r * x_stride + t * 256 + lane * 8);
+      const uint4 ga = ld_stream16(dy + r * dy_stride + t * 256 + lane * 8);
+      const TX* xe = reinterpret_cast<const TX*>(&xa);
+      const TX* ge = reinterpret_cast<const TX*>(&ga);
+      #pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        xv[t][k] = to_float(xe[k]);
+        gv[t][k] = to_float(ge[k]);
+        ss = fmaf(xv[t][k], xv[t][k], ss);
+        sg = fmaf(wv[t][k] * gv[t][k], xv[t][k], sg);
+      }
+    }
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      sg += __shfl_xor_sync(0xffffffffu, sg, o);
+    }
+    const float rstd = rsqrtf(ss * (1.f / D) + eps);
+    const float kk = rstd * rstd * rstd * sg * (1.f / D);
+    #pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      uint4 oa;
+      TX* oe = reinterpret_cast<TX*>(&oa);
+      #pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        oe[k] = from_float<TX>(rstd * wv[t][k] * gv[t][k] - xv[t][k] * kk);
+        const float xhat = to_float(from_float<TW>(xv[t][k] * rstd));
+        acc[t][k] = fmaf(gv[t][k], xhat, acc[t][k]);
+      }
+      *reinterpret_cast<uint4*>(dx + r * dx_stride + t * 256 + lane * 8) = oa;
+    }
+  }
+  #pragma unroll
+  for (int t = 0; t < NT; ++t)
+    #pragma unroll
+    for (int k = 0; k < 8; ++k) atomicAdd(&s_dw[t * 256 + lane * 8 + k], acc[t][k]);
+  __syncthreads();
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    const float g = s_dw[c];
+    if (g != 0.f) atomicAdd(&dw[c], g);
+  }
+}
+
 template <typename TX, typename TW, typename TDY>
 int launch_bwd(const void* x, const void* w, const void* dy, void* dx, float* dw, int64_t rows, int d,
                int64_t xs, int64_t dys, int64_t dxs, float eps, cudaStream_t st) {
+  if constexpr (sizeof(TX) == 2 && std::is_same<TX, TDY>::value) {
+    const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)dy % 16 == 0) && ((uintptr_t)dx % 16 == 0) &&
+                         xs % 8 == 0 && dys % 8 == 0 && dxs % 8 == 0;
+    if (aligned && (d == 512 || d == 768 || d == 1024)) {
+      int64_t nblk = (rows + 7) / 8;
+      if (nblk > 148 * 4) nblk = 148 * 4;
+#define T5B_RMSB_VEC(NT)                                                                            \
+      rmsnorm_bwd_vec_kernel<TX, TW, NT><<<(unsigned)nblk, 256, 0, st>>>(                               \
+          (const TX*)x, (const TW*)w, (const TX*)dy, (TX*)dx, dw, rows, xs, dys, dxs, eps)
+      if (d == 512) T5B_RMSB_VEC(2); else if (d == 768) T5B_RMSB_VEC(3); else T5B_RMSB_VEC(4);
+#undef T5B_RMSB_VEC
+      return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;
+    }
+  }
   const size_t smem = (size_t)d * sizeof(float);
   if (smem > 200 * 1024) return T5B_ERR_SHAPE;
   auto kern = rmsnorm_bwd_kernel<TX, TW, TDY>;
