@@ -152,6 +152,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary kernel measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--train", action="store_true",
+                    help="time forward + backward of the same workload (the training step of the attention core) "
+                         "instead of the forward: a second workload, used for the backward kernels' profile")
     ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128],
                     help="64: the headline workload; 128: the same workload at the T5-3B/11B head size "
                          "(a second tile geometry of the kernel; used for its profile)")
@@ -195,10 +198,21 @@ def main():
     sets = [make_set() for _ in range(n_sets)]
     table = (torch.randn((w["num_buckets"], H), generator=g, device=dev) * 0.1).to(dt)
 
+    if args.train:
+        w["name"] += ", forward + backward"
+        for st_ in sets:
+            for t_ in st_:
+                t_.requires_grad_(True)
+        table.requires_grad_(True)
+        dout = torch.randn((B, H, L, D), generator=g, device=dev, dtype=torch.float32).to(dt)
+
     def step(i):
         q, k, v = sets[i % n_sets]
-        return t5b.flash_attention_with_fusing_bias(q, k, v, table, causal=False, sm_scale=1.0,
-                                                    NUM_BUCKETS=w["num_buckets"], MAX_DISTANCE=w["max_distance"])
+        o_ = t5b.flash_attention_with_fusing_bias(q, k, v, table, causal=False, sm_scale=1.0,
+                                                  NUM_BUCKETS=w["num_buckets"], MAX_DISTANCE=w["max_distance"])
+        if args.train:
+            o_.backward(dout)
+        return o_
 
     def barrier():
         if world > 1:
@@ -224,7 +238,8 @@ def main():
     ms_total = float(t.item())
     t5b.check_device_status(dev)
     ms_step = ms_total / args.steps
-    fl = flops_per_step(w)
+    # forward: 2 matrix products; training step: + the 5 a backward needs (2.5 x forward)
+    fl = flops_per_step(w) * (3.5 if args.train else 1.0)
     value = world * fl / (ms_step * 1e-3) / 1e12
 
     # ---- end to end through the public API with host buffers (pinned): every step copies its
@@ -232,7 +247,7 @@ def main():
     # on their own streams with two buffer slots, so that the upload of step i+1 and the
     # download of step i-1 overlap the kernel of step i (as a serving loop would do it).
     e2e_steps = max(3, min(args.steps, 20))
-    host_sets = [[t_.contiguous().cpu().pin_memory() for t_ in sets[i % n_sets]] for i in range(2)]
+    host_sets = [[t_.detach().contiguous().cpu().pin_memory() for t_ in sets[i % n_sets]] for i in range(2)]
     host_out = [torch.empty((B, H, L, D), dtype=dt).pin_memory() for _ in range(2)]
     dev_in = [[torch.empty((B, H, L, D), dtype=dt, device=dev) for _ in range(3)] for _ in range(2)]
     main = torch.cuda.current_stream(dev)
@@ -249,7 +264,7 @@ def main():
                 d_.copy_(h_, non_blocking=True)
             ev_in[s_].record(up)
         main.wait_event(ev_in[s_])
-        o = t5b.flash_attention_with_fusing_bias(dev_in[s_][0], dev_in[s_][1], dev_in[s_][2], table, causal=False,
+        o = t5b.flash_attention_with_fusing_bias(dev_in[s_][0], dev_in[s_][1], dev_in[s_][2], table.detach(), causal=False,
                                                  sm_scale=1.0, NUM_BUCKETS=w["num_buckets"],
                                                  MAX_DISTANCE=w["max_distance"])
         ev_done[s_].record(main)
@@ -290,7 +305,8 @@ def main():
         peaks = measured_peaks()
         achieved = fl / (ms_step * 1e-3) / 1e12
         line = {
-            "metric": "fused_bias_attention_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "metric": "fused_bias_attention_fwd_bwd_tflops" if args.train else "fused_bias_attention_fwd_tflops",
+            "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": w["name"], "B_per_gpu": B, "H": H, "M": L, "N": L, "D": D,
@@ -299,11 +315,13 @@ def main():
                        "l2": f"inputs rotate over {n_sets} sets ({n_sets * set_bytes / 2**20:.0f} MiB > 126 MiB L2)"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["tflops"],
-                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH if D == WORKLOAD["D"] else None,
-                         "peak_source": peaks["source"], "kernel": "attn_fwd_kernel<bf16>"},
+                         "traffic": NCU_DRAM_BYTES_PER_LAUNCH if (D == WORKLOAD["D"] and not args.train) else None,
+                         "peak_source": peaks["source"],
+                         "kernel": "attn_fwd_kernel + attn_bwd_dq_kernel + attn_bwd_dkv_kernel" if args.train
+                                   else "attn_fwd_kernel<bf16>"},
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": set_bytes,
                     "d2h_bytes_per_step": B * H * L * D * 2, "ms_per_step": e2e_ms, "steps": e2e_steps},
-            "gpu_launches": args.steps,
+            "gpu_launches": args.steps * (4 if args.train else 1),
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:

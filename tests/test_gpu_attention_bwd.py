@@ -124,3 +124,33 @@ def test_backward_of_unsupported_shapes_is_refused():
     out = t5b.flash_attention_with_fusing_bias(q, q.detach(), q.detach(), None, sm_scale=1.0)
     with pytest.raises(NotImplementedError):
         out.sum().backward()
+
+
+def test_backward_with_empty_sides_returns_zero_gradients():
+    t5b = _ops()
+    dt = torch.bfloat16
+    q = torch.randn(1, 2, 5, 64, device="cuda", dtype=dt, requires_grad=True)
+    k = torch.randn(1, 2, 0, 64, device="cuda", dtype=dt, requires_grad=True)
+    v = torch.randn(1, 2, 0, 64, device="cuda", dtype=dt, requires_grad=True)
+    table = torch.randn(32, 2, device="cuda", dtype=dt, requires_grad=True)
+    out = t5b.flash_attention_with_fusing_bias(q, k, v, table, sm_scale=1.0)
+    assert torch.count_nonzero(out) == 0
+    out.sum().backward()
+    assert torch.count_nonzero(q.grad) == 0 and k.grad.shape == k.shape and torch.count_nonzero(table.grad) == 0
+
+
+def test_gradients_do_not_depend_on_how_dout_is_laid_out():
+    # a transposed (non-contiguous) upstream gradient is accepted as it is or copied; same result
+    t5b = _ops()
+    dt = torch.bfloat16
+    q, k, v = (seeded((1, 2, 200, 64), s, 0.5, dtype=dt).cuda().requires_grad_(True) for s in (1, 2, 3))
+    dout = seeded((1, 200, 2, 64), 5, dtype=dt).cuda()
+    grads = []
+    for d in (dout.transpose(1, 2), dout.transpose(1, 2).contiguous()):
+        for t in (q, k, v):
+            t.grad = None
+        t5b.flash_attention_with_fusing_bias(q, k, v, None, sm_scale=1.0).backward(d)
+        grads.append([t.grad.clone() for t in (q, k, v)])
+    torch.cuda.synchronize()
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)

@@ -676,46 +676,49 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       }
       const float* vl = &ctl->vec[s][0][half * 32];
       const float* vd = &ctl->vec[s][1][half * 32];
-      uint32_t pp[16], pd[16];
       // fast path (uniform over the block): every key of the tile is inside the sequence, no
-      // causal boundary crosses the tile, one bias value
+      // causal boundary crosses the tile, one bias value.  Two halves of 16 columns: each is
+      // stored as soon as it is packed, which keeps the live registers below the limit.
       const int q_lo = q_off + (i_first + i) * BT;      // position of the tile's first query
       const bool tile_masked = (key0 + BM > len_k) || (p.causal && key0 + BM - 1 > q_lo);
-      if (!tile_masked && bias_mode != 2) {
-        #pragma unroll
-        for (int ii = 0; ii < 16; ++ii) {
-          const float2 l2 = *reinterpret_cast<const float2*>(vl + 2 * ii);
-          const float2 d2 = *reinterpret_cast<const float2*>(vd + 2 * ii);
-          float x0, x1, g0, g1, e0, e1;
-          fma2(x0, x1, __uint_as_float(sv[2 * ii]), __uint_as_float(sv[2 * ii + 1]), scale, bias_const);
-          x0 -= l2.x; x1 -= l2.y;
-          g0 = __uint_as_float(dp[2 * ii]) - d2.x; g1 = __uint_as_float(dp[2 * ii + 1]) - d2.y;
-          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-          mul2(e0, e1, p0, p1, g0, g1);
-          pp[ii] = pack2<kBf16>(p0, p1);
-          pd[ii] = pack2<kBf16>(e0, e1);
-        }
-      } else {
-        #pragma unroll
-        for (int ii = 0; ii < 16; ++ii) {
-          float pv[2], dv2[2];
+      #pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t pp[8], pd[8];
+        if (!tile_masked && bias_mode != 2) {
           #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int c = 2 * ii + u;
-            const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
-            float x = fmaf(__uint_as_float(sv[c]), scale, bias) - vl[c];
-            // masked: key outside the sequence, or (causal) after the query
-            if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
-            const float pr = fast_exp2(x);
-            pv[u] = pr;
-            dv2[u] = pr * (__uint_as_float(dp[c]) - vd[c]);
+          for (int ii = 0; ii < 8; ++ii) {
+            const int c = 16 * hh + 2 * ii;
+            const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
+            const float2 d2 = *reinterpret_cast<const float2*>(vd + c);
+            float x0, x1, e0, e1;
+            fma2(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, bias_const);
+            const float p0 = fast_exp2(x0 - l2.x), p1 = fast_exp2(x1 - l2.y);
+            mul2(e0, e1, p0, p1, __uint_as_float(dp[c]) - d2.x, __uint_as_float(dp[c + 1]) - d2.y);
+            pp[ii] = pack2<kBf16>(p0, p1);
+            pd[ii] = pack2<kBf16>(e0, e1);
           }
-          pp[ii] = pack2<kBf16>(pv[0], pv[1]);
-          pd[ii] = pack2<kBf16>(dv2[0], dv2[1]);
+        } else {
+          #pragma unroll
+          for (int ii = 0; ii < 8; ++ii) {
+            float pv[2], dv2[2];
+            #pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int c = 16 * hh + 2 * ii + u;
+              const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
+              float x = fmaf(__uint_as_float(sv[c]), scale, bias) - vl[c];
+              // masked: key outside the sequence, or (causal) after the query
+              if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
+              const float pr = fast_exp2(x);
+              pv[u] = pr;
+              dv2[u] = pr * (__uint_as_float(dp[c]) - vd[c]);
+            }
+            pp[ii] = pack2<kBf16>(pv[0], pv[1]);
+            pd[ii] = pack2<kBf16>(dv2[0], dv2[1]);
+          }
         }
+        tmem_st_x8(tST + 8 * hh, pp);
+        tmem_st_x8(tDPT + 8 * hh, pd);
       }
-      tmem_st_x16(tST, pp);
-      tmem_st_x16(tDPT, pd);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
