@@ -17,8 +17,8 @@ def _ops():
 
 def _cuda_grads(q, k, v, table, dout, dt, **kw):
     t5b = _ops()
-    qc, kc, vc = (t.to("cuda", dt).requires_grad_(True) for t in (q, k, v))
-    tc = None if table is None else table.to("cuda", dt).requires_grad_(True)
+    qc, kc, vc = (t.detach().to("cuda", dt).requires_grad_(True) for t in (q, k, v))
+    tc = None if table is None else table.detach().to("cuda", dt).requires_grad_(True)
     out = t5b.flash_attention_with_fusing_bias(qc, kc, vc, tc, sm_scale=kw.pop("sm_scale", 1.0), **kw)
     out.backward(dout.to("cuda", dt))
     torch.cuda.synchronize()
@@ -27,8 +27,8 @@ def _cuda_grads(q, k, v, table, dout, dt, **kw):
 
 
 def _oracle_grads(q, k, v, table, dout, **kw):
-    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
-    tf = None if table is None else table.float().requires_grad_(True)
+    qf, kf, vf = (t.detach().float().clone().requires_grad_(True) for t in (q, k, v))
+    tf = None if table is None else table.detach().float().clone().requires_grad_(True)
     out = orc.attention_basic(qf, kf, vf, tf, **kw)
     (out * dout.float()).sum().backward()
     return out.detach(), qf.grad, kf.grad, vf.grad, (None if tf is None else tf.grad)
@@ -118,12 +118,56 @@ def test_varlen_gradients_vs_oracle(causal):
         check_grad_close(g, w, f"varlen causal={causal} {nm}")
 
 
-def test_backward_of_unsupported_shapes_is_refused():
+SIMT_CASES = [
+    # dtype, D, B, H, M, N, causal, q_pos_offset
+    (torch.float32, 64, 2, 8, 512, 512, False, None),     # the reference's float32 parity config
+    (torch.float32, 64, 1, 2, 200, 333, True, None),
+    (torch.float32, 16, 1, 2, 100, 100, False, None),
+    (torch.float32, 128, 1, 2, 70, 150, False, 0),
+    (torch.bfloat16, 32, 1, 2, 130, 130, True, None),
+    (torch.bfloat16, 128, 1, 2, 300, 300, False, None),
+    (torch.float16, 64, 1, 2, 100, 100, False, None),       # kernel="simt" on a tensor-core shape
+]
+
+
+@pytest.mark.parametrize("dt,D,B,H,M,N,causal,off", SIMT_CASES)
+def test_cuda_core_backward_vs_oracle(dt, D, B, H, M, N, causal, off):
+    # float32 tensors and head dims other than 64 take the CUDA-core backward (float32 arithmetic)
+    q = seeded((B, H, M, D), 1, 0.5, dtype=dt)
+    k = seeded((B, H, N, D), 2, 0.5, dtype=dt)
+    v = seeded((B, H, N, D), 3, dtype=dt)
+    dout = seeded((B, H, M, D), 5, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    want = _oracle_grads(q, k, v, table, dout, causal=causal, q_pos_offset=off)
+    kw = dict(kernel="simt") if (dt != torch.float32 and D == 64) else {}
+    got = _cuda_grads(q, k, v, table, dout, dt, causal=causal, q_pos_offset=off, **kw)
+    rel = 2e-4 if dt == torch.float32 else 1e-2
+    check_close(got[0], want[0], dt, "out")
+    for g, w, nm in zip(got[1:], want[1:], ("dq", "dk", "dv", "dtable")):
+        check_grad_close(g, w, f"{dt} d{D} {nm}", rel=rel, floor=(0.05 if dt == torch.float32 else 2.0) if nm == "dtable" else 1e-6)
+
+
+def test_cuda_core_backward_packed_sequences_float32():
     t5b = _ops()
-    q = torch.randn(1, 2, 64, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
-    out = t5b.flash_attention_with_fusing_bias(q, q.detach(), q.detach(), None, sm_scale=1.0)
-    with pytest.raises(NotImplementedError):
-        out.sum().backward()
+    lens_q, lens_k = [5, 40, 0, 33], [9, 40, 7, 70]
+    cq = torch.tensor(np.concatenate([[0], np.cumsum(lens_q)]), dtype=torch.int32)
+    ck = torch.tensor(np.concatenate([[0], np.cumsum(lens_k)]), dtype=torch.int32)
+    H = 2
+    q = seeded((int(cq[-1]), H, 32), 1, 0.5)
+    k, v = seeded((int(ck[-1]), H, 32), 2, 0.5), seeded((int(ck[-1]), H, 32), 3)
+    dout = seeded((int(cq[-1]), H, 32), 5)
+    table = seeded((32, H), 4, 0.1)
+    qf, kf, vf, tf = (t.clone().requires_grad_(True) for t in (q, k, v, table))
+    want = orc.attention_basic_varlen(qf, kf, vf, tf, cq, ck, causal=False)
+    (want * dout).sum().backward()
+    qc, kc, vc, tc = (t.cuda().requires_grad_(True) for t in (q, k, v, table))
+    out = t5b.flash_attention_with_fusing_bias_varlen(qc, kc, vc, tc, cq.cuda(), ck.cuda(), max(lens_q), max(lens_k),
+                                                      sm_scale=1.0)
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    for g, w, nm in ((qc.grad, qf.grad, "dq"), (kc.grad, kf.grad, "dk"), (vc.grad, vf.grad, "dv"),
+                     (tc.grad, tf.grad, "dtable")):
+        check_grad_close(g, w, "packed float32 " + nm, rel=2e-4, floor=0.05 if nm == "dtable" else 1e-6)
 
 
 def test_backward_with_empty_sides_returns_zero_gradients():

@@ -68,7 +68,7 @@ def _unit_stride_last(t):
 def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
                                      NUM_BUCKETS=32, MAX_DISTANCE=128, *, q_pos_offset=None,
                                      return_lse=False, kernel="auto", balance_last_wave=True):
-    """See `_dense_forward`; differentiable when an input requires grad (bf16/fp16, head dim 64)."""
+    """See `_dense_forward`; differentiable in q, k, v and the bias table."""
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _DenseAttention.apply(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset,
                                          kernel, balance_last_wave)
@@ -139,7 +139,7 @@ def flash_attention_with_fusing_bias_varlen(q, k, v, bias, cu_seqlens_q, cu_seql
                                             max_seqlen_q, max_seqlen_k, causal=False, sm_scale=None,
                                             NUM_BUCKETS=32, MAX_DISTANCE=128, *, return_lse=False,
                                             kernel="auto"):
-    """See `_varlen_forward`; differentiable when an input requires grad (bf16/fp16, head dim 64)."""
+    """See `_varlen_forward`; differentiable in q, k, v and the bias table."""
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _VarlenAttention.apply(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                                           causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, kernel)
@@ -240,8 +240,8 @@ def _attention_backward(keep, out, lse, dout, varlen):
     with torch.cuda.device(q.device):
         st = nat.lib().t5b_attention_bwd(g, nat.stream_ptr(q.device))
     if st == nat.ERR_UNSUPPORTED:
-        raise NotImplementedError("the attention backward runs on the tensor-core path only: bf16/fp16, "
-                                  "head dim 64, 16-byte aligned rows")
+        raise NotImplementedError("no backward kernel for this call (max_distance above 2048, or "
+                                  "kernel='tcgen05' on a shape its backward does not take: bf16/fp16, head dim 64)")
     nat.check(st, "flash_attention_with_fusing_bias (backward)")
     if dtable is not None:
         dtable = dtable[: table.shape[0]].to(table.dtype)

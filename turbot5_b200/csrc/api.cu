@@ -79,8 +79,9 @@ extern "C" int t5b_attention_bwd(const t5b_attn_bwd_args* g, void* stream) {
     const int st = make_bucket_spec(a->num_buckets, a->max_distance, a->causal ? 0 : 1, &spec);
     if (st != T5B_OK) return st;
   }
-  if (!sm100_bwd_supports(*g)) return T5B_ERR_UNSUPPORTED;
-  return sm100_attention_bwd(*g, spec, (cudaStream_t)stream);
+  if (a->kernel == T5B_KERNEL_TCGEN05 && !sm100_bwd_supports(*g)) return T5B_ERR_UNSUPPORTED;
+  if (a->kernel != T5B_KERNEL_SIMT && sm100_bwd_supports(*g)) return sm100_attention_bwd(*g, spec, (cudaStream_t)stream);
+  return simt_attention_bwd(*g, spec, (cudaStream_t)stream);
 }
 
 extern "C" int64_t t5b_attention_workspace_bytes(const t5b_attn_args* a) {

@@ -94,41 +94,6 @@ __global__ void bwd_delta_kernel(const AttnParams p, const BwdExtra e, long long
   }
 }
 
-// Sequence and tile of block `blk` in the concatenated per-sequence tile lists of `cu`
-// (ceil(len / tile) tiles each).  Called by one full warp; result valid in every lane.
-__device__ __forceinline__ bool find_seq_tile(const int32_t* cu, int B, int tile, int blk, int& seq, int& tile_in_seq) {
-  const int lane = threadIdx.x & 31;
-  int acc = 0;
-  for (int b0 = 0; b0 < B; b0 += 32) {
-    const int bb = b0 + lane;
-    int nt = 0;
-    if (bb < B) nt = (cu[bb + 1] - cu[bb] + tile - 1) / tile;
-    int incl = nt;
-    #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
-    }
-    const int excl = acc + incl - nt;
-    const bool mine = blk >= excl && blk < excl + nt;
-    const unsigned m = __ballot_sync(0xffffffffu, mine);
-    if (m) {
-      const int src = __ffs(m) - 1;
-      seq = b0 + src;
-      tile_in_seq = blk - __shfl_sync(0xffffffffu, excl, src);
-      return true;
-    }
-    acc += __shfl_sync(0xffffffffu, incl, 31);
-  }
-  return false;
-}
-
-// lse (natural log) -> log2 domain; rows that saw no key (-inf) or lie outside the tensor
-// get +inf, so that their probabilities come out as exactly 0
-__device__ __forceinline__ float lse_to_log2(float lse, bool valid) {
-  return (valid && lse > -INFINITY) ? lse * kLog2e : INFINITY;
-}
-
 enum {
   B_RES_FULL = 0,                    // the block's resident tiles (Q,dO | K,V)
   B_A_FULL = 1,                      // [STAGES] streamed tile A (K | Q)

@@ -125,6 +125,41 @@ __device__ __forceinline__ TileWork dense_tile(const AttnParams& p, int blk_x, i
   w.qpos0 = p.q_pos_offset + w.q_row0;
   return w;
 }
+// Sequence and tile of block `blk` in the concatenated per-sequence tile lists of `cu`
+// (ceil(len / tile) tiles each).  Called by one full warp; result valid in every lane.
+__device__ __forceinline__ bool find_seq_tile(const int32_t* cu, int B, int tile, int blk, int& seq, int& tile_in_seq) {
+  const int lane = threadIdx.x & 31;
+  int acc = 0;
+  for (int b0 = 0; b0 < B; b0 += 32) {
+    const int bb = b0 + lane;
+    int nt = 0;
+    if (bb < B) nt = (cu[bb + 1] - cu[bb] + tile - 1) / tile;
+    int incl = nt;
+    #pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int excl = acc + incl - nt;
+    const bool mine = blk >= excl && blk < excl + nt;
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (m) {
+      const int src = __ffs(m) - 1;
+      seq = b0 + src;
+      tile_in_seq = blk - __shfl_sync(0xffffffffu, excl, src);
+      return true;
+    }
+    acc += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  return false;
+}
+
+// lse (natural log) -> log2 domain; rows that saw no key (-inf) or lie outside the tensor
+// get +inf, so that their probabilities come out as exactly 0
+__device__ __forceinline__ float lse_to_log2(float lse, bool valid) {
+  return (valid && lse > -INFINITY) ? lse * kLog2e : INFINITY;
+}
+
 #endif
 
 bool sm100_supports(const t5b_attn_args& a);
@@ -132,5 +167,6 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
 int simt_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream);
 bool sm100_bwd_supports(const t5b_attn_bwd_args& g);
 int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cudaStream_t stream);
+int simt_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cudaStream_t stream);
 
 }  // namespace t5b
