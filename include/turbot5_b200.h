@@ -143,9 +143,16 @@ typedef struct {
   void* dq; void* dk; void* dv;
   float* dtable;
   float* delta;
+  /* Optional scratch (may be NULL), t5b_attention_bwd_workspace_bytes() bytes, 256-byte aligned,
+   * ALL ZERO before its first use (the kernels leave it all zero): lets the tensor-core kernels
+   * split the tiles of a partially filled last wave of blocks and add the partial gradients up
+   * in float32.  One buffer per stream in flight. */
+  void* workspace;
+  int64_t workspace_bytes;
 } t5b_attn_bwd_args;
 
 T5B_API int t5b_attention_bwd(const t5b_attn_bwd_args* args, void* stream);
+T5B_API int64_t t5b_attention_bwd_workspace_bytes(const t5b_attn_bwd_args* args);
 
 /* ---- split-KV flash decoding ---------------------------------------------------
  * Stands in for the split/merge semantics of flash_attn_v2_fwd

@@ -20,7 +20,7 @@ KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMT = 0, 1, 2
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
 SYMBOLS = ("t5b_status_string", "t5b_abi_version", "t5b_bucket_table_host", "t5b_bucket_indices",
-           "t5b_attention_fwd", "t5b_attention_workspace_bytes", "t5b_attention_bwd", "t5b_decode_workspace_bytes", "t5b_decode_num_splits",
+           "t5b_attention_fwd", "t5b_attention_workspace_bytes", "t5b_attention_bwd", "t5b_attention_bwd_workspace_bytes", "t5b_decode_workspace_bytes", "t5b_decode_num_splits",
            "t5b_decode_fwd", "t5b_decode_static_scratch_bytes", "t5b_decode_fwd_static_scratch",
            "t5b_rmsnorm_fwd", "t5b_rmsnorm_bwd", "t5b_unpad_plan", "t5b_gather_rows",
            "t5b_scatter_rows")
@@ -51,6 +51,7 @@ class AttnBwdArgs(C.Structure):
         ("do_stride_b", C.c_int64), ("do_stride_h", C.c_int64), ("do_stride_m", C.c_int64),
         ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
         ("dtable", C.c_void_p), ("delta", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -95,6 +96,8 @@ def lib():
     L.t5b_attention_fwd.argtypes = [C.POINTER(AttnArgs), C.c_void_p]
     L.t5b_attention_bwd.restype = C.c_int
     L.t5b_attention_bwd.argtypes = [C.POINTER(AttnBwdArgs), C.c_void_p]
+    L.t5b_attention_bwd_workspace_bytes.restype = C.c_int64
+    L.t5b_attention_bwd_workspace_bytes.argtypes = [C.POINTER(AttnBwdArgs)]
     L.t5b_attention_workspace_bytes.restype = C.c_int64
     L.t5b_attention_workspace_bytes.argtypes = [C.POINTER(AttnArgs)]
     L.t5b_decode_workspace_bytes.restype = C.c_int64

@@ -237,7 +237,12 @@ def _attention_backward(keep, out, lse, dout, varlen):
         dtable = torch.zeros((g.fwd.num_buckets, H), dtype=torch.float32, device=q.device)
     delta = torch.empty_like(lse)
     g.dtable, g.delta = nat.ptr(dtable), delta.data_ptr()
+    g.workspace, g.workspace_bytes = None, 0
     with torch.cuda.device(q.device):
+        need = nat.lib().t5b_attention_bwd_workspace_bytes(g)
+        if need > 0:
+            ws = _scratch(q.device, "attn_bwd", need)      # all zero at rest (the kernels restore it)
+            g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
         st = nat.lib().t5b_attention_bwd(g, nat.stream_ptr(q.device))
     if st == nat.ERR_UNSUPPORTED:
         raise NotImplementedError("no backward kernel for this call (max_distance above 2048, or "

@@ -84,6 +84,13 @@ extern "C" int t5b_attention_bwd(const t5b_attn_bwd_args* g, void* stream) {
   return simt_attention_bwd(*g, spec, (cudaStream_t)stream);
 }
 
+extern "C" int64_t t5b_attention_bwd_workspace_bytes(const t5b_attn_bwd_args* g) {
+  if (!g) return 0;
+  const t5b_attn_args* a = &g->fwd;
+  if (a->B <= 0 || a->H <= 0 || a->M <= 0 || a->N <= 0 || a->kernel == T5B_KERNEL_SIMT) return 0;
+  return sm100_bwd_workspace_bytes(*g);
+}
+
 extern "C" int64_t t5b_attention_workspace_bytes(const t5b_attn_args* a) {
   if (!a || a->B <= 0 || a->H <= 0 || a->M <= 0 || a->N <= 0) return 0;
   if (a->kernel == T5B_KERNEL_SIMT || !sm100_supports(*a)) return 0;

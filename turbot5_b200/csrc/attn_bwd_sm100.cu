@@ -49,6 +49,13 @@ struct BwdExtra {
   float* dtable;
   float* delta;
   float sm_scale;
+  // Last-wave balancing (dense, non-causal launches): blocks at or beyond *_tail_first share a
+  // tile *_parts ways along the streamed dimension; their partial gradients are additive (the
+  // log-sum-exp is global), so they meet in float32 scratch rows through atomics, and the last
+  // part to arrive (a counter per row half) rounds the row to the output and zeroes the scratch.
+  int32_t q_tail_first, q_parts, k_tail_first, k_parts;
+  int32_t* ws_cnt_q; float* ws_dq;
+  int32_t* ws_cnt_k; float* ws_dk; float* ws_dv;
 };
 
 struct __align__(16) Control {
@@ -130,9 +137,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   // ---- work item: as the forward kernel (query tile of a (batch, head) or packed sequence)
   TileWork* shared_work = reinterpret_cast<TileWork*>(&ctl->work[0]);
   TileWork w;
-  int h, batch_idx = 0;
+  int h, batch_idx = 0, part = 0, parts = 1, tail_slot = 0;
   if (p.cu_q == nullptr) {
-    const int tile_lin = (int)blockIdx.x;
+    int tile_lin = (int)blockIdx.x;
+    if (tile_lin >= e.q_tail_first) {
+      const int ee = tile_lin - e.q_tail_first;
+      parts = e.q_parts;
+      tail_slot = ee / parts;
+      part = ee - tail_slot * parts;
+      tile_lin = e.q_tail_first + tail_slot;
+    }
     const int tx = tile_lin % p.tiles_x;
     const int hb = tile_lin / p.tiles_x;
     h = hb % p.H;
@@ -152,7 +166,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const int k_row0 = w.k_row0, len_k = w.len_k, qpos0 = w.qpos0;
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
-  const int n_kv = kv_end > 0 ? (kv_end + BT - 1) / BT : 0;
+  const int n_kv_all = kv_end > 0 ? (kv_end + BT - 1) / BT : 0;
+  const int kv_per = (n_kv_all + parts - 1) / parts;
+  const int kv_first = min(part * kv_per, n_kv_all);      // this block's key tiles: [kv_first, kv_first + n_kv)
+  const int n_kv = min(n_kv_all, kv_first + kv_per) - kv_first;
 
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -215,10 +232,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const uint32_t ph = (uint32_t)((j / STAGES) & 1);
         if (j >= STAGES && !mbar_wait_bounded(bar(B_A_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
         mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
-        tma_load_4d(sK + s * SMALL_BYTES, &tmap_k, bar(B_A_FULL + s), 0, k_row0 + j * BT, h, b);
+        tma_load_4d(sK + s * SMALL_BYTES, &tmap_k, bar(B_A_FULL + s), 0, k_row0 + (kv_first + j) * BT, h, b);
         if (j >= STAGES && !mbar_wait_bounded(bar(B_B_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
         mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
-        tma_load_4d(sV + s * SMALL_BYTES, &tmap_v, bar(B_B_FULL + s), 0, k_row0 + j * BT, h, b);
+        tma_load_4d(sV + s * SMALL_BYTES, &tmap_v, bar(B_B_FULL + s), 0, k_row0 + (kv_first + j) * BT, h, b);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -285,7 +302,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     bool ok = true;
 
     for (int j = 0; j < n_kv; ++j) {
-      const int n0 = j * BT;
+      const int n0 = (kv_first + j) * BT;
       const int c0 = half * 32;
       if (!mbar_wait_bounded_warp(bar(B_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
@@ -372,14 +389,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       uint8_t* drow = reinterpret_cast<uint8_t*>(e.dq) + half * 64 +
                       2 * ((int64_t)b * p.q_stride_b + (int64_t)h * p.q_stride_h + row * p.q_stride_m);
       const float sc = e.sm_scale;
+      float o[32];
       #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint4 w4;
-        w4.x = pack2<kBf16>(__uint_as_float(v[8 * i + 0]) * sc, __uint_as_float(v[8 * i + 1]) * sc);
-        w4.y = pack2<kBf16>(__uint_as_float(v[8 * i + 2]) * sc, __uint_as_float(v[8 * i + 3]) * sc);
-        w4.z = pack2<kBf16>(__uint_as_float(v[8 * i + 4]) * sc, __uint_as_float(v[8 * i + 5]) * sc);
-        w4.w = pack2<kBf16>(__uint_as_float(v[8 * i + 6]) * sc, __uint_as_float(v[8 * i + 7]) * sc);
-        if (row_ok) *reinterpret_cast<uint4*>(drow + i * 16) = w4;
+      for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * sc;
+      bool write_out = row_ok;
+      if (parts > 1 && row_ok) {
+        float* acc = e.ws_dq + ((int64_t)tail_slot * BM + r) * HD + half * 32;
+        #pragma unroll
+        for (int i = 0; i < 32; ++i) atomicAdd(acc + i, o[i]);
+        __threadfence();
+        int* counter = e.ws_cnt_q + ((int64_t)tail_slot * BM + r) * 2 + half;
+        write_out = (atomicAdd(counter, 1) == parts - 1);
+        if (write_out) {
+          __threadfence();
+          #pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 t4 = __ldcg(reinterpret_cast<const float4*>(acc) + i);
+            o[4 * i] = t4.x; o[4 * i + 1] = t4.y; o[4 * i + 2] = t4.z; o[4 * i + 3] = t4.w;
+            reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          *counter = 0;        // scratch and counter are left as they were found: zero
+        }
+      }
+      if (write_out) {
+        #pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 w4;
+          w4.x = pack2<kBf16>(o[8 * i + 0], o[8 * i + 1]);
+          w4.y = pack2<kBf16>(o[8 * i + 2], o[8 * i + 3]);
+          w4.z = pack2<kBf16>(o[8 * i + 4], o[8 * i + 5]);
+          w4.w = pack2<kBf16>(o[8 * i + 6], o[8 * i + 7]);
+          *reinterpret_cast<uint4*>(drow + i * 16) = w4;
+        }
       }
     }
     if (has_bias) {
@@ -439,12 +480,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // ---- work item: a 128-key tile of one (batch, head) or packed sequence
-  int h, b = 0, batch_idx = 0;
+  int h, b = 0, batch_idx = 0, part = 0, parts = 1, tail_slot = 0;
   int key0;            // first key of the tile inside its sequence
   int k_row0 = 0, len_k, q_row0 = 0, len_q, q_off;
   if (p.cu_k == nullptr) {
     const int tiles_k = (p.N + BM - 1) / BM;
-    const int tile_lin = (int)blockIdx.x;
+    int tile_lin = (int)blockIdx.x;
+    if (tile_lin >= e.k_tail_first) {
+      const int ee = tile_lin - e.k_tail_first;
+      parts = e.k_parts;
+      tail_slot = ee / parts;
+      part = ee - tail_slot * parts;
+      tile_lin = e.k_tail_first + tail_slot;
+    }
     const int tx = tile_lin % tiles_k;
     const int hb = tile_lin / tiles_k;
     h = hb % p.H;
@@ -471,7 +519,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   int i_first = 0;
   if (p.causal) i_first = max(0, key0 - q_off) / BT;
   const int n_qt_all = (len_q + BT - 1) / BT;
-  const int n_qt = max(0, n_qt_all - i_first);
+  int n_qt = max(0, n_qt_all - i_first);
+  if (parts > 1) {       // this block's share of the query tiles
+    const int per = (n_qt + parts - 1) / parts;
+    const int first = min(part * per, n_qt);
+    n_qt = min(n_qt, first + per) - first;
+    i_first += first;
+  }
 
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -712,14 +766,38 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         }
         const float sc = t == 0 ? 1.f : e.sm_scale;
         uint8_t* dst = t == 0 ? dvrow : dkrow;
+        float o[32];
         #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 w4;
-          w4.x = pack2<kBf16>(__uint_as_float(v[8 * i + 0]) * sc, __uint_as_float(v[8 * i + 1]) * sc);
-          w4.y = pack2<kBf16>(__uint_as_float(v[8 * i + 2]) * sc, __uint_as_float(v[8 * i + 3]) * sc);
-          w4.z = pack2<kBf16>(__uint_as_float(v[8 * i + 4]) * sc, __uint_as_float(v[8 * i + 5]) * sc);
-          w4.w = pack2<kBf16>(__uint_as_float(v[8 * i + 6]) * sc, __uint_as_float(v[8 * i + 7]) * sc);
-          if (key_ok) *reinterpret_cast<uint4*>(dst + i * 16) = w4;
+        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * sc;
+        bool write_out = key_ok;
+        if (parts > 1 && key_ok) {
+          float* acc = (t == 0 ? e.ws_dv : e.ws_dk) + ((int64_t)tail_slot * BM + r) * HD + half * 32;
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) atomicAdd(acc + i, o[i]);
+          __threadfence();
+          int* counter = e.ws_cnt_k + (((int64_t)tail_slot * BM + r) * 2 + half) * 2 + t;
+          write_out = (atomicAdd(counter, 1) == parts - 1);
+          if (write_out) {
+            __threadfence();
+            #pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 t4 = __ldcg(reinterpret_cast<const float4*>(acc) + i);
+              o[4 * i] = t4.x; o[4 * i + 1] = t4.y; o[4 * i + 2] = t4.z; o[4 * i + 3] = t4.w;
+              reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            *counter = 0;
+          }
+        }
+        if (write_out) {
+          #pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 w4;
+            w4.x = pack2<kBf16>(o[8 * i + 0], o[8 * i + 1]);
+            w4.y = pack2<kBf16>(o[8 * i + 2], o[8 * i + 3]);
+            w4.z = pack2<kBf16>(o[8 * i + 4], o[8 * i + 5]);
+            w4.w = pack2<kBf16>(o[8 * i + 6], o[8 * i + 7]);
+            *reinterpret_cast<uint4*>(dst + i * 16) = w4;
+          }
         }
       }
     }
@@ -735,6 +813,56 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 }
 
 }  // namespace sm100b
+
+// Last-wave plan of the two backward kernels (see BwdExtra).  The counter areas have a fixed
+// size per device; the float32 rows follow.  Everything in the scratch is zero between launches.
+struct BwdPlan {
+  int q_tail_first, q_parts, q_rem, k_tail_first, k_parts, k_rem;
+  int64_t cnt_bytes, dq_bytes, dk_bytes;
+  int64_t bytes() const { return (q_parts > 1 || k_parts > 1) ? 2 * cnt_bytes + dq_bytes + 2 * dk_bytes : 0; }
+};
+
+static BwdPlan sm100_bwd_plan(const t5b_attn_args& a) {
+  using namespace sm100b;
+  BwdPlan t;
+  const long long nq = (long long)((a.M + BM - 1) / BM) * a.H * a.B;
+  const long long nk = (long long)((a.N + BM - 1) / BM) * a.H * a.B;
+  t.q_tail_first = (int)(nq > 0x7fffffffLL ? 0x7fffffff : nq);
+  t.k_tail_first = (int)(nk > 0x7fffffffLL ? 0x7fffffff : nk);
+  t.q_parts = t.k_parts = 1;
+  t.q_rem = t.k_rem = 0;
+  t.cnt_bytes = t.dq_bytes = t.dk_bytes = 0;
+  if (a.cu_seqlens_q != nullptr || a.causal || nq > 0x3fffffffLL || nk > 0x3fffffffLL) return t;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+    cudaGetLastError();
+    return t;
+  }
+  const int slots = 2 * sms;
+  auto al = [](int64_t x) { return (x + 255) / 256 * 256; };
+  auto split = [&](long long n_total, int n_stream, int& tail_first, int& parts, int& rem) {
+    rem = (int)(n_total % slots);
+    if (rem == 0) return;
+    int pp = slots / rem;
+    if (pp > n_stream / 16) pp = n_stream / 16;   // at least 16 streamed tiles (1024 rows) per part
+    if (pp > 8) pp = 8;
+    if (pp < 2) { rem = 0; return; }
+    parts = pp;
+    tail_first = (int)(n_total - rem);
+  };
+  split(nq, (a.N + BT - 1) / BT, t.q_tail_first, t.q_parts, t.q_rem);
+  split(nk, (a.M + BT - 1) / BT, t.k_tail_first, t.k_parts, t.k_rem);
+  t.cnt_bytes = al((int64_t)slots * BM * 2 * 2 * 4);
+  t.dq_bytes = al((int64_t)t.q_rem * BM * HD * 4);
+  t.dk_bytes = al((int64_t)t.k_rem * BM * HD * 4);
+  return t;
+}
+
+int64_t sm100_bwd_workspace_bytes(const t5b_attn_bwd_args& g) {
+  if (!sm100_bwd_supports(g)) return 0;
+  return sm100_bwd_plan(g.fwd).bytes();
+}
 
 // True when the tensor-core backward can take this problem.
 bool sm100_bwd_supports(const t5b_attn_bwd_args& g) {
@@ -759,6 +887,26 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
   e.do_stride_b = g.do_stride_b; e.do_stride_h = g.do_stride_h; e.do_stride_m = g.do_stride_m;
   e.dq = g.dq; e.dk = g.dk; e.dv = g.dv;
   e.dtable = g.dtable; e.delta = g.delta; e.sm_scale = a.sm_scale;
+  BwdPlan plan = sm100_bwd_plan(a);
+  const bool use_ws = plan.bytes() > 0 && g.workspace != nullptr && g.workspace_bytes >= plan.bytes() &&
+                      ((uintptr_t)g.workspace & 255) == 0;
+  if (!use_ws) {
+    plan.q_parts = plan.k_parts = 1;
+    plan.q_tail_first = plan.k_tail_first = 0x7fffffff;
+    plan.q_rem = plan.k_rem = 0;
+  }
+  if (plan.q_parts <= 1) plan.q_tail_first = 0x7fffffff;
+  if (plan.k_parts <= 1) plan.k_tail_first = 0x7fffffff;
+  e.q_tail_first = plan.q_tail_first; e.q_parts = plan.q_parts;
+  e.k_tail_first = plan.k_tail_first; e.k_parts = plan.k_parts;
+  {
+    char* ws = use_ws ? (char*)g.workspace : nullptr;
+    e.ws_cnt_q = (int32_t*)ws;
+    e.ws_cnt_k = (int32_t*)(ws ? ws + plan.cnt_bytes : nullptr);
+    e.ws_dq = (float*)(ws ? ws + 2 * plan.cnt_bytes : nullptr);
+    e.ws_dk = (float*)(ws ? ws + 2 * plan.cnt_bytes + plan.dq_bytes : nullptr);
+    e.ws_dv = (float*)(ws ? ws + 2 * plan.cnt_bytes + plan.dq_bytes + plan.dk_bytes : nullptr);
+  }
 
   const long long rows_q = varlen ? (long long)a.total_q : (long long)a.B * a.M;
   const long long rows_k = varlen ? (long long)a.total_k : (long long)a.B * a.N;
@@ -811,8 +959,10 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
     gq = dim3((unsigned)((long long)a.total_q / BM + a.B), (unsigned)a.H, 1);
     gk = dim3((unsigned)((long long)a.total_k / BM + a.B), (unsigned)a.H, 1);
   } else {
-    const long long nq = (long long)p.tiles_x * a.H * a.B;
-    const long long nk = (long long)((a.N + BM - 1) / BM) * a.H * a.B;
+    long long nq = (long long)p.tiles_x * a.H * a.B;
+    long long nk = (long long)((a.N + BM - 1) / BM) * a.H * a.B;
+    if (plan.q_parts > 1) nq = plan.q_tail_first + (long long)plan.q_rem * plan.q_parts;
+    if (plan.k_parts > 1) nk = plan.k_tail_first + (long long)plan.k_rem * plan.k_parts;
     if (nq > 0x7fffffffLL || nk > 0x7fffffffLL) return T5B_ERR_SHAPE;
     gq = dim3((unsigned)nq, 1, 1);
     gk = dim3((unsigned)nk, 1, 1);

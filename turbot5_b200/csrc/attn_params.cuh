@@ -167,6 +167,7 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
 int simt_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream);
 bool sm100_bwd_supports(const t5b_attn_bwd_args& g);
 int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cudaStream_t stream);
+int64_t sm100_bwd_workspace_bytes(const t5b_attn_bwd_args& g);
 int simt_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cudaStream_t stream);
 
 }  // namespace t5b
