@@ -131,8 +131,8 @@ T5B_API int64_t t5b_attention_workspace_bytes(const t5b_attn_args* args);
  *   dtable  float32 [num_buckets, H], contiguous; the gradient of the bias table is ADDED to
  *           it (the caller zeroes it); NULL when fwd.table is NULL.
  *   delta   float32 scratch of the shape of lse.
- * bf16/fp16 with head dim 64 and 16-byte aligned rows run on the tensor-core kernels; everything
- * else the forward accepts (float32, head dims 16/32/128) on CUDA-core kernels; fwd.kernel
+ * bf16/fp16 with head dim 64 or 128 and 16-byte aligned rows run on the tensor-core kernels;
+ * everything else the forward accepts (float32, head dims 16/32) on CUDA-core kernels; fwd.kernel
  * selects as in the forward.  M > 0 and N > 0 (T5B_ERR_UNSUPPORTED otherwise: the gradients are
  * zero and the caller writes them).
  */

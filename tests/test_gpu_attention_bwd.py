@@ -141,12 +141,61 @@ def test_cuda_core_backward_vs_oracle(dt, D, B, H, M, N, causal, off):
     dout = seeded((B, H, M, D), 5, dtype=dt)
     table = seeded((32, H), 4, 0.1, dtype=dt)
     want = _oracle_grads(q, k, v, table, dout, causal=causal, q_pos_offset=off)
-    kw = dict(kernel="simt") if (dt != torch.float32 and D == 64) else {}
+    kw = dict(kernel="simt") if (dt != torch.float32 and D in (64, 128)) else {}
     got = _cuda_grads(q, k, v, table, dout, dt, causal=causal, q_pos_offset=off, **kw)
     rel = 2e-4 if dt == torch.float32 else 1e-2
     check_close(got[0], want[0], dt, "out")
     for g, w, nm in zip(got[1:], want[1:], ("dq", "dk", "dv", "dtable")):
         check_grad_close(g, w, f"{dt} d{D} {nm}", rel=rel, floor=(0.05 if dt == torch.float32 else 2.0) if nm == "dtable" else 1e-6)
+
+
+CASES_D128 = [
+    (2, 3, 512, 512, False, None),
+    (1, 2, 777, 777, True, None),
+    (2, 2, 128, 1024, False, 0),
+    (1, 2, 200, 555, True, None),
+    (1, 2, 300, 300, False, 4000),
+    (1, 2, 2048, 2048, False, None),     # last wave split
+]
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,M,N,causal,off", CASES_D128)
+def test_head_dim_128_tensor_core_backward_vs_oracle(B, H, M, N, causal, off, dt):
+    q = seeded((B, H, M, 128), 1, 0.35, dtype=dt)
+    k = seeded((B, H, N, 128), 2, 0.35, dtype=dt)
+    v = seeded((B, H, N, 128), 3, dtype=dt)
+    dout = seeded((B, H, M, 128), 5, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    want = _oracle_grads(q, k, v, table, dout, causal=causal, q_pos_offset=off)
+    got = _cuda_grads(q, k, v, table, dout, dt, causal=causal, q_pos_offset=off, kernel="tcgen05")
+    what = f"d128 {(B, H, M, N, causal, off)}"
+    check_close(got[0], want[0], dt, what + " out")
+    for g, w, nm in zip(got[1:], want[1:], ("dq", "dk", "dv", "dtable")):
+        check_grad_close(g, w, what + " " + nm, floor=2.0 if nm == "dtable" else 1e-6)
+
+
+def test_head_dim_128_backward_packed_sequences():
+    t5b = _ops()
+    dt = torch.bfloat16
+    lens = [5, 128, 0, 129, 300, 1, 257, 64]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    T, H = int(cu[-1]), 2
+    q, k, v = seeded((T, H, 128), 1, 0.35, dtype=dt), seeded((T, H, 128), 2, 0.35, dtype=dt), seeded((T, H, 128), 3, dtype=dt)
+    dout = seeded((T, H, 128), 5, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    qf, kf, vf, tf = (t.float().clone().requires_grad_(True) for t in (q, k, v, table))
+    want = orc.attention_basic_varlen(qf, kf, vf, tf, cu, cu, causal=True)
+    (want * dout.float()).sum().backward()
+    qc, kc, vc, tc = (t.cuda().requires_grad_(True) for t in (q, k, v, table))
+    out = t5b.flash_attention_with_fusing_bias_varlen(qc, kc, vc, tc, cu.cuda(), cu.cuda(), max(lens), max(lens),
+                                                      causal=True, sm_scale=1.0, kernel="tcgen05")
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    for g, w, nm in ((qc.grad, qf.grad, "dq"), (kc.grad, kf.grad, "dk"), (vc.grad, vf.grad, "dv"),
+                     (tc.grad, tf.grad, "dtable")):
+        check_grad_close(g, w, "d128 packed " + nm, floor=2.0 if nm == "dtable" else 1e-6)
 
 
 def test_cuda_core_backward_packed_sequences_float32():

@@ -1,4 +1,4 @@
-// Backward of the fused relative-position-bias attention for sm_100a (bf16/fp16, head dim 64).
+// Backward of the fused relative-position-bias attention for sm_100a (bf16/fp16, head dim 64 or 128).
 //
 // Three launches, as the reference's backward (src/turbot5/ops/fused_bias_attention.py:62-147):
 //
@@ -31,16 +31,27 @@ using sm100::pack2;
 
 constexpr int BM = 128;            // rows of the tile a block owns (MMA M)
 constexpr int BT = 64;             // rows of a streamed tile
-constexpr int HD = 64;
 constexpr int STAGES = 3;            // the streamed tiles stay resident until the LAST product of their step
-constexpr int BIG_BYTES = BM * 128;     // [128 rows][64 dims] 16-bit, 128-byte swizzle
-constexpr int SMALL_BYTES = BT * 128;   // [64 rows][64 dims]
 constexpr int NUM_THREADS = 320;
 constexpr int WARP_TMA = 8, WARP_MMA = 9;
-constexpr int TMEM_COLS = 256;
 constexpr int LUT_PAD = BM + BT;
 constexpr int MAX_BUCKETS = 2 * kMaxBucketsPerSide;
-constexpr int SMEM_TILES = 2 * BIG_BYTES + 2 * STAGES * SMALL_BYTES;   // 80 KB in both kernels
+
+// Geometry per head dim.  A row of 128 dims is two 128-byte-swizzled sub-tiles of 64 dims (two TMA
+// boxes; the K loop of the first products walks both; an MN-major operand spans two swizzle atoms,
+// leading byte offset = one sub-tile).  Head dim 64: 80 KB of tiles and <= 256 TMEM columns, two
+// blocks per SM.  Head dim 128: 160 KB and up to 384 columns, one block per SM.
+template <int HD_>
+struct BGeo {
+  static constexpr int HD = HD_;
+  static constexpr int NSUB = HD_ / 64;
+  static constexpr int SUB_BIG = BM * 128, SUB_SMALL = BT * 128;
+  static constexpr int BIG_BYTES = NSUB * SUB_BIG, SMALL_BYTES = NSUB * SUB_SMALL;
+  static constexpr int SMEM_TILES = 2 * BIG_BYTES + 2 * STAGES * SMALL_BYTES;
+  static constexpr int TMEM_COLS = HD_ == 64 ? 256 : 512;
+  static constexpr int OH = HD_ / 2;                      // output columns per softmax thread
+  static constexpr int BLOCKS_PER_SM = HD_ == 64 ? 2 : 1;
+};
 
 struct BwdExtra {
   const void* dout;
@@ -67,9 +78,10 @@ struct __align__(16) Control {
   float hist[MAX_BUCKETS];      // dq kernel: bias-table gradient of this block
 };
 
+template <int HD>
 __host__ __device__ inline size_t smem_bytes(int lut_entries) {
   // float bias per delta, float gradient per delta, int16 bucket per delta
-  return 1024 + SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 10;
+  return 1024 + BGeo<HD>::SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 10;
 }
 
 // ---------------------------------------------------------------- delta = rowsum(dO o O)
@@ -94,7 +106,8 @@ __global__ void bwd_delta_kernel(const AttnParams p, const BwdExtra e, long long
     }
     const T* o = reinterpret_cast<const T*>(p.out) + o_off;
     const T* d = reinterpret_cast<const T*>(e.dout) + do_off;
-    float s = to_float(o[lane]) * to_float(d[lane]) + to_float(o[lane + 32]) * to_float(d[lane + 32]);
+    float s = 0.f;
+    for (int c = lane; c < p.D; c += 32) s = fmaf(to_float(o[c]), to_float(d[c]), s);
     #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
     if (lane == 0) e.delta[i] = s;      // same indexing as lse: (b,h,m) dense, (row,h) packed
@@ -116,13 +129,17 @@ enum {
 static_assert(B_NUM <= 24, "barrier slots");
 
 // ======================================================================== dQ and dtable
-template <bool kBf16>
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+template <bool kBf16, int HD>
+__global__ void __launch_bounds__(NUM_THREADS, (HD == 64 ? 2 : 1))
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                    const __grid_constant__ AttnParams p, const __grid_constant__ BwdExtra e,
                    const __grid_constant__ BucketSpec spec) {
-  constexpr int COL_S = 0, COL_DP = 64, COL_DS = 128, COL_DQ = 160;
+  using G = BGeo<HD>;
+  constexpr int NSUB = G::NSUB, SUB_BIG = G::SUB_BIG, SUB_SMALL = G::SUB_SMALL;
+  constexpr int BIG_BYTES = G::BIG_BYTES, SMALL_BYTES = G::SMALL_BYTES, SMEM_TILES = G::SMEM_TILES;
+  constexpr int TMEM_COLS = G::TMEM_COLS, OH = G::OH;
+  constexpr int COL_S = 0, COL_DP = 64, COL_DS = 128, COL_DQ = 160;      // dQ: HD columns from 160
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -225,37 +242,50 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   if (warp == WARP_TMA) {
     if (lane == 0 && n_kv > 0) {
       mbar_expect_tx(bar(B_RES_FULL), 2 * BIG_BYTES);
-      tma_load_4d(sQ, &tmap_q, bar(B_RES_FULL), 0, q_row0, h, b);
-      tma_load_4d(sDO, &tmap_do, bar(B_RES_FULL), 0, q_row0, h, b);
+      #pragma unroll
+      for (int u = 0; u < NSUB; ++u) {
+        tma_load_4d(sQ + u * SUB_BIG, &tmap_q, bar(B_RES_FULL), 64 * u, q_row0, h, b);
+        tma_load_4d(sDO + u * SUB_BIG, &tmap_do, bar(B_RES_FULL), 64 * u, q_row0, h, b);
+      }
       for (int j = 0; j < n_kv; ++j) {
         const int s = j % STAGES;
         const uint32_t ph = (uint32_t)((j / STAGES) & 1);
         if (j >= STAGES && !mbar_wait_bounded(bar(B_A_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
         mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
-        tma_load_4d(sK + s * SMALL_BYTES, &tmap_k, bar(B_A_FULL + s), 0, k_row0 + (kv_first + j) * BT, h, b);
+        #pragma unroll
+        for (int u = 0; u < NSUB; ++u)
+          tma_load_4d(sK + s * SMALL_BYTES + u * SUB_SMALL, &tmap_k, bar(B_A_FULL + s), 64 * u, k_row0 + (kv_first + j) * BT, h, b);
         if (j >= STAGES && !mbar_wait_bounded(bar(B_B_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
         mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
-        tma_load_4d(sV + s * SMALL_BYTES, &tmap_v, bar(B_B_FULL + s), 0, k_row0 + (kv_first + j) * BT, h, b);
+        #pragma unroll
+        for (int u = 0; u < NSUB; ++u)
+          tma_load_4d(sV + s * SMALL_BYTES + u * SUB_SMALL, &tmap_v, bar(B_B_FULL + s), 64 * u, k_row0 + (kv_first + j) * BT, h, b);
       }
     }
   } else if (warp == WARP_MMA) {
     if (lane == 0 && n_kv > 0) {
       constexpr uint32_t IDESC_SS = make_idesc_f16(kBf16, kBf16, BM, BT, false, false);   // 128 x 64 keys
       constexpr uint32_t IDESC_DQ = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);    // K as MN-major B
-      const uint64_t dq_ = make_smem_desc_sw128(sQ, 16, 1024);
-      const uint64_t ddo = make_smem_desc_sw128(sDO, 16, 1024);
       auto issue_s = [&](int j) -> bool {
         const int s = j % STAGES;
         const uint32_t ph = (uint32_t)((j / STAGES) & 1);
         if (!mbar_wait_bounded(bar(B_A_FULL + s), ph, abort_flag)) return false;
         if (!mbar_wait_bounded(bar(B_B_FULL + s), ph, abort_flag)) return false;
         tc_fence_after();
-        const uint64_t dk = make_smem_desc_sw128(sK + s * SMALL_BYTES, 16, 1024);
-        const uint64_t dv = make_smem_desc_sw128(sV + s * SMALL_BYTES, 16, 1024);
         #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) umma_ss(tmem + COL_S, dq_ + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), IDESC_SS, k > 0);
+        for (int u = 0; u < NSUB; ++u) {
+          const uint64_t dq_ = make_smem_desc_sw128(sQ + u * SUB_BIG, 16, 1024);
+          const uint64_t dk = make_smem_desc_sw128(sK + s * SMALL_BYTES + u * SUB_SMALL, 16, 1024);
+          #pragma unroll
+          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_S, dq_ + (uint64_t)(2 * k), dk + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
+        }
         #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) umma_ss(tmem + COL_DP, ddo + (uint64_t)(2 * k), dv + (uint64_t)(2 * k), IDESC_SS, k > 0);
+        for (int u = 0; u < NSUB; ++u) {
+          const uint64_t ddo = make_smem_desc_sw128(sDO + u * SUB_BIG, 16, 1024);
+          const uint64_t dv = make_smem_desc_sw128(sV + s * SMALL_BYTES + u * SUB_SMALL, 16, 1024);
+          #pragma unroll
+          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_DP, ddo + (uint64_t)(2 * k), dv + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
+        }
         tc_commit(bar(B_S_FULL));
         tc_commit(bar(B_B_EMPTY + s));      // V is not needed again
         return true;
@@ -275,7 +305,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         // dQ += dS K: the K tile [64 keys][64 dims] read as an MN-major B operand
         #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
-          const uint64_t dkm = make_smem_desc_sw128(sK + s * SMALL_BYTES + k * 2048, 16, 1024);
+          const uint64_t dkm = make_smem_desc_sw128(sK + s * SMALL_BYTES + k * 2048, NSUB > 1 ? SUB_SMALL : 16, 1024);
           umma_ts(tmem + COL_DQ, tmem + COL_DS + k * 8, dkm, IDESC_DQ, (j > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar(B_O_DONE));
@@ -289,7 +319,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const uint32_t tS = tmem + lane_base + COL_S + half * 32;
     const uint32_t tDP = tmem + lane_base + COL_DP + half * 32;
     const uint32_t tDS = tmem + lane_base + COL_DS + half * 16;
-    const uint32_t tDQ = tmem + lane_base + COL_DQ + half * 32;
+    const uint32_t tDQ = tmem + lane_base + COL_DQ + half * OH;
     const float scale = p.scale_log2;
     const int qpos = qpos0 + r;
     const bool row_ok = r < rows_in_tile;
@@ -378,32 +408,35 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tc_fence_after();
     }
     if (ok) {          // warp-uniform: tcgen05.ld is a whole-warp instruction; only the stores depend on the row
-      uint32_t v[32];
-      if (n_kv > 0) {
-        tmem_ld_x32(tDQ, v);
-        tmem_ld_wait();
-      } else {
-        #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0u;
-      }
-      uint8_t* drow = reinterpret_cast<uint8_t*>(e.dq) + half * 64 +
-                      2 * ((int64_t)b * p.q_stride_b + (int64_t)h * p.q_stride_h + row * p.q_stride_m);
       const float sc = e.sm_scale;
-      float o[32];
+      float o[OH];
       #pragma unroll
-      for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * sc;
+      for (int c = 0; c < OH / 32; ++c) {
+        uint32_t v[32];
+        if (n_kv > 0) {
+          tmem_ld_x32(tDQ + 32 * c, v);
+          tmem_ld_wait();
+        } else {
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        #pragma unroll
+        for (int i = 0; i < 32; ++i) o[32 * c + i] = __uint_as_float(v[i]) * sc;
+      }
+      uint8_t* drow = reinterpret_cast<uint8_t*>(e.dq) + half * OH * 2 +
+                      2 * ((int64_t)b * p.q_stride_b + (int64_t)h * p.q_stride_h + row * p.q_stride_m);
       bool write_out = row_ok;
       if (parts > 1 && row_ok) {
-        float* acc = e.ws_dq + ((int64_t)tail_slot * BM + r) * HD + half * 32;
+        float* acc = e.ws_dq + ((int64_t)tail_slot * BM + r) * HD + half * OH;
         #pragma unroll
-        for (int i = 0; i < 32; ++i) atomicAdd(acc + i, o[i]);
+        for (int i = 0; i < OH; ++i) atomicAdd(acc + i, o[i]);
         __threadfence();
         int* counter = e.ws_cnt_q + ((int64_t)tail_slot * BM + r) * 2 + half;
         write_out = (atomicAdd(counter, 1) == parts - 1);
         if (write_out) {
           __threadfence();
           #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < OH / 4; ++i) {
             const float4 t4 = __ldcg(reinterpret_cast<const float4*>(acc) + i);
             o[4 * i] = t4.x; o[4 * i + 1] = t4.y; o[4 * i + 2] = t4.z; o[4 * i + 3] = t4.w;
             reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -413,7 +446,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
       if (write_out) {
         #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < OH / 8; ++i) {
           uint4 w4;
           w4.x = pack2<kBf16>(o[8 * i + 0], o[8 * i + 1]);
           w4.y = pack2<kBf16>(o[8 * i + 2], o[8 * i + 3]);
@@ -458,8 +491,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 }
 
 // ======================================================================== dK and dV
-template <bool kBf16>
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+template <bool kBf16, int HD>
+__global__ void __launch_bounds__(NUM_THREADS, (HD == 64 ? 2 : 1))
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                     const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                     const __grid_constant__ AttnParams p, const __grid_constant__ BwdExtra e,
@@ -467,7 +500,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   // tensor memory: S^T and dP^T (64 fp32 columns each, keys in the lanes); P^T and dS^T are
   // written over them in place: the 32 query columns of row half q sit, packed, in the first
   // 16 columns of that half's own 32 (a K=16 step of the second MMA takes any column address)
-  constexpr int COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 192;
+  using G = BGeo<HD>;
+  constexpr int NSUB = G::NSUB, SUB_BIG = G::SUB_BIG, SUB_SMALL = G::SUB_SMALL;
+  constexpr int BIG_BYTES = G::BIG_BYTES, SMALL_BYTES = G::SMALL_BYTES, SMEM_TILES = G::SMEM_TILES;
+  constexpr int TMEM_COLS = G::TMEM_COLS, OH = G::OH;
+  constexpr int COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 128 + HD;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -573,8 +610,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     if (n_qt > 0) {
       if (lane == 0) {
         mbar_expect_tx(bar(B_RES_FULL), 2 * BIG_BYTES);
-        tma_load_4d(sK, &tmap_k, bar(B_RES_FULL), 0, k_row0 + key0, h, b);
-        tma_load_4d(sV, &tmap_v, bar(B_RES_FULL), 0, k_row0 + key0, h, b);
+        #pragma unroll
+        for (int u = 0; u < NSUB; ++u) {
+          tma_load_4d(sK + u * SUB_BIG, &tmap_k, bar(B_RES_FULL), 64 * u, k_row0 + key0, h, b);
+          tma_load_4d(sV + u * SUB_BIG, &tmap_v, bar(B_RES_FULL), 64 * u, k_row0 + key0, h, b);
+        }
       }
       bool okp = true;
       for (int i = 0; i < n_qt; ++i) {
@@ -589,9 +629,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         }
         if (lane == 0) {
           mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
-          tma_load_4d(sQ + s * SMALL_BYTES, &tmap_q, bar(B_A_FULL + s), 0, q_row0 + m0, h, b);
+          #pragma unroll
+          for (int u = 0; u < NSUB; ++u)
+            tma_load_4d(sQ + s * SMALL_BYTES + u * SUB_SMALL, &tmap_q, bar(B_A_FULL + s), 64 * u, q_row0 + m0, h, b);
           mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
-          tma_load_4d(sDO + s * SMALL_BYTES, &tmap_do, bar(B_B_FULL + s), 0, q_row0 + m0, h, b);
+          #pragma unroll
+          for (int u = 0; u < NSUB; ++u)
+            tma_load_4d(sDO + s * SMALL_BYTES + u * SUB_SMALL, &tmap_do, bar(B_B_FULL + s), 64 * u, q_row0 + m0, h, b);
         }
         #pragma unroll
         for (int u = 0; u < 2; ++u) {
@@ -611,20 +655,26 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     if (lane == 0 && n_qt > 0) {
       constexpr uint32_t IDESC_SS = make_idesc_f16(kBf16, kBf16, BM, BT, false, false);   // 128 keys x 64 queries
       constexpr uint32_t IDESC_TS = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);    // dO / Q as MN-major B
-      const uint64_t dk = make_smem_desc_sw128(sK, 16, 1024);
-      const uint64_t dv = make_smem_desc_sw128(sV, 16, 1024);
       auto issue_s = [&](int i) -> bool {
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)((i / STAGES) & 1);
         if (!mbar_wait_bounded(bar(B_A_FULL + s), ph, abort_flag)) return false;
         if (!mbar_wait_bounded(bar(B_B_FULL + s), ph, abort_flag)) return false;
         tc_fence_after();
-        const uint64_t dq_ = make_smem_desc_sw128(sQ + s * SMALL_BYTES, 16, 1024);
-        const uint64_t ddo = make_smem_desc_sw128(sDO + s * SMALL_BYTES, 16, 1024);
         #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) umma_ss(tmem + COL_ST, dk + (uint64_t)(2 * k), dq_ + (uint64_t)(2 * k), IDESC_SS, k > 0);
+        for (int u = 0; u < NSUB; ++u) {
+          const uint64_t dk = make_smem_desc_sw128(sK + u * SUB_BIG, 16, 1024);
+          const uint64_t dq_ = make_smem_desc_sw128(sQ + s * SMALL_BYTES + u * SUB_SMALL, 16, 1024);
+          #pragma unroll
+          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_ST, dk + (uint64_t)(2 * k), dq_ + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
+        }
         #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) umma_ss(tmem + COL_DPT, dv + (uint64_t)(2 * k), ddo + (uint64_t)(2 * k), IDESC_SS, k > 0);
+        for (int u = 0; u < NSUB; ++u) {
+          const uint64_t dv = make_smem_desc_sw128(sV + u * SUB_BIG, 16, 1024);
+          const uint64_t ddo = make_smem_desc_sw128(sDO + s * SMALL_BYTES + u * SUB_SMALL, 16, 1024);
+          #pragma unroll
+          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_DPT, dv + (uint64_t)(2 * k), ddo + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
+        }
         tc_commit(bar(B_S_FULL));
         return true;
       };
@@ -638,14 +688,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {       // 16 queries per step
           const uint32_t a_off = (uint32_t)(k < 2 ? 8 * k : 32 + 8 * (k - 2));
-          const uint64_t ddo = make_smem_desc_sw128(sDO + s * SMALL_BYTES + k * 2048, 16, 1024);
+          const uint64_t ddo = make_smem_desc_sw128(sDO + s * SMALL_BYTES + k * 2048, NSUB > 1 ? SUB_SMALL : 16, 1024);
           umma_ts(tmem + COL_DV, tmem + COL_ST + a_off, ddo, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar(B_B_EMPTY + s));
         #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
           const uint32_t a_off = (uint32_t)(k < 2 ? 8 * k : 32 + 8 * (k - 2));
-          const uint64_t dq_ = make_smem_desc_sw128(sQ + s * SMALL_BYTES + k * 2048, 16, 1024);
+          const uint64_t dq_ = make_smem_desc_sw128(sQ + s * SMALL_BYTES + k * 2048, NSUB > 1 ? SUB_SMALL : 16, 1024);
           umma_ts(tmem + COL_DK, tmem + COL_DPT + a_off, dq_, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar(B_A_EMPTY + s));
@@ -750,37 +800,40 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     }
     if (ok) {          // warp-uniform (see the dQ kernel); only the stores depend on the key row
       const int64_t krow = (int64_t)k_row0 + key;
-      uint8_t* dvrow = reinterpret_cast<uint8_t*>(e.dv) + half * 64 +
+      uint8_t* dvrow = reinterpret_cast<uint8_t*>(e.dv) + half * OH * 2 +
                        2 * ((int64_t)b * p.v_stride_b + (int64_t)h * p.v_stride_h + krow * p.v_stride_n);
-      uint8_t* dkrow = reinterpret_cast<uint8_t*>(e.dk) + half * 64 +
+      uint8_t* dkrow = reinterpret_cast<uint8_t*>(e.dk) + half * OH * 2 +
                        2 * ((int64_t)b * p.k_stride_b + (int64_t)h * p.k_stride_h + krow * p.k_stride_n);
-      #pragma unroll
+      #pragma unroll 1
       for (int t = 0; t < 2; ++t) {
-        uint32_t v[32];
-        if (n_qt > 0) {
-          tmem_ld_x32(tmem + lane_base + (t == 0 ? COL_DV : COL_DK) + half * 32, v);
-          tmem_ld_wait();
-        } else {
-          #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0u;
-        }
         const float sc = t == 0 ? 1.f : e.sm_scale;
         uint8_t* dst = t == 0 ? dvrow : dkrow;
-        float o[32];
+        float o[OH];
         #pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * sc;
+        for (int c = 0; c < OH / 32; ++c) {
+          uint32_t v[32];
+          if (n_qt > 0) {
+            tmem_ld_x32(tmem + lane_base + (t == 0 ? COL_DV : COL_DK) + half * OH + 32 * c, v);
+            tmem_ld_wait();
+          } else {
+            #pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          #pragma unroll
+          for (int i = 0; i < 32; ++i) o[32 * c + i] = __uint_as_float(v[i]) * sc;
+        }
         bool write_out = key_ok;
         if (parts > 1 && key_ok) {
-          float* acc = (t == 0 ? e.ws_dv : e.ws_dk) + ((int64_t)tail_slot * BM + r) * HD + half * 32;
+          float* acc = (t == 0 ? e.ws_dv : e.ws_dk) + ((int64_t)tail_slot * BM + r) * HD + half * OH;
           #pragma unroll
-          for (int i = 0; i < 32; ++i) atomicAdd(acc + i, o[i]);
+          for (int i = 0; i < OH; ++i) atomicAdd(acc + i, o[i]);
           __threadfence();
           int* counter = e.ws_cnt_k + (((int64_t)tail_slot * BM + r) * 2 + half) * 2 + t;
           write_out = (atomicAdd(counter, 1) == parts - 1);
           if (write_out) {
             __threadfence();
             #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < OH / 4; ++i) {
               const float4 t4 = __ldcg(reinterpret_cast<const float4*>(acc) + i);
               o[4 * i] = t4.x; o[4 * i + 1] = t4.y; o[4 * i + 2] = t4.z; o[4 * i + 3] = t4.w;
               reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -790,7 +843,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         }
         if (write_out) {
           #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < OH / 8; ++i) {
             uint4 w4;
             w4.x = pack2<kBf16>(o[8 * i + 0], o[8 * i + 1]);
             w4.y = pack2<kBf16>(o[8 * i + 2], o[8 * i + 3]);
@@ -824,6 +877,7 @@ struct BwdPlan {
 
 static BwdPlan sm100_bwd_plan(const t5b_attn_args& a) {
   using namespace sm100b;
+  const int HD = a.D;
   BwdPlan t;
   const long long nq = (long long)((a.M + BM - 1) / BM) * a.H * a.B;
   const long long nk = (long long)((a.N + BM - 1) / BM) * a.H * a.B;
@@ -839,7 +893,7 @@ static BwdPlan sm100_bwd_plan(const t5b_attn_args& a) {
     cudaGetLastError();
     return t;
   }
-  const int slots = 2 * sms;
+  const int slots = (HD == 64 ? 2 : 1) * sms;
   auto al = [](int64_t x) { return (x + 255) / 256 * 256; };
   auto split = [&](long long n_total, int n_stream, int& tail_first, int& parts, int& rem) {
     rem = (int)(n_total % slots);
@@ -867,7 +921,7 @@ int64_t sm100_bwd_workspace_bytes(const t5b_attn_bwd_args& g) {
 // True when the tensor-core backward can take this problem.
 bool sm100_bwd_supports(const t5b_attn_bwd_args& g) {
   const t5b_attn_args& a = g.fwd;
-  if (!sm100_supports(a) || a.D != 64) return false;
+  if (!sm100_supports(a)) return false;       // bf16/fp16, head dim 64 or 128, aligned
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   if (!al16(g.dout) || !al16(g.dq) || !al16(g.dk) || !al16(g.dv)) return false;
   const int64_t s[] = {g.do_stride_b, g.do_stride_h, g.do_stride_m};
@@ -880,6 +934,7 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
   const t5b_attn_args& a = g.fwd;
   const bool varlen = a.cu_seqlens_q != nullptr;
   const bool bf16 = a.dtype == T5B_BF16;
+  const int HD = a.D;
   AttnParams p = make_attn_params(a);
   p.tiles_x = (a.M + BM - 1) / BM;
   BwdExtra e;
@@ -938,15 +993,18 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
   if ((st = make_tmap(&do64, g.dout, bf16, HD, BT, Mr, a.H, Bm, g.do_stride_m, g.do_stride_h, dsb)) != T5B_OK) return st;
 
   const int lut_n = a.table ? 2 * spec.max_distance + 1 + 2 * LUT_PAD : 0;
-  const size_t smem = smem_bytes(lut_n);
-  auto kq = bf16 ? attn_bwd_dq_kernel<true> : attn_bwd_dq_kernel<false>;
-  auto kkv = bf16 ? attn_bwd_dkv_kernel<true> : attn_bwd_dkv_kernel<false>;
-  static bool attr_set[64][2] = {};
+  const size_t smem = HD == 64 ? smem_bytes<64>(lut_n) : smem_bytes<128>(lut_n);
+  auto kq = HD == 64 ? (bf16 ? attn_bwd_dq_kernel<true, 64> : attn_bwd_dq_kernel<false, 64>)
+                     : (bf16 ? attn_bwd_dq_kernel<true, 128> : attn_bwd_dq_kernel<false, 128>);
+  auto kkv = HD == 64 ? (bf16 ? attn_bwd_dkv_kernel<true, 64> : attn_bwd_dkv_kernel<false, 64>)
+                      : (bf16 ? attn_bwd_dkv_kernel<true, 128> : attn_bwd_dkv_kernel<false, 128>);
+  static bool attr_set[64][4] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  const int which = bf16 ? 1 : 0;
+  const int which = (bf16 ? 1 : 0) + (HD == 64 ? 0 : 2);
   if (dev < 0 || dev >= 64 || !attr_set[dev][which]) {
-    const int smem_max = (int)smem_bytes(2 * 2048 + 1 + 2 * LUT_PAD);
+    const int lut_max = 2 * 2048 + 1 + 2 * LUT_PAD;
+    const int smem_max = (int)(HD == 64 ? smem_bytes<64>(lut_max) : smem_bytes<128>(lut_max));
     if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) != cudaSuccess ||
         cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) != cudaSuccess) {
       cudaGetLastError();
