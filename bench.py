@@ -457,6 +457,16 @@ def secondary_measurements(t5b, dev):
     gbs = 3 * xg.numel() * 2 / (ms * 1e-3) / 1e9
     out["rmsnorm_bwd_100000x768_bf16"] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"]}
     del xg, wg, dyg, dxg
+    # block-local attention (T5LocalAttention): 1 x 12 heads x 65536 tokens, blocks of 512 rows, each seeing
+    # 3 x 512 keys: FLOPs counted over the visible window only
+    ql, kl, vl_ = [torch.randn((1, 65536, 12, 64), generator=g, device=dev, dtype=torch.float32).to(dt).transpose(1, 2)
+                   for _ in range(3)]
+    ms = _time(lambda: t5b.flash_attention_with_fusing_bias(ql, kl, vl_, table, sm_scale=1.0, local_block=512), 20)
+    fl = 4.0 * 12 * 65536 * (3 * 512) * 64
+    out["local_attention_H12_L65536_block512"] = {"ms": ms, "TFLOP/s": fl / (ms * 1e-3) / 1e12,
+                                                  "tokens_per_s": 65536 / (ms * 1e-3),
+                                                  "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"]}
+    del ql, kl, vl_
     # head dim 128 (the T5-3B / 11B head size): same sequence length, 3 rotating input sets
     # (3 x 151 MB > L2), T5 bias, bf16
     sets = [[(torch.randn((2, 8192, 12, 128), generator=g, device=dev, dtype=torch.float32) * 0.5).to(dt).transpose(1, 2)

@@ -157,6 +157,43 @@ def attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
     return out
 
 
+def local_attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: Optional[torch.Tensor],
+                          block_len: int, num_buckets: int = 32, max_distance: int = 128) -> torch.Tensor:
+    """Block-local attention core of `T5LocalAttention.forward`
+    (src/turbot5/model/attentions.py:553-650, helpers src/turbot5/model/utils.py:99-140).
+
+    (B,H,L,D) float tensors.  The sequence is zero-padded to a multiple of `block_len` (a shorter
+    sequence is a single block of its own length), split into blocks, and the queries of block i
+    attend to the keys of blocks i-1, i, i+1; the missing neighbours of the first and last block
+    are all-zero blocks that are NOT masked (score = bias only), exactly as the reference
+    concatenates them.  Bias: bidirectional buckets of (key position - query position) inside the
+    3-block window (`compute_bias(block_len)`, attentions.py:529-551).
+    """
+    B, H, L, D = q.shape
+    bl = block_len if L >= block_len else L
+    pad = (-L) % bl
+    f = lambda x: torch.nn.functional.pad(x.float(), (0, 0, 0, pad))
+    qp, kp, vp = f(q), f(k), f(v)
+    nblk = (L + pad) // bl
+    qb = qp.view(B, H, nblk, bl, D)
+
+    def three(x):
+        xb = x.view(B, H, nblk, bl, D)
+        z = torch.zeros_like(xb[:, :, :1])
+        ext = torch.cat([z, xb, z], dim=2)                      # blocks -1 .. nblk
+        return torch.cat([ext[:, :, 0:nblk], ext[:, :, 1:nblk + 1], ext[:, :, 2:nblk + 2]], dim=3)   # (B,H,nblk,3bl,D)
+    kc, vc = three(kp), three(vp)
+    scores = torch.einsum("bhnqd,bhnkd->bhnqk", qb, kc)
+    if table is not None:
+        mem = torch.arange(3 * bl)
+        ctx = mem[bl:2 * bl]
+        bucket = relative_position_bucket(mem[None, :] - ctx[:, None], True, num_buckets, max_distance)
+        bias = table.float()[torch.as_tensor(bucket, dtype=torch.long)]     # (bl, 3bl, H)
+        scores = scores + bias.permute(2, 0, 1)[None, :, None]
+    out = torch.einsum("bhnqk,bhnkd->bhnqd", torch.softmax(scores, dim=-1), vc)
+    return out.reshape(B, H, nblk * bl, D)[:, :, :L]
+
+
 def attention_basic_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                            table: Optional[torch.Tensor], cu_seqlens_q, cu_seqlens_k,
                            causal: bool = False, sm_scale: float = 1.0,

@@ -15,6 +15,7 @@ Fixtures written:
                    of (num_buckets, max_distance, bidirectional) settings, from
                    `T5Attention._relative_position_bucket`.
   attention_grad.npz  the same two functions under autograd: gradients of q, k, v and the table
+  local.npz        `T5LocalAttention.forward` (block-local attention) with permutation projections
   attention.npz    small seeded q/k/v/table cases through `compute_bias` +
                    `naive_torch_attention_with_bias` (float32 math on bf16-representable
                    inputs, stored as bf16 bit patterns), incl. cached
@@ -218,6 +219,37 @@ def main(ref_root: str):
         grads[name + "_meta"] = np.asarray([B, H, M, N, D, int(dec), nb, md], dtype=np.int64)
     grads["names"] = np.asarray([s[0] for s in gspecs])
     np.savez_compressed(os.path.join(here, "attention_grad.npz"), **grads)
+
+    # ------------------------------------------------- block-local attention
+    # T5LocalAttention.forward with permutation matrices as q/k/v/o projections, so that the
+    # module output is the attention core's output on bf16-exact q, k, v
+    from turbot5.model.attentions import T5LocalAttention
+    local = {}
+    lspecs = [("loc_ragged", 1, 300, 128), ("loc_short", 2, 100, 512), ("loc_even", 1, 512, 256), ("loc_long", 1, 1100, 384)]
+    H, D = 2, 64
+    for name, B, L, bl in lspecs:
+        cfg = T5Config(d_model=H * D, d_kv=D, num_heads=H, relative_attention_num_buckets=32,
+                       relative_attention_max_distance=128, is_decoder=False, dropout_rate=0.0,
+                       tie_word_embeddings=False, sliding_window=bl)
+        cfg.use_triton = False
+        att = T5LocalAttention(cfg, has_relative_attention_bias=True).eval()
+        gperm = torch.Generator().manual_seed(600 + L)
+        eye = torch.eye(H * D)
+        pk_, pv_ = torch.randperm(H * D, generator=gperm), torch.randperm(H * D, generator=gperm)
+        table = seeded((32, H), 700 + L, 0.1).bfloat16().float()
+        hidden = seeded((B, L, H * D), 800 + L).bfloat16().float()
+        with torch.no_grad():
+            att.q.weight.copy_(eye); att.k.weight.copy_(eye[pk_]); att.v.weight.copy_(eye[pv_]); att.o.weight.copy_(eye)
+            att.relative_attention_bias.weight.copy_(table)
+            out = att(hidden)[0]
+        local[name + "_hidden"] = bf16_bits(hidden)
+        local[name + "_table"] = bf16_bits(table)
+        local[name + "_kperm"] = pk_.numpy()
+        local[name + "_vperm"] = pv_.numpy()
+        local[name + "_out"] = out.numpy()
+        local[name + "_meta"] = np.asarray([B, H, L, D, bl], dtype=np.int64)
+    local["names"] = np.asarray([s_[0] for s_ in lspecs])
+    np.savez_compressed(os.path.join(here, "local.npz"), **local)
 
     rn = {}
     for tag, xdt, wdt in (("f32", torch.float32, torch.float32),

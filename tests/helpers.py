@@ -89,3 +89,15 @@ def check_grad_close(got, want, what="", rel=2e-2, floor=1e-6):
     mx, mean = diff.max().item() / scale, diff.mean().item() / scale
     assert mx <= rel and mean <= rel / 10, f"{what}: max error {mx:.3e}, mean error {mean:.3e} of max |grad| {scale:.3e}"
     return mx, mean
+
+
+def local_case(z, name):
+    """q, k, v (B,H,L,D) of a block-local fixture (the module's projections are permutations)."""
+    B, H, L, D, bl = [int(x) for x in z[name + "_meta"]]
+    hidden = from_bf16_bits(z[name + "_hidden"])
+    shape = lambda x: x.view(B, L, H, D).transpose(1, 2)
+    q = shape(hidden)
+    k = shape(hidden[..., torch.from_numpy(z[name + "_kperm"])])
+    v = shape(hidden[..., torch.from_numpy(z[name + "_vperm"])])
+    want = torch.from_numpy(z[name + "_out"]).view(B, L, H, D).transpose(1, 2)
+    return q, k, v, from_bf16_bits(z[name + "_table"]), bl, want

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import t5_oracle as orc
-from tests.helpers import attention_case, check_close, load, seeded
+from tests.helpers import attention_case, check_close, load, local_case, seeded
 
 pytestmark = pytest.mark.gpu
 
@@ -408,3 +408,38 @@ def test_scores_that_keep_growing_take_the_rescale_path(dt, step, D):
     for kernel in ("tcgen05",):
         out = _run_dense(q, k, v, table, dt, kernel, q_pos_offset=0)
         check_close(out, want, dt, f"growing scores {dt} {step} d{D}")
+
+
+# ---- block-local attention (T5LocalAttention): keys of the three neighbouring blocks only
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("name", ["loc_ragged", "loc_short", "loc_even", "loc_long"])
+def test_block_local_attention_vs_reference_fixture(name, dt):
+    t5b = _ops()
+    q, k, v, table, bl, want = local_case(load("local.npz"), name)
+    out = t5b.flash_attention_with_fusing_bias(q.to("cuda", dt), k.to("cuda", dt), v.to("cuda", dt),
+                                               table.to("cuda", dt), sm_scale=1.0, local_block=bl)
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    check_close(out, want, dt, name)
+
+
+@pytest.mark.parametrize("D,L,bl", [(64, 4096, 512), (128, 2048, 256), (64, 1000, 128), (64, 700, 1024)])
+def test_block_local_attention_seeded_vs_oracle(D, L, bl):
+    t5b = _ops()
+    dt = torch.bfloat16
+    q, k, v = (seeded((2, 3, L, D), s, 0.5 if D == 128 else 1.0, dtype=dt) for s in (1, 2, 3))
+    table = seeded((32, 3), 4, 0.1, dtype=dt)
+    want = orc.local_attention_basic(q, k, v, table, bl)
+    out = t5b.flash_attention_with_fusing_bias(q.cuda(), k.cuda(), v.cuda(), table.cuda(), sm_scale=1.0, local_block=bl)
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    check_close(out, want, dt, f"local d{D} L{L} block {bl}")
+
+
+def test_block_local_attention_refuses_what_it_cannot_do():
+    t5b = _ops()
+    q = torch.randn(1, 2, 600, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):      # blocks of 100 rows would cut through the 128-row query tiles
+        t5b.flash_attention_with_fusing_bias(q, q, q, None, sm_scale=1.0, local_block=100)
+    with pytest.raises(RuntimeError):
+        t5b.flash_attention_with_fusing_bias(q.float(), q.float(), q.float(), None, sm_scale=1.0, local_block=128)

@@ -368,3 +368,29 @@ def test_module_training_step_gradients_vs_oracle_layer():
         else:
             for b, n in enumerate(mask_lens):
                 check_grad_close(hc.grad[b, :n], hf.grad[b, :n], f"{tag} dhidden row {b}", rel=3e-2)
+
+
+def test_local_attention_module_matches_reference_module_fixture():
+    # T5LocalFlashAttention with the fixture's permutation projections against the output of the
+    # reference's T5LocalAttention module
+    import numpy as np
+    from tests.helpers import from_bf16_bits
+    t5b = _ops()
+    z = load("local.npz")
+    for name in ("loc_ragged", "loc_short", "loc_long"):
+        B, H, L, D, bl = [int(x) for x in z[name + "_meta"]]
+        cfg = _Cfg(d_model=H * D, d_kv=D, num_heads=H, sliding_window=bl)
+        mod = t5b.T5ATTENTION_TYPES["local"](cfg, has_relative_attention_bias=True)
+        eye = torch.eye(H * D)
+        with torch.no_grad():
+            mod.q.weight.copy_(eye)
+            mod.k.weight.copy_(eye[torch.from_numpy(z[name + "_kperm"])])
+            mod.v.weight.copy_(eye[torch.from_numpy(z[name + "_vperm"])])
+            mod.o.weight.copy_(eye)
+            mod.relative_attention_bias.weight.copy_(from_bf16_bits(z[name + "_table"]))
+        mod = mod.cuda().to(torch.bfloat16).eval()
+        hidden = from_bf16_bits(z[name + "_hidden"]).to(torch.bfloat16)
+        with torch.no_grad():
+            out, present, pb = mod(hidden.cuda())
+        assert present is None
+        check_close(out, torch.from_numpy(z[name + "_out"]), torch.bfloat16, name)

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import t5_oracle as orc
-from tests.helpers import attention_case, from_bf16_bits, load, seeded
+from tests.helpers import attention_case, from_bf16_bits, load, local_case, seeded
 
 
 def test_bucket_tables_bit_exact():
@@ -176,3 +176,10 @@ def test_attention_gradients_under_autograd(name):
     for got, key in ((q.grad, "_dq"), (k.grad, "_dk"), (v.grad, "_dv"), (table.grad, "_dtable")):
         want = torch.from_numpy(z[name + key])
         assert (got - want).abs().max().item() <= 1e-4 * max(1.0, want.abs().max().item()), (name, key)
+
+
+@pytest.mark.parametrize("name", ["loc_ragged", "loc_short", "loc_even", "loc_long"])
+def test_block_local_attention_oracle(name):
+    q, k, v, table, bl, want = local_case(load("local.npz"), name)
+    got = orc.local_attention_basic(q, k, v, table, bl)
+    assert (got - want).abs().max().item() <= 2e-5

@@ -10,13 +10,13 @@ from .attention import (check_device_status, flash_attention_with_fusing_bias,
                         flash_attention_with_fusing_bias_varlen, flash_decoding_with_fusing_bias,
                         relative_position_bucket_grid, relative_position_bucket_table)
 
-from .modules import (RMSLayerNorm, T5ATTENTION_TYPES, T5FlashAttention, T5LayerNorm,
+from .modules import (RMSLayerNorm, T5ATTENTION_TYPES, T5FlashAttention, T5LayerNorm, T5LocalFlashAttention,
                       rms_layer_norm)
 from .padding import get_unpad_plan, pad_rows, unpad_rows
 from .sequence_parallel import sequence_parallel_attention, shard_bounds, shard_size
 
 __all__ = [
-    "T5ATTENTION_TYPES", "T5FlashAttention", "T5LayerNorm", "RMSLayerNorm", "rms_layer_norm",
+    "T5ATTENTION_TYPES", "T5FlashAttention", "T5LocalFlashAttention", "T5LayerNorm", "RMSLayerNorm", "rms_layer_norm",
     "get_unpad_plan", "unpad_rows", "pad_rows",
     "sequence_parallel_attention", "shard_bounds", "shard_size",
     "flash_attention_with_fusing_bias", "flash_attention_with_fusing_bias_varlen",

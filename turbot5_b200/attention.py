@@ -67,8 +67,14 @@ def _unit_stride_last(t):
 
 def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
                                      NUM_BUCKETS=32, MAX_DISTANCE=128, *, q_pos_offset=None,
-                                     return_lse=False, kernel="auto", balance_last_wave=True):
-    """See `_dense_forward`; differentiable in q, k, v and the bias table."""
+                                     return_lse=False, kernel="auto", balance_last_wave=True, local_block=None):
+    """See `_dense_forward`; differentiable in q, k, v and the bias table (not with `local_block`)."""
+    if local_block:
+        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
+            raise NotImplementedError("block-local attention has no backward kernel")
+        return _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset=0,
+                              return_lse=return_lse, kernel=kernel, balance_last_wave=False,
+                              local_block=int(local_block))
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _DenseAttention.apply(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset,
                                          kernel, balance_last_wave)
@@ -78,7 +84,8 @@ def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
 
 
 def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *,
-                   q_pos_offset=None, return_lse=False, kernel="auto", balance_last_wave=True, _keep=None):
+                   q_pos_offset=None, return_lse=False, kernel="auto", balance_last_wave=True, _keep=None,
+                   local_block=0):
     """softmax(sm_scale * Q K^T + T5 bias(n - m) [+ causal mask]) V without an L x L tensor.
 
     q (B,H,M,D), k/v (B,H,N,D), any batch/head/row strides (last dim contiguous);
@@ -123,6 +130,7 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
     a.kernel = {"auto": nat.KERNEL_AUTO, "tcgen05": nat.KERNEL_TCGEN05, "simt": nat.KERNEL_SIMT}[kernel]
     a.sm_scale = float(sm_scale)
     a.workspace, a.workspace_bytes = None, 0
+    a.local_block = int(local_block)
     with torch.cuda.device(q.device):
         if balance_last_wave:
             need = nat.lib().t5b_attention_workspace_bytes(a)
@@ -195,6 +203,7 @@ def _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max
     a.kernel = {"auto": nat.KERNEL_AUTO, "tcgen05": nat.KERNEL_TCGEN05, "simt": nat.KERNEL_SIMT}[kernel]
     a.sm_scale = float(sm_scale)
     a.workspace, a.workspace_bytes = None, 0
+    a.local_block = 0
     with torch.cuda.device(q.device):
         nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)),
                   "flash_attention_with_fusing_bias_varlen")

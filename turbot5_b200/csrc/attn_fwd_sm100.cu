@@ -185,16 +185,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (w.b < 0) return;   // block beyond the last tile: uniform exit, nothing allocated yet
   }
   const int b = w.b, q_row0 = w.q_row0, rows_in_tile = w.rows_in_tile;
-  const int k_row0 = w.k_row0, len_k = w.len_k, qpos0 = w.qpos0;
+  const int k_row0 = w.k_row0, qpos0 = w.qpos0;
+  int len_k = w.len_k;
+  // Block-local attention (T5LocalAttention, src/turbot5/model/attentions.py:523-650): the rows of
+  // block i of `local_block` queries see the keys of blocks i-1, i, i+1 and nothing else.  Keys
+  // before 0 or after the end are the reference's zero padding blocks: they are NOT masked (their
+  // scores are the bare bias) and the TMA zero fill supplies them.  So the key range becomes
+  // [n_base, len_k) with a negative n_base for the first block and len_k past the tensor's end.
+  int n_base = 0;
+  if (p.local_block > 0) {
+    const int bl = p.M < p.local_block ? p.M : p.local_block;      // a shorter sequence is one block
+    const int blk = q_row0 / bl;
+    n_base = (blk - 1) * bl;
+    len_k = (blk + 2) * bl;
+  }
 
   // keys this tile can see
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
-  const int n_kv_all = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+  const int n_kv_all = kv_end > n_base ? (kv_end - n_base + BN - 1) / BN : 0;
   // this block's share of the key tiles: [kv_first, kv_first + n_kv)
   const int kv_per = (n_kv_all + parts - 1) / parts;
   const int kv_first = min(part * kv_per, n_kv_all);
   const int n_kv = min(n_kv_all, kv_first + kv_per) - kv_first;
+  const int n_first = n_base + kv_first * BN;       // first key of this block's first tile
 
   // ---------------------------------------------------------------- set-up
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
@@ -258,12 +272,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         mbar_expect_tx(bar(BAR_K_FULL + s), KV_BYTES);
         #pragma unroll
         for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sK + s * KV_BYTES + u * SUB_KV, &tmap_k, bar(BAR_K_FULL + s), 64 * u, k_row0 + (kv_first + j) * BN, h, b);
+          tma_load_4d(sK + s * KV_BYTES + u * SUB_KV, &tmap_k, bar(BAR_K_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
         if (j >= STAGES && !mbar_wait_bounded(bar(BAR_V_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
         mbar_expect_tx(bar(BAR_V_FULL + s), KV_BYTES);
         #pragma unroll
         for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sV + s * KV_BYTES + u * SUB_KV, &tmap_v, bar(BAR_V_FULL + s), 64 * u, k_row0 + (kv_first + j) * BN, h, b);
+          tma_load_4d(sV + s * KV_BYTES + u * SUB_KV, &tmap_v, bar(BAR_V_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -342,7 +356,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     bool ok = true;
 
     for (int j = 0; j < n_kv; ++j) {
-      const int n0 = (kv_first + j) * BN;          // first key of the tile
+      const int n0 = n_first + j * BN;             // first key of the tile
       const int c0 = half * NH;                    // first column of this thread inside the tile
       if (!mbar_wait_bounded_warp(bar(BAR_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
@@ -613,6 +627,13 @@ bool sm100_supports(const t5b_attn_args& a) {
   if (a.dtype != T5B_BF16 && a.dtype != T5B_F16) return false;
   if (a.D != 64 && a.D != 128) return false;
   if (a.max_distance > 2048 && a.table) return false;
+  if (a.local_block < 0) return false;
+  if (a.local_block > 0) {
+    // block-local attention: dense self-attention without a causal mask; a 128-row query tile
+    // must lie inside one block
+    if (a.cu_seqlens_q != nullptr || a.causal || a.M != a.N || a.q_pos_offset != 0) return false;
+    if (a.M > a.local_block && (a.local_block % 128) != 0) return false;
+  }
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   if (!al16(a.q) || !al16(a.k) || !al16(a.v) || !al16(a.out)) return false;
   const int64_t s[] = {a.q_stride_b, a.q_stride_h, a.q_stride_m, a.k_stride_b, a.k_stride_h, a.k_stride_n,
@@ -634,7 +655,7 @@ TailPlan sm100_tail_plan(const t5b_attn_args& a) {
   t.tail_first = t.n_total;
   t.parts = 1;
   t.counters_bytes = t.ml_bytes = t.o_bytes = 0;
-  if (a.cu_seqlens_q != nullptr || a.causal || n_total > 0x3fffffffLL) return t;
+  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || n_total > 0x3fffffffLL) return t;
   static int sms[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return t; }

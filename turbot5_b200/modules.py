@@ -209,6 +209,49 @@ class T5FlashAttention(nn.Module):
         return outputs
 
 
+class T5LocalFlashAttention(T5FlashAttention):
+    """Block-local attention (LongT5-style) on the fused-bias kernel: `T5LocalAttention` of the
+    reference (src/turbot5/model/attentions.py:523-650) without its reshapes.
+
+    The reference splits q/k/v into blocks of `config.sliding_window` rows, concatenates each
+    block's two neighbours (zero blocks at the ends) and materialises a (block, 3 x block) bias; here
+    the same kernel that serves full attention walks only the three blocks of keys a query tile
+    can see, the zero blocks come from the TMA's out-of-bounds fill, and the bias is looked up
+    per element as always.  Encoder self-attention without a padding mask (the reference adds
+    -1e10 at masked keys: not expressed here yet), no cache; forward only.
+    """
+
+    def __init__(self, config, has_relative_attention_bias=False, **kwargs):
+        super().__init__(config, cross_attention=False, has_relative_attention_bias=has_relative_attention_bias)
+        self.block_len = config.sliding_window
+
+    def forward(self, hidden_states, mask=None, position_bias=None, layer_head_mask=None, past_key_value=None,
+                use_cache=None, output_attentions=False, **kwargs):
+        if mask is not None:
+            raise NotImplementedError("T5LocalFlashAttention does not take a padding mask yet")
+        if self.is_decoder:
+            raise NotImplementedError("T5LocalFlashAttention covers encoder self-attention only")
+        batch_size, seq_length = hidden_states.shape[:2]
+        H, D = self.n_heads, self.key_value_proj_dim
+        shape = lambda x: x.view(batch_size, -1, H, D).transpose(1, 2)
+        q, k, v = shape(self.q(hidden_states)), shape(self.k(hidden_states)), shape(self.v(hidden_states))
+        table = None
+        if position_bias is not None:
+            table = position_bias
+        elif self.has_relative_attention_bias:
+            table = self.relative_attention_bias.weight
+        attn = flash_attention_with_fusing_bias(q, k, v, table, causal=False, sm_scale=1.0,
+                                                NUM_BUCKETS=self.relative_attention_num_buckets,
+                                                MAX_DISTANCE=self.relative_attention_max_distance,
+                                                local_block=self.block_len)
+        out = self.o(attn.transpose(1, 2).contiguous().view(batch_size, -1, self.inner_dim))
+        outputs = (out, None, table)
+        if output_attentions:
+            outputs = outputs + (None,)
+        return outputs
+
+
 T5ATTENTION_TYPES = {
     "flash": T5FlashAttention,
+    "local": T5LocalFlashAttention,
 }
