@@ -116,8 +116,8 @@ typedef struct {
    * the keys of blocks i-1, i and i+1; a sequence shorter than local_block is one block; keys
    * before the first or after the last token are the reference's zero padding blocks and take
    * part unmasked.  Dense self-attention (M == N, q_pos_offset 0), not causal, tensor-core
-   * forward only (bf16/fp16, head dim 64/128; local_block a multiple of 128 unless the sequence
-   * fits in one block), T5B_ERR_UNSUPPORTED otherwise.  0: off. */
+   * kernels only, forward and backward (bf16/fp16, head dim 64/128; local_block a multiple of
+   * 128 unless the sequence fits in one block), T5B_ERR_UNSUPPORTED otherwise.  0: off. */
   int32_t local_block;
 } t5b_attn_args;
 

@@ -269,3 +269,23 @@ def test_last_wave_split_leaves_its_scratch_clean():
     for key, ws in att._workspaces.items():
         if key[0] == "attn_bwd":
             assert torch.count_nonzero(ws) == 0
+
+
+@pytest.mark.parametrize("D,L,bl", [(64, 1024, 256), (64, 300, 128), (64, 200, 512), (128, 768, 128)])
+def test_block_local_attention_gradients_vs_oracle(D, L, bl):
+    t5b = _ops()
+    dt = torch.bfloat16
+    q, k, v = (seeded((1, 2, L, D), s, 0.5 if D == 64 else 0.35, dtype=dt) for s in (1, 2, 3))
+    dout = seeded((1, 2, L, D), 5, dtype=dt)
+    table = seeded((32, 2), 4, 0.1, dtype=dt)
+    ref = [t.float().clone().requires_grad_(True) for t in (q, k, v, table)]
+    want = orc.local_attention_basic(*ref, bl)
+    (want * dout.float()).sum().backward()
+    leaves = [t.cuda().requires_grad_(True) for t in (q, k, v, table)]
+    out = t5b.flash_attention_with_fusing_bias(*leaves, sm_scale=1.0, local_block=bl)
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    check_close(out.detach(), want.detach(), dt, "local out")
+    for g, w, nm in zip(leaves, ref, ("dq", "dk", "dv", "dtable")):
+        check_grad_close(g.grad, w.grad, f"local d{D} L{L} block {bl} {nm}", floor=2.0 if nm == "dtable" else 1e-6)

@@ -68,19 +68,18 @@ def _unit_stride_last(t):
 def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
                                      NUM_BUCKETS=32, MAX_DISTANCE=128, *, q_pos_offset=None,
                                      return_lse=False, kernel="auto", balance_last_wave=True, local_block=None):
-    """See `_dense_forward`; differentiable in q, k, v and the bias table (not with `local_block`)."""
+    """See `_dense_forward`; differentiable in q, k, v and the bias table.  `local_block` turns the
+    call into block-local attention (T5LocalAttention: the keys of the three neighbouring blocks)."""
+    local_block = int(local_block or 0)
     if local_block:
-        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
-            raise NotImplementedError("block-local attention has no backward kernel")
-        return _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset=0,
-                              return_lse=return_lse, kernel=kernel, balance_last_wave=False,
-                              local_block=int(local_block))
+        q_pos_offset, balance_last_wave = 0, False
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _DenseAttention.apply(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset,
-                                         kernel, balance_last_wave)
+                                         kernel, balance_last_wave, local_block)
         return (out, lse) if return_lse else out
     return _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset=q_pos_offset,
-                          return_lse=return_lse, kernel=kernel, balance_last_wave=balance_last_wave)
+                          return_lse=return_lse, kernel=kernel, balance_last_wave=balance_last_wave,
+                          local_block=local_block)
 
 
 def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *,
@@ -267,11 +266,12 @@ class _DenseAttention(torch.autograd.Function):
     (src/turbot5/ops/fused_bias_attention.py:822-873)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset, kernel, balance):
+    def forward(ctx, q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset, kernel, balance,
+                local_block=0):
         keep = {}
         out, lse = _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE,
                                   q_pos_offset=q_pos_offset, return_lse=True, kernel=kernel,
-                                  balance_last_wave=balance, _keep=keep)
+                                  balance_last_wave=balance, _keep=keep, local_block=local_block)
         ctx.keep = keep
         ctx.save_for_backward(out, lse)
         ctx.mark_non_differentiable(lse)
@@ -281,7 +281,7 @@ class _DenseAttention(torch.autograd.Function):
     def backward(ctx, dout, _dlse):
         out, lse = ctx.saved_tensors
         dq, dk, dv, dtable = _attention_backward(ctx.keep, out, lse, dout, varlen=False)
-        return dq, dk, dv, dtable, None, None, None, None, None, None, None
+        return dq, dk, dv, dtable, None, None, None, None, None, None, None, None
 
 
 class _VarlenAttention(torch.autograd.Function):

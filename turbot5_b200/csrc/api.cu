@@ -71,7 +71,7 @@ extern "C" int t5b_attention_bwd(const t5b_attn_bwd_args* g, void* stream) {
   }
   if (!a->q || !a->k || !a->v || !a->out || !a->lse) return T5B_ERR_ARG;
   if (!g->dout || !g->dq || !g->dk || !g->dv || !g->delta) return T5B_ERR_ARG;
-  if (a->local_block != 0) return T5B_ERR_UNSUPPORTED;      // block-local attention: forward only
+  if (a->local_block != 0 && (!sm100_bwd_supports(*g) || a->kernel == T5B_KERNEL_SIMT)) return T5B_ERR_UNSUPPORTED;
   if (a->table && !g->dtable) return T5B_ERR_ARG;
   if ((varlen ? a->total_k : a->N) == 0 || (varlen ? a->total_q : a->M) == 0) return T5B_ERR_UNSUPPORTED;
   BucketSpec spec;

@@ -180,13 +180,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (w.b < 0) return;
   }
   const int b = w.b, q_row0 = w.q_row0, rows_in_tile = w.rows_in_tile;
-  const int k_row0 = w.k_row0, len_k = w.len_k, qpos0 = w.qpos0;
+  const int k_row0 = w.k_row0, qpos0 = w.qpos0;
+  int len_k = w.len_k, n_base = 0;
+  if (p.local_block > 0) {
+    // block-local attention: the keys of the three neighbouring blocks, the zero padding blocks
+    // beyond either end included and unmasked (see attn_fwd_sm100.cu)
+    const int bl = p.M < p.local_block ? p.M : p.local_block;
+    const int blk = q_row0 / bl;
+    n_base = (blk - 1) * bl;
+    len_k = (blk + 2) * bl;
+  }
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
-  const int n_kv_all = kv_end > 0 ? (kv_end + BT - 1) / BT : 0;
+  const int n_kv_all = kv_end > n_base ? (kv_end - n_base + BT - 1) / BT : 0;
   const int kv_per = (n_kv_all + parts - 1) / parts;
   const int kv_first = min(part * kv_per, n_kv_all);      // this block's key tiles: [kv_first, kv_first + n_kv)
   const int n_kv = min(n_kv_all, kv_first + kv_per) - kv_first;
+  const int n_first = n_base + kv_first * BT;
 
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -254,12 +264,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
         #pragma unroll
         for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sK + s * SMALL_BYTES + u * SUB_SMALL, &tmap_k, bar(B_A_FULL + s), 64 * u, k_row0 + (kv_first + j) * BT, h, b);
+          tma_load_4d(sK + s * SMALL_BYTES + u * SUB_SMALL, &tmap_k, bar(B_A_FULL + s), 64 * u, k_row0 + n_first + j * BT, h, b);
         if (j >= STAGES && !mbar_wait_bounded(bar(B_B_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
         mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
         #pragma unroll
         for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sV + s * SMALL_BYTES + u * SUB_SMALL, &tmap_v, bar(B_B_FULL + s), 64 * u, k_row0 + (kv_first + j) * BT, h, b);
+          tma_load_4d(sV + s * SMALL_BYTES + u * SUB_SMALL, &tmap_v, bar(B_B_FULL + s), 64 * u, k_row0 + n_first + j * BT, h, b);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -332,7 +342,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     bool ok = true;
 
     for (int j = 0; j < n_kv; ++j) {
-      const int n0 = (kv_first + j) * BT;
+      const int n0 = n_first + j * BT;
       const int c0 = half * 32;
       if (!mbar_wait_bounded_warp(bar(B_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
@@ -555,7 +565,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   // query tiles that can see a key of this tile: causal keeps q_off + m >= key
   int i_first = 0;
   if (p.causal) i_first = max(0, key0 - q_off) / BT;
-  const int n_qt_all = (len_q + BT - 1) / BT;
+  int n_qt_all = (len_q + BT - 1) / BT;
+  if (p.local_block > 0) {
+    // block-local attention: only the queries of the three neighbouring blocks see this key tile
+    const int bl = p.M < p.local_block ? p.M : p.local_block;
+    const int kb = key0 / bl;
+    i_first = max(0, (kb - 1) * bl) / BT;
+    n_qt_all = (min(len_q, (kb + 2) * bl) + BT - 1) / BT;
+  }
   int n_qt = max(0, n_qt_all - i_first);
   if (parts > 1) {       // this block's share of the query tiles
     const int per = (n_qt + parts - 1) / parts;
@@ -886,7 +903,7 @@ static BwdPlan sm100_bwd_plan(const t5b_attn_args& a) {
   t.q_parts = t.k_parts = 1;
   t.q_rem = t.k_rem = 0;
   t.cnt_bytes = t.dq_bytes = t.dk_bytes = 0;
-  if (a.cu_seqlens_q != nullptr || a.causal || nq > 0x3fffffffLL || nk > 0x3fffffffLL) return t;
+  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || nq > 0x3fffffffLL || nk > 0x3fffffffLL) return t;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {

@@ -218,7 +218,7 @@ class T5LocalFlashAttention(T5FlashAttention):
     the same kernel that serves full attention walks only the three blocks of keys a query tile
     can see, the zero blocks come from the TMA's out-of-bounds fill, and the bias is looked up
     per element as always.  Encoder self-attention without a padding mask (the reference adds
-    -1e10 at masked keys: not expressed here yet), no cache; forward only.
+    -1e10 at masked keys: not expressed here yet), no cache; differentiable.
     """
 
     def __init__(self, config, has_relative_attention_bias=False, **kwargs):
