@@ -494,6 +494,14 @@ def secondary_measurements(t5b, dev):
             ms = _time(lambda: enc(ids), 5, warm=2)
         out[f"t5_base_encoder_fwd_{Bt}x{Lt}"] = {"ms": ms, "tokens_per_s": Bt * Lt / (ms * 1e-3)}
     del enc
+    # the same encoder with block-local self-attention (blocks of 512) over one 65 536-token sequence
+    cfg_l = T5StackConfig(attention_type="local", sliding_window=512)
+    enc = T5Stack(cfg_l, torch.nn.Embedding(cfg_l.vocab_size, cfg_l.d_model), is_decoder=False).to(dev).to(dt).eval()
+    ids = torch.randint(0, cfg_l.vocab_size, (1, 65536), generator=g, device=dev)
+    with torch.no_grad():
+        ms = _time(lambda: enc(ids), 5, warm=2)
+    out["t5_base_local_encoder_fwd_1x65536"] = {"ms": ms, "tokens_per_s": 65536 / (ms * 1e-3)}
+    del enc
     # T5-large-shaped greedy decoding (24 decoder layers, d_model 1024, 16 x 64 heads, d_ff 4096 ReLU as in
     # the original T5-large; random init, bf16): batch 64 against an encoder memory of 8192 states.  Every
     # step streams the cross-attention K/V of all layers (51.5 GB) through the split-KV kernel.

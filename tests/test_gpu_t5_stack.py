@@ -109,3 +109,17 @@ def test_training_step_through_the_stack_gives_finite_gradients_everywhere():
         assert prm.grad is not None, name
         assert torch.isfinite(prm.grad.float()).all(), name
         assert prm.grad.float().abs().sum().item() > 0, name
+
+
+def test_local_encoder_matches_the_full_encoder_when_one_block_covers_everything_but_the_padding_blocks():
+    # a "local" encoder whose window is longer than the sequence differs from the full encoder only
+    # by the reference's unmasked zero padding blocks; with blocks shorter than the sequence it must
+    # differ; both run end to end and give finite outputs
+    ids = torch.randint(0, 128, (2, 300), generator=torch.Generator().manual_seed(3)).cuda()
+    full = _model(torch.bfloat16, d_model=128, num_heads=2, d_ff=256)
+    local = _model(torch.bfloat16, d_model=128, num_heads=2, d_ff=256, attention_type="local", sliding_window=128)
+    with torch.no_grad():
+        a = full.encoder(ids)
+        b = local.encoder(ids)
+    assert a.shape == b.shape and torch.isfinite(b.float()).all()
+    assert (a.float() - b.float()).abs().max().item() > 1e-3

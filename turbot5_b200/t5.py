@@ -25,7 +25,7 @@ import torch
 from torch import nn
 
 from .attention import flash_attention_with_fusing_bias, flash_decoding_with_fusing_bias
-from .modules import T5FlashAttention, T5LayerNorm
+from .modules import T5ATTENTION_TYPES, T5FlashAttention, T5LayerNorm
 
 
 @dataclass
@@ -45,6 +45,8 @@ class T5StackConfig:
     tie_word_embeddings: bool = False
     is_decoder: bool = False
     decoder_start_token_id: int = 0
+    attention_type: str = "flash"              # encoder self-attention: "flash" (full) or "local" (block-local)
+    sliding_window: int = 512                  # block length of the "local" type
 
 
 class T5DenseGatedActDense(nn.Module):
@@ -82,7 +84,9 @@ class T5LayerFF(nn.Module):
 class T5LayerSelfAttention(nn.Module):
     def __init__(self, cfg, has_relative_attention_bias):
         super().__init__()
-        self.SelfAttention = T5FlashAttention(cfg, has_relative_attention_bias=has_relative_attention_bias)
+        # the decoder always attends fully (as in the reference, src/turbot5/model/modeling.py:134-135)
+        kind = T5FlashAttention if cfg.is_decoder else T5ATTENTION_TYPES[cfg.attention_type]
+        self.SelfAttention = kind(cfg, has_relative_attention_bias=has_relative_attention_bias)
         self.layer_norm = T5LayerNorm(cfg.d_model, eps=cfg.layer_norm_epsilon)
 
 
