@@ -515,6 +515,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   constexpr int BIG_BYTES = G::BIG_BYTES, SMALL_BYTES = G::SMALL_BYTES, SMEM_TILES = G::SMEM_TILES;
   constexpr int TMEM_COLS = G::TMEM_COLS, OH = G::OH;
   constexpr int COL_ST = 0, COL_DPT = 64, COL_DV = 128, COL_DK = 128 + HD;
+  // Head dim 128 owns the SM alone (512 columns): the 128 spare columns hold a second S^T / dP^T
+  // pair, so the first products of tile i+1 run while the softmax warps work on tile i.
+  constexpr int NBUF = HD == 128 ? 2 : 1;
+  constexpr int COL_BUF1 = 128 + 2 * HD;        // 384: offset of the second pair
+  constexpr int B_S_FULL1 = B_S_FREE;           // second buffer's barrier (the slot is free in this kernel)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -593,6 +598,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       mbar_init(bar(B_B_EMPTY + s), 1);
     }
     mbar_init(bar(B_S_FULL), 1);
+    mbar_init(bar(B_S_FULL1), 1);
     mbar_init(bar(B_P_FULL), 8);
     mbar_init(bar(B_O_DONE), 1);
     fence_barrier_init();
@@ -673,6 +679,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       constexpr uint32_t IDESC_SS = make_idesc_f16(kBf16, kBf16, BM, BT, false, false);   // 128 keys x 64 queries
       constexpr uint32_t IDESC_TS = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);    // dO / Q as MN-major B
       auto issue_s = [&](int i) -> bool {
+        const uint32_t boff = (NBUF == 2 && (i & 1)) ? (uint32_t)COL_BUF1 : 0u;
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)((i / STAGES) & 1);
         if (!mbar_wait_bounded(bar(B_A_FULL + s), ph, abort_flag)) return false;
@@ -683,54 +690,55 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           const uint64_t dk = make_smem_desc_sw128(sK + u * SUB_BIG, 16, 1024);
           const uint64_t dq_ = make_smem_desc_sw128(sQ + s * SMALL_BYTES + u * SUB_SMALL, 16, 1024);
           #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_ST, dk + (uint64_t)(2 * k), dq_ + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
+          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_ST + boff, dk + (uint64_t)(2 * k), dq_ + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
         }
         #pragma unroll
         for (int u = 0; u < NSUB; ++u) {
           const uint64_t dv = make_smem_desc_sw128(sV + u * SUB_BIG, 16, 1024);
           const uint64_t ddo = make_smem_desc_sw128(sDO + s * SMALL_BYTES + u * SUB_SMALL, 16, 1024);
           #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_DPT, dv + (uint64_t)(2 * k), ddo + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
+          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_DPT + boff, dv + (uint64_t)(2 * k), ddo + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
         }
-        tc_commit(bar(B_S_FULL));
+        tc_commit(bar((NBUF == 2 && (i & 1)) ? B_S_FULL1 : B_S_FULL));
         return true;
       };
       bool ok = mbar_wait_bounded(bar(B_RES_FULL), 0, abort_flag);
       if (!ok) fail_code = 20;
       if (ok && !issue_s(0)) { ok = false; fail_code = 21; }
+      if (ok && NBUF == 2 && n_qt > 1 && !issue_s(1)) { ok = false; fail_code = 21; }
       for (int i = 0; ok && i < n_qt; ++i) {
         const int s = i % STAGES;
+        const uint32_t boff = (NBUF == 2 && (i & 1)) ? (uint32_t)COL_BUF1 : 0u;
         if (!mbar_wait_bounded(bar(B_P_FULL), (uint32_t)(i & 1), abort_flag)) { fail_code = 22; break; }
         tc_fence_after();
         #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {       // 16 queries per step
           const uint32_t a_off = (uint32_t)(k < 2 ? 8 * k : 32 + 8 * (k - 2));
           const uint64_t ddo = make_smem_desc_sw128(sDO + s * SMALL_BYTES + k * 2048, NSUB > 1 ? SUB_SMALL : 16, 1024);
-          umma_ts(tmem + COL_DV, tmem + COL_ST + a_off, ddo, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
+          umma_ts(tmem + COL_DV, tmem + COL_ST + boff + a_off, ddo, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar(B_B_EMPTY + s));
         #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
           const uint32_t a_off = (uint32_t)(k < 2 ? 8 * k : 32 + 8 * (k - 2));
           const uint64_t dq_ = make_smem_desc_sw128(sQ + s * SMALL_BYTES + k * 2048, NSUB > 1 ? SUB_SMALL : 16, 1024);
-          umma_ts(tmem + COL_DK, tmem + COL_DPT + a_off, dq_, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
+          umma_ts(tmem + COL_DK, tmem + COL_DPT + boff + a_off, dq_, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar(B_A_EMPTY + s));
-        if (i + 1 < n_qt) {
+        if (i + NBUF < n_qt) {
           // the tensor core runs MMAs in issue order: S^T / dP^T may be overwritten once the
           // products that read P^T / dS^T from the same columns are queued
-          if (!issue_s(i + 1)) { fail_code = 23; break; }
-        } else {
-          tc_commit(bar(B_O_DONE));
+          if (!issue_s(i + NBUF)) { fail_code = 23; break; }
         }
+        if (i + 1 == n_qt) tc_commit(bar(B_O_DONE));
       }
     }
   } else if (warp < 8) {
     const int quarter = warp & 3, half = warp >> 2;
     const int r = quarter * 32 + lane;               // key row inside the tile
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tST = tmem + lane_base + COL_ST + half * 32;
-    const uint32_t tDPT = tmem + lane_base + COL_DPT + half * 32;
+    const uint32_t tST0 = tmem + lane_base + COL_ST + half * 32;
+    const uint32_t tDPT0 = tmem + lane_base + COL_DPT + half * 32;
     const float scale = p.scale_log2;
     const int key = key0 + r;
     const bool key_ok = r < keys_in_tile;
@@ -739,7 +747,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     for (int i = 0; i < n_qt; ++i) {
       const int s = i % STAGES;
       const int m0 = (i_first + i) * BT + half * 32;     // first query of this thread's columns
-      if (!mbar_wait_bounded_warp(bar(B_S_FULL), (uint32_t)(i & 1), abort_flag)) { ok = false; fail_code = 30; break; }
+      const uint32_t boff = (NBUF == 2 && (i & 1)) ? (uint32_t)COL_BUF1 : 0u;
+      const uint32_t tST = tST0 + boff, tDPT = tDPT0 + boff;
+      if (!mbar_wait_bounded_warp(bar((NBUF == 2 && (i & 1)) ? B_S_FULL1 : B_S_FULL), (uint32_t)((i / NBUF) & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
       uint32_t sv[32], dp[32];
       tmem_ld_x32(tST, sv);
