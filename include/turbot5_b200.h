@@ -119,15 +119,6 @@ typedef struct {
    * kernels only, forward and backward (bf16/fp16, head dim 64/128; local_block a multiple of
    * 128 unless the sequence fits in one block), T5B_ERR_UNSUPPORTED otherwise.  0: off. */
   int32_t local_block;
-  /* Optional per-batch lengths for right-padded dense batches (int32[B] device arrays; NULL =
-   * every row / key is real): keys n >= seqlens_k[b] are masked, query rows m >= seqlens_q[b]
-   * return zeros (and zero gradients).  Positions are those of the padded tensor, as in the
-   * reference's `basic` path with its additive padding mask.  Replaces the unpad / varlen / pad
-   * round trip of the reference's flash module (src/turbot5/model/attentions.py:440-466,
-   * src/turbot5/model/padding.py:113-150) for masks that are a prefix of ones.  Tensor-core
-   * kernels only (T5B_ERR_UNSUPPORTED otherwise).  With local_block only keys inside the
-   * tensor are masked; the reference's zero padding blocks stay visible. */
-  const int32_t* seqlens_q; const int32_t* seqlens_k;
 } t5b_attn_args;
 
 T5B_API int t5b_attention_fwd(const t5b_attn_args* args, void* stream);

@@ -158,8 +158,7 @@ def attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
 
 
 def local_attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: Optional[torch.Tensor],
-                          block_len: int, num_buckets: int = 32, max_distance: int = 128,
-                          key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          block_len: int, num_buckets: int = 32, max_distance: int = 128) -> torch.Tensor:
     """Block-local attention core of `T5LocalAttention.forward`
     (src/turbot5/model/attentions.py:553-650, helpers src/turbot5/model/utils.py:99-140).
 
@@ -168,10 +167,7 @@ def local_attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tab
     attend to the keys of blocks i-1, i, i+1; the missing neighbours of the first and last block
     are all-zero blocks that are NOT masked (score = bias only), exactly as the reference
     concatenates them.  Bias: bidirectional buckets of (key position - query position) inside the
-    3-block window (`compute_bias(block_len)`, attentions.py:529-551).  `key_padding_mask` (B, L),
-    non-zero = keep: masked keys get the reference's additive -1e10 (attentions.py:600-603); the
-    zero blocks and the padding up to a multiple of the block length stay unmasked (the mask is
-    padded with the "keep" value of the additive form, 0).
+    3-block window (`compute_bias(block_len)`, attentions.py:529-551).
     """
     B, H, L, D = q.shape
     bl = block_len if L >= block_len else L
@@ -194,13 +190,6 @@ def local_attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tab
         bucket = relative_position_bucket(mem[None, :] - ctx[:, None], True, num_buckets, max_distance)
         bias = table.float()[torch.as_tensor(bucket, dtype=torch.long)]     # (bl, 3bl, H)
         scores = scores + bias.permute(2, 0, 1)[None, :, None]
-    if key_padding_mask is not None:
-        add = torch.where(key_padding_mask != 0, 0.0, -1e10).float()                 # (B, L)
-        add = torch.nn.functional.pad(add, (0, pad)).view(B, nblk, bl)
-        z = torch.zeros_like(add[:, :1])
-        ext = torch.cat([z, add, z], dim=1)
-        add3 = torch.cat([ext[:, 0:nblk], ext[:, 1:nblk + 1], ext[:, 2:nblk + 2]], dim=2)   # (B, nblk, 3bl)
-        scores = scores + add3[:, None, :, None, :]
     out = torch.einsum("bhnqk,bhnkd->bhnqd", torch.softmax(scores, dim=-1), vc)
     return out.reshape(B, H, nblk * bl, D)[:, :, :L]
 

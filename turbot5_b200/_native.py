@@ -43,7 +43,6 @@ class AttnArgs(C.Structure):
         ("q_pos_offset", C.c_int32), ("kernel", C.c_int32), ("sm_scale", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("local_block", C.c_int32),
-        ("seqlens_q", C.c_void_p), ("seqlens_k", C.c_void_p),
     ]
 
 

@@ -67,28 +67,24 @@ def _unit_stride_last(t):
 
 def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
                                      NUM_BUCKETS=32, MAX_DISTANCE=128, *, q_pos_offset=None,
-                                     return_lse=False, kernel="auto", balance_last_wave=True, local_block=None,
-                                     seqlens_q=None, seqlens_k=None):
+                                     return_lse=False, kernel="auto", balance_last_wave=True, local_block=None):
     """See `_dense_forward`; differentiable in q, k, v and the bias table.  `local_block` turns the
-    call into block-local attention (T5LocalAttention: the keys of the three neighbouring blocks).
-    `seqlens_q` / `seqlens_k` (int32 (B,) on the device) describe a right-padded batch: keys beyond
-    a row's length are masked, query rows beyond it come back as zeros -- the padded tensors are
-    read in place, nothing is packed or scattered."""
+    call into block-local attention (T5LocalAttention: the keys of the three neighbouring blocks)."""
     local_block = int(local_block or 0)
     if local_block:
         q_pos_offset, balance_last_wave = 0, False
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _DenseAttention.apply(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset,
-                                         kernel, balance_last_wave, local_block, seqlens_q, seqlens_k)
+                                         kernel, balance_last_wave, local_block)
         return (out, lse) if return_lse else out
     return _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset=q_pos_offset,
                           return_lse=return_lse, kernel=kernel, balance_last_wave=balance_last_wave,
-                          local_block=local_block, seqlens_q=seqlens_q, seqlens_k=seqlens_k)
+                          local_block=local_block)
 
 
 def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *,
                    q_pos_offset=None, return_lse=False, kernel="auto", balance_last_wave=True, _keep=None,
-                   local_block=0, seqlens_q=None, seqlens_k=None):
+                   local_block=0):
     """softmax(sm_scale * Q K^T + T5 bias(n - m) [+ causal mask]) V without an L x L tensor.
 
     q (B,H,M,D), k/v (B,H,N,D), any batch/head/row strides (last dim contiguous);
@@ -134,12 +130,6 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
     a.sm_scale = float(sm_scale)
     a.workspace, a.workspace_bytes = None, 0
     a.local_block = int(local_block)
-    for name, sl in (("seqlens_q", seqlens_q), ("seqlens_k", seqlens_k)):
-        if sl is not None:
-            nat.require_cuda(sl)
-            if sl.dtype != torch.int32 or sl.shape != (B,) or not sl.is_contiguous():
-                raise TypeError(f"{name} must be a contiguous int32 tensor of shape ({B},)")
-    a.seqlens_q, a.seqlens_k = nat.ptr(seqlens_q), nat.ptr(seqlens_k)
     with torch.cuda.device(q.device):
         if balance_last_wave:
             need = nat.lib().t5b_attention_workspace_bytes(a)
@@ -148,7 +138,7 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
                 a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)), "flash_attention_with_fusing_bias")
     if _keep is not None:
-        _keep.update(args=a, q=q, k=k, v=v, table=table, seqlens=(seqlens_q, seqlens_k))
+        _keep.update(args=a, q=q, k=k, v=v, table=table)
     return (out, lse) if return_lse else out
 
 
@@ -277,12 +267,11 @@ class _DenseAttention(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset, kernel, balance,
-                local_block=0, seqlens_q=None, seqlens_k=None):
+                local_block=0):
         keep = {}
         out, lse = _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE,
                                   q_pos_offset=q_pos_offset, return_lse=True, kernel=kernel,
-                                  balance_last_wave=balance, _keep=keep, local_block=local_block,
-                                  seqlens_q=seqlens_q, seqlens_k=seqlens_k)
+                                  balance_last_wave=balance, _keep=keep, local_block=local_block)
         ctx.keep = keep
         ctx.save_for_backward(out, lse)
         ctx.mark_non_differentiable(lse)
@@ -292,7 +281,7 @@ class _DenseAttention(torch.autograd.Function):
     def backward(ctx, dout, _dlse):
         out, lse = ctx.saved_tensors
         dq, dk, dv, dtable = _attention_backward(ctx.keep, out, lse, dout, varlen=False)
-        return dq, dk, dv, dtable, None, None, None, None, None, None, None, None, None, None
+        return dq, dk, dv, dtable, None, None, None, None, None, None, None, None
 
 
 class _VarlenAttention(torch.autograd.Function):

@@ -50,8 +50,7 @@ extern "C" int t5b_attention_fwd(const t5b_attn_args* a, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   const bool tc_ok = sm100_supports(*a) && (varlen ? a->total_k : a->N) > 0;
   if (a->kernel == T5B_KERNEL_TCGEN05 && !tc_ok) return T5B_ERR_UNSUPPORTED;
-  const bool tc_only = a->local_block != 0 || a->seqlens_q != nullptr || a->seqlens_k != nullptr;
-  if (tc_only && (!tc_ok || a->kernel == T5B_KERNEL_SIMT)) return T5B_ERR_UNSUPPORTED;
+  if (a->local_block != 0 && (!tc_ok || a->kernel == T5B_KERNEL_SIMT)) return T5B_ERR_UNSUPPORTED;
   if (a->kernel != T5B_KERNEL_SIMT && tc_ok) return sm100_attention_fwd(*a, spec, st);
   return simt_attention_fwd(*a, spec, st);
 }
@@ -72,8 +71,7 @@ extern "C" int t5b_attention_bwd(const t5b_attn_bwd_args* g, void* stream) {
   }
   if (!a->q || !a->k || !a->v || !a->out || !a->lse) return T5B_ERR_ARG;
   if (!g->dout || !g->dq || !g->dk || !g->dv || !g->delta) return T5B_ERR_ARG;
-  const bool tc_only = a->local_block != 0 || a->seqlens_q != nullptr || a->seqlens_k != nullptr;
-  if (tc_only && (!sm100_bwd_supports(*g) || a->kernel == T5B_KERNEL_SIMT)) return T5B_ERR_UNSUPPORTED;
+  if (a->local_block != 0 && (!sm100_bwd_supports(*g) || a->kernel == T5B_KERNEL_SIMT)) return T5B_ERR_UNSUPPORTED;
   if (a->table && !g->dtable) return T5B_ERR_ARG;
   if ((varlen ? a->total_k : a->N) == 0 || (varlen ? a->total_q : a->M) == 0) return T5B_ERR_UNSUPPORTED;
   BucketSpec spec;

@@ -182,20 +182,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const int b = w.b, q_row0 = w.q_row0, rows_in_tile = w.rows_in_tile;
   const int k_row0 = w.k_row0, qpos0 = w.qpos0;
   int len_k = w.len_k, n_base = 0;
-  int pad_lo = 0x3fffffff, pad_hi = 0x3fffffff;      // padding keys inside the tensor (see the forward)
   if (p.local_block > 0) {
     // block-local attention: the keys of the three neighbouring blocks, the zero padding blocks
     // beyond either end included and unmasked (see attn_fwd_sm100.cu)
     const int bl = p.M < p.local_block ? p.M : p.local_block;
     const int blk = q_row0 / bl;
-    if (p.seqlens_k != nullptr) { pad_lo = len_k; pad_hi = p.N; }
     n_base = (blk - 1) * bl;
     len_k = (blk + 2) * bl;
   }
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
-  // a tile made of padding rows only: nothing to do, dQ = 0
-  const int n_kv_all = (kv_end > n_base && w.rows_valid > 0) ? (kv_end - n_base + BT - 1) / BT : 0;
+  const int n_kv_all = kv_end > n_base ? (kv_end - n_base + BT - 1) / BT : 0;
   const int kv_per = (n_kv_all + parts - 1) / parts;
   const int kv_first = min(part * kv_per, n_kv_all);      // this block's key tiles: [kv_first, kv_first + n_kv)
   const int n_kv = min(n_kv_all, kv_first + kv_per) - kv_first;
@@ -357,8 +354,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_S_FREE));
 
-      const bool need_mask = (n0 + BT > len_k) || (p.causal && (n0 + BT - 1 > qpos0)) ||
-                             (n0 < pad_hi && n0 + BT > pad_lo);
+      const bool need_mask = (n0 + BT > len_k) || (p.causal && (n0 + BT - 1 > qpos0));
       int bias_mode = 0;
       float bias_const = 0.f;
       if (has_bias) {
@@ -394,7 +390,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const int c = 2 * i + u;
             const float bias = bias_mode == 2 ? lut[lut0 + c] : bias_const;
             float x = fmaf(__uint_as_float(sv[c]), scale, bias) - lse2;
-            if (need_mask && (c >= n_valid || (n0 + c0 + c >= pad_lo && n0 + c0 + c < pad_hi))) x = -INFINITY;
+            if (need_mask && c >= n_valid) x = -INFINITY;
             const float pr = fast_exp2(x);
             const float d = pr * (__uint_as_float(dp[c]) - delta_r);
             dsv[u] = d;
@@ -554,9 +550,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     h = hb % p.H;
     batch_idx = b = hb / p.H;
     key0 = tx * BM;
-    len_k = p.seqlens_k ? min(max(p.seqlens_k[b], 0), p.N) : p.N;
-    len_q = p.seqlens_q ? min(max(p.seqlens_q[b], 0), p.M) : p.M;
-    q_off = p.q_pos_offset;
+    len_k = p.N; len_q = p.M; q_off = p.q_pos_offset;
   } else {
     h = blockIdx.y;
     if (warp == 0) {
@@ -573,8 +567,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     q_off = len_k - len_q;
   }
   const int keys_in_tile = min(BM, len_k - key0);
-  // rows of the tile that exist in the tensor but hold padding keys: their gradients are zero
-  const int keys_in_tensor = p.cu_k == nullptr ? min(BM, p.N - key0) : keys_in_tile;
   // query tiles that can see a key of this tile: causal keeps q_off + m >= key
   int i_first = 0;
   if (p.causal) i_first = max(0, key0 - q_off) / BT;
@@ -586,7 +578,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     i_first = max(0, (kb - 1) * bl) / BT;
     n_qt_all = (min(len_q, (kb + 2) * bl) + BT - 1) / BT;
   }
-  int n_qt = keys_in_tile > 0 ? max(0, n_qt_all - i_first) : 0;      // a tile of padding keys only: dK = dV = 0
+  int n_qt = max(0, n_qt_all - i_first);
   if (parts > 1) {       // this block's share of the query tiles
     const int per = (n_qt + parts - 1) / parts;
     const int first = min(part * per, n_qt);
@@ -857,7 +849,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           #pragma unroll
           for (int i = 0; i < 32; ++i) o[32 * c + i] = __uint_as_float(v[i]) * sc;
         }
-        bool write_out = r < keys_in_tensor;       // padding keys inside the tensor get their zeros
+        bool write_out = key_ok;
         if (parts > 1 && key_ok) {
           float* acc = (t == 0 ? e.ws_dv : e.ws_dk) + ((int64_t)tail_slot * BM + r) * HD + half * OH;
           #pragma unroll
@@ -921,8 +913,7 @@ static BwdPlan sm100_bwd_plan(const t5b_attn_args& a) {
   t.q_parts = t.k_parts = 1;
   t.q_rem = t.k_rem = 0;
   t.cnt_bytes = t.dq_bytes = t.dk_bytes = 0;
-  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || a.seqlens_q != nullptr || a.seqlens_k != nullptr ||
-      nq > 0x3fffffffLL || nk > 0x3fffffffLL) return t;
+  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || nq > 0x3fffffffLL || nk > 0x3fffffffLL) return t;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {

@@ -184,7 +184,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     w = *shared_work;
     if (w.b < 0) return;   // block beyond the last tile: uniform exit, nothing allocated yet
   }
-  const int b = w.b, q_row0 = w.q_row0, rows_in_tile = w.rows_in_tile, rows_valid = w.rows_valid;
+  const int b = w.b, q_row0 = w.q_row0, rows_in_tile = w.rows_in_tile;
   const int k_row0 = w.k_row0, qpos0 = w.qpos0;
   int len_k = w.len_k;
   // Block-local attention (T5LocalAttention, src/turbot5/model/attentions.py:523-650): the rows of
@@ -193,13 +193,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // scores are the bare bias) and the TMA zero fill supplies them.  So the key range becomes
   // [n_base, len_k) with a negative n_base for the first block and len_k past the tensor's end.
   int n_base = 0;
-  // keys [pad_lo, pad_hi) are padding tokens inside the tensor (right-padded batch): masked.  Only
-  // block-local attention needs the interval: elsewhere len_k itself ends at the last real key.
-  int pad_lo = 0x3fffffff, pad_hi = 0x3fffffff;
   if (p.local_block > 0) {
     const int bl = p.M < p.local_block ? p.M : p.local_block;      // a shorter sequence is one block
     const int blk = q_row0 / bl;
-    if (p.seqlens_k != nullptr) { pad_lo = len_k; pad_hi = p.N; }
     n_base = (blk - 1) * bl;
     len_k = (blk + 2) * bl;
   }
@@ -207,8 +203,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // keys this tile can see
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
-  // a tile made of padding rows only has nothing to do: its rows come out as zeros
-  const int n_kv_all = (kv_end > n_base && rows_valid > 0) ? (kv_end - n_base + BN - 1) / BN : 0;
+  const int n_kv_all = kv_end > n_base ? (kv_end - n_base + BN - 1) / BN : 0;
   // this block's share of the key tiles: [kv_first, kv_first + n_kv)
   const int kv_per = (n_kv_all + parts - 1) / parts;
   const int kv_first = min(part * kv_per, n_kv_all);
@@ -376,8 +371,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (lane == 0) mbar_arrive(bar(BAR_S_FREE));
 
       // tile classification (uniform over the block)
-      const bool need_mask = (n0 + BN > len_k) || (p.causal && (n0 + BN - 1 > qpos0)) ||
-                             (rows_valid < rows_in_tile) || (n0 < pad_hi && n0 + BN > pad_lo);
+      const bool need_mask = (n0 + BN > len_k) || (p.causal && (n0 + BN - 1 > qpos0));
       int bias_mode = 0;            // 0 none, 1 constant over the tile, 2 per element
       float bias_const = 0.f;
       if (has_bias) {
@@ -409,16 +403,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         } else {
           // per-row window into the padded table: column c of this tile reads brow[c]
           const float* brow = lut + (n0 + c0 - qpos + md + LUT_PAD);
-          // columns < n_valid are visible (none for a padding row), except the padding keys
-          const int n_valid = r < rows_valid ? (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0 : 0;
-          const int pl = pad_lo - n0 - c0, ph = pad_hi - n0 - c0;
+          const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;   // columns < n_valid are visible
           #pragma unroll
           for (int c = 0; c < NCH; ++c) {
             #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float bias = bias_mode == 2 ? brow[c * 32 + i] : bias_const;
               float x = fmaf(__uint_as_float(sv[c][i]), scale, bias);
-              if (need_mask && (c * 32 + i >= n_valid || (c * 32 + i >= pl && c * 32 + i < ph))) x = -INFINITY;
+              if (need_mask && (c * 32 + i >= n_valid)) x = -INFINITY;
               sv[c][i] = __float_as_uint(x);
               if ((i & 3) == 0) m0 = fmaxf(m0, x); else if ((i & 3) == 1) m1 = fmaxf(m1, x);
               else if ((i & 3) == 2) m2 = fmaxf(m2, x); else m3 = fmaxf(m3, x);
@@ -642,7 +634,6 @@ bool sm100_supports(const t5b_attn_args& a) {
     if (a.cu_seqlens_q != nullptr || a.causal || a.M != a.N || a.q_pos_offset != 0) return false;
     if (a.M > a.local_block && (a.local_block % 128) != 0) return false;
   }
-  if ((a.seqlens_q != nullptr || a.seqlens_k != nullptr) && a.cu_seqlens_q != nullptr) return false;
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   if (!al16(a.q) || !al16(a.k) || !al16(a.v) || !al16(a.out)) return false;
   const int64_t s[] = {a.q_stride_b, a.q_stride_h, a.q_stride_m, a.k_stride_b, a.k_stride_h, a.k_stride_n,
@@ -664,8 +655,7 @@ TailPlan sm100_tail_plan(const t5b_attn_args& a) {
   t.tail_first = t.n_total;
   t.parts = 1;
   t.counters_bytes = t.ml_bytes = t.o_bytes = 0;
-  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || a.seqlens_q != nullptr || a.seqlens_k != nullptr ||
-      n_total > 0x3fffffffLL) return t;
+  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || n_total > 0x3fffffffLL) return t;
   static int sms[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return t; }

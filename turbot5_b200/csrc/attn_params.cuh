@@ -10,7 +10,6 @@ struct AttnParams {
   float* lse;
   const void* table;
   const int32_t* cu_q; const int32_t* cu_k;
-  const int32_t* seqlens_q; const int32_t* seqlens_k;   // dense, right-padded batches (may be null)
   int32_t* status;
   int64_t q_stride_b, q_stride_h, q_stride_m;
   int64_t k_stride_b, k_stride_h, k_stride_n;
@@ -45,7 +44,6 @@ inline AttnParams make_attn_params(const t5b_attn_args& a) {
   p.q = a.q; p.k = a.k; p.v = a.v; p.out = a.out;
   p.lse = a.lse; p.table = a.table;
   p.cu_q = a.cu_seqlens_q; p.cu_k = a.cu_seqlens_k;
-  p.seqlens_q = a.seqlens_q; p.seqlens_k = a.seqlens_k;
   p.status = a.device_status;
   p.q_stride_b = a.q_stride_b; p.q_stride_h = a.q_stride_h; p.q_stride_m = a.q_stride_m;
   p.k_stride_b = a.k_stride_b; p.k_stride_h = a.k_stride_h; p.k_stride_n = a.k_stride_n;
@@ -71,7 +69,6 @@ struct TileWork {
   int k_row0;        // first key row of the sequence (0 for dense)
   int len_k;
   int qpos0;         // key-coordinate position of the tile's first query row
-  int rows_valid;    // rows of the tile that are real queries (<= rows_in_tile; right-padded batches)
 };
 
 #ifdef __CUDACC__
@@ -103,7 +100,7 @@ __device__ __forceinline__ TileWork find_varlen_tile(const AttnParams& p, int bl
     acc += __shfl_sync(0xffffffffu, incl, 31);
   }
   TileWork w;
-  w.b = -1; w.q_row0 = 0; w.rows_in_tile = 0; w.k_row0 = 0; w.len_k = 0; w.qpos0 = 0; w.rows_valid = 0;
+  w.b = -1; w.q_row0 = 0; w.rows_in_tile = 0; w.k_row0 = 0; w.len_k = 0; w.qpos0 = 0;
   if (found_b >= 0) {
     const int q0 = p.cu_q[found_b], q1 = p.cu_q[found_b + 1];
     const int k0 = p.cu_k[found_b], k1 = p.cu_k[found_b + 1];
@@ -113,7 +110,6 @@ __device__ __forceinline__ TileWork find_varlen_tile(const AttnParams& p, int bl
     w.k_row0 = k0;
     w.len_k = k1 - k0;
     w.qpos0 = (k1 - k0) - (q1 - q0) + tile_in_seq * TILE_M;
-    w.rows_valid = w.rows_in_tile;
   }
   return w;
 }
@@ -127,10 +123,8 @@ __device__ __forceinline__ TileWork dense_tile(const AttnParams& p, int blk_x, i
   w.q_row0 = t * TILE_M;
   w.rows_in_tile = min(TILE_M, p.M - w.q_row0);
   w.k_row0 = 0;
-  w.len_k = p.seqlens_k ? min(max(p.seqlens_k[blk_z], 0), p.N) : p.N;
+  w.len_k = p.N;
   w.qpos0 = p.q_pos_offset + w.q_row0;
-  w.rows_valid = w.rows_in_tile;
-  if (p.seqlens_q) w.rows_valid = min(w.rows_in_tile, max(p.seqlens_q[blk_z] - w.q_row0, 0));
   return w;
 }
 // Sequence and tile of block `blk` in the concatenated per-sequence tile lists of `cu`

@@ -134,12 +134,6 @@ class T5FlashAttention(nn.Module):
         self.causal = config.is_decoder and not cross_attention
         # decoding steps with at most this many query rows use the split-KV kernel
         self.decode_max_rows = 8
-        # True: padding masks are known to be prefixes of ones (right-padded batches, what the T5
-        # tokenizers produce).  The padded tensors are then read in place with per-row lengths
-        # instead of being packed, run through the packed-sequence kernel and scattered back.
-        # Positions are those of the padded tensor either way.  Off by default: an arbitrary mask
-        # (holes, left padding) needs the packing path.
-        self.right_padded_masks = bool(getattr(config, "right_padded_masks", False))
 
     def forward(self, hidden_states, mask=None, key_value_states=None, position_bias=None,
                 past_key_value=None, layer_head_mask=None, query_length=None, use_cache=False,
@@ -187,15 +181,6 @@ class T5FlashAttention(nn.Module):
                                                         causal=self.causal, sm_scale=1.0,
                                                         NUM_BUCKETS=nb, MAX_DISTANCE=md,
                                                         q_pos_offset=0 if key_value_states is not None else None)
-        elif self.right_padded_masks:
-            if mask.dim() != 2:
-                raise ValueError("T5FlashAttention takes the raw 0/1 (batch, key_length) mask")
-            lens = (mask != 0).sum(dim=-1).to(torch.int32)          # on the device, no read-back
-            self_attn = query_states.shape[2] == key_states.shape[2] and key_value_states is None
-            attn = flash_attention_with_fusing_bias(query_states, key_states, value_states, table,
-                                                    causal=self.causal, sm_scale=1.0, NUM_BUCKETS=nb, MAX_DISTANCE=md,
-                                                    q_pos_offset=0 if key_value_states is not None else None,
-                                                    seqlens_q=lens if self_attn else None, seqlens_k=lens)
         else:
             # padded batch: pack the kept tokens, run the packed-sequence kernel, scatter back
             if mask.dim() != 2:
@@ -232,9 +217,8 @@ class T5LocalFlashAttention(T5FlashAttention):
     block's two neighbours (zero blocks at the ends) and materialises a (block, 3 x block) bias; here
     the same kernel that serves full attention walks only the three blocks of keys a query tile
     can see, the zero blocks come from the TMA's out-of-bounds fill, and the bias is looked up
-    per element as always.  Encoder self-attention, no cache; differentiable.  A padding mask is
-    taken for right-padded batches (`config.right_padded_masks`): the keys beyond a row's length
-    are masked as the reference's -1e10 does, its zero padding blocks stay visible.
+    per element as always.  Encoder self-attention without a padding mask (the reference adds
+    -1e10 at masked keys: not expressed here yet), no cache; differentiable.
     """
 
     def __init__(self, config, has_relative_attention_bias=False, **kwargs):
@@ -243,13 +227,8 @@ class T5LocalFlashAttention(T5FlashAttention):
 
     def forward(self, hidden_states, mask=None, position_bias=None, layer_head_mask=None, past_key_value=None,
                 use_cache=None, output_attentions=False, **kwargs):
-        lens = None
         if mask is not None:
-            # the reference adds -1e10 at masked keys; here: right-padded batches only
-            if not self.right_padded_masks:
-                raise NotImplementedError("T5LocalFlashAttention takes padding masks of right-padded batches only: "
-                                          "set config.right_padded_masks = True")
-            lens = (mask != 0).sum(dim=-1).to(torch.int32)
+            raise NotImplementedError("T5LocalFlashAttention does not take a padding mask yet")
         if self.is_decoder:
             raise NotImplementedError("T5LocalFlashAttention covers encoder self-attention only")
         batch_size, seq_length = hidden_states.shape[:2]
@@ -264,7 +243,7 @@ class T5LocalFlashAttention(T5FlashAttention):
         attn = flash_attention_with_fusing_bias(q, k, v, table, causal=False, sm_scale=1.0,
                                                 NUM_BUCKETS=self.relative_attention_num_buckets,
                                                 MAX_DISTANCE=self.relative_attention_max_distance,
-                                                local_block=self.block_len, seqlens_k=lens)
+                                                local_block=self.block_len)
         out = self.o(attn.transpose(1, 2).contiguous().view(batch_size, -1, self.inner_dim))
         outputs = (out, None, table)
         if output_attentions:

@@ -47,7 +47,6 @@ class T5StackConfig:
     decoder_start_token_id: int = 0
     attention_type: str = "flash"              # encoder self-attention: "flash" (full) or "local" (block-local)
     sliding_window: int = 512                  # block length of the "local" type
-    right_padded_masks: bool = False           # padding masks are prefixes of ones: read padded tensors in place
 
 
 class T5DenseGatedActDense(nn.Module):
