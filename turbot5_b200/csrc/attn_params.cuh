@@ -79,25 +79,37 @@ template <int TILE_M>
 __device__ __forceinline__ TileWork find_varlen_tile(const AttnParams& p, int blk) {
   const int lane = threadIdx.x & 31;
   int found_b = -1, tile_in_seq = 0, acc = 0;
-  for (int b0 = 0; b0 < p.B && found_b < 0; b0 += 32) {
-    const int bb = b0 + lane;
-    int nt = 0;
-    if (bb < p.B) nt = (p.cu_q[bb + 1] - p.cu_q[bb] + TILE_M - 1) / TILE_M;
-    int incl = nt;
-    #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
+  // Longest sequences first: a tile's work grows with its sequence's key count, and a long tile
+  // scheduled last leaves the GPU mostly idle while it finishes.  Without sorting anything, the
+  // sequences are taken in four classes by key count (quarters of max_seqlen_k = p.N, the
+  // caller's upper bound; 0 or a too small bound just puts everything into the first class),
+  // each class in index order.
+  const int t1 = (int)(((long long)p.N * 3) >> 2), t2 = p.N >> 1, t3 = p.N >> 2;
+  for (int cls = 0; cls < 4 && found_b < 0; ++cls) {
+    for (int b0 = 0; b0 < p.B && found_b < 0; b0 += 32) {
+      const int bb = b0 + lane;
+      int nt = 0;
+      if (bb < p.B) {
+        const int lk = p.cu_k[bb + 1] - p.cu_k[bb];
+        const int c = lk > t1 ? 0 : (lk > t2 ? 1 : (lk > t3 ? 2 : 3));
+        if (c == cls) nt = (p.cu_q[bb + 1] - p.cu_q[bb] + TILE_M - 1) / TILE_M;
+      }
+      int incl = nt;
+      #pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      const int excl = acc + incl - nt;
+      const bool mine = blk >= excl && blk < excl + nt;
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (m) {
+        const int src = __ffs(m) - 1;
+        found_b = b0 + src;
+        tile_in_seq = blk - __shfl_sync(0xffffffffu, excl, src);
+      }
+      acc += __shfl_sync(0xffffffffu, incl, 31);
     }
-    const int excl = acc + incl - nt;
-    const bool mine = blk >= excl && blk < excl + nt;
-    const unsigned m = __ballot_sync(0xffffffffu, mine);
-    if (m) {
-      const int src = __ffs(m) - 1;
-      found_b = b0 + src;
-      tile_in_seq = blk - __shfl_sync(0xffffffffu, excl, src);
-    }
-    acc += __shfl_sync(0xffffffffu, incl, 31);
   }
   TileWork w;
   w.b = -1; w.q_row0 = 0; w.rows_in_tile = 0; w.k_row0 = 0; w.len_k = 0; w.qpos0 = 0;
