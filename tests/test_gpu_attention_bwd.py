@@ -289,3 +289,21 @@ def test_block_local_attention_gradients_vs_oracle(D, L, bl):
     check_close(out.detach(), want.detach(), dt, "local out")
     for g, w, nm in zip(leaves, ref, ("dq", "dk", "dv", "dtable")):
         check_grad_close(g.grad, w.grad, f"local d{D} L{L} block {bl} {nm}", floor=2.0 if nm == "dtable" else 1e-6)
+
+
+def test_gradients_at_a_long_sequence():
+    # 4096 x 4096 keys, two heads: every tile class of the backward kernels (far tiles with one bias
+    # bucket, diagonal tiles with per-element bias, the split last wave) in one call, against float32
+    # autograd of the oracle on the whole problem
+    dt = torch.bfloat16
+    B, H, L = 1, 2, 4096
+    q = seeded((B, H, L, 64), 1, 0.5, dtype=dt)
+    k = seeded((B, H, L, 64), 2, 0.5, dtype=dt)
+    v = seeded((B, H, L, 64), 3, dtype=dt)
+    dout = seeded((B, H, L, 64), 5, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    want = _oracle_grads(q, k, v, table, dout)
+    got = _cuda_grads(q, k, v, table, dout, dt)
+    check_close(got[0], want[0], dt, "out")
+    for g, w, nm in zip(got[1:], want[1:], ("dq", "dk", "dv", "dtable")):
+        check_grad_close(g, w, "4k " + nm, floor=2.0 if nm == "dtable" else 1e-6)
