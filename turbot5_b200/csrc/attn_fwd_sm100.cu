@@ -23,6 +23,10 @@
 //               powers of two, which lets the two threads of a row agree after the
 //               exponentials instead of before them (see the loop).
 //
+// At head dim 64 one thread (warp 8) both loads and issues the matrix products -- every refill of
+// the K/V ring waits on an event at least half a tile old, so it never blocks -- and the block has
+// nine warps; at head dim 128 the loads keep warp 8 and the products move to warp 9.
+//
 // Head dim 64 uses 128-key tiles, head dim 128 uses 64-key tiles whose rows are two
 // 128-byte-swizzled sub-tiles; either way two blocks fit on an SM (<= 256 TMEM columns and
 // 80-96 KB of tiles each), so one block's softmax overlaps the other block's matrix products.
@@ -42,9 +46,9 @@ namespace sm100 {
 
 constexpr int BM = 128;            // query rows per block
 constexpr int STAGES = 2;          // K/V ring depth
-constexpr int NUM_THREADS = 320;
+constexpr int MAX_THREADS = 320;
 constexpr int SOFTMAX_THREADS = 256;
-constexpr int WARP_TMA = 8, WARP_MMA = 9;
+constexpr int WARP_TMA = 8;
 constexpr int TMEM_COLS = 256;
 
 // Tile geometry per head dim.  Head dim 64: 128 keys per tile.  Head dim 128: 64 keys per tile,
@@ -128,13 +132,18 @@ __device__ __forceinline__ uint32_t scale_packed(uint32_t v, float beta) {
 template <bool kBf16> constexpr float kRescaleThreshold = kBf16 ? 40.f : 10.f;
 
 template <bool kBf16, int HD>
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+__global__ void __launch_bounds__(HD == 64 ? 288 : MAX_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v,
                 const __grid_constant__ AttnParams p,
                 const __grid_constant__ BucketSpec spec) {
   using G = Geo<HD>;
+  // head dim 64: warp 8 does the loads and the matrix products (288 threads); head dim 128: the
+  // loads keep a warp of their own (its tiles are shorter, the refill has less slack)
+  constexpr bool kOneIoThread = HD == 64;
+  constexpr int NUM_THREADS = kOneIoThread ? 288 : MAX_THREADS;
+  constexpr int WARP_MMA = kOneIoThread ? 8 : 9;
   constexpr int BN = G::BN, NSUB = G::NSUB, SUB_Q = G::SUB_Q, SUB_KV = G::SUB_KV;
   constexpr int Q_BYTES = G::Q_BYTES, KV_BYTES = G::KV_BYTES, SMEM_TILES = G::SMEM_TILES;
   constexpr int COL_S = G::COL_S, COL_P = G::COL_P, COL_O = G::COL_O;
@@ -259,7 +268,82 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   volatile int* abort_flag = &ctl->abort_flag;
   int fail_code = 0;
 
-  if (warp == WARP_TMA) {
+  if (kOneIoThread && warp == WARP_MMA) {
+    // ============================================================ loads and matrix products, one thread
+    // (head dim 64).  Every ring refill waits on an event that lies at least half a tile back, so
+    // the thread never blocks on them, and the block has one warp less to schedule and poll.
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t IDESC_QK = make_idesc_f16(kBf16, kBf16, BM, BN, false, false);
+      constexpr uint32_t IDESC_PV = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);
+      auto load_k = [&](int j) {
+        const int s = j % STAGES;
+        mbar_expect_tx(bar(BAR_K_FULL + s), KV_BYTES);
+        #pragma unroll
+        for (int u = 0; u < NSUB; ++u)
+          tma_load_4d(sK + s * KV_BYTES + u * SUB_KV, &tmap_k, bar(BAR_K_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
+      };
+      auto load_v = [&](int j) {
+        const int s = j % STAGES;
+        mbar_expect_tx(bar(BAR_V_FULL + s), KV_BYTES);
+        #pragma unroll
+        for (int u = 0; u < NSUB; ++u)
+          tma_load_4d(sV + s * KV_BYTES + u * SUB_KV, &tmap_v, bar(BAR_V_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
+      };
+      auto issue_qk = [&](int j) -> bool {
+        const int s = j % STAGES;
+        if (!mbar_wait_bounded(bar(BAR_K_FULL + s), (uint32_t)((j / STAGES) & 1), abort_flag)) return false;
+        tc_fence_after();
+        #pragma unroll
+        for (int u = 0; u < NSUB; ++u) {
+          const uint64_t da = make_smem_desc_sw128(sQ + u * SUB_Q, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sK + s * KV_BYTES + u * SUB_KV, 16, 1024);
+          #pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_ss(tmem + COL_S, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC_QK, (u | k) > 0);
+        }
+        tc_commit(bar(BAR_S_FULL));
+        tc_commit(bar(BAR_K_EMPTY + s));
+        return true;
+      };
+      mbar_expect_tx(bar(BAR_Q_FULL), Q_BYTES);
+      #pragma unroll
+      for (int u = 0; u < NSUB; ++u) tma_load_4d(sQ + u * SUB_Q, &tmap_q, bar(BAR_Q_FULL), 64 * u, q_row0, h, b);
+      load_k(0); load_v(0);
+      if (n_kv > 1) { load_k(1); load_v(1); }
+      bool ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0, abort_flag);
+      if (!ok) fail_code = 20;
+      if (ok && !issue_qk(0)) { ok = false; fail_code = 21; }
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j % STAGES;
+        if (j + 1 < n_kv) {
+          if (!mbar_wait_bounded(bar(BAR_S_FREE), (uint32_t)(j & 1), abort_flag)) { fail_code = 25; break; }
+          tc_fence_after();
+          if (!issue_qk(j + 1)) { fail_code = 23; break; }
+        }
+        // refill the ring: K(j+2) into the slot of K(j) (QK(j) finished before S(j) could be copied),
+        // V(j+1) into the slot of V(j-1) (PV(j-1) was issued a tile ago)
+        if (j + 2 < n_kv) {
+          if (!mbar_wait_bounded(bar(BAR_K_EMPTY + s), (uint32_t)((j / STAGES) & 1), abort_flag)) { fail_code = 10; break; }
+          load_k(j + 2);
+        }
+        if (j >= 1 && j + 1 < n_kv) {
+          if (!mbar_wait_bounded(bar(BAR_V_EMPTY + ((j - 1) % STAGES)), (uint32_t)(((j - 1) / STAGES) & 1), abort_flag)) { fail_code = 11; break; }
+          load_v(j + 1);
+        }
+        if (!mbar_wait_bounded(bar(BAR_P_FULL), (uint32_t)(j & 1), abort_flag)) { fail_code = 22; break; }
+        tc_fence_after();
+        if (!mbar_wait_bounded(bar(BAR_V_FULL + s), (uint32_t)((j / STAGES) & 1), abort_flag)) { fail_code = 24; break; }
+        tc_fence_after();
+        #pragma unroll
+        for (int k = 0; k < BN / 16; ++k) {
+          const uint64_t dv = make_smem_desc_sw128(sV + s * KV_BYTES + k * 2048, NSUB > 1 ? SUB_KV : 16, 1024);
+          umma_ts(tmem + COL_O, tmem + COL_P + k * 8, dv, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(BAR_O_DONE));
+        tc_commit(bar(BAR_V_EMPTY + s));
+      }
+    }
+  } else if (!kOneIoThread && warp == WARP_TMA) {
     // ============================================================ TMA producer
     if (lane == 0 && n_kv > 0) {
       mbar_expect_tx(bar(BAR_Q_FULL), Q_BYTES);
@@ -280,7 +364,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           tma_load_4d(sV + s * KV_BYTES + u * SUB_KV, &tmap_v, bar(BAR_V_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
       }
     }
-  } else if (warp == WARP_MMA) {
+  } else if (!kOneIoThread && warp == WARP_MMA) {
     // ============================================================ MMA issuer
     if (lane == 0 && n_kv > 0) {
       constexpr uint32_t IDESC_QK = make_idesc_f16(kBf16, kBf16, BM, BN, false, false);
@@ -743,7 +827,7 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
     }
     if (dev >= 0 && dev < 64) attr_set[dev][which] = true;
   }
-  kern<<<grid, NUM_THREADS, smem, stream>>>(mq, mk, mv, p, spec);
+  kern<<<grid, HD == 64 ? 288 : MAX_THREADS, smem, stream>>>(mq, mk, mv, p, spec);
   return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;
 }
 
