@@ -74,7 +74,7 @@ struct __align__(16) Control {
   uint32_t tmem_base;
   int abort_flag;
   int work[6];
-  float vec[STAGES][2][BT];     // dkv kernel: lse (log2 domain) and delta of the streamed query tile
+  float vec[STAGES][2][BT];     // dkv kernel: -lse (log2 domain) and -delta of the streamed query tile
   float hist[MAX_BUCKETS];      // dq kernel: bias-table gradient of this block
 };
 
@@ -667,8 +667,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           const bool valid = m < len_q;
           const int64_t idx = p.cu_q == nullptr ? ((int64_t)batch_idx * p.H + h) * p.M + m
                                                 : ((int64_t)q_row0 + m) * p.H + h;
-          ctl->vec[s][0][c] = lse_to_log2(valid ? p.lse[idx] : 0.f, valid);
-          ctl->vec[s][1][c] = valid ? e.delta[idx] : 0.f;
+          // stored negated: the softmax warps add them with packed adds
+          ctl->vec[s][0][c] = -lse_to_log2(valid ? p.lse[idx] : 0.f, valid);
+          ctl->vec[s][1][c] = valid ? -e.delta[idx] : 0.f;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_A_FULL + s));
@@ -786,10 +787,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             const int c = 16 * hh + 2 * ii;
             const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
             const float2 d2 = *reinterpret_cast<const float2*>(vd + c);
-            float x0, x1, e0, e1;
+            float x0, x1, g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]), e0, e1;
             fma2(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, bias_const);
-            const float p0 = fast_exp2(x0 - l2.x), p1 = fast_exp2(x1 - l2.y);
-            mul2(e0, e1, p0, p1, __uint_as_float(dp[c]) - d2.x, __uint_as_float(dp[c + 1]) - d2.y);
+            add2(x0, x1, l2.x, l2.y);          // - lse
+            add2(g0, g1, d2.x, d2.y);          // dP - delta
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            mul2(e0, e1, p0, p1, g0, g1);
             pp[ii] = pack2<kBf16>(p0, p1);
             pd[ii] = pack2<kBf16>(e0, e1);
           }
@@ -801,12 +804,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             for (int u = 0; u < 2; ++u) {
               const int c = 16 * hh + 2 * ii + u;
               const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
-              float x = fmaf(__uint_as_float(sv[c]), scale, bias) - vl[c];
+              float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
               // masked: key outside the sequence, or (causal) after the query
               if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
               const float pr = fast_exp2(x);
               pv[u] = pr;
-              dv2[u] = pr * (__uint_as_float(dp[c]) - vd[c]);
+              dv2[u] = pr * (__uint_as_float(dp[c]) + vd[c]);
             }
             pp[ii] = pack2<kBf16>(pv[0], pv[1]);
             pd[ii] = pack2<kBf16>(dv2[0], dv2[1]);
