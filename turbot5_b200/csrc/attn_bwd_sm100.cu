@@ -36,6 +36,17 @@ constexpr int NUM_THREADS = 320;
 constexpr int WARP_TMA = 8, WARP_MMA = 9;
 constexpr int LUT_PAD = BM + BT;
 constexpr int MAX_BUCKETS = 2 * kMaxBucketsPerSide;
+// dq kernel, bias-table gradient of the tiles near the diagonal: a warp owns a 32 x 32 piece of
+// the tile (lane = row, register = column) whose elements fall on 63 diagonals.  Each warp sums
+// them in a private window of shared memory with plain 128-bit read-modify-writes: the lanes are
+// split into four groups by (lane & 3), each with its own copy of the window, so that within a
+// batch of four columns no two lanes touch the same word; __syncwarp() orders the batches.  The
+// copies start at word offsets whose banks make every quarter-warp access conflict-free, and
+// each is shifted by ((group + 1) & 3) words so that the four words of a batch are 16-byte aligned.
+constexpr int DIAG_GROUP_WORDS = 68;
+constexpr int DIAG_WARP_WORDS = 220 + DIAG_GROUP_WORDS;      // group bases 0, 72, 144, 220
+constexpr int DIAG_BYTES = 8 * DIAG_WARP_WORDS * 4;
+__device__ __forceinline__ int diag_group_base(int g) { return g == 3 ? 220 : 72 * g; }
 
 // Geometry per head dim.  A row of 128 dims is two 128-byte-swizzled sub-tiles of 64 dims (two TMA
 // boxes; the K loop of the first products walks both; an MN-major operand spans two swizzle atoms,
@@ -81,7 +92,7 @@ struct __align__(16) Control {
 template <int HD>
 __host__ __device__ inline size_t smem_bytes(int lut_entries) {
   // float bias per delta, float gradient per delta, int16 bucket per delta
-  return 1024 + BGeo<HD>::SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 10;
+  return 1024 + BGeo<HD>::SMEM_TILES + sizeof(Control) + 16 + (size_t)lut_entries * 10 + 16 + DIAG_BYTES;
 }
 
 // ---------------------------------------------------------------- delta = rowsum(dO o O)
@@ -232,6 +243,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   // Folded into buckets once, at the end of the block.
   float* dlut = lut + lut_n;
   int16_t* lutb = reinterpret_cast<int16_t*>(dlut + lut_n);
+  float* diag = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(lutb + lut_n) + 15) & ~uintptr_t(15));
   const bool has_bias = p.table != nullptr;
   if (has_bias) {
     for (int i = tid; i < lut_n; i += NUM_THREADS) {
@@ -240,6 +252,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       dlut[i] = 0.f;
       lutb[i] = (int16_t)bucket;
     }
+    for (int i = tid; i < 8 * DIAG_WARP_WORDS; i += NUM_THREADS) diag[i] = 0.f;
     for (int i = tid; i < MAX_BUCKETS; i += NUM_THREADS) ctl->hist[i] = 0.f;
   }
   tc_fence_before();
@@ -381,6 +394,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           pk[i] = pack2<kBf16>(d0, d1);
         }
         ds_sum = a0 + a1;
+      } else if (!need_mask) {
+        // whole tile visible, bias per element (near the diagonal); dS stays in sv for the
+        // bias-table gradient below
+        const float nl = -lse2, nd = -delta_r;
+        const float* lrow = lut + lut0;
+        #pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float x0 = lrow[2 * i], x1 = lrow[2 * i + 1], g0, g1, d0, d1;
+          add2(x0, x1, nl, nl);
+          fma2v(x0, x1, __uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1]), scale, x0, x1);
+          fma2(g0, g1, __uint_as_float(dp[2 * i]), __uint_as_float(dp[2 * i + 1]), 1.f, nd);
+          mul2(d0, d1, fast_exp2(x0), fast_exp2(x1), g0, g1);
+          sv[2 * i] = __float_as_uint(d0); sv[2 * i + 1] = __float_as_uint(d1);
+          pk[i] = pack2<kBf16>(d0, d1);
+        }
       } else {
         #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -394,7 +422,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const float pr = fast_exp2(x);
             const float d = pr * (__uint_as_float(dp[c]) - delta_r);
             dsv[u] = d;
-            if (bias_mode == 2) atomicAdd(&dlut[lut0 + c], d);
+            if (bias_mode == 2) sv[c] = __float_as_uint(d);
             else ds_sum += d;
           }
           pk[i] = pack2<kBf16>(dsv[0], dsv[1]);
@@ -411,6 +439,36 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_P_FULL));
+      // (after dS is published: the matrix product runs while the warp does its bookkeeping)
+      if (bias_mode == 2) {
+        // element (lane, c) lies on diagonal t = c - lane + 31 of this warp's piece
+        float* wdiag = diag + warp * DIAG_WARP_WORDS;
+        const int g = lane & 3;
+        float* mine = wdiag + diag_group_base(g) + ((g + 1) & 3) + 31 - lane;
+        #pragma unroll
+        for (int bq = 0; bq < 8; ++bq) {
+          float4 a4 = *reinterpret_cast<float4*>(mine + 4 * bq);
+          a4.x += __uint_as_float(sv[4 * bq]);     a4.y += __uint_as_float(sv[4 * bq + 1]);
+          a4.z += __uint_as_float(sv[4 * bq + 2]); a4.w += __uint_as_float(sv[4 * bq + 3]);
+          *reinterpret_cast<float4*>(mine + 4 * bq) = a4;
+          __syncwarp();
+        }
+        // fold the four copies, clear them, and add the 63 sums to the block's table of deltas
+        #pragma unroll
+        for (int tt = 0; tt < 2; ++tt) {
+          const int t = lane + 32 * tt;
+          float sum = 0.f;
+          #pragma unroll
+          for (int gg = 0; gg < 4; ++gg) {
+            float* w_ = wdiag + diag_group_base(gg) + ((gg + 1) & 3) + t;
+            sum += *w_;
+            *w_ = 0.f;
+          }
+          // lane 31 of the second round (t = 63) holds no diagonal: its words are never written
+          if (t < 63 && sum != 0.f) atomicAdd(&dlut[lut0 + lane - 31 + t], sum);
+        }
+        __syncwarp();
+      }
     }
 
     if (ok && n_kv > 0) {
@@ -790,6 +848,23 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             float x0, x1, g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]), e0, e1;
             fma2(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, bias_const);
             add2(x0, x1, l2.x, l2.y);          // - lse
+            add2(g0, g1, d2.x, d2.y);          // dP - delta
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            mul2(e0, e1, p0, p1, g0, g1);
+            pp[ii] = pack2<kBf16>(p0, p1);
+            pd[ii] = pack2<kBf16>(e0, e1);
+          }
+        } else if (!tile_masked) {
+          // whole tile visible, bias per element (near the diagonal)
+          const float* lrow = lut + lut0;
+          #pragma unroll
+          for (int ii = 0; ii < 8; ++ii) {
+            const int c = 16 * hh + 2 * ii;
+            const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
+            const float2 d2 = *reinterpret_cast<const float2*>(vd + c);
+            float x0 = lrow[-c], x1 = lrow[-c - 1], g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]), e0, e1;
+            add2(x0, x1, l2.x, l2.y);          // bias - lse
+            fma2v(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, x0, x1);
             add2(g0, g1, d2.x, d2.y);          // dP - delta
             const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
             mul2(e0, e1, p0, p1, g0, g1);

@@ -258,6 +258,13 @@ __device__ __forceinline__ void fma2(float& d0, float& d1, float a0, float a1, f
       "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
       : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
 }
+// (d0, d1) = (a0, a1) * (b, b) + (c0, c1)
+__device__ __forceinline__ void fma2v(float& d0, float& d1, float a0, float a1, float b, float c0, float c1) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %6};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b), "f"(c0), "f"(c1));
+}
 // (d0, d1) = (a0, a1) * (b0, b1)
 __device__ __forceinline__ void mul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
   asm("{\n\t.reg .b64 ra, rb, rd;\n\t"
