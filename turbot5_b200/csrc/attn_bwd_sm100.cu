@@ -96,32 +96,44 @@ __host__ __device__ inline size_t smem_bytes(int lut_entries) {
 }
 
 // ---------------------------------------------------------------- delta = rowsum(dO o O)
-template <typename T>
-__global__ void bwd_delta_kernel(const AttnParams p, const BwdExtra e, long long n_rows) {
-  const int lane = threadIdx.x & 31;
-  const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
-  for (long long i = warp0; i < n_rows; i += n_warps) {
-    int64_t o_off, do_off;
-    if (p.cu_q == nullptr) {
-      const int m = (int)(i % p.M);
-      const long long bh = i / p.M;
-      const int h = (int)(bh % p.H), b = (int)(bh / p.H);
-      o_off = (int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + (int64_t)m * p.o_stride_m;
-      do_off = (int64_t)b * e.do_stride_b + (int64_t)h * e.do_stride_h + (int64_t)m * e.do_stride_m;
-    } else {
-      const int h = (int)(i % p.H);
-      const long long row = i / p.H;
-      o_off = (int64_t)h * p.o_stride_h + row * p.o_stride_m;
-      do_off = (int64_t)h * e.do_stride_h + row * e.do_stride_m;
-    }
-    const T* o = reinterpret_cast<const T*>(p.out) + o_off;
-    const T* d = reinterpret_cast<const T*>(e.dout) + do_off;
+// HD / 8 lanes per row, one 16-byte load of O and of dO each (rows and strides are 16-byte
+// aligned: both tensors are also read or written 16 bytes at a time by the other kernels).
+template <typename T, int HD>
+__global__ void __launch_bounds__(256) bwd_delta_kernel(const AttnParams p, const BwdExtra e, long long n_rows) {
+  constexpr int LPR = HD / 8, RPW = 32 / LPR;          // lanes per row, rows per warp
+  const int lane = threadIdx.x & 31, sub = lane % LPR;
+  const long long group0 = ((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5) * RPW + lane / LPR;
+  const long long stride = (((long long)gridDim.x * blockDim.x) >> 5) * RPW;
+  // whole warps iterate together (the shuffles below are warp-wide); rows past the end add zeros
+  const long long n_iter = (n_rows + stride - 1) / stride;
+  for (long long it = 0; it < n_iter; ++it) {
+    const long long i = group0 + it * stride;
+    const bool valid = i < n_rows;
     float s = 0.f;
-    for (int c = lane; c < p.D; c += 32) s = fmaf(to_float(o[c]), to_float(d[c]), s);
+    if (valid) {
+      int64_t o_off, do_off;
+      if (p.cu_q == nullptr) {
+        const int m = (int)(i % p.M);
+        const long long bh = i / p.M;
+        const int h = (int)(bh % p.H), b = (int)(bh / p.H);
+        o_off = (int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + (int64_t)m * p.o_stride_m;
+        do_off = (int64_t)b * e.do_stride_b + (int64_t)h * e.do_stride_h + (int64_t)m * e.do_stride_m;
+      } else {
+        const int h = (int)(i % p.H);
+        const long long row = i / p.H;
+        o_off = (int64_t)h * p.o_stride_h + row * p.o_stride_m;
+        do_off = (int64_t)h * e.do_stride_h + row * e.do_stride_m;
+      }
+      const uint4 ov = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.out) + o_off) + sub);
+      const uint4 dv = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(e.dout) + do_off) + sub);
+      const T* o8 = reinterpret_cast<const T*>(&ov);
+      const T* d8 = reinterpret_cast<const T*>(&dv);
+      #pragma unroll
+      for (int c = 0; c < 8; ++c) s = fmaf(to_float(o8[c]), to_float(d8[c]), s);
+    }
     #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) e.delta[i] = s;      // same indexing as lse: (b,h,m) dense, (row,h) packed
+    for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (valid && sub == 0) e.delta[i] = s;      // same indexing as lse: (b,h,m) dense, (row,h) packed
   }
 }
 
@@ -1073,11 +1085,18 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
   // 1. delta
   {
     const long long n_rows = rows_q * a.H;
-    long long blocks = (n_rows + 7) / 8;
+    const int rows_per_block = 8 * (32 / (HD / 8));
+    long long blocks = (n_rows + rows_per_block - 1) / rows_per_block;
     if (blocks > 148LL * 16) blocks = 148LL * 16;
     if (blocks > 0) {
-      if (bf16) bwd_delta_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(p, e, n_rows);
-      else bwd_delta_kernel<__half><<<(unsigned)blocks, 256, 0, stream>>>(p, e, n_rows);
+      const unsigned nb = (unsigned)blocks;
+      if (HD == 64) {
+        if (bf16) bwd_delta_kernel<__nv_bfloat16, 64><<<nb, 256, 0, stream>>>(p, e, n_rows);
+        else bwd_delta_kernel<__half, 64><<<nb, 256, 0, stream>>>(p, e, n_rows);
+      } else {
+        if (bf16) bwd_delta_kernel<__nv_bfloat16, 128><<<nb, 256, 0, stream>>>(p, e, n_rows);
+        else bwd_delta_kernel<__half, 128><<<nb, 256, 0, stream>>>(p, e, n_rows);
+      }
       if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
     }
   }
