@@ -223,7 +223,20 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-  if (tid == 0) {
+  auto load_kv_tile = [&](int j) {
+    const int s = j % STAGES;
+    mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
+    #pragma unroll
+    for (int u = 0; u < NSUB; ++u)
+      tma_load_4d(sK + s * SMALL_BYTES + u * SUB_SMALL, &tmap_k, bar(B_A_FULL + s), 64 * u, k_row0 + n_first + j * BT, h, b);
+    mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
+    #pragma unroll
+    for (int u = 0; u < NSUB; ++u)
+      tma_load_4d(sV + s * SMALL_BYTES + u * SUB_SMALL, &tmap_v, bar(B_B_FULL + s), 64 * u, k_row0 + n_first + j * BT, h, b);
+  };
+  if (warp == WARP_TMA && lane == 0) {
+    // the loading thread sets up the barriers itself and starts the block's first loads at once:
+    // they are in flight while the other threads build the bias tables below
     ctl->abort_flag = 0;
     mbar_init(bar(B_RES_FULL), 1);
     for (int s = 0; s < STAGES; ++s) {
@@ -238,10 +251,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     mbar_init(bar(B_O_DONE), 1);
     fence_barrier_init();
     fence_proxy_async();
-  }
-  if (warp == WARP_TMA && lane == 0) {
-    tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_do);
-    tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
+    if (n_kv > 0) {
+      mbar_expect_tx(bar(B_RES_FULL), 2 * BIG_BYTES);
+      #pragma unroll
+      for (int u = 0; u < NSUB; ++u) {
+        tma_load_4d(sQ + u * SUB_BIG, &tmap_q, bar(B_RES_FULL), 64 * u, q_row0, h, b);
+        tma_load_4d(sDO + u * SUB_BIG, &tmap_do, bar(B_RES_FULL), 64 * u, q_row0, h, b);
+      }
+      for (int j = 0; j < STAGES && j < n_kv; ++j) load_kv_tile(j);
+    }
   }
   if (warp == WARP_MMA) {
     tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
@@ -258,11 +276,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   float* diag = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(lutb + lut_n) + 15) & ~uintptr_t(15));
   const bool has_bias = p.table != nullptr;
   if (has_bias) {
-    for (int i = tid; i < lut_n; i += NUM_THREADS) {
-      const int bucket = bucket_of_delta(spec, i - md - LUT_PAD);
-      lut[i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
-      dlut[i] = 0.f;
-      lutb[i] = (int16_t)bucket;
+    // one bucket search and one table load per delta in [-md, md]; beyond, the bucket no longer
+    // changes and the padding is filled with the two end values
+    for (int i = tid; i <= 2 * md; i += NUM_THREADS) {
+      const int bucket = bucket_of_delta(spec, i - md);
+      lut[LUT_PAD + i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
+      lutb[LUT_PAD + i] = (int16_t)bucket;
+    }
+    for (int i = tid; i < lut_n; i += NUM_THREADS) dlut[i] = 0.f;
+    __syncthreads();
+    {
+      const float lo_v = lut[LUT_PAD], hi_v = lut[LUT_PAD + 2 * md];
+      const int16_t lo_b = lutb[LUT_PAD], hi_b = lutb[LUT_PAD + 2 * md];
+      for (int i = tid; i < LUT_PAD; i += NUM_THREADS) {
+        lut[i] = lo_v; lutb[i] = lo_b;
+        lut[LUT_PAD + 2 * md + 1 + i] = hi_v; lutb[LUT_PAD + 2 * md + 1 + i] = hi_b;
+      }
     }
     for (int i = tid; i < 8 * DIAG_WARP_WORDS; i += NUM_THREADS) diag[i] = 0.f;
     for (int i = tid; i < MAX_BUCKETS; i += NUM_THREADS) ctl->hist[i] = 0.f;
@@ -275,26 +304,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   int fail_code = 0;
 
   if (warp == WARP_TMA) {
-    if (lane == 0 && n_kv > 0) {
-      mbar_expect_tx(bar(B_RES_FULL), 2 * BIG_BYTES);
-      #pragma unroll
-      for (int u = 0; u < NSUB; ++u) {
-        tma_load_4d(sQ + u * SUB_BIG, &tmap_q, bar(B_RES_FULL), 64 * u, q_row0, h, b);
-        tma_load_4d(sDO + u * SUB_BIG, &tmap_do, bar(B_RES_FULL), 64 * u, q_row0, h, b);
-      }
-      for (int j = 0; j < n_kv; ++j) {
+    if (lane == 0) {
+      for (int j = STAGES; j < n_kv; ++j) {        // the first STAGES tiles were requested above
         const int s = j % STAGES;
         const uint32_t ph = (uint32_t)((j / STAGES) & 1);
-        if (j >= STAGES && !mbar_wait_bounded(bar(B_A_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
-        mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
-        #pragma unroll
-        for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sK + s * SMALL_BYTES + u * SUB_SMALL, &tmap_k, bar(B_A_FULL + s), 64 * u, k_row0 + n_first + j * BT, h, b);
-        if (j >= STAGES && !mbar_wait_bounded(bar(B_B_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
-        mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
-        #pragma unroll
-        for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sV + s * SMALL_BYTES + u * SUB_SMALL, &tmap_v, bar(B_B_FULL + s), 64 * u, k_row0 + n_first + j * BT, h, b);
+        if (!mbar_wait_bounded(bar(B_A_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
+        if (!mbar_wait_bounded(bar(B_B_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
+        load_kv_tile(j);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -553,9 +569,24 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   tc_fence_before();
   __syncthreads();
   if (has_bias && e.dtable != nullptr) {
-    for (int i = tid; i < lut_n; i += NUM_THREADS) {
-      const float g = dlut[i];
-      if (g != 0.f) atomicAdd(&ctl->hist[lutb[i]], g);
+    // deltas -> buckets: a bucket covers a run of consecutive deltas, so each warp sums the runs
+    // inside its 32 entries with shuffles and only the first lane of a run touches the histogram
+    // (one shared-memory atomic per run instead of 32 lanes retrying on the same word)
+    for (int i0 = warp * 32; i0 < lut_n; i0 += NUM_THREADS) {
+      const int i = i0 + lane;
+      float g = i < lut_n ? dlut[i] : 0.f;
+      const int bk = i < lut_n ? (int)lutb[i] : -1;
+      const int prev = __shfl_up_sync(0xffffffffu, bk, 1);
+      const bool head = lane == 0 || prev != bk;
+      const unsigned heads = __ballot_sync(0xffffffffu, head);
+      const int run = __popc(heads & (0xffffffffu >> (31 - lane)));      // index of this lane's run
+      #pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float v = __shfl_down_sync(0xffffffffu, g, off);
+        const int r2 = __shfl_down_sync(0xffffffffu, run, off);
+        if (lane + off < 32 && r2 == run) g += v;
+      }
+      if (head && bk >= 0 && g != 0.f) atomicAdd(&ctl->hist[bk], g);
     }
     __syncthreads();
     const int nb = spec.bidirectional ? 2 * spec.n_side : spec.n_side;
@@ -658,7 +689,19 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-  if (tid == 0) {
+  auto load_q_tile = [&](int i) {
+    const int s = i % STAGES;
+    const int m0 = (i_first + i) * BT;
+    mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
+    #pragma unroll
+    for (int u = 0; u < NSUB; ++u)
+      tma_load_4d(sQ + s * SMALL_BYTES + u * SUB_SMALL, &tmap_q, bar(B_A_FULL + s), 64 * u, q_row0 + m0, h, b);
+    mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
+    #pragma unroll
+    for (int u = 0; u < NSUB; ++u)
+      tma_load_4d(sDO + s * SMALL_BYTES + u * SUB_SMALL, &tmap_do, bar(B_B_FULL + s), 64 * u, q_row0 + m0, h, b);
+  };
+  if (warp == WARP_TMA && lane == 0) {       // as in the dQ kernel: barriers, then the first loads at once
     ctl->abort_flag = 0;
     mbar_init(bar(B_RES_FULL), 1);
     for (int s = 0; s < STAGES; ++s) {
@@ -673,10 +716,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     mbar_init(bar(B_O_DONE), 1);
     fence_barrier_init();
     fence_proxy_async();
-  }
-  if (warp == WARP_TMA && lane == 0) {
-    tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_do);
-    tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
+    if (n_qt > 0) {
+      mbar_expect_tx(bar(B_RES_FULL), 2 * BIG_BYTES);
+      #pragma unroll
+      for (int u = 0; u < NSUB; ++u) {
+        tma_load_4d(sK + u * SUB_BIG, &tmap_k, bar(B_RES_FULL), 64 * u, k_row0 + key0, h, b);
+        tma_load_4d(sV + u * SUB_BIG, &tmap_v, bar(B_RES_FULL), 64 * u, k_row0 + key0, h, b);
+      }
+      for (int i = 0; i < STAGES && i < n_qt; ++i) load_q_tile(i);
+    }
   }
   if (warp == WARP_MMA) {
     tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
@@ -686,9 +734,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const int lut_n = 2 * md + 1 + 2 * LUT_PAD;
   const bool has_bias = p.table != nullptr;
   if (has_bias) {
-    for (int i = tid; i < lut_n; i += NUM_THREADS) {
-      const int bucket = bucket_of_delta(spec, i - md - LUT_PAD);
-      lut[i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
+    for (int i = tid; i <= 2 * md; i += NUM_THREADS) {       // as in the dQ kernel
+      const int bucket = bucket_of_delta(spec, i - md);
+      lut[LUT_PAD + i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
+    }
+    __syncthreads();
+    const float lo_v = lut[LUT_PAD], hi_v = lut[LUT_PAD + 2 * md];
+    for (int i = tid; i < LUT_PAD; i += NUM_THREADS) {
+      lut[i] = lo_v;
+      lut[LUT_PAD + 2 * md + 1 + i] = hi_v;
     }
   }
   tc_fence_before();
@@ -701,14 +755,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   if (warp == WARP_TMA) {
     // whole warp: lane 0 drives the TMA, all lanes fetch the lse / delta of the query tile
     if (n_qt > 0) {
-      if (lane == 0) {
-        mbar_expect_tx(bar(B_RES_FULL), 2 * BIG_BYTES);
-        #pragma unroll
-        for (int u = 0; u < NSUB; ++u) {
-          tma_load_4d(sK + u * SUB_BIG, &tmap_k, bar(B_RES_FULL), 64 * u, k_row0 + key0, h, b);
-          tma_load_4d(sV + u * SUB_BIG, &tmap_v, bar(B_RES_FULL), 64 * u, k_row0 + key0, h, b);
-        }
-      }
       bool okp = true;
       for (int i = 0; i < n_qt; ++i) {
         const int s = i % STAGES;
@@ -720,16 +766,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           if (okp && !mbar_wait_bounded(bar(B_B_EMPTY + s), ph ^ 1u, abort_flag)) { okp = false; }
           if (!__all_sync(0xffffffffu, okp)) { fail_code = 10; break; }
         }
-        if (lane == 0) {
-          mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
-          #pragma unroll
-          for (int u = 0; u < NSUB; ++u)
-            tma_load_4d(sQ + s * SMALL_BYTES + u * SUB_SMALL, &tmap_q, bar(B_A_FULL + s), 64 * u, q_row0 + m0, h, b);
-          mbar_expect_tx(bar(B_B_FULL + s), SMALL_BYTES);
-          #pragma unroll
-          for (int u = 0; u < NSUB; ++u)
-            tma_load_4d(sDO + s * SMALL_BYTES + u * SUB_SMALL, &tmap_do, bar(B_B_FULL + s), 64 * u, q_row0 + m0, h, b);
-        }
+        if (lane == 0 && i >= STAGES) load_q_tile(i);      // the first STAGES tiles were requested above
         #pragma unroll
         for (int u = 0; u < 2; ++u) {
           const int c = lane + 32 * u;

@@ -256,9 +256,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const int md = spec.max_distance;
   const int lut_n = 2 * md + 1 + 2 * LUT_PAD;
   if (p.table != nullptr) {
-    for (int i = tid; i < lut_n; i += NUM_THREADS) {
-      const int bucket = bucket_of_delta(spec, i - md - LUT_PAD);
-      lut[i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
+    // one bucket search and one table load per delta in [-md, md]; beyond, the bucket no longer
+    // changes and the padding is filled with the two end values
+    for (int i = tid; i <= 2 * md; i += NUM_THREADS) {
+      const int bucket = bucket_of_delta(spec, i - md);
+      lut[LUT_PAD + i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
+    }
+    __syncthreads();
+    const float lo_v = lut[LUT_PAD], hi_v = lut[LUT_PAD + 2 * md];
+    for (int i = tid; i < LUT_PAD; i += NUM_THREADS) {
+      lut[i] = lo_v;
+      lut[LUT_PAD + 2 * md + 1 + i] = hi_v;
     }
   }
   tc_fence_before();
