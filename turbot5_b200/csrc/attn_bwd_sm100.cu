@@ -223,6 +223,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  // this thread's row statistics, requested before the set-up below so that the latency of the
+  // two reads is over by the time the first scores arrive
+  float lse_raw = 0.f, delta_r = 0.f;
+  if (warp < 8) {
+    const int r_ = (warp & 3) * 32 + lane;
+    if (r_ < rows_in_tile) {
+      const int64_t row_ = (int64_t)q_row0 + r_;
+      const int64_t idx_ = p.cu_q == nullptr ? ((int64_t)batch_idx * p.H + h) * p.M + row_ : row_ * p.H + h;
+      lse_raw = p.lse[idx_];
+      delta_r = e.delta[idx_];
+    }
+  }
   auto load_kv_tile = [&](int j) {
     const int s = j % STAGES;
     mbar_expect_tx(bar(B_A_FULL + s), SMALL_BYTES);
@@ -279,7 +291,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     // one bucket search and one table load per delta in [-md, md]; beyond, the bucket no longer
     // changes and the padding is filled with the two end values
     for (int i = tid; i <= 2 * md; i += NUM_THREADS) {
-      const int bucket = bucket_of_delta(spec, i - md);
+      const int bucket = bucket_of_delta_counted(spec, i - md);
       lut[LUT_PAD + i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
       lutb[LUT_PAD + i] = (int16_t)bucket;
     }
@@ -375,9 +387,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int qpos = qpos0 + r;
     const bool row_ok = r < rows_in_tile;
     const int64_t row = (int64_t)q_row0 + r;
-    const int64_t stat_idx = p.cu_q == nullptr ? ((int64_t)batch_idx * p.H + h) * p.M + row : row * p.H + h;
-    const float lse2 = lse_to_log2(row_ok ? p.lse[stat_idx] : 0.f, row_ok);
-    const float delta_r = row_ok ? e.delta[stat_idx] : 0.f;
+    const float lse2 = lse_to_log2(lse_raw, row_ok);
     // bias-table gradient of tiles that lie entirely beyond +-max_distance: one bucket each
     float far_neg = 0.f, far_pos = 0.f;
     bool ok = true;
@@ -689,6 +699,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  // producer warp: lse / delta of the first query tile, requested before the set-up below
+  float pre_l[2] = {0.f, 0.f}, pre_d[2] = {0.f, 0.f};
+  auto stat_index = [&](int m) -> int64_t {
+    return p.cu_q == nullptr ? ((int64_t)batch_idx * p.H + h) * p.M + m : ((int64_t)q_row0 + m) * p.H + h;
+  };
+  if (warp == WARP_TMA && n_qt > 0) {
+    #pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int m = i_first * BT + lane + 32 * u;
+      if (m < len_q) { pre_l[u] = p.lse[stat_index(m)]; pre_d[u] = e.delta[stat_index(m)]; }
+    }
+  }
   auto load_q_tile = [&](int i) {
     const int s = i % STAGES;
     const int m0 = (i_first + i) * BT;
@@ -735,7 +757,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   const bool has_bias = p.table != nullptr;
   if (has_bias) {
     for (int i = tid; i <= 2 * md; i += NUM_THREADS) {       // as in the dQ kernel
-      const int bucket = bucket_of_delta(spec, i - md);
+      const int bucket = bucket_of_delta_counted(spec, i - md);
       lut[LUT_PAD + i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
     }
     __syncthreads();
@@ -772,11 +794,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           const int c = lane + 32 * u;
           const int m = m0 + c;
           const bool valid = m < len_q;
-          const int64_t idx = p.cu_q == nullptr ? ((int64_t)batch_idx * p.H + h) * p.M + m
-                                                : ((int64_t)q_row0 + m) * p.H + h;
+          const int64_t idx = stat_index(m);
+          const float l_ = i == 0 ? pre_l[u] : (valid ? p.lse[idx] : 0.f);
+          const float d_ = i == 0 ? pre_d[u] : (valid ? e.delta[idx] : 0.f);
           // stored negated: the softmax warps add them with packed adds
-          ctl->vec[s][0][c] = -lse_to_log2(valid ? p.lse[idx] : 0.f, valid);
-          ctl->vec[s][1][c] = valid ? -e.delta[idx] : 0.f;
+          ctl->vec[s][0][c] = -lse_to_log2(l_, valid);
+          ctl->vec[s][1][c] = valid ? -d_ : 0.f;
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_A_FULL + s));

@@ -222,7 +222,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // ---------------------------------------------------------------- set-up
   const uint32_t bar0 = smem_u32(&ctl->bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-  if (tid == 0) {
+  auto load_k = [&](int j) {
+    const int s = j % STAGES;
+    mbar_expect_tx(bar(BAR_K_FULL + s), KV_BYTES);
+    #pragma unroll
+    for (int u = 0; u < NSUB; ++u)
+      tma_load_4d(sK + s * KV_BYTES + u * SUB_KV, &tmap_k, bar(BAR_K_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
+  };
+  auto load_v = [&](int j) {
+    const int s = j % STAGES;
+    mbar_expect_tx(bar(BAR_V_FULL + s), KV_BYTES);
+    #pragma unroll
+    for (int u = 0; u < NSUB; ++u)
+      tma_load_4d(sV + s * KV_BYTES + u * SUB_KV, &tmap_v, bar(BAR_V_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
+  };
+  // The loading thread sets up the barriers itself and requests Q and the first STAGES key/value
+  // tiles at once: they are in flight while the other threads build the bias table below.
+  if (warp == (kOneIoThread ? WARP_MMA : WARP_TMA) && lane == 0) {
     ctl->abort_flag = 0;
     mbar_init(bar(BAR_Q_FULL), 1);
     for (int s = 0; s < STAGES; ++s) {
@@ -240,12 +256,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (int qd = 0; qd < 4; ++qd) mbar_init(bar(BAR_PAIR + qd), 2);
     fence_barrier_init();
     fence_proxy_async();
+    if (n_kv > 0) {
+      mbar_expect_tx(bar(BAR_Q_FULL), Q_BYTES);
+      #pragma unroll
+      for (int u = 0; u < NSUB; ++u) tma_load_4d(sQ + u * SUB_Q, &tmap_q, bar(BAR_Q_FULL), 64 * u, q_row0, h, b);
+      for (int j = 0; j < STAGES && j < n_kv; ++j) { load_k(j); load_v(j); }
+    }
   }
-  if (warp == WARP_TMA && lane == 0) {
-    tma_prefetch_desc(&tmap_q);
-    tma_prefetch_desc(&tmap_k);
-    tma_prefetch_desc(&tmap_v);
-  }
+  __syncwarp();
   if (warp == WARP_MMA) {
     tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
     tmem_relinquish();
@@ -259,7 +277,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // one bucket search and one table load per delta in [-md, md]; beyond, the bucket no longer
     // changes and the padding is filled with the two end values
     for (int i = tid; i <= 2 * md; i += NUM_THREADS) {
-      const int bucket = bucket_of_delta(spec, i - md);
+      const int bucket = bucket_of_delta_counted(spec, i - md);
       lut[LUT_PAD + i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
     }
     __syncthreads();
@@ -283,20 +301,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (lane == 0 && n_kv > 0) {
       constexpr uint32_t IDESC_QK = make_idesc_f16(kBf16, kBf16, BM, BN, false, false);
       constexpr uint32_t IDESC_PV = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);
-      auto load_k = [&](int j) {
-        const int s = j % STAGES;
-        mbar_expect_tx(bar(BAR_K_FULL + s), KV_BYTES);
-        #pragma unroll
-        for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sK + s * KV_BYTES + u * SUB_KV, &tmap_k, bar(BAR_K_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
-      };
-      auto load_v = [&](int j) {
-        const int s = j % STAGES;
-        mbar_expect_tx(bar(BAR_V_FULL + s), KV_BYTES);
-        #pragma unroll
-        for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sV + s * KV_BYTES + u * SUB_KV, &tmap_v, bar(BAR_V_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
-      };
       auto issue_qk = [&](int j) -> bool {
         const int s = j % STAGES;
         if (!mbar_wait_bounded(bar(BAR_K_FULL + s), (uint32_t)((j / STAGES) & 1), abort_flag)) return false;
@@ -313,11 +317,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         tc_commit(bar(BAR_K_EMPTY + s));
         return true;
       };
-      mbar_expect_tx(bar(BAR_Q_FULL), Q_BYTES);
-      #pragma unroll
-      for (int u = 0; u < NSUB; ++u) tma_load_4d(sQ + u * SUB_Q, &tmap_q, bar(BAR_Q_FULL), 64 * u, q_row0, h, b);
-      load_k(0); load_v(0);
-      if (n_kv > 1) { load_k(1); load_v(1); }
+      static_assert(STAGES == 2, "the refills below assume the two tiles requested during set-up");
       bool ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0, abort_flag);
       if (!ok) fail_code = 20;
       if (ok && !issue_qk(0)) { ok = false; fail_code = 21; }
@@ -353,23 +353,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     }
   } else if (!kOneIoThread && warp == WARP_TMA) {
     // ============================================================ TMA producer
-    if (lane == 0 && n_kv > 0) {
-      mbar_expect_tx(bar(BAR_Q_FULL), Q_BYTES);
-      #pragma unroll
-      for (int u = 0; u < NSUB; ++u) tma_load_4d(sQ + u * SUB_Q, &tmap_q, bar(BAR_Q_FULL), 64 * u, q_row0, h, b);
-      for (int j = 0; j < n_kv; ++j) {
+    if (lane == 0) {
+      for (int j = STAGES; j < n_kv; ++j) {        // the first STAGES tiles were requested during set-up
         const int s = j % STAGES;
         const uint32_t ph = (uint32_t)((j / STAGES) & 1);
-        if (j >= STAGES && !mbar_wait_bounded(bar(BAR_K_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
-        mbar_expect_tx(bar(BAR_K_FULL + s), KV_BYTES);
-        #pragma unroll
-        for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sK + s * KV_BYTES + u * SUB_KV, &tmap_k, bar(BAR_K_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
-        if (j >= STAGES && !mbar_wait_bounded(bar(BAR_V_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
-        mbar_expect_tx(bar(BAR_V_FULL + s), KV_BYTES);
-        #pragma unroll
-        for (int u = 0; u < NSUB; ++u)
-          tma_load_4d(sV + s * KV_BYTES + u * SUB_KV, &tmap_v, bar(BAR_V_FULL + s), 64 * u, k_row0 + n_first + j * BN, h, b);
+        if (!mbar_wait_bounded(bar(BAR_K_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 10; break; }
+        load_k(j);
+        if (!mbar_wait_bounded(bar(BAR_V_EMPTY + s), ph ^ 1u, abort_flag)) { fail_code = 11; break; }
+        load_v(j);
       }
     }
   } else if (!kOneIoThread && warp == WARP_MMA) {

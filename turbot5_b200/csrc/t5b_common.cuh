@@ -41,6 +41,18 @@ __device__ __forceinline__ int bucket_of_delta(const BucketSpec& s, int delta) {
   return lo + ((s.bidirectional && delta > 0) ? s.n_side : 0);
 }
 
+// The same bucket, found by counting the thresholds that do not exceed |delta|: every lane reads
+// the same threshold in the same iteration (one broadcast read of the kernel parameters), where
+// the binary search reads a different one per lane and is serialised.  For building a table of
+// consecutive deltas with a whole block.
+__device__ __forceinline__ int bucket_of_delta_counted(const BucketSpec& s, int delta) {
+  int d = s.bidirectional ? (delta < 0 ? -delta : delta) : (delta < 0 ? -delta : 0);
+  d = min(d, s.max_distance);
+  int n = 0;
+  for (int k = 0; k < s.n_first; ++k) n += ((int)s.first[k] <= d) ? 1 : 0;
+  return n + ((s.bidirectional && delta > 0) ? s.n_side : 0);
+}
+
 template <typename T> __device__ __forceinline__ float to_float(T x);
 template <> __device__ __forceinline__ float to_float<float>(float x) { return x; }
 template <> __device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
