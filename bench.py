@@ -141,7 +141,30 @@ def run_reference(args, rank, world):
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    _emit(line)
+
+
+_JSON_FD = None
+
+
+def _keep_stdout_for_json():
+    """Library banners (NCCL prints its version on stdout when the first communicator is made) must not
+    land beside the one JSON line: file descriptor 1 is pointed at stderr for the run and the line is
+    written to the saved descriptor."""
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def _emit(line):
+    text = json.dumps(line) + "\n"
+    if _JSON_FD is not None:
+        sys.stdout.flush()
+        os.write(_JSON_FD, text.encode())
+    else:
+        print(text, end="", flush=True)
 
 
 def main():
@@ -180,6 +203,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        _keep_stdout_for_json()
         dist.init_process_group("nccl", device_id=dev)
 
     w = dict(WORKLOAD)
@@ -335,7 +359,7 @@ def main():
             line["secondary"] = secondary
         if sp_line:
             line["sequence_parallel"] = sp_line
-        print(json.dumps(line), flush=True)
+        _emit(line)
     if world > 1:
         dist.destroy_process_group()
 
