@@ -78,6 +78,34 @@ def test_seeded_gradients_vs_oracle(B, H, M, N, causal, off, dt):
         check_grad_close(g, w, what + " " + nm, floor=2.0 if nm == "dtable" else 1e-6)
 
 
+BUCKET_CASES = [
+    # num_buckets, max_distance, causal, L: the per-delta tables, their padding and the fold of the
+    # bias-table gradient into buckets, for geometries other than T5's 32 / 128
+    (32, 128, True, 1100),      # unidirectional buckets over many tiles
+    (64, 256, False, 900),      # the window around the diagonal is wider than a tile pair
+    (16, 32, False, 700),       # narrow window: most tiles lie beyond +-max_distance
+    (128, 1024, False, 640),    # every tile is inside the window
+    (8, 20, True, 333),
+]
+
+
+@pytest.mark.parametrize("nb,md,causal,L", BUCKET_CASES)
+def test_bucket_geometries_gradients_vs_oracle(nb, md, causal, L):
+    dt = torch.bfloat16
+    B, H = 1, 2
+    q = seeded((B, H, L, 64), 11, 0.5, dtype=dt)
+    k = seeded((B, H, L, 64), 12, 0.5, dtype=dt)
+    v = seeded((B, H, L, 64), 13, dtype=dt)
+    dout = seeded((B, H, L, 64), 15, dtype=dt)
+    table = seeded((nb, H), 14, 0.2, dtype=dt)
+    want = _oracle_grads(q, k, v, table, dout, causal=causal, num_buckets=nb, max_distance=md)
+    got = _cuda_grads(q, k, v, table, dout, dt, causal=causal, NUM_BUCKETS=nb, MAX_DISTANCE=md)
+    what = f"{(nb, md, causal, L)}"
+    check_close(got[0], want[0], dt, what + " out")
+    for g, w, nm in zip(got[1:], want[1:], ("dq", "dk", "dv", "dtable")):
+        check_grad_close(g, w, what + " " + nm, floor=2.0 if nm == "dtable" else 1e-6)
+
+
 def test_no_bias_scale_and_strided_views():
     # BHLD views of BLHD buffers, sm_scale != 1, no table: gradients keep the inputs' layout
     t5b = _ops()
