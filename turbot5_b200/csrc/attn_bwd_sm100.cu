@@ -147,6 +147,7 @@ enum {
   B_S_FREE,
   B_P_FULL,
   B_O_DONE,
+  B_P_FULL1,                         // dK/dV kernel with two S^T/dP^T pairs: P_FULL of the odd tiles
   B_NUM
 };
 static_assert(B_NUM <= 24, "barrier slots");
@@ -735,6 +736,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     mbar_init(bar(B_S_FULL), 1);
     mbar_init(bar(B_S_FULL1), 1);
     mbar_init(bar(B_P_FULL), 8);
+    mbar_init(bar(B_P_FULL1), 8);
     mbar_init(bar(B_O_DONE), 1);
     fence_barrier_init();
     fence_proxy_async();
@@ -840,7 +842,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       for (int i = 0; ok && i < n_qt; ++i) {
         const int s = i % STAGES;
         const uint32_t boff = (NBUF == 2 && (i & 1)) ? (uint32_t)COL_BUF1 : 0u;
-        if (!mbar_wait_bounded(bar(B_P_FULL), (uint32_t)(i & 1), abort_flag)) { fail_code = 22; break; }
+        // With two S^T/dP^T pairs the softmax warps can finish tile i+1 without anything further from
+        // this thread (its products were queued a tile ago), so a barrier shared by all tiles could
+        // complete two phases between two looks of this thread and the parity test would then wait
+        // for ever.  One barrier per pair: its next phase needs S^T(i+2), queued below this wait.
+        if (!mbar_wait_bounded(bar((NBUF == 2 && (i & 1)) ? B_P_FULL1 : B_P_FULL), (uint32_t)((i / NBUF) & 1), abort_flag)) { fail_code = 22; break; }
         tc_fence_after();
         #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {       // 16 queries per step
@@ -968,7 +974,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_P_FULL));
+      if (lane == 0) mbar_arrive(bar((NBUF == 2 && (i & 1)) ? B_P_FULL1 : B_P_FULL));
     }
 
     if (ok && n_qt > 0) {
