@@ -147,7 +147,9 @@ enum {
   B_S_FREE,
   B_P_FULL,
   B_O_DONE,
-  B_P_FULL1,                         // dK/dV kernel with two S^T/dP^T pairs: P_FULL of the odd tiles
+  B_P_FULL1,
+  B_DP_FULL,                         // dkv kernel: dP^T of a tile (S^T has its own barrier)
+  B_DP_FULL1,
   B_NUM
 };
 static_assert(B_NUM <= 24, "barrier slots");
@@ -631,7 +633,6 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   // pair, so the first products of tile i+1 run while the softmax warps work on tile i.
   constexpr int NBUF = HD == 128 ? 2 : 1;
   constexpr int COL_BUF1 = 128 + 2 * HD;        // 384: offset of the second pair
-  constexpr int B_S_FULL1 = B_S_FREE;           // second buffer's barrier (the slot is free in this kernel)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -734,7 +735,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       mbar_init(bar(B_B_EMPTY + s), 1);
     }
     mbar_init(bar(B_S_FULL), 1);
-    mbar_init(bar(B_S_FULL1), 1);
+    mbar_init(bar(B_DP_FULL), 1);
+    mbar_init(bar(B_DP_FULL1), 1);
     mbar_init(bar(B_P_FULL), 8);
     mbar_init(bar(B_P_FULL1), 8);
     mbar_init(bar(B_O_DONE), 1);
@@ -811,12 +813,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     if (lane == 0 && n_qt > 0) {
       constexpr uint32_t IDESC_SS = make_idesc_f16(kBf16, kBf16, BM, BT, false, false);   // 128 keys x 64 queries
       constexpr uint32_t IDESC_TS = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);    // dO / Q as MN-major B
-      auto issue_s = [&](int i) -> bool {
+      // S^T and dP^T of a tile are queued separately, each behind the product that still reads the
+      // columns it overwrites (dV reads P^T, dK reads dS^T), and each with its own barrier: the
+      // softmax warps start on the exponentials while dK and dP^T are still running
+      auto issue_st = [&](int i) -> bool {
         const uint32_t boff = (NBUF == 2 && (i & 1)) ? (uint32_t)COL_BUF1 : 0u;
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)((i / STAGES) & 1);
         if (!mbar_wait_bounded(bar(B_A_FULL + s), ph, abort_flag)) return false;
-        if (!mbar_wait_bounded(bar(B_B_FULL + s), ph, abort_flag)) return false;
         tc_fence_after();
         #pragma unroll
         for (int u = 0; u < NSUB; ++u) {
@@ -825,6 +829,16 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           #pragma unroll
           for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_ST + boff, dk + (uint64_t)(2 * k), dq_ + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
         }
+        // with two pairs the softmax warps take S^T and dP^T together: one barrier, after dP^T
+        if (NBUF == 1) tc_commit(bar(B_S_FULL));
+        return true;
+      };
+      auto issue_dpt = [&](int i) -> bool {
+        const uint32_t boff = (NBUF == 2 && (i & 1)) ? (uint32_t)COL_BUF1 : 0u;
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)((i / STAGES) & 1);
+        if (!mbar_wait_bounded(bar(B_B_FULL + s), ph, abort_flag)) return false;
+        tc_fence_after();
         #pragma unroll
         for (int u = 0; u < NSUB; ++u) {
           const uint64_t dv = make_smem_desc_sw128(sV + u * SUB_BIG, 16, 1024);
@@ -832,13 +846,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           #pragma unroll
           for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_DPT + boff, dv + (uint64_t)(2 * k), ddo + (uint64_t)(2 * k), IDESC_SS, (u | k) > 0);
         }
-        tc_commit(bar((NBUF == 2 && (i & 1)) ? B_S_FULL1 : B_S_FULL));
+        tc_commit(bar((NBUF == 2 && (i & 1)) ? B_DP_FULL1 : B_DP_FULL));
         return true;
       };
       bool ok = mbar_wait_bounded(bar(B_RES_FULL), 0, abort_flag);
       if (!ok) fail_code = 20;
-      if (ok && !issue_s(0)) { ok = false; fail_code = 21; }
-      if (ok && NBUF == 2 && n_qt > 1 && !issue_s(1)) { ok = false; fail_code = 21; }
+      if (ok && !(issue_st(0) && issue_dpt(0))) { ok = false; fail_code = 21; }
+      if (ok && NBUF == 2 && n_qt > 1 && !(issue_st(1) && issue_dpt(1))) { ok = false; fail_code = 21; }
       for (int i = 0; ok && i < n_qt; ++i) {
         const int s = i % STAGES;
         const uint32_t boff = (NBUF == 2 && (i & 1)) ? (uint32_t)COL_BUF1 : 0u;
@@ -855,6 +869,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           umma_ts(tmem + COL_DV, tmem + COL_ST + boff + a_off, ddo, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar(B_B_EMPTY + s));
+        // the tensor core runs MMAs in issue order: S^T / dP^T may be overwritten once the
+        // products that read P^T / dS^T from the same columns are queued
+        if (NBUF == 1 && i + 1 < n_qt && !issue_st(i + 1)) { fail_code = 23; break; }
         #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
           const uint32_t a_off = (uint32_t)(k < 2 ? 8 * k : 32 + 8 * (k - 2));
@@ -862,11 +879,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           umma_ts(tmem + COL_DK, tmem + COL_DPT + boff + a_off, dq_, IDESC_TS, (i > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(bar(B_A_EMPTY + s));
-        if (i + NBUF < n_qt) {
-          // the tensor core runs MMAs in issue order: S^T / dP^T may be overwritten once the
-          // products that read P^T / dS^T from the same columns are queued
-          if (!issue_s(i + NBUF)) { fail_code = 23; break; }
-        }
+        if (NBUF == 2 && i + 2 < n_qt && !issue_st(i + 2)) { fail_code = 23; break; }
+        if (i + NBUF < n_qt && !issue_dpt(i + NBUF)) { fail_code = 24; break; }
         if (i + 1 == n_qt) tc_commit(bar(B_O_DONE));
       }
     }
@@ -886,11 +900,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       const int m0 = (i_first + i) * BT + half * 32;     // first query of this thread's columns
       const uint32_t boff = (NBUF == 2 && (i & 1)) ? (uint32_t)COL_BUF1 : 0u;
       const uint32_t tST = tST0 + boff, tDPT = tDPT0 + boff;
-      if (!mbar_wait_bounded_warp(bar((NBUF == 2 && (i & 1)) ? B_S_FULL1 : B_S_FULL), (uint32_t)((i / NBUF) & 1), abort_flag)) { ok = false; fail_code = 30; break; }
+      if (!mbar_wait_bounded_warp(bar(NBUF == 1 ? B_S_FULL : ((i & 1) ? B_DP_FULL1 : B_DP_FULL)), (uint32_t)((i / NBUF) & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
-      uint32_t sv[32], dp[32];
+      uint32_t sv[32];
       tmem_ld_x32(tST, sv);
-      tmem_ld_x32(tDPT, dp);
       // the lse / delta vectors of this stage were published on the same barrier as the Q tile
       // (long complete: the matrix products above needed it); observing it here orders the reads
       if (!mbar_wait_bounded_warp(bar(B_A_FULL + s), (uint32_t)((i / STAGES) & 1), abort_flag)) { ok = false; fail_code = 33; break; }
@@ -914,62 +927,141 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       // stored as soon as it is packed, which keeps the live registers below the limit.
       const int q_lo = q_off + (i_first + i) * BT;      // position of the tile's first query
       const bool tile_masked = (key0 + BM > len_k) || (p.causal && key0 + BM - 1 > q_lo);
-      #pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        uint32_t pp[8], pd[8];
-        if (!tile_masked && bias_mode != 2) {
-          #pragma unroll
-          for (int ii = 0; ii < 8; ++ii) {
-            const int c = 16 * hh + 2 * ii;
-            const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
-            const float2 d2 = *reinterpret_cast<const float2*>(vd + c);
-            float x0, x1, g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]), e0, e1;
-            fma2(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, bias_const);
-            add2(x0, x1, l2.x, l2.y);          // - lse
-            add2(g0, g1, d2.x, d2.y);          // dP - delta
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-            mul2(e0, e1, p0, p1, g0, g1);
-            pp[ii] = pack2<kBf16>(p0, p1);
-            pd[ii] = pack2<kBf16>(e0, e1);
-          }
-        } else if (!tile_masked) {
-          // whole tile visible, bias per element (near the diagonal)
-          const float* lrow = lut + lut0;
-          #pragma unroll
-          for (int ii = 0; ii < 8; ++ii) {
-            const int c = 16 * hh + 2 * ii;
-            const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
-            const float2 d2 = *reinterpret_cast<const float2*>(vd + c);
-            float x0 = lrow[-c], x1 = lrow[-c - 1], g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]), e0, e1;
-            add2(x0, x1, l2.x, l2.y);          // bias - lse
-            fma2v(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, x0, x1);
-            add2(g0, g1, d2.x, d2.y);          // dP - delta
-            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-            mul2(e0, e1, p0, p1, g0, g1);
-            pp[ii] = pack2<kBf16>(p0, p1);
-            pd[ii] = pack2<kBf16>(e0, e1);
-          }
-        } else {
-          #pragma unroll
-          for (int ii = 0; ii < 8; ++ii) {
-            float pv[2], dv2[2];
+      if constexpr (NBUF == 1) {
+        // pass 1: P^T = exp2(S^T scale + bias - lse), kept in sv as float32 and stored as the A
+        // operand of the dV product.  Two halves of 16 columns, each stored as soon as it is packed.
+        #pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t pp[8];
+          if (!tile_masked && bias_mode != 2) {
             #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int c = 16 * hh + 2 * ii + u;
-              const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
-              float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
-              // masked: key outside the sequence, or (causal) after the query
-              if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
-              const float pr = fast_exp2(x);
-              pv[u] = pr;
-              dv2[u] = pr * (__uint_as_float(dp[c]) + vd[c]);
+            for (int ii = 0; ii < 8; ++ii) {
+              const int c = 16 * hh + 2 * ii;
+              const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
+              float x0, x1;
+              fma2(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, bias_const);
+              add2(x0, x1, l2.x, l2.y);          // - lse
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              sv[c] = __float_as_uint(p0); sv[c + 1] = __float_as_uint(p1);
+              pp[ii] = pack2<kBf16>(p0, p1);
             }
-            pp[ii] = pack2<kBf16>(pv[0], pv[1]);
-            pd[ii] = pack2<kBf16>(dv2[0], dv2[1]);
+          } else if (!tile_masked) {
+            // whole tile visible, bias per element (near the diagonal)
+            const float* lrow = lut + lut0;
+            #pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+              const int c = 16 * hh + 2 * ii;
+              const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
+              float x0 = lrow[-c], x1 = lrow[-c - 1];
+              add2(x0, x1, l2.x, l2.y);          // bias - lse
+              fma2v(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, x0, x1);
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              sv[c] = __float_as_uint(p0); sv[c + 1] = __float_as_uint(p1);
+              pp[ii] = pack2<kBf16>(p0, p1);
+            }
+          } else {
+            #pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+              float pv[2];
+              #pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int c = 16 * hh + 2 * ii + u;
+                const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
+                float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
+                // masked: key outside the sequence, or (causal) after the query
+                if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
+                pv[u] = fast_exp2(x);
+                sv[c] = __float_as_uint(pv[u]);
+              }
+              pp[ii] = pack2<kBf16>(pv[0], pv[1]);
+            }
+          }
+          tmem_st_x8(tST + 8 * hh, pp);
+        }
+        // pass 2: dS^T = P^T o (dP^T - delta), once dP^T has arrived
+        if (!mbar_wait_bounded_warp(bar((NBUF == 2 && (i & 1)) ? B_DP_FULL1 : B_DP_FULL), (uint32_t)((i / NBUF) & 1), abort_flag)) { ok = false; fail_code = 34; break; }
+        tc_fence_after();
+        {
+          uint32_t dp[32];
+          tmem_ld_x32(tDPT, dp);
+          tmem_ld_wait();
+          #pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t pd[8];
+            #pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+              const int c = 16 * hh + 2 * ii;
+              const float2 d2 = *reinterpret_cast<const float2*>(vd + c);
+              float g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]), e0, e1;
+              add2(g0, g1, d2.x, d2.y);          // dP - delta
+              mul2(e0, e1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), g0, g1);
+              pd[ii] = pack2<kBf16>(e0, e1);
+            }
+            tmem_st_x8(tDPT + 8 * hh, pd);
           }
         }
-        tmem_st_x8(tST + 8 * hh, pp);
-        tmem_st_x8(tDPT + 8 * hh, pd);
+      } else {
+        // two S^T/dP^T pairs (head dim 128): both products of this tile were queued a tile ago, one pass
+        uint32_t dp[32];
+        tmem_ld_x32(tDPT, dp);
+        tmem_ld_wait();
+        #pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t pp[8], pd[8];
+          if (!tile_masked && bias_mode != 2) {
+            #pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+              const int c = 16 * hh + 2 * ii;
+              const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
+              const float2 d2 = *reinterpret_cast<const float2*>(vd + c);
+              float x0, x1, g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]), e0, e1;
+              fma2(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, bias_const);
+              add2(x0, x1, l2.x, l2.y);          // - lse
+              add2(g0, g1, d2.x, d2.y);          // dP - delta
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              mul2(e0, e1, p0, p1, g0, g1);
+              pp[ii] = pack2<kBf16>(p0, p1);
+              pd[ii] = pack2<kBf16>(e0, e1);
+            }
+          } else if (!tile_masked) {
+            // whole tile visible, bias per element (near the diagonal)
+            const float* lrow = lut + lut0;
+            #pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+              const int c = 16 * hh + 2 * ii;
+              const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
+              const float2 d2 = *reinterpret_cast<const float2*>(vd + c);
+              float x0 = lrow[-c], x1 = lrow[-c - 1], g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]), e0, e1;
+              add2(x0, x1, l2.x, l2.y);          // bias - lse
+              fma2v(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, x0, x1);
+              add2(g0, g1, d2.x, d2.y);          // dP - delta
+              const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+              mul2(e0, e1, p0, p1, g0, g1);
+              pp[ii] = pack2<kBf16>(p0, p1);
+              pd[ii] = pack2<kBf16>(e0, e1);
+            }
+          } else {
+            #pragma unroll
+            for (int ii = 0; ii < 8; ++ii) {
+              float pv[2], dv2[2];
+              #pragma unroll
+              for (int u = 0; u < 2; ++u) {
+                const int c = 16 * hh + 2 * ii + u;
+                const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
+                float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
+                // masked: key outside the sequence, or (causal) after the query
+                if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
+                const float pr = fast_exp2(x);
+                pv[u] = pr;
+                dv2[u] = pr * (__uint_as_float(dp[c]) + vd[c]);
+              }
+              pp[ii] = pack2<kBf16>(pv[0], pv[1]);
+              pd[ii] = pack2<kBf16>(dv2[0], dv2[1]);
+            }
+          }
+          tmem_st_x8(tST + 8 * hh, pp);
+          tmem_st_x8(tDPT + 8 * hh, pd);
+        }
       }
       tmem_st_wait();
       tc_fence_before();
