@@ -150,6 +150,7 @@ enum {
   B_P_FULL1,
   B_DP_FULL,                         // dkv kernel: dP^T of a tile (S^T has its own barrier)
   B_DP_FULL1,
+  B_PT_FULL,                         // dkv kernel, one S^T/dP^T pair: P^T of a tile is stored (dS^T follows on P_FULL)
   B_NUM
 };
 static_assert(B_NUM <= 24, "barrier slots");
@@ -739,6 +740,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     mbar_init(bar(B_DP_FULL1), 1);
     mbar_init(bar(B_P_FULL), 8);
     mbar_init(bar(B_P_FULL1), 8);
+    mbar_init(bar(B_PT_FULL), 8);
     mbar_init(bar(B_O_DONE), 1);
     fence_barrier_init();
     fence_proxy_async();
@@ -860,7 +862,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         // this thread (its products were queued a tile ago), so a barrier shared by all tiles could
         // complete two phases between two looks of this thread and the parity test would then wait
         // for ever.  One barrier per pair: its next phase needs S^T(i+2), queued below this wait.
-        if (!mbar_wait_bounded(bar((NBUF == 2 && (i & 1)) ? B_P_FULL1 : B_P_FULL), (uint32_t)((i / NBUF) & 1), abort_flag)) { fail_code = 22; break; }
+        // One pair: dV(i) and S^T(i+1) are queued as soon as P^T(i) is stored (B_PT_FULL), while the
+        // softmax warps still form dS^T(i); dK(i) and dP^T(i+1) follow on P_FULL.  The next phase of
+        // either barrier needs a product that is queued after the wait on its current phase.
+        if (!mbar_wait_bounded(bar(NBUF == 1 ? B_PT_FULL : ((i & 1) ? B_P_FULL1 : B_P_FULL)), (uint32_t)((i / NBUF) & 1), abort_flag)) { fail_code = 22; break; }
         tc_fence_after();
         #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {       // 16 queries per step
@@ -872,6 +877,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
         // the tensor core runs MMAs in issue order: S^T / dP^T may be overwritten once the
         // products that read P^T / dS^T from the same columns are queued
         if (NBUF == 1 && i + 1 < n_qt && !issue_st(i + 1)) { fail_code = 23; break; }
+        if (NBUF == 1) {
+          if (!mbar_wait_bounded(bar(B_P_FULL), (uint32_t)(i & 1), abort_flag)) { fail_code = 26; break; }
+          tc_fence_after();
+        }
         #pragma unroll
         for (int k = 0; k < BT / 16; ++k) {
           const uint32_t a_off = (uint32_t)(k < 2 ? 8 * k : 32 + 8 * (k - 2));
@@ -978,6 +987,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           }
           tmem_st_x8(tST + 8 * hh, pp);
         }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_PT_FULL));
         // pass 2: dS^T = P^T o (dP^T - delta), once dP^T has arrived
         if (!mbar_wait_bounded_warp(bar((NBUF == 2 && (i & 1)) ? B_DP_FULL1 : B_DP_FULL), (uint32_t)((i / NBUF) & 1), abort_flag)) { ok = false; fail_code = 34; break; }
         tc_fence_after();
