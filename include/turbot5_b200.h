@@ -41,9 +41,14 @@ typedef enum {
 typedef enum { T5B_F32 = 0, T5B_F16 = 1, T5B_BF16 = 2 } t5b_dtype;
 
 /* Which kernel family a forward call should use.  AUTO picks the tcgen05/TMA
- * kernel whenever dtype/shape/alignment allow (bf16 or fp16, head dim 64,
- * 16-byte aligned rows) and the CUDA-core kernel otherwise. */
-typedef enum { T5B_KERNEL_AUTO = 0, T5B_KERNEL_TCGEN05 = 1, T5B_KERNEL_SIMT = 2 } t5b_kernel;
+ * kernel whenever dtype/shape/alignment allow (bf16 or fp16, head dim 64 or 128,
+ * 16-byte aligned pointers and strides) and the CUDA-core kernel otherwise.
+ * TCGEN05_POLYEXP is the tcgen05 kernel with EVERY exponential of an unmasked tile
+ * evaluated by its FMA-pipe polynomial (the default kernel sends only a share of
+ * them that way); it exists so that tests can pin that code path on its own. */
+typedef enum {
+  T5B_KERNEL_AUTO = 0, T5B_KERNEL_TCGEN05 = 1, T5B_KERNEL_SIMT = 2, T5B_KERNEL_TCGEN05_POLYEXP = 3
+} t5b_kernel;
 
 T5B_API const char* t5b_status_string(int status);
 T5B_API int t5b_abi_version(void);

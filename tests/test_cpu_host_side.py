@@ -43,6 +43,39 @@ def test_struct_layouts_match_header_field_order():
         assert names == [f[0] for f in cls._fields_], cname
 
 
+def _header_fields(cname):
+    header = open(os.path.join(ROOT, "include", "turbot5_b200.h")).read()
+    end = header.index("} " + cname + ";")
+    body = header[header.rindex("typedef struct {", 0, end) + len("typedef struct {"):end]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    fields = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        ctype = "ptr" if "*" in decl else decl.split()[0]
+        parts = decl.replace("*", " ").split(",")
+        fields.append((parts[0].split()[-1], ctype))
+        fields += [(p.strip(), ctype) for p in parts[1:]]
+    return fields
+
+
+def test_integration_stub_struct_matches_header():
+    """The ctypes struct a maintainer would paste from INTEGRATION.md has the header's fields, in
+    order and with the header's types (a struct that is short or reordered corrupts calls)."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    start = text.index("class _AttnArgs(C.Structure)")
+    end = text.index("_lib.t5b_attention_fwd.argtypes")
+    scope = {"C": ctypes}
+    exec(text[start:end], scope)
+    stub = scope["_AttnArgs"]
+    ctype_of = {"ptr": ctypes.c_void_p, "int64_t": ctypes.c_int64, "int32_t": ctypes.c_int32, "float": ctypes.c_float}
+    want = [(n, ctype_of[t]) for n, t in _header_fields("t5b_attn_args")]
+    assert [(n, t) for n, t in stub._fields_] == want
+    from turbot5_b200 import _native as nat
+    assert ctypes.sizeof(stub) == ctypes.sizeof(nat.AttnArgs)
+
+
 def test_host_bucket_table_bit_exact_vs_reference_fixture():
     import turbot5_b200 as t5b
     z = load("buckets.npz")

@@ -113,6 +113,27 @@ def test_seeded_vs_oracle_bf16(B, H, M, N, causal, off, kernel):
     check_close(out, want, dt, f"{(B, H, M, N, causal, off)}")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,M,N,causal,off", [(2, 3, 1024, 1024, False, None), (1, 2, 512, 1536, False, 0),
+                                                 (1, 2, 640, 640, True, None), (1, 2, 384, 384, False, 4000)])
+def test_every_exponential_on_the_fma_pipe(B, H, M, N, causal, off, dtype):
+    """kernel='tcgen05_polyexp' sends every exponential of an unmasked tile through the
+    range-reduction + cubic path that the default kernel may use for a share of the columns;
+    same tolerances as the hardware ex2 path."""
+    q = seeded((B, H, M, 64), 11, dtype=dtype)
+    k = seeded((B, H, N, 64), 12, dtype=dtype)
+    v = seeded((B, H, N, 64), 13, dtype=dtype)
+    table = seeded((32, H), 14, 0.1, dtype=dtype)
+    want = orc.attention_basic(q, k, v, table, causal=causal, q_pos_offset=off)
+    out = _run_dense(q, k, v, table, dtype, "tcgen05_polyexp", causal=causal, q_pos_offset=off)
+    check_close(out, want, dtype, f"polyexp {(B, H, M, N, causal, off)}")
+    # far-apart scores: exponents down to the clamp (2^-123) and a rescale of the running maximum
+    q2 = q * 6.0
+    want = orc.attention_basic(q2, k, v, table, causal=causal, q_pos_offset=off)
+    out = _run_dense(q2, k, v, table, dtype, "tcgen05_polyexp", causal=causal, q_pos_offset=off)
+    check_close(out, want, dtype, f"polyexp wide {(B, H, M, N, causal, off)}")
+
+
 @pytest.mark.parametrize("kernel", KERNELS_16BIT)
 def test_no_bias_and_scale(kernel):
     dt = torch.bfloat16

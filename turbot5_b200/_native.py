@@ -15,7 +15,9 @@ LIB_PATH = os.path.join(_HERE, "libturbot5_b200.so")
 OK = 0
 ERR_UNSUPPORTED = 10
 F32, F16, BF16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMT = 0, 1, 2
+KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMT, KERNEL_TCGEN05_POLYEXP = 0, 1, 2, 3
+KERNELS = {"auto": KERNEL_AUTO, "tcgen05": KERNEL_TCGEN05, "simt": KERNEL_SIMT,
+           "tcgen05_polyexp": KERNEL_TCGEN05_POLYEXP}
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 

@@ -126,7 +126,7 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
     a.causal = int(bool(causal))
     a.num_buckets, a.max_distance = int(NUM_BUCKETS), int(MAX_DISTANCE)
     a.q_pos_offset = (N - M) if q_pos_offset is None else int(q_pos_offset)
-    a.kernel = {"auto": nat.KERNEL_AUTO, "tcgen05": nat.KERNEL_TCGEN05, "simt": nat.KERNEL_SIMT}[kernel]
+    a.kernel = nat.KERNELS[kernel]
     a.sm_scale = float(sm_scale)
     a.workspace, a.workspace_bytes = None, 0
     a.local_block = int(local_block)
@@ -199,7 +199,7 @@ def _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max
     a.causal = int(bool(causal))
     a.num_buckets, a.max_distance = int(NUM_BUCKETS), int(MAX_DISTANCE)
     a.q_pos_offset = 0
-    a.kernel = {"auto": nat.KERNEL_AUTO, "tcgen05": nat.KERNEL_TCGEN05, "simt": nat.KERNEL_SIMT}[kernel]
+    a.kernel = nat.KERNELS[kernel]
     a.sm_scale = float(sm_scale)
     a.workspace, a.workspace_bytes = None, 0
     a.local_block = 0

@@ -23,6 +23,8 @@
 #include "attn_params.cuh"
 #include "attn_sm100_util.cuh"
 
+#include <atomic>
+
 namespace t5b {
 namespace sm100b {
 
@@ -1293,11 +1295,11 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
                      : (bf16 ? attn_bwd_dq_kernel<true, 128> : attn_bwd_dq_kernel<false, 128>);
   auto kkv = HD == 64 ? (bf16 ? attn_bwd_dkv_kernel<true, 64> : attn_bwd_dkv_kernel<false, 64>)
                       : (bf16 ? attn_bwd_dkv_kernel<true, 128> : attn_bwd_dkv_kernel<false, 128>);
-  static bool attr_set[64][4] = {};
+  static std::atomic<bool> attr_set[64][4];   // any thread may get here first
   int dev = 0;
   cudaGetDevice(&dev);
   const int which = (bf16 ? 1 : 0) + (HD == 64 ? 0 : 2);
-  if (dev < 0 || dev >= 64 || !attr_set[dev][which]) {
+  if (dev < 0 || dev >= 64 || !attr_set[dev][which].load(std::memory_order_acquire)) {
     const int lut_max = 2 * 2048 + 1 + 2 * LUT_PAD;
     const int smem_max = (int)(HD == 64 ? smem_bytes<64>(lut_max) : smem_bytes<128>(lut_max));
     if (cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) != cudaSuccess ||
@@ -1305,7 +1307,7 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
       cudaGetLastError();
       return T5B_ERR_LAUNCH;
     }
-    if (dev >= 0 && dev < 64) attr_set[dev][which] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev][which].store(true, std::memory_order_release);
   }
   dim3 gq, gk;
   if (varlen) {

@@ -40,10 +40,21 @@
 #include "attn_params.cuh"
 #include "attn_sm100_util.cuh"
 
+#include <atomic>
+
 namespace t5b {
 
 namespace sm100 {
 
+// Head dim 64: column pairs of every 8 whose exponentials run on the FMA pipe.  Measured on B200 at
+// B2 H12 L8192: 0 -> 0.594 ms, 2 -> 0.648 ms, i.e. in THIS kernel (two threads per row, 96 registers,
+// bound by issue slots and latency rather than by the exponential unit alone) the extra FMA-pipe
+// instructions cost more than the freed ex2 slots give back, so the default is 0.  More registers do
+// not help either: 18 warps per SM put 5 on one scheduler, 16384 / (5 x 32) = 102 registers is the
+// ceiling for two blocks per SM (a 104- or 112-register build runs one block per SM: 0.88-0.97 ms).
+#ifndef T5B_FWD_POLY64
+#define T5B_FWD_POLY64 0
+#endif
 constexpr int BM = 128;            // query rows per block
 constexpr int STAGES = 2;          // K/V ring depth
 constexpr int MAX_THREADS = 320;
@@ -123,6 +134,66 @@ __device__ __forceinline__ uint32_t scale_packed(uint32_t v, float beta) {
   return pack2<kBf16>(lo * beta, hi * beta);
 }
 
+
+// ---- packed 2 x fp32 values held in one 64-bit register pair
+__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpk2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
+// Exponentials on the FMA pipe.  The exponential unit retires 16 ex2 per clock per SM, and at head
+// dim 64 that is the scarcest resource of this kernel; the FMA pipe has room.  A compile-time share
+// of each thread's column pairs (kPoly of every 8) is therefore computed as
+//   2^(s*mul + add) = 2^n * g * 2^f,  n = rint(add) + rint(s*mul),  f = s*mul - rint(s*mul) in [-1/2, 1/2],
+//   g = 2^(add - rint(add))  (one ex2 per thread and tile, folded into the coefficients),
+// with n found by adding 1.5 * 2^23 (the sum's low mantissa bits then hold n), a cubic for 2^f
+// (relative error 7.5e-5: P is rounded to 8 or 11 bits afterwards) and n added to the exponent field
+// by one integer add.  s is clamped from below so that the exponent field stays positive.
+constexpr float kExpMagic = 12582912.f;      // 1.5 * 2^23
+constexpr float kExpC0 = 0x1.fff694p-1f, kExpC1 = 0x1.62f31ap-1f, kExpC2 = 0x1.f0ddf6p-3f, kExpC3 = 0x1.c3f6fp-5f;
+// pair i (of the 16 pairs of a 32-column chunk) goes to the FMA pipe when this is true: k of every 8, evenly spread
+__host__ __device__ constexpr bool poly_pair(int i, int k) { return ((i % 8 + 1) * k / 8) != ((i % 8) * k / 8); }
+
+struct PolyExp {
+  uint64_t mul, m1, c0, c1, c2, c3;
+  float lo;
+  // mul > 0
+  __device__ __forceinline__ void setup(float e_mul, float inv_mul, float e_add) {
+    const float a_int = rintf(e_add);
+    const float g = fast_exp2(e_add - a_int);
+    mul = pk2(e_mul, e_mul);
+    m1 = pk2(kExpMagic + a_int, kExpMagic + a_int);
+    c0 = pk2(g * kExpC0, g * kExpC0);
+    c1 = pk2(g * kExpC1, g * kExpC1);
+    c2 = pk2(g * kExpC2, g * kExpC2);
+    c3 = pk2(g * kExpC3, g * kExpC3);
+    lo = (-123.f - a_int) * inv_mul;
+  }
+  __device__ __forceinline__ void eval(float s0, float s1, float& p0, float& p1) const {
+    const uint64_t s = pk2(fmaxf(s0, lo), fmaxf(s1, lo));
+    const uint64_t t = ffma2(s, mul, m1);                     // magic + n
+    const uint64_t nk = ffma2(t, pk2(-1.f, -1.f), m1);        // -rint(s*mul), exact
+    const uint64_t f = ffma2(s, mul, nk);
+    uint64_t q = ffma2(f, c3, c2);
+    q = ffma2(q, f, c1);
+    q = ffma2(q, f, c0);
+    float t0, t1, q0, q1;
+    unpk2(t, t0, t1);
+    unpk2(q, q0, q1);
+    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+  }
+};
+
 // kBf16: element type of Q/K/V/out (P uses the same type: tcgen05.mma kind::f16
 // takes A and B of one format; mixing fp16 P with bf16 V is an illegal instruction).
 // O and the row sum are rescaled only when a row maximum grows by more than this many powers
@@ -131,7 +202,9 @@ __device__ __forceinline__ uint32_t scale_packed(uint32_t v, float beta) {
 // rounding stays relative; fp16 P must stay below 65504, hence 2^10.
 template <bool kBf16> constexpr float kRescaleThreshold = kBf16 ? 40.f : 10.f;
 
-template <bool kBf16, int HD>
+// kPoly: of every 8 column pairs of an unmasked tile, this many take their exponentials on the FMA
+// pipe (PolyExp above) instead of the exponential unit; 8 = all of them (used by the parity tests).
+template <bool kBf16, int HD, int kPoly>
 __global__ void __launch_bounds__(HD == 64 ? 288 : MAX_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k,
@@ -421,6 +494,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     const uint32_t tP = tmem + lane_base + COL_P + half * (NH / 2);
     const uint32_t tO = tmem + lane_base + COL_O + half * OH;
     const float scale = p.scale_log2;
+    const float inv_scale = 1.f / scale;
     const bool has_bias = p.table != nullptr;
     const int qpos = qpos0 + r;
     // Rendezvous of the two warps that share this lane quarter: an mbarrier with a bounded
@@ -533,15 +607,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // The scores die as they are consumed.
       uint32_t pk[NCH][16];
       float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
-      #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
+      if (kPoly > 0 && !need_mask && scale > 0.f) {
+        // unmasked tile: kPoly of every 8 column pairs on the FMA pipe, the rest on the exponential unit
+        PolyExp pe;
+        pe.setup(e_mul, fast ? inv_scale : 1.f, e_add);
         #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float x0, x1;
-          fma2(x0, x1, __uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]), e_mul, e_add);
-          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-          pk[c][i] = pack2<kBf16>(p0, p1);
-          if (i & 1) add2(t2, t3, p0, p1); else add2(t0, t1, p0, p1);
+        for (int c = 0; c < NCH; ++c) {
+          #pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float p0, p1;
+            if (poly_pair(i, kPoly)) {
+              pe.eval(__uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]), p0, p1);
+            } else {
+              float x0, x1;
+              fma2(x0, x1, __uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]), e_mul, e_add);
+              p0 = fast_exp2(x0);
+              p1 = fast_exp2(x1);
+            }
+            pk[c][i] = pack2<kBf16>(p0, p1);
+            if (i & 1) add2(t2, t3, p0, p1); else add2(t0, t1, p0, p1);
+          }
+        }
+      } else {
+        #pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          #pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float x0, x1;
+            fma2(x0, x1, __uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]), e_mul, e_add);
+            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+            pk[c][i] = pack2<kBf16>(p0, p1);
+            if (i & 1) add2(t2, t3, p0, p1); else add2(t0, t1, p0, p1);
+          }
         }
       }
       float t_sum = (t0 + t1) + (t2 + t3);
@@ -739,15 +836,15 @@ TailPlan sm100_tail_plan(const t5b_attn_args& a) {
   t.parts = 1;
   t.counters_bytes = t.ml_bytes = t.o_bytes = 0;
   if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || n_total > 0x3fffffffLL) return t;
-  static int sms[64] = {};
+  static std::atomic<int> sms[64];     // SM count per device, 0 = not asked yet (any thread may get here first)
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return t; }
-  if (sms[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { cudaGetLastError(); return t; }
-    sms[dev] = n;
+  int n_sm = sms[dev].load(std::memory_order_relaxed);
+  if (n_sm == 0) {
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) { cudaGetLastError(); return t; }
+    sms[dev].store(n_sm, std::memory_order_relaxed);
   }
-  const int slots = 2 * sms[dev];
+  const int slots = 2 * n_sm;
   const int rem = (int)(n_total % slots);
   const int n_kv = (a.N + BN - 1) / BN;
   if (rem == 0) return t;
@@ -811,20 +908,27 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
     grid = dim3((unsigned)blocks, 1, 1);
   }
   if (grid.y > 65535 || grid.z > 65535) return T5B_ERR_SHAPE;
-  auto kern = HD == 64 ? (bf16 ? attn_fwd_kernel<true, 64> : attn_fwd_kernel<false, 64>)
-                       : (bf16 ? attn_fwd_kernel<true, 128> : attn_fwd_kernel<false, 128>);
-  // opt in to > 48 KB of dynamic shared memory once per device and kernel
-  static bool attr_set[64][4] = {};
+  // kernel variant: [head dim 128][bf16][every exponential on the FMA pipe]
+  using KernelFn = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, AttnParams, BucketSpec);
+  static const KernelFn kernels[2][2][2] = {
+      {{attn_fwd_kernel<false, 64, T5B_FWD_POLY64>, attn_fwd_kernel<false, 64, 8>},
+       {attn_fwd_kernel<true, 64, T5B_FWD_POLY64>, attn_fwd_kernel<true, 64, 8>}},
+      {{attn_fwd_kernel<false, 128, 0>, attn_fwd_kernel<false, 128, 8>},
+       {attn_fwd_kernel<true, 128, 0>, attn_fwd_kernel<true, 128, 8>}}};
+  const int all_poly = a.kernel == T5B_KERNEL_TCGEN05_POLYEXP ? 1 : 0;
+  const KernelFn kern = kernels[HD == 64 ? 0 : 1][bf16 ? 1 : 0][all_poly];
+  // opt in to > 48 KB of dynamic shared memory once per device and kernel (any thread may get here first)
+  static std::atomic<bool> attr_set[64][8];
   int dev = 0;
   cudaGetDevice(&dev);
-  const int which = (bf16 ? 1 : 0) + (HD == 64 ? 0 : 2);
+  const int which = (bf16 ? 1 : 0) + (HD == 64 ? 0 : 2) + 4 * all_poly;
   const size_t smem_max = HD == 64 ? smem_bytes<64>(2 * 2048 + 1 + 2 * LUT_PAD) : smem_bytes<128>(2 * 2048 + 1 + 2 * LUT_PAD);
-  if (dev < 0 || dev >= 64 || !attr_set[dev][which]) {
+  if (dev < 0 || dev >= 64 || !attr_set[dev][which].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max) != cudaSuccess) {
       cudaGetLastError();
       return T5B_ERR_LAUNCH;
     }
-    if (dev >= 0 && dev < 64) attr_set[dev][which] = true;
+    if (dev >= 0 && dev < 64) attr_set[dev][which].store(true, std::memory_order_release);
   }
   kern<<<grid, HD == 64 ? 288 : MAX_THREADS, smem, stream>>>(mq, mk, mv, p, spec);
   return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;

@@ -170,8 +170,12 @@ class T5FlashAttention(nn.Module):
         table = position_bias if (position_bias is not None and position_bias.dim() == 2) else None
         nb, md = self.relative_attention_num_buckets, self.relative_attention_max_distance
 
+        needs_grad = torch.is_grad_enabled() and any(
+            t is not None and t.requires_grad for t in (query_states, key_states, value_states, table))
         if mask is None:
-            if seq_length <= self.decode_max_rows and key_states.shape[2] > seq_length:
+            # the split-KV decoding operator has no backward: a short decoder input in training
+            # (e.g. a few target tokens against a long encoder memory) takes the dense operator
+            if seq_length <= self.decode_max_rows and key_states.shape[2] > seq_length and not needs_grad:
                 attn = flash_decoding_with_fusing_bias(query_states, key_states, value_states, table,
                                                        causal=self.causal, sm_scale=1.0,
                                                        NUM_BUCKETS=nb, MAX_DISTANCE=md,
@@ -188,7 +192,10 @@ class T5FlashAttention(nn.Module):
             plan_k = get_unpad_plan(mask)
             k_p = unpad_rows(key_states.transpose(1, 2), plan_k)
             v_p = unpad_rows(value_states.transpose(1, 2), plan_k)
-            if query_states.shape[2] == key_states.shape[2]:
+            # The mask describes the KEYS.  Only in plain self-attention (no encoder memory, no
+            # cache) are the queries the same padded tokens; in cross attention the decoder rows
+            # are all real even when the decoder happens to be as long as the encoder.
+            if key_value_states is None and past_key_value is None:
                 plan_q = plan_k
                 q_p = unpad_rows(query_states.transpose(1, 2), plan_q)
             else:
