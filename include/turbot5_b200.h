@@ -45,9 +45,14 @@ typedef enum { T5B_F32 = 0, T5B_F16 = 1, T5B_BF16 = 2 } t5b_dtype;
  * 16-byte aligned pointers and strides) and the CUDA-core kernel otherwise.
  * TCGEN05_POLYEXP is the tcgen05 kernel with EVERY exponential of an unmasked tile
  * evaluated by its FMA-pipe polynomial (the default kernel sends only a share of
- * them that way); it exists so that tests can pin that code path on its own. */
+ * them that way); it exists so that tests can pin that code path on its own.
+ * The tcgen05 family has a second forward kernel at head dim 64 that gives a block two
+ * 128-row query tiles and one thread per row; TCGEN05_2TILE selects it where it applies
+ * (full attention, more than 128 query rows; the default kernel otherwise).  It is slower
+ * than the default on B200 today and is kept selectable for measurement. */
 typedef enum {
-  T5B_KERNEL_AUTO = 0, T5B_KERNEL_TCGEN05 = 1, T5B_KERNEL_SIMT = 2, T5B_KERNEL_TCGEN05_POLYEXP = 3
+  T5B_KERNEL_AUTO = 0, T5B_KERNEL_TCGEN05 = 1, T5B_KERNEL_SIMT = 2, T5B_KERNEL_TCGEN05_POLYEXP = 3,
+  T5B_KERNEL_TCGEN05_2TILE = 4
 } t5b_kernel;
 
 T5B_API const char* t5b_status_string(int status);
@@ -124,6 +129,11 @@ typedef struct {
    * kernels only, forward and backward (bf16/fp16, head dim 64/128; local_block a multiple of
    * 128 unless the sequence fits in one block), T5B_ERR_UNSUPPORTED otherwise.  0: off. */
   int32_t local_block;
+  /* != 0: `out` is float32 (same element strides) although q/k/v are bf16/fp16: a partial result
+   * over a slice of the keys that t5b_attention_merge combines with others before the one rounding
+   * to the element type.  Tensor-core forward kernels only (T5B_ERR_UNSUPPORTED otherwise); pass
+   * lse as well, the merge needs it. */
+  int32_t out_f32;
 } t5b_attn_args;
 
 T5B_API int t5b_attention_fwd(const t5b_attn_args* args, void* stream);
@@ -239,6 +249,51 @@ T5B_API int t5b_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* 
                             int64_t rows, int32_t d, int64_t x_row_stride, int64_t dy_row_stride,
                             int64_t dx_row_stride, int32_t x_dtype, int32_t w_dtype, float eps,
                             void* stream);
+
+/* ---- merge of attention results over disjoint key ranges ---------------------------
+ * out = sum_i w_i * part_out[i],  w_i = exp(part_lse[i] - max_j part_lse[j]) / sum: each part is
+ * a forward call over its own slice of the keys (out_f32 set, lse requested, q_pos_offset shifted
+ * by the slice's first key), and the merged result equals the call over all keys.  The rule is
+ * the split merge of src/turbot5/ops/flash_decoding.py:47-55; the reference has no caller for
+ * it on full attention -- here the sequence-parallel encoder uses it to start on the keys a GPU
+ * already holds while the other GPUs' keys are still arriving.  part_out[i]: float32 (B,H,M,D),
+ * all parts with the same element strides part_stride_*; part_lse[i]: float32 (B,H,M) contiguous,
+ * natural log, -inf for a row that saw no key in that part; out: out_dtype, strides o_stride_*;
+ * lse_out: optional merged log-sum-exp. */
+#define T5B_MERGE_MAX_PARTS 8
+typedef struct {
+  const float* part_out[T5B_MERGE_MAX_PARTS];
+  const float* part_lse[T5B_MERGE_MAX_PARTS];
+  void* out;
+  float* lse_out;
+  int64_t part_stride_b, part_stride_h, part_stride_m;
+  int64_t o_stride_b, o_stride_h, o_stride_m;
+  int32_t n_parts;
+  int32_t out_dtype;      /* t5b_dtype of out */
+  int32_t B, H, M, D;
+} t5b_merge_args;
+
+T5B_API int t5b_attention_merge(const t5b_merge_args* args, void* stream);
+
+/* ---- residual add + T5 RMSNorm in one pass ---------------------------------------
+ * hidden_out = hidden + branch (rounded to the element type, as the residual adds of
+ * T5LayerSelfAttention / T5LayerFF do, src/turbot5/model/modeling.py:124-128, 142-164);
+ * normed = T5 RMSNorm(hidden_out) with the rounding points of t5b_rmsnorm_fwd
+ * (src/turbot5/model/modules.py:52-60).  hidden_out may alias hidden.  bf16/fp16 rows of
+ * d elements (d % 8 == 0, d <= 2048), 16-byte aligned, row strides in elements; the weight
+ * has the element type or is float32 (normed keeps the element type either way). */
+T5B_API int t5b_add_rmsnorm_fwd(const void* hidden, const void* branch, const void* weight, void* hidden_out,
+                                void* normed, int64_t rows, int32_t d, int64_t hidden_stride,
+                                int64_t branch_stride, int64_t hidden_out_stride, int64_t normed_stride,
+                                int32_t dtype, int32_t w_dtype, float eps, void* stream);
+
+/* ---- gated GELU over one concatenated projection -------------------------------------
+ * out[r, c] = round(gelu_tanh(x[r, c])) * x[r, d_ff + c] for x = hidden @ [wi_0; wi_1]^T, the
+ * middle of T5DenseGatedActDense (src/turbot5/model/modeling.py:83-100; the reference's own
+ * fused version is src/turbot5/ops/gated_mlp.py:83-225).  bf16/fp16, d_ff % 8 == 0, 16-byte
+ * aligned rows, row strides in elements. */
+T5B_API int t5b_gated_gelu_fwd(const void* x, void* out, int64_t rows, int32_t d_ff, int64_t x_stride,
+                               int64_t out_stride, int32_t dtype, void* stream);
 
 /* ---- unpad / pad glue -----------------------------------------------------------
  * Stand in for _get_unpad_data, index_first_axis and pad_input

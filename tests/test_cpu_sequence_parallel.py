@@ -83,3 +83,101 @@ def test_shard_bounds_cover_the_sequence():
             assert spans[0][0] == 0 and spans[-1][1] == L
             assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
             assert all(hi - lo <= sp.shard_size(L, world) for lo, hi in spans)
+
+
+# ---------------------------------------------------------------------------
+# the token-sharded encoder stack on two CPU ranks against the unsharded stack oracle
+# ---------------------------------------------------------------------------
+class _CpuOps:
+    """Stand-ins for the library operators, built from the oracle (float32 on the CPU)."""
+
+    @staticmethod
+    def rms_layer_norm(x, w, eps):
+        from oracle import t5_oracle as orc
+        return orc.t5_layer_norm(x, w, eps)
+
+    @staticmethod
+    def add_rms_layer_norm(hidden, branch, w, eps, inplace=False):
+        from oracle import t5_oracle as orc
+        s = hidden + branch
+        return s, orc.t5_layer_norm(s, w, eps)
+
+    @staticmethod
+    def gated_gelu(x):
+        f = x.shape[-1] // 2
+        return torch.nn.functional.gelu(x[..., :f], approximate="tanh") * x[..., f:]
+
+    @staticmethod
+    def attention(q, k, v, bias, causal, sm_scale, nb, md, q_pos_offset):
+        return _oracle_attention(q, k, v, bias, causal=causal, sm_scale=sm_scale, NUM_BUCKETS=nb, MAX_DISTANCE=md,
+                                 q_pos_offset=q_pos_offset)
+
+    @staticmethod
+    def partial(q, k, v, bias, causal, sm_scale, nb, md, q_pos_offset):
+        # (normalised output, log-sum-exp) over a slice of the keys, written out plainly
+        from oracle import t5_oracle as orc
+        M, N = q.shape[2], k.shape[2]
+        s = torch.einsum("bhmd,bhnd->bhmn", q.float(), k.float()) * sm_scale
+        if bias is not None:
+            s = s + orc.compute_bias(bias.float(), M, N, not causal, nb, md, q_pos_offset=q_pos_offset)
+        if causal:
+            qpos = torch.arange(M)[:, None] + q_pos_offset
+            s = s.masked_fill(torch.arange(N)[None, :] > qpos, float("-inf"))
+        lse = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse)[..., None])
+        return torch.einsum("bhmn,bhnd->bhmd", p, v.float()), lse
+
+    @staticmethod
+    def merge(parts, dtype):
+        lse = torch.stack([l for _, l in parts])
+        mx = lse.max(0).values
+        w = torch.exp(lse - torch.where(torch.isinf(mx), torch.zeros_like(mx), mx))
+        out = sum(wi[..., None] * o for wi, (o, _) in zip(w, parts)) / w.sum(0).clamp_min(1e-38)[..., None]
+        return out.to(dtype)
+
+
+def _stack_worker(rank, world, port, seq_len, overlap, out_queue):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import t5_oracle as orc
+        from tests.helpers import seed_named_parameters
+        from turbot5_b200 import sequence_parallel as sp
+        from turbot5_b200.t5 import T5Stack, T5StackConfig
+        cfgd = dict(vocab_size=64, d_model=32, d_kv=8, num_heads=4, d_ff=48, num_layers=3, num_decoder_layers=0,
+                    relative_attention_num_buckets=32, relative_attention_max_distance=16)
+        cfg = T5StackConfig(**cfgd)
+        enc = seed_named_parameters(T5Stack(cfg, torch.nn.Embedding(cfg.vocab_size, cfg.d_model), is_decoder=False), 0).eval()
+        ids = torch.randint(0, cfg.vocab_size, (1, seq_len), generator=torch.Generator().manual_seed(5))
+        S = sp.shard_size(seq_len, world)
+        lo, hi = sp.shard_bounds(seq_len, world, rank)
+        local = torch.zeros((1, S), dtype=torch.long)
+        local[:, :hi - lo] = ids[:, lo:hi]
+        got = enc.forward_fused(local, seq_len=seq_len, overlap=overlap, ops=_CpuOps)
+        w = {"encoder." + k: v.detach() for k, v in enc.state_dict().items()}
+        w["shared.weight"] = enc.embed_tokens.weight.detach()
+        want = orc.t5_stack_forward(w, cfgd, ids)
+        err = (got[:, :hi - lo] - want[:, lo:hi]).abs().max().item()
+        single = enc.forward_fused(ids, ops=_CpuOps) if rank == 0 else None
+        err1 = (single - want).abs().max().item() if single is not None else 0.0
+        out_queue.put((rank, err, err1))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("seq_len,overlap", [(48, True), (45, True), (45, False)])
+def test_two_rank_sharded_encoder_matches_unsharded_oracle(seq_len, overlap):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_stack_worker, args=(r, world, port, seq_len, overlap, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, err1 in results:
+        assert err < 1e-4 and err1 < 1e-4, (rank, err, err1)

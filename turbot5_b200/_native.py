@@ -15,9 +15,9 @@ LIB_PATH = os.path.join(_HERE, "libturbot5_b200.so")
 OK = 0
 ERR_UNSUPPORTED = 10
 F32, F16, BF16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMT, KERNEL_TCGEN05_POLYEXP = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMT, KERNEL_TCGEN05_POLYEXP, KERNEL_TCGEN05_2TILE = 0, 1, 2, 3, 4
 KERNELS = {"auto": KERNEL_AUTO, "tcgen05": KERNEL_TCGEN05, "simt": KERNEL_SIMT,
-           "tcgen05_polyexp": KERNEL_TCGEN05_POLYEXP}
+           "tcgen05_polyexp": KERNEL_TCGEN05_POLYEXP, "tcgen05_2tile": KERNEL_TCGEN05_2TILE}
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
@@ -25,7 +25,7 @@ SYMBOLS = ("t5b_status_string", "t5b_abi_version", "t5b_bucket_table_host", "t5b
            "t5b_attention_fwd", "t5b_attention_workspace_bytes", "t5b_attention_bwd", "t5b_attention_bwd_workspace_bytes", "t5b_decode_workspace_bytes", "t5b_decode_num_splits",
            "t5b_decode_fwd", "t5b_decode_static_scratch_bytes", "t5b_decode_fwd_static_scratch",
            "t5b_rmsnorm_fwd", "t5b_rmsnorm_bwd", "t5b_unpad_plan", "t5b_gather_rows",
-           "t5b_scatter_rows")
+           "t5b_scatter_rows", "t5b_attention_merge", "t5b_add_rmsnorm_fwd", "t5b_gated_gelu_fwd")
 
 
 class AttnArgs(C.Structure):
@@ -44,7 +44,7 @@ class AttnArgs(C.Structure):
         ("causal", C.c_int32), ("num_buckets", C.c_int32), ("max_distance", C.c_int32),
         ("q_pos_offset", C.c_int32), ("kernel", C.c_int32), ("sm_scale", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
-        ("local_block", C.c_int32),
+        ("local_block", C.c_int32), ("out_f32", C.c_int32),
     ]
 
 
@@ -55,6 +55,20 @@ class AttnBwdArgs(C.Structure):
         ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
         ("dtable", C.c_void_p), ("delta", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+    ]
+
+
+MERGE_MAX_PARTS = 8
+
+
+class MergeArgs(C.Structure):
+    _fields_ = [
+        ("part_out", C.c_void_p * MERGE_MAX_PARTS), ("part_lse", C.c_void_p * MERGE_MAX_PARTS),
+        ("out", C.c_void_p), ("lse_out", C.c_void_p),
+        ("part_stride_b", C.c_int64), ("part_stride_h", C.c_int64), ("part_stride_m", C.c_int64),
+        ("o_stride_b", C.c_int64), ("o_stride_h", C.c_int64), ("o_stride_m", C.c_int64),
+        ("n_parts", C.c_int32), ("out_dtype", C.c_int32),
+        ("B", C.c_int32), ("H", C.c_int32), ("M", C.c_int32), ("D", C.c_int32),
     ]
 
 
@@ -122,6 +136,14 @@ def lib():
     L.t5b_unpad_plan.restype = C.c_int
     L.t5b_unpad_plan.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.c_void_p]
+    L.t5b_attention_merge.restype = C.c_int
+    L.t5b_attention_merge.argtypes = [C.POINTER(MergeArgs), C.c_void_p]
+    L.t5b_add_rmsnorm_fwd.restype = C.c_int
+    L.t5b_add_rmsnorm_fwd.argtypes = [C.c_void_p] * 5 + [C.c_int64, C.c_int32] + [C.c_int64] * 4 + \
+                                      [C.c_int32, C.c_int32, C.c_float, C.c_void_p]
+    L.t5b_gated_gelu_fwd.restype = C.c_int
+    L.t5b_gated_gelu_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int64, C.c_int32,
+                                     C.c_void_p]
     for name in ("t5b_gather_rows", "t5b_scatter_rows"):
         fn = getattr(L, name)
         fn.restype = C.c_int

@@ -84,7 +84,7 @@ def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
 
 def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *,
                    q_pos_offset=None, return_lse=False, kernel="auto", balance_last_wave=True, _keep=None,
-                   local_block=0):
+                   local_block=0, out_f32=False):
     """softmax(sm_scale * Q K^T + T5 bias(n - m) [+ causal mask]) V without an L x L tensor.
 
     q (B,H,M,D), k/v (B,H,N,D), any batch/head/row strides (last dim contiguous);
@@ -106,11 +106,13 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
         sm_scale = 1.0 / math.sqrt(D)
     q, k, v = _unit_stride_last(q), _unit_stride_last(k), _unit_stride_last(v)
     table, tdt, ts0 = _table_args(bias, H)
-    out = torch.empty_like(q)          # preserves q's strides (BHLD view of a BLHD buffer stays free to unshape)
+    out_dtype = torch.float32 if out_f32 else q.dtype
+    out = torch.empty_like(q, dtype=out_dtype)   # preserves q's layout (BHLD view of a BLHD buffer stays free to unshape)
     if out.stride(-1) != 1:
-        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
     lse = torch.empty((B, H, M), dtype=torch.float32, device=q.device) if return_lse else None
     a = nat.AttnArgs()
+    a.out_f32 = int(bool(out_f32))
     a.q, a.k, a.v, a.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
     a.lse, a.table = nat.ptr(lse), nat.ptr(table)
     a.cu_seqlens_q = a.cu_seqlens_k = None
@@ -136,9 +138,59 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
             if need > 0:
                 ws = _scratch(q.device, "attn", need)
                 a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-        nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)), "flash_attention_with_fusing_bias")
+        st = nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device))
+        if st == nat.ERR_UNSUPPORTED and out_f32:
+            raise NotImplementedError("float32 partial outputs need the tensor-core forward kernels")
+        nat.check(st, "flash_attention_with_fusing_bias")
     if _keep is not None:
         _keep.update(args=a, q=q, k=k, v=v, table=table)
+    return (out, lse) if return_lse else out
+
+
+def flash_attention_partial(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *,
+                            q_pos_offset=0, kernel="auto"):
+    """Attention of q over a SLICE of the keys: returns (out, lse) with `out` in float32, for
+    `merge_attention_partials`.  `q_pos_offset` is the position of query row 0 relative to the
+    slice's first key (absolute query position minus the slice's first key position; may be
+    negative).  Forward only."""
+    try:
+        return _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset=q_pos_offset,
+                              return_lse=True, kernel=kernel, out_f32=True)
+    except NotImplementedError:
+        # shapes the tensor-core kernels do not take: the partial is rounded to the element type first
+        out, lse = _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE,
+                                  q_pos_offset=q_pos_offset, return_lse=True, kernel=kernel)
+        return out.float(), lse
+
+
+def merge_attention_partials(parts, dtype, return_lse=False):
+    """Combine `(out float32 (B,H,M,D), lse float32 (B,H,M))` pairs computed over disjoint key
+    slices into the attention over all of them (one rounding to `dtype`).  The result has the
+    layout of the first partial."""
+    if not 1 <= len(parts) <= nat.MERGE_MAX_PARTS:
+        raise ValueError(f"between 1 and {nat.MERGE_MAX_PARTS} partial results can be merged")
+    o0 = parts[0][0]
+    nat.require_cuda(o0)
+    B, H, M, D = o0.shape
+    outs, lses = [], []
+    for o, l in parts:
+        if o.dtype != torch.float32 or l.dtype != torch.float32 or o.shape != o0.shape or l.shape != (B, H, M):
+            raise ValueError("partials must be float32 (B,H,M,D) outputs with float32 (B,H,M) log-sum-exps")
+        outs.append(o if o.stride() == o0.stride() else o.contiguous() if o0.is_contiguous() else
+                    torch.empty_like(o0).copy_(o))
+        lses.append(l.contiguous())
+    out = torch.empty_like(o0, dtype=dtype)
+    lse = torch.empty((B, H, M), dtype=torch.float32, device=o0.device) if return_lse else None
+    a = nat.MergeArgs()
+    for i, (o, l) in enumerate(zip(outs, lses)):
+        a.part_out[i], a.part_lse[i] = o.data_ptr(), l.data_ptr()
+    a.out, a.lse_out = out.data_ptr(), nat.ptr(lse)
+    a.part_stride_b, a.part_stride_h, a.part_stride_m = o0.stride(0), o0.stride(1), o0.stride(2)
+    a.o_stride_b, a.o_stride_h, a.o_stride_m = out.stride(0), out.stride(1), out.stride(2)
+    a.n_parts, a.out_dtype = len(parts), nat.dtype_code(dtype)
+    a.B, a.H, a.M, a.D = B, H, M, D
+    with torch.cuda.device(o0.device):
+        nat.check(nat.lib().t5b_attention_merge(a, nat.stream_ptr(o0.device)), "merge_attention_partials")
     return (out, lse) if return_lse else out
 
 

@@ -12,8 +12,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libturbot5_b200.so")
-SOURCES = ["api.cu", "bucket.cu", "attn_fwd_sm100.cu", "attn_bwd_sm100.cu", "attn_fwd_simt.cu", "attn_bwd_simt.cu", "decode.cu",
-           "rmsnorm.cu", "padding.cu"]
+SOURCES = ["api.cu", "bucket.cu", "attn_fwd_sm100.cu", "attn_fwd2_sm100.cu", "attn_bwd_sm100.cu", "attn_fwd_simt.cu", "attn_bwd_simt.cu", "decode.cu",
+           "rmsnorm.cu", "padding.cu", "fused_ops.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -38,7 +38,7 @@ extern "C" int t5b_attention_fwd(const t5b_attn_args* a, void* stream) {
   }
   if (!a->q || !a->out) return T5B_ERR_ARG;
   if ((!a->k || !a->v) && (varlen ? a->total_k : a->N) > 0) return T5B_ERR_ARG;
-  if (a->kernel < T5B_KERNEL_AUTO || a->kernel > T5B_KERNEL_TCGEN05_POLYEXP) return T5B_ERR_ARG;
+  if (a->kernel < T5B_KERNEL_AUTO || a->kernel > T5B_KERNEL_TCGEN05_2TILE) return T5B_ERR_ARG;
 
   BucketSpec spec;
   spec.n_side = 2; spec.bidirectional = 0; spec.max_distance = 1; spec.n_first = 0;
@@ -49,8 +49,9 @@ extern "C" int t5b_attention_fwd(const t5b_attn_args* a, void* stream) {
   }
   cudaStream_t st = (cudaStream_t)stream;
   const bool tc_ok = sm100_supports(*a) && (varlen ? a->total_k : a->N) > 0;
-  if ((a->kernel == T5B_KERNEL_TCGEN05 || a->kernel == T5B_KERNEL_TCGEN05_POLYEXP) && !tc_ok) return T5B_ERR_UNSUPPORTED;
+  if (a->kernel != T5B_KERNEL_AUTO && a->kernel != T5B_KERNEL_SIMT && !tc_ok) return T5B_ERR_UNSUPPORTED;
   if (a->local_block != 0 && (!tc_ok || a->kernel == T5B_KERNEL_SIMT)) return T5B_ERR_UNSUPPORTED;
+  if (a->out_f32 != 0 && (!tc_ok || a->kernel == T5B_KERNEL_SIMT)) return T5B_ERR_UNSUPPORTED;
   if (a->kernel != T5B_KERNEL_SIMT && tc_ok) return sm100_attention_fwd(*a, spec, st);
   return simt_attention_fwd(*a, spec, st);
 }
@@ -81,7 +82,7 @@ extern "C" int t5b_attention_bwd(const t5b_attn_bwd_args* g, void* stream) {
     const int st = make_bucket_spec(a->num_buckets, a->max_distance, a->causal ? 0 : 1, &spec);
     if (st != T5B_OK) return st;
   }
-  if ((a->kernel == T5B_KERNEL_TCGEN05 || a->kernel == T5B_KERNEL_TCGEN05_POLYEXP) && !sm100_bwd_supports(*g)) return T5B_ERR_UNSUPPORTED;
+  if (a->kernel != T5B_KERNEL_AUTO && a->kernel != T5B_KERNEL_SIMT && !sm100_bwd_supports(*g)) return T5B_ERR_UNSUPPORTED;
   if (a->kernel != T5B_KERNEL_SIMT && sm100_bwd_supports(*g)) return sm100_attention_bwd(*g, spec, (cudaStream_t)stream);
   return simt_attention_bwd(*g, spec, (cudaStream_t)stream);
 }

@@ -113,95 +113,6 @@ __host__ __device__ inline size_t smem_bytes(int lut_entries) {
 }
 
 
-// 2^-k for a non-negative whole number k held in a float (0 once it leaves the normal range).
-__device__ __forceinline__ float pow2_neg(float k) {
-  return k >= 127.f ? 0.f : __int_as_float((127 - (int)k) << 23);
-}
-
-// Both halves of a packed pair times a power of two (exact unless the result leaves the
-// normal range, where it no longer matters).
-template <bool kBf16>
-__device__ __forceinline__ uint32_t scale_packed(uint32_t v, float beta) {
-  float lo, hi;
-  if (kBf16) {
-    lo = __uint_as_float(v << 16);
-    hi = __uint_as_float(v & 0xffff0000u);
-  } else {
-    const __half2 h = *reinterpret_cast<const __half2*>(&v);
-    lo = __low2float(h);
-    hi = __high2float(h);
-  }
-  return pack2<kBf16>(lo * beta, hi * beta);
-}
-
-
-// ---- packed 2 x fp32 values held in one 64-bit register pair
-__device__ __forceinline__ uint64_t pk2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpk2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-
-// Exponentials on the FMA pipe.  The exponential unit retires 16 ex2 per clock per SM, and at head
-// dim 64 that is the scarcest resource of this kernel; the FMA pipe has room.  A compile-time share
-// of each thread's column pairs (kPoly of every 8) is therefore computed as
-//   2^(s*mul + add) = 2^n * g * 2^f,  n = rint(add) + rint(s*mul),  f = s*mul - rint(s*mul) in [-1/2, 1/2],
-//   g = 2^(add - rint(add))  (one ex2 per thread and tile, folded into the coefficients),
-// with n found by adding 1.5 * 2^23 (the sum's low mantissa bits then hold n), a cubic for 2^f
-// (relative error 7.5e-5: P is rounded to 8 or 11 bits afterwards) and n added to the exponent field
-// by one integer add.  s is clamped from below so that the exponent field stays positive.
-constexpr float kExpMagic = 12582912.f;      // 1.5 * 2^23
-constexpr float kExpC0 = 0x1.fff694p-1f, kExpC1 = 0x1.62f31ap-1f, kExpC2 = 0x1.f0ddf6p-3f, kExpC3 = 0x1.c3f6fp-5f;
-// pair i (of the 16 pairs of a 32-column chunk) goes to the FMA pipe when this is true: k of every 8, evenly spread
-__host__ __device__ constexpr bool poly_pair(int i, int k) { return ((i % 8 + 1) * k / 8) != ((i % 8) * k / 8); }
-
-struct PolyExp {
-  uint64_t mul, m1, c0, c1, c2, c3;
-  float lo;
-  // mul > 0
-  __device__ __forceinline__ void setup(float e_mul, float inv_mul, float e_add) {
-    const float a_int = rintf(e_add);
-    const float g = fast_exp2(e_add - a_int);
-    mul = pk2(e_mul, e_mul);
-    m1 = pk2(kExpMagic + a_int, kExpMagic + a_int);
-    c0 = pk2(g * kExpC0, g * kExpC0);
-    c1 = pk2(g * kExpC1, g * kExpC1);
-    c2 = pk2(g * kExpC2, g * kExpC2);
-    c3 = pk2(g * kExpC3, g * kExpC3);
-    lo = (-123.f - a_int) * inv_mul;
-  }
-  __device__ __forceinline__ void eval(float s0, float s1, float& p0, float& p1) const {
-    const uint64_t s = pk2(fmaxf(s0, lo), fmaxf(s1, lo));
-    const uint64_t t = ffma2(s, mul, m1);                     // magic + n
-    const uint64_t nk = ffma2(t, pk2(-1.f, -1.f), m1);        // -rint(s*mul), exact
-    const uint64_t f = ffma2(s, mul, nk);
-    uint64_t q = ffma2(f, c3, c2);
-    q = ffma2(q, f, c1);
-    q = ffma2(q, f, c0);
-    float t0, t1, q0, q1;
-    unpk2(t, t0, t1);
-    unpk2(q, q0, q1);
-    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
-    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
-  }
-};
-
-// kBf16: element type of Q/K/V/out (P uses the same type: tcgen05.mma kind::f16
-// takes A and B of one format; mixing fp16 P with bf16 V is an illegal instruction).
-// O and the row sum are rescaled only when a row maximum grows by more than this many powers
-// of two over the value the exponentials are taken against.  Until then P may exceed 1: bf16
-// has the exponent range of fp32, so P <= 2^40 (and O, l <= 2^40 x keys x |v|) is harmless and
-// rounding stays relative; fp16 P must stay below 65504, hence 2^10.
-template <bool kBf16> constexpr float kRescaleThreshold = kBf16 ? 40.f : 10.f;
-
 // kPoly: of every 8 column pairs of an unmasked tile, this many take their exponentials on the FMA
 // pipe (PolyExp above) instead of the exponential unit; 8 = all of them (used by the parity tests).
 template <bool kBf16, int HD, int kPoly>
@@ -546,16 +457,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       {
         float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
         if (fast) {
+          // eight independent chains of two-input maxima (the three-input form is no faster per
+          // element on this pipe and its chains are half as many)
+          float m4 = -INFINITY, m5 = -INFINITY, m6 = -INFINITY, m7 = -INFINITY;
           #pragma unroll
           for (int c = 0; c < NCH; ++c)
             #pragma unroll
             for (int i = 0; i < 32; i += 8) {
-              m0 = max3(m0, __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
-              m1 = max3(m1, __uint_as_float(sv[c][i + 2]), __uint_as_float(sv[c][i + 3]));
-              m2 = max3(m2, __uint_as_float(sv[c][i + 4]), __uint_as_float(sv[c][i + 5]));
-              m3 = max3(m3, __uint_as_float(sv[c][i + 6]), __uint_as_float(sv[c][i + 7]));
+              m0 = fmaxf(m0, __uint_as_float(sv[c][i]));     m1 = fmaxf(m1, __uint_as_float(sv[c][i + 1]));
+              m2 = fmaxf(m2, __uint_as_float(sv[c][i + 2])); m3 = fmaxf(m3, __uint_as_float(sv[c][i + 3]));
+              m4 = fmaxf(m4, __uint_as_float(sv[c][i + 4])); m5 = fmaxf(m5, __uint_as_float(sv[c][i + 5]));
+              m6 = fmaxf(m6, __uint_as_float(sv[c][i + 6])); m7 = fmaxf(m7, __uint_as_float(sv[c][i + 7]));
             }
-          top_raw = max3(fmaxf(m0, m1), m2, m3);
+          top_raw = fmaxf(fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)), fmaxf(fmaxf(m4, m5), fmaxf(m6, m7)));
           mx = fmaf(top_raw, scale, bias_const);
         } else {
           // per-row window into the padded table: column c of this tile reads brow[c]
@@ -607,9 +521,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // The scores die as they are consumed.
       uint32_t pk[NCH][16];
       float t0 = 0.f, t1 = 0.f, t2 = 0.f, t3 = 0.f;
-      if (kPoly > 0 && !need_mask && scale > 0.f) {
+      const bool poly_ok = kPoly > 0 && !need_mask && scale > 0.f;
+      PolyExp pe;
+      if (poly_ok) {
         // unmasked tile: kPoly of every 8 column pairs on the FMA pipe, the rest on the exponential unit
-        PolyExp pe;
         pe.setup(e_mul, fast ? inv_scale : 1.f, e_add);
         #pragma unroll
         for (int c = 0; c < NCH; ++c) {
@@ -647,7 +562,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // largest one is not exactly 1, so when one key dominates a row its rounding error
         // (up to 2^-9 relative) would pass straight into the output.  Count that element in
         // the row sum as the tensor core sees it: same arithmetic as pass 2, then rounded.
-        const float p_top = fast_exp2(fmaf(top_raw, e_mul, e_add));
+        // (the same arithmetic as the element itself: with every pair on the FMA pipe that is the polynomial)
+        float p_top = fast_exp2(fmaf(top_raw, e_mul, e_add)), p_dup;
+        if (kPoly == 8 && poly_ok) pe.eval(top_raw, top_raw, p_top, p_dup);
         t_sum += __bfloat162float(__float2bfloat16_rn(p_top)) - p_top;
       }
 
@@ -710,8 +627,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     if (ok) {
       const bool row_ok = r < rows_in_tile;
       const int64_t row = (int64_t)q_row0 + r;
-      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + half * OH * 2 +
-                      2 * ((int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + row * p.o_stride_m);
+      const int64_t o_off = (int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + row * p.o_stride_m + half * OH;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + 2 * o_off;
       float o[OH];
       #pragma unroll
       for (int c = 0; c < OH / 32; ++c) {
@@ -771,6 +688,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       if (write_out) {
         const float inv_l = l_sum > 0.f ? 1.f / l_sum : 0.f;
+        if (p.out_f32) {
+          float4* of = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o_off);
+          #pragma unroll
+          for (int i = 0; i < OH / 4; ++i)
+            of[i] = make_float4(o[4 * i] * inv_l, o[4 * i + 1] * inv_l, o[4 * i + 2] * inv_l, o[4 * i + 3] * inv_l);
+        } else
         #pragma unroll
         for (int i = 0; i < OH / 8; ++i) {
           uint4 w4;
@@ -827,6 +750,7 @@ bool sm100_supports(const t5b_attn_args& a) {
 // the keys so that the wave finishes in a fraction of a block time.
 TailPlan sm100_tail_plan(const t5b_attn_args& a) {
   using namespace sm100;
+  if (sm100w_prefers(a)) return sm100w_tail_plan(a);
   const int HD = a.D, BN = a.D == 64 ? Geo<64>::BN : Geo<128>::BN;
   TailPlan t;
   t.tiles_x = (a.M + BM - 1) / BM;
@@ -865,6 +789,7 @@ TailPlan sm100_tail_plan(const t5b_attn_args& a) {
 
 int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream) {
   using namespace sm100;
+  if (sm100w_prefers(a)) return sm100w_attention_fwd(a, spec, stream);
   const bool varlen = a.cu_seqlens_q != nullptr;
   const bool bf16 = a.dtype == T5B_BF16;
   const int HD = a.D;

@@ -21,6 +21,7 @@ struct AttnParams {
   int32_t causal;
   int32_t q_pos_offset;
   int32_t local_block;   // > 0: block-local attention (tensor-core forward only)
+  int32_t out_f32;       // != 0: out is float32 (a partial result for the merge kernel)
   float scale_log2;   // sm_scale * log2(e): softmax runs in the base-2 domain
   // Dense tensor-core launches use a 1-D grid over (query tile, head, batch).  Blocks at or
   // beyond `tail_first` share a query tile `tail_parts` ways along the keys and merge through
@@ -55,6 +56,7 @@ inline AttnParams make_attn_params(const t5b_attn_args& a) {
   p.causal = a.causal;
   p.q_pos_offset = a.q_pos_offset;
   p.local_block = a.local_block;
+  p.out_f32 = a.out_f32;
   p.scale_log2 = a.sm_scale * kLog2e;
   p.tiles_x = 0; p.tail_first = 0x7fffffff; p.tail_parts = 1;
   p.ws_counters = nullptr; p.ws_ml = nullptr; p.ws_o = nullptr;
@@ -178,6 +180,10 @@ __device__ __forceinline__ float lse_to_log2(float lse, bool valid) {
 
 bool sm100_supports(const t5b_attn_args& a);
 int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream);
+// two-tile kernel (head dim 64, more than 128 query rows): chosen inside sm100_attention_fwd / sm100_tail_plan
+bool sm100w_prefers(const t5b_attn_args& a);
+TailPlan sm100w_tail_plan(const t5b_attn_args& a);
+int sm100w_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream);
 int simt_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStream_t stream);
 bool sm100_bwd_supports(const t5b_attn_bwd_args& g);
 int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cudaStream_t stream);

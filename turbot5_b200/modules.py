@@ -73,6 +73,53 @@ def _rms_layer_norm_fwd(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6
     return (y, rstd) if return_rstd else y
 
 
+def add_rms_layer_norm(hidden: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                       inplace: bool = False):
+    """(hidden + branch, T5 RMSNorm(hidden + branch)) in one pass over memory: the residual add that
+    closes a sub-layer fused with the norm that opens the next one
+    (src/turbot5/model/modeling.py:124-128,142-164 + src/turbot5/model/modules.py:52-60).  bf16/fp16,
+    forward only; with `inplace` the sum overwrites `hidden`."""
+    nat.require_cuda(hidden, branch, weight)
+    d = hidden.shape[-1]
+    if branch.shape != hidden.shape or branch.dtype != hidden.dtype or weight.shape != (d,):
+        raise ValueError("hidden and branch must match; weight must have the size of the last dimension")
+    h2, b2 = hidden.reshape(-1, d), branch.reshape(-1, d)
+    if h2.stride(-1) != 1:
+        h2 = h2.contiguous()
+    if b2.stride(-1) != 1:
+        b2 = b2.contiguous()
+    same = inplace and h2.data_ptr() == hidden.data_ptr()
+    h_out = h2 if same else torch.empty((h2.shape[0], d), dtype=hidden.dtype, device=hidden.device)
+    normed = torch.empty((h2.shape[0], d), dtype=hidden.dtype, device=hidden.device)
+    weight = weight.contiguous()
+    with torch.cuda.device(hidden.device):
+        nat.check(nat.lib().t5b_add_rmsnorm_fwd(h2.data_ptr(), b2.data_ptr(), weight.data_ptr(), h_out.data_ptr(),
+                                                normed.data_ptr(), h2.shape[0], d, h2.stride(0), b2.stride(0),
+                                                h_out.stride(0), normed.stride(0), nat.dtype_code(hidden.dtype),
+                                                nat.dtype_code(weight.dtype), float(eps),
+                                                nat.stream_ptr(hidden.device)), "add_rms_layer_norm")
+    return h_out.view(hidden.shape), normed.view(hidden.shape)
+
+
+def gated_gelu(x: torch.Tensor) -> torch.Tensor:
+    """gelu_tanh(x[..., :F]) * x[..., F:] for the output x of one matrix product with the
+    concatenated wi_0 | wi_1 weights (T5DenseGatedActDense, src/turbot5/model/modeling.py:83-100).
+    bf16/fp16, forward only."""
+    nat.require_cuda(x)
+    f2 = x.shape[-1]
+    if f2 % 2:
+        raise ValueError("the last dimension holds the two projections side by side")
+    x2 = x.reshape(-1, f2)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], f2 // 2), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        nat.check(nat.lib().t5b_gated_gelu_fwd(x2.data_ptr(), out.data_ptr(), x2.shape[0], f2 // 2, x2.stride(0),
+                                               out.stride(0), nat.dtype_code(x.dtype), nat.stream_ptr(x.device)),
+                  "gated_gelu")
+    return out.view(*x.shape[:-1], f2 // 2)
+
+
 class RMSLayerNorm:
     """`RMSLayerNorm.apply(x, weight, eps)` call shape of the reference."""
 

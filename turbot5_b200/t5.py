@@ -25,7 +25,8 @@ import torch
 from torch import nn
 
 from .attention import flash_attention_with_fusing_bias, flash_decoding_with_fusing_bias
-from .modules import T5ATTENTION_TYPES, T5FlashAttention, T5LayerNorm
+from .modules import (T5ATTENTION_TYPES, T5FlashAttention, T5LayerNorm, add_rms_layer_norm, gated_gelu,
+                      rms_layer_norm)
 
 
 @dataclass
@@ -47,6 +48,17 @@ class T5StackConfig:
     decoder_start_token_id: int = 0
     attention_type: str = "flash"              # encoder self-attention: "flash" (full) or "local" (block-local)
     sliding_window: int = 512                  # block length of the "local" type
+
+
+class _FusedOps:
+    """Library operators behind `T5Stack.forward_fused`."""
+    from .sequence_parallel import _DeviceOps as _sp
+    rms_layer_norm = staticmethod(rms_layer_norm)
+    add_rms_layer_norm = staticmethod(add_rms_layer_norm)
+    gated_gelu = staticmethod(gated_gelu)
+    attention = _sp.attention
+    partial = _sp.partial
+    merge = _sp.merge
 
 
 class T5DenseGatedActDense(nn.Module):
@@ -151,6 +163,88 @@ class T5Stack(nn.Module):
                                                      key_value_states=encoder_hidden_states)[0]
             hidden = blk.layer[-1](hidden)
         return self.final_layer_norm(hidden).to(hidden.dtype)
+
+    # ---- inference pass of an encoder with the token-wise work fused around the attention path
+    def _stacked_weights(self, i):
+        """Per block: [q; k; v], [k; v] and [wi_0; wi_1] weights stacked once, so each group is one
+        matrix product.  Rebuilt when a parameter has been modified in place or replaced."""
+        blk = self.block[i]
+        att, ff = blk.layer[0].SelfAttention, blk.layer[-1].DenseReluDense
+        gated = hasattr(ff, "wi_0")
+        src = [att.q.weight, att.k.weight, att.v.weight] + ([ff.wi_0.weight, ff.wi_1.weight] if gated else [])
+        key = tuple((w.data_ptr(), w._version, w.dtype, w.device) for w in src)
+        cache = self.__dict__.setdefault("_stacked", {})
+        hit = cache.get(i)
+        if hit is None or hit[0] != key:
+            with torch.no_grad():
+                w = dict(qkv=torch.cat(src[:3], 0), kv=torch.cat(src[1:3], 0))
+                if gated:
+                    w["wi"] = torch.cat(src[3:], 0)
+            cache[i] = hit = (key, w)
+        return hit[1]
+
+    @torch.no_grad()
+    def forward_fused(self, input_ids=None, inputs_embeds=None, seq_len=None, group=None, overlap=True, ops=None):
+        """Encoder forward pass (no padding mask, no gradients) in eight launches per block:
+        stacked q/k/v projection, attention, output projection, residual add fused with the next
+        RMSNorm, stacked wi_0|wi_1 projection, gated GELU, wo projection, residual add + RMSNorm.
+        Same arithmetic and rounding points as `forward` (the block of
+        src/turbot5/model/modeling.py:124-128,142-164, 221-342).
+
+        With `seq_len` given the pass is sequence parallel: `input_ids` / `inputs_embeds` hold this
+        rank's token shard (B, S), S = ceil(seq_len / world), every token-wise operation runs on
+        the shard, and each attention layer gathers the other ranks' keys and values (see
+        `sequence_parallel_attention_overlapped`; `overlap=False` gathers first and attends once).
+        Returns the normed hidden states of the rows this call was given.  `ops` replaces the
+        library operators (an object with rms_layer_norm, add_rms_layer_norm, gated_gelu, attention
+        and the three functions `sequence_parallel_attention_overlapped` takes): tests of the
+        sharding logic on CPU ranks pass reference implementations.
+        """
+        ops = ops or _FusedOps
+        if self.is_decoder:
+            raise ValueError("forward_fused covers encoder stacks")
+        cfg = self.cfg
+        x = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+        B, S, _ = x.shape
+        H, D = cfg.num_heads, cfg.d_kv
+        HD = H * D
+        nb, md = cfg.relative_attention_num_buckets, cfg.relative_attention_max_distance
+        table = self._table()
+        x = x.contiguous() if inputs_embeds is None else x.clone(memory_format=torch.contiguous_format)
+        normed = ops.rms_layer_norm(x, self.block[0].layer[0].layer_norm.weight, cfg.layer_norm_epsilon).to(x.dtype)
+        if seq_len is not None:
+            from . import sequence_parallel as sp
+        for i, blk in enumerate(self.block):
+            att, ffl = blk.layer[0].SelfAttention, blk.layer[-1]
+            if type(att) is not T5FlashAttention:
+                raise ValueError("forward_fused covers full attention (attention_type='flash')")
+            w = self._stacked_weights(i)
+            if seq_len is None:
+                qkv = nn.functional.linear(normed, w["qkv"])
+                q, k, v = (qkv[..., j * HD:(j + 1) * HD].unflatten(-1, (H, D)).transpose(1, 2) for j in range(3))
+                attn = ops.attention(q, k, v, table, False, 1.0, nb, md, 0).transpose(1, 2)
+            else:
+                q = nn.functional.linear(normed, att.q.weight).view(B, S, H, D)
+                kv = nn.functional.linear(normed, w["kv"])
+                if overlap:
+                    attn = sp.sequence_parallel_attention_overlapped(q, kv, table, seq_len, sm_scale=1.0, NUM_BUCKETS=nb,
+                                                                     MAX_DISTANCE=md, group=group, ops=ops)
+                else:
+                    k, v = kv[..., :HD].reshape(B, S, H, D), kv[..., HD:].reshape(B, S, H, D)
+                    attn = sp.sequence_parallel_attention(
+                        q, k, v, table, seq_len, sm_scale=1.0, NUM_BUCKETS=nb, MAX_DISTANCE=md, group=group,
+                        attention_fn=lambda q_, k_, v_, b_, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset:
+                        ops.attention(q_, k_, v_, b_, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset))
+            o = nn.functional.linear(attn.reshape(B, S, HD), att.o.weight)
+            x, normed = ops.add_rms_layer_norm(x, o, ffl.layer_norm.weight, cfg.layer_norm_epsilon, inplace=True)
+            ff = ffl.DenseReluDense
+            if "wi" in w:
+                f = nn.functional.linear(ops.gated_gelu(nn.functional.linear(normed, w["wi"])), ff.wo.weight)
+            else:
+                f = ff(normed)
+            nxt = self.block[i + 1].layer[0].layer_norm if i + 1 < len(self.block) else self.final_layer_norm
+            x, normed = ops.add_rms_layer_norm(x, f, nxt.weight, cfg.layer_norm_epsilon, inplace=True)
+        return normed
 
     # ---- generation with a preallocated cache (decoder only)
     def new_cache(self, encoder_hidden_states, max_len) -> DecoderCache:
