@@ -280,14 +280,17 @@ def t5_attention_layer(hidden: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor,
                        key_value_states: Optional[torch.Tensor] = None,
                        key_padding_mask: Optional[torch.Tensor] = None,
                        past_key_value: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-                       causal: Optional[bool] = None):
+                       causal: Optional[bool] = None, round_to: Optional[torch.dtype] = None):
     """`T5Attention.forward` (src/turbot5/model/attentions.py:144-257) on CPU.
 
     `key_padding_mask` is the raw 0/1 (B, N) mask; padded keys get -inf-like
     additive bias (the stack's extended mask, finfo.min) and padded query rows
     are returned as the reference would compute them (callers compare valid
     rows only, since the flash module returns zeros there).  `causal` defaults
-    to `is_decoder and key_value_states is None`.  Returns (out, (k, v)).
+    to `is_decoder and key_value_states is None`.  Returns (out, (k, v)).  With `round_to`
+    (bfloat16 / float16) the projections q, k, v and the attention output are rounded to that type
+    where the module running in that type stores them (its linears return that type); all
+    arithmetic stays float32.
     """
     B, L, _ = hidden.shape
     if causal is None:
@@ -296,9 +299,10 @@ def t5_attention_layer(hidden: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor,
     def shape(x):
         return x.view(B, -1, n_heads, d_kv).transpose(1, 2)
 
-    qh = shape(hidden @ wq.t())
+    rnd = (lambda x: x) if round_to is None else (lambda x: x.to(round_to).to(hidden.dtype))
+    qh = shape(rnd(hidden @ wq.t()))
     src = hidden if key_value_states is None else key_value_states
-    kh, vh = shape(src @ wk.t()), shape(src @ wv.t())
+    kh, vh = shape(rnd(src @ wk.t())), shape(rnd(src @ wv.t()))
     if past_key_value is not None and key_value_states is None:
         kh = torch.cat([past_key_value[0], kh], dim=2)
         vh = torch.cat([past_key_value[1], vh], dim=2)
@@ -318,7 +322,7 @@ def t5_attention_layer(hidden: torch.Tensor, wq: torch.Tensor, wk: torch.Tensor,
         pm = (1.0 - key_padding_mask.to(hidden.dtype))[:, None, None, :] * torch.finfo(hidden.dtype).min
         bias = pm if bias is None else bias + pm
     o = naive_attention_with_bias(qh, kh, vh, bias)
-    o = o.transpose(1, 2).contiguous().view(B, -1, n_heads * d_kv)
+    o = rnd(o.transpose(1, 2).contiguous().view(B, -1, n_heads * d_kv))
     return o @ wo.t(), (kh, vh)
 
 

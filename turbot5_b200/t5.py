@@ -410,7 +410,11 @@ class T5ForConditionalGeneration(nn.Module):
         return self.lm_head(decoder_hidden)
 
     def forward(self, input_ids, decoder_input_ids, attention_mask=None):
-        enc = self.encoder(input_ids, attention_mask=attention_mask)
+        if attention_mask is None and not torch.is_grad_enabled() and self.cfg.attention_type == "flash" and \
+                input_ids.is_cuda and self.shared.weight.dtype in (torch.bfloat16, torch.float16):
+            enc = self.encoder.forward_fused(input_ids)       # inference: fused token-wise kernels
+        else:
+            enc = self.encoder(input_ids, attention_mask=attention_mask)
         dec = self.decoder(decoder_input_ids, encoder_hidden_states=enc, encoder_attention_mask=attention_mask)
         return self.logits(dec)
 
