@@ -509,9 +509,13 @@ def sequence_parallel_measurement(t5b, dev, rank, world, dist):
                                                      sm_scale=1.0, q_pos_offset=lo - hi))
             return merge_attention_partials(parts, dt)
         ms_compute = _time_ranks(compute_only, 3, dev, world, dist)
-        layer["ms_same_kernels_without_communication"] = ms_compute
+        ms_single = _time_ranks(lambda: t5b.flash_attention_with_fusing_bias(
+            q.transpose(1, 2), heads(kv_all, 0, 0, L), heads(kv_all, HD, 0, L), table, sm_scale=1.0, q_pos_offset=lo),
+            3, dev, world, dist)
+        layer["ms_overlapped_kernels_without_communication"] = ms_compute
+        layer["ms_single_call_without_communication"] = ms_single
         layer["exposed_gather_ms_overlapped"] = ms_ovl - ms_compute
-        layer["exposed_gather_ms_gather_then_attend"] = ms_seq - fl / world / (fl / (ms_compute * 1e-3)) * 1e3
+        layer["exposed_gather_ms_gather_then_attend"] = ms_seq - ms_single
     else:
         kv_all = kv
     out["one_attention_layer"] = layer

@@ -257,3 +257,22 @@ def test_short_decoder_training_keeps_gradients():
     with torch.no_grad():
         out_eval = cross(hid.detach(), key_value_states=enc.detach())[0]       # the decoding kernel
     check_close(out_eval, out.detach(), dt, "decode path vs dense path")
+
+
+def test_fused_encoder_decoder_forward_equals_the_module_passes():
+    from turbot5_b200.t5 import T5ForConditionalGeneration, T5StackConfig
+    over = dict(d_model=128, num_heads=4, d_ff=256)
+    model = seed_named_parameters(T5ForConditionalGeneration(T5StackConfig(**{**TINY_T5, **over})), 0)
+    model = model.cuda().to(torch.bfloat16).eval()
+    g = torch.Generator().manual_seed(21)
+    ids, dec = torch.randint(0, 128, (2, 300), generator=g), torch.randint(0, 128, (2, 150), generator=g)
+    with torch.no_grad():
+        fused = model(ids.cuda(), dec.cuda())                                  # inference: both stacks fused
+        enc = model.encoder(ids.cuda())
+        plain = model.logits(model.decoder(dec.cuda(), encoder_hidden_states=enc))
+    assert (fused.float() - plain.float()).abs().max().item() <= 0.05 * plain.float().abs().max().item()
+    assert (fused.float() - plain.float()).abs().mean().item() <= 5e-3 * plain.float().abs().mean().item()
+    w = {k: v.detach().float().cpu() for k, v in model.state_dict().items()}
+    _, want = orc.t5_model_logits(w, {**TINY_T5, **over}, ids, dec)
+    rel = lambda t: ((t.float().cpu() - want).abs().mean() / want.abs().mean()).item()
+    assert rel(fused) < 1e-1 and rel(fused) <= 1.1 * rel(plain) + 1e-3

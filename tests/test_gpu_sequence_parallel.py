@@ -60,7 +60,29 @@ def _worker(rank, world, port, L, q_out):
                                                     v.cuda().transpose(1, 2), table, sm_scale=1.0).transpose(1, 2)
         torch.cuda.synchronize()
         err = (o[:, :hi - lo].float() - full[:, lo:hi].float()).abs().max().item()
-        q_out.put((rank, err))
+        # the overlapped path: one gather of the stacked k|v projection, partial results over the local
+        # keys and over the gathered keys on either side, merged; checked against the CPU oracle
+        from oracle import t5_oracle as orc
+        kv = torch.cat([shard(k).reshape(1, S, H * 64), shard(v).reshape(1, S, H * 64)], dim=-1).contiguous()
+        o2 = t5b.sequence_parallel_attention_overlapped(shard(q), kv, table, L, sm_scale=1.0)
+        torch.cuda.synchronize()
+        t5b.check_device_status()
+        want = orc.attention_basic(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), table.cpu(),
+                                   q_pos_offset=0).transpose(1, 2)
+        d2 = (o2[:, :hi - lo].float().cpu() - want[:, lo:hi]).abs()
+        # the token-sharded encoder stack against the unsharded pass on this GPU
+        from tests.helpers import TINY_T5, seed_named_parameters
+        from turbot5_b200.t5 import T5Stack, T5StackConfig
+        cfg = T5StackConfig(**{**TINY_T5, "d_model": 128, "num_heads": 4, "d_ff": 256, "num_layers": 3})
+        enc = seed_named_parameters(T5Stack(cfg, torch.nn.Embedding(cfg.vocab_size, cfg.d_model), is_decoder=False), 0)
+        enc = enc.cuda().to(dt).eval()
+        ids = torch.randint(0, cfg.vocab_size, (1, L), generator=torch.Generator().manual_seed(5))
+        local = torch.zeros((1, S), dtype=torch.long)
+        local[:, :hi - lo] = ids[:, lo:hi]
+        got = enc.forward_fused(local.cuda(), seq_len=L)[0, :hi - lo].float()
+        ref = enc.forward_fused(ids.cuda())[0, lo:hi].float()
+        rel = ((got - ref).abs().mean() / ref.abs().mean()).item()
+        q_out.put((rank, err, d2.max().item(), d2.mean().item(), rel))
     finally:
         dist.destroy_process_group()
 
@@ -78,7 +100,9 @@ def test_two_gpu_shards_equal_single_gpu_result():
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for rank, err in results:
+    for rank, err, mx, mean, rel in results:
         # same kernel, same keys, same offsets; rows sit in other tiles than in the unsharded
         # call, so rounding may differ in the last bit
         assert err <= 2e-2, (rank, err)
+        assert mx <= 2e-2 and mean <= 2e-3, (rank, mx, mean)       # overlapped path vs the oracle
+        assert rel <= 2e-2, (rank, rel)                            # sharded stack vs unsharded stack (bf16, 3 layers)

@@ -6,19 +6,21 @@ function names, backed by hand-written CUDA behind a C ABI
 other backend: operators raise if the library is missing or a tensor is not on a
 CUDA device.
 """
-from .attention import (check_device_status, flash_attention_with_fusing_bias,
+from .attention import (check_device_status, flash_attention_partial, flash_attention_with_fusing_bias,
                         flash_attention_with_fusing_bias_varlen, flash_decoding_with_fusing_bias,
-                        relative_position_bucket_grid, relative_position_bucket_table)
+                        merge_attention_partials, relative_position_bucket_grid, relative_position_bucket_table)
 
 from .modules import (RMSLayerNorm, T5ATTENTION_TYPES, T5FlashAttention, T5LayerNorm, T5LocalFlashAttention,
-                      rms_layer_norm)
+                      add_rms_layer_norm, gated_gelu, rms_layer_norm)
 from .padding import get_unpad_plan, pad_rows, unpad_rows
-from .sequence_parallel import sequence_parallel_attention, shard_bounds, shard_size
+from .sequence_parallel import (sequence_parallel_attention, sequence_parallel_attention_overlapped, shard_bounds,
+                                shard_size)
 
 __all__ = [
     "T5ATTENTION_TYPES", "T5FlashAttention", "T5LocalFlashAttention", "T5LayerNorm", "RMSLayerNorm", "rms_layer_norm",
     "get_unpad_plan", "unpad_rows", "pad_rows",
-    "sequence_parallel_attention", "shard_bounds", "shard_size",
+    "add_rms_layer_norm", "gated_gelu", "flash_attention_partial", "merge_attention_partials",
+    "sequence_parallel_attention", "sequence_parallel_attention_overlapped", "shard_bounds", "shard_size",
     "flash_attention_with_fusing_bias", "flash_attention_with_fusing_bias_varlen",
     "flash_decoding_with_fusing_bias", "relative_position_bucket_table",
     "relative_position_bucket_grid", "check_device_status",

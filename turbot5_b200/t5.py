@@ -166,52 +166,60 @@ class T5Stack(nn.Module):
 
     # ---- inference pass of an encoder with the token-wise work fused around the attention path
     def _stacked_weights(self, i):
-        """Per block: [q; k; v], [k; v] and [wi_0; wi_1] weights stacked once, so each group is one
-        matrix product.  Rebuilt when a parameter has been modified in place or replaced."""
+        """Per block: [q; k; v], [k; v], the cross-attention [k; v] and [wi_0; wi_1] weights stacked once,
+        so each group is one matrix product.  Rebuilt when a parameter has been modified in place or
+        replaced."""
         blk = self.block[i]
         att, ff = blk.layer[0].SelfAttention, blk.layer[-1].DenseReluDense
         gated = hasattr(ff, "wi_0")
-        src = [att.q.weight, att.k.weight, att.v.weight] + ([ff.wi_0.weight, ff.wi_1.weight] if gated else [])
-        key = tuple((w.data_ptr(), w._version, w.dtype, w.device) for w in src)
+        groups = dict(qkv=[att.q.weight, att.k.weight, att.v.weight], kv=[att.k.weight, att.v.weight])
+        if self.is_decoder:
+            catt = blk.layer[1].EncDecAttention
+            groups["ckv"] = [catt.k.weight, catt.v.weight]
+        if gated:
+            groups["wi"] = [ff.wi_0.weight, ff.wi_1.weight]
+        key = tuple((w.data_ptr(), w._version, w.dtype, w.device) for ws in groups.values() for w in ws)
         cache = self.__dict__.setdefault("_stacked", {})
         hit = cache.get(i)
         if hit is None or hit[0] != key:
             with torch.no_grad():
-                w = dict(qkv=torch.cat(src[:3], 0), kv=torch.cat(src[1:3], 0))
-                if gated:
-                    w["wi"] = torch.cat(src[3:], 0)
-            cache[i] = hit = (key, w)
+                cache[i] = hit = (key, {name: torch.cat(ws, 0) for name, ws in groups.items()})
         return hit[1]
 
     @torch.no_grad()
-    def forward_fused(self, input_ids=None, inputs_embeds=None, seq_len=None, group=None, overlap=True, ops=None):
-        """Encoder forward pass (no padding mask, no gradients) in eight launches per block:
-        stacked q/k/v projection, attention, output projection, residual add fused with the next
-        RMSNorm, stacked wi_0|wi_1 projection, gated GELU, wo projection, residual add + RMSNorm.
-        Same arithmetic and rounding points as `forward` (the block of
-        src/turbot5/model/modeling.py:124-128,142-164, 221-342).
+    def forward_fused(self, input_ids=None, inputs_embeds=None, seq_len=None, group=None, overlap=True, ops=None,
+                      encoder_hidden_states=None):
+        """Forward pass without padding masks and without gradients, with the token-wise work fused
+        around the attention path: per encoder block eight launches -- stacked q/k/v projection,
+        attention, output projection, residual add fused with the next RMSNorm, stacked wi_0|wi_1
+        projection, gated GELU, wo projection, residual add + RMSNorm -- and five more per decoder
+        block for the cross attention (q projection, stacked k/v projection of the encoder states,
+        attention, output projection, residual add + RMSNorm).  Same arithmetic and rounding points
+        as `forward` (the blocks of src/turbot5/model/modeling.py:124-128,142-164,166-219,221-342).
 
-        With `seq_len` given the pass is sequence parallel: `input_ids` / `inputs_embeds` hold this
-        rank's token shard (B, S), S = ceil(seq_len / world), every token-wise operation runs on
-        the shard, and each attention layer gathers the other ranks' keys and values (see
-        `sequence_parallel_attention_overlapped`; `overlap=False` gathers first and attends once).
-        Returns the normed hidden states of the rows this call was given.  `ops` replaces the
-        library operators (an object with rms_layer_norm, add_rms_layer_norm, gated_gelu, attention
-        and the three functions `sequence_parallel_attention_overlapped` takes): tests of the
-        sharding logic on CPU ranks pass reference implementations.
+        With `seq_len` given the pass is sequence parallel (encoder stacks): `input_ids` /
+        `inputs_embeds` hold this rank's token shard (B, S), S = ceil(seq_len / world), every
+        token-wise operation runs on the shard, and each attention layer gathers the other ranks'
+        keys and values (see `sequence_parallel_attention_overlapped`; `overlap=False` gathers first
+        and attends once).  Returns the normed hidden states of the rows this call was given.
+        `ops` replaces the library operators (an object with rms_layer_norm, add_rms_layer_norm,
+        gated_gelu, attention and the partial / merge pair of the sequence-parallel path): tests of
+        the sharding logic on CPU ranks pass reference implementations.
         """
         ops = ops or _FusedOps
-        if self.is_decoder:
-            raise ValueError("forward_fused covers encoder stacks")
         cfg = self.cfg
+        if self.is_decoder and (encoder_hidden_states is None or seq_len is not None):
+            raise ValueError("a decoder stack needs encoder_hidden_states and is not sequence parallel")
         x = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
         B, S, _ = x.shape
         H, D = cfg.num_heads, cfg.d_kv
         HD = H * D
         nb, md = cfg.relative_attention_num_buckets, cfg.relative_attention_max_distance
+        eps = cfg.layer_norm_epsilon
         table = self._table()
+        heads = lambda t: t.unflatten(-1, (H, D)).transpose(1, 2)        # (B, L, H*D) -> (B, H, L, D) view
         x = x.contiguous() if inputs_embeds is None else x.clone(memory_format=torch.contiguous_format)
-        normed = ops.rms_layer_norm(x, self.block[0].layer[0].layer_norm.weight, cfg.layer_norm_epsilon).to(x.dtype)
+        normed = ops.rms_layer_norm(x, self.block[0].layer[0].layer_norm.weight, eps).to(x.dtype)
         if seq_len is not None:
             from . import sequence_parallel as sp
         for i, blk in enumerate(self.block):
@@ -221,8 +229,8 @@ class T5Stack(nn.Module):
             w = self._stacked_weights(i)
             if seq_len is None:
                 qkv = nn.functional.linear(normed, w["qkv"])
-                q, k, v = (qkv[..., j * HD:(j + 1) * HD].unflatten(-1, (H, D)).transpose(1, 2) for j in range(3))
-                attn = ops.attention(q, k, v, table, False, 1.0, nb, md, 0).transpose(1, 2)
+                q, k, v = (heads(qkv[..., j * HD:(j + 1) * HD]) for j in range(3))
+                attn = ops.attention(q, k, v, table, self.is_decoder, 1.0, nb, md, 0).transpose(1, 2)
             else:
                 q = nn.functional.linear(normed, att.q.weight).view(B, S, H, D)
                 kv = nn.functional.linear(normed, w["kv"])
@@ -236,14 +244,22 @@ class T5Stack(nn.Module):
                         attention_fn=lambda q_, k_, v_, b_, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset:
                         ops.attention(q_, k_, v_, b_, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset))
             o = nn.functional.linear(attn.reshape(B, S, HD), att.o.weight)
-            x, normed = ops.add_rms_layer_norm(x, o, ffl.layer_norm.weight, cfg.layer_norm_epsilon, inplace=True)
+            if self.is_decoder:
+                ca = blk.layer[1]
+                x, normed = ops.add_rms_layer_norm(x, o, ca.layer_norm.weight, eps, inplace=True)
+                catt = ca.EncDecAttention
+                q = heads(nn.functional.linear(normed, catt.q.weight))
+                ckv = nn.functional.linear(encoder_hidden_states, w["ckv"])
+                attn = ops.attention(q, heads(ckv[..., :HD]), heads(ckv[..., HD:]), None, False, 1.0, nb, md, 0)
+                o = nn.functional.linear(attn.transpose(1, 2).reshape(B, S, HD), catt.o.weight)
+            x, normed = ops.add_rms_layer_norm(x, o, ffl.layer_norm.weight, eps, inplace=True)
             ff = ffl.DenseReluDense
             if "wi" in w:
                 f = nn.functional.linear(ops.gated_gelu(nn.functional.linear(normed, w["wi"])), ff.wo.weight)
             else:
                 f = ff(normed)
             nxt = self.block[i + 1].layer[0].layer_norm if i + 1 < len(self.block) else self.final_layer_norm
-            x, normed = ops.add_rms_layer_norm(x, f, nxt.weight, cfg.layer_norm_epsilon, inplace=True)
+            x, normed = ops.add_rms_layer_norm(x, f, nxt.weight, eps, inplace=True)
         return normed
 
     # ---- generation with a preallocated cache (decoder only)
@@ -412,9 +428,10 @@ class T5ForConditionalGeneration(nn.Module):
     def forward(self, input_ids, decoder_input_ids, attention_mask=None):
         if attention_mask is None and not torch.is_grad_enabled() and self.cfg.attention_type == "flash" and \
                 input_ids.is_cuda and self.shared.weight.dtype in (torch.bfloat16, torch.float16):
-            enc = self.encoder.forward_fused(input_ids)       # inference: fused token-wise kernels
-        else:
-            enc = self.encoder(input_ids, attention_mask=attention_mask)
+            # inference without padding: fused token-wise kernels in both stacks
+            enc = self.encoder.forward_fused(input_ids)
+            return self.logits(self.decoder.forward_fused(decoder_input_ids, encoder_hidden_states=enc))
+        enc = self.encoder(input_ids, attention_mask=attention_mask)
         dec = self.decoder(decoder_input_ids, encoder_hidden_states=enc, encoder_attention_mask=attention_mask)
         return self.logits(dec)
 
