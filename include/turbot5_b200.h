@@ -32,7 +32,7 @@ typedef enum {
   T5B_ERR_HEAD_DIM = 4,       /* head dim not in {16, 32, 64, 128}                       */
   T5B_ERR_ARG = 5,            /* null pointer, bad flag, bad bucket settings             */
   T5B_ERR_LAUNCH = 6,         /* the CUDA runtime refused the launch                     */
-  T5B_ERR_DEVICE_TIMEOUT = 7, /* reported through the device status word (see below)     */
+  T5B_ERR_DEVICE_TIMEOUT = 7, /* t5b_check_status: a kernel's bounded wait ran out        */
   T5B_ERR_WORKSPACE = 8,      /* scratch buffer missing or too small                     */
   T5B_ERR_DRIVER = 9,         /* tensor-map encode entry point unavailable / failed      */
   T5B_ERR_UNSUPPORTED = 10    /* valid request the library has no kernel for             */
@@ -57,6 +57,20 @@ typedef enum {
 
 T5B_API const char* t5b_status_string(int status);
 T5B_API int t5b_abi_version(void);
+
+/* ---- device-side waits that ran out ----------------------------------------------
+ * No counterpart in the reference (its Triton kernels have no waits of their own).  Every wait
+ * inside the tensor-core kernels is bounded; one that runs out stores a non-zero code in the
+ * int32 device word the call was given (device_status) and the kernel returns.
+ * t5b_check_status is the one entry point that SYNCHRONISES: it waits for `stream`, reads the
+ * word, and returns T5B_OK if it is zero, else T5B_ERR_DEVICE_TIMEOUT after storing the code in
+ * *code_out (optional) and clearing the word.
+ * t5b_selftest_bounded_wait launches a one-block kernel whose threads wait, with a limit of
+ * limit_cycles SM cycles (1 .. 2e9), on a barrier that nobody arrives at, so that the give-up
+ * path can be exercised on purpose: afterwards the word holds 9001 and the GPU is as usable
+ * as before. */
+T5B_API int t5b_check_status(int32_t* device_status, int32_t* code_out, void* stream);
+T5B_API int t5b_selftest_bounded_wait(int32_t* device_status, int64_t limit_cycles, void* stream);
 
 /* ---- relative-position buckets ------------------------------------------------
  * Stands in for T5Attention._relative_position_bucket
@@ -224,7 +238,10 @@ T5B_API int t5b_decode_fwd(const t5b_decode_args* args, void* stream);
  * The first call on each device looks up the array's device address; make it
  * before any stream capture begins.  All calls share the array: the counters are
  * cleared on `stream` before each launch, and calls whose kernels overlap on the
- * GPU (issued on different streams) race on it -- issue them on one stream. */
+ * GPU (issued on different streams) race on it -- issue them on one stream.  Arguments are
+ * checked before anything is queued: a refused call leaves the array untouched.  The address
+ * looked up on the first call is kept for the life of the process; do not call this entry point
+ * again after a cudaDeviceReset. */
 T5B_API int64_t t5b_decode_static_scratch_bytes(void);
 T5B_API int t5b_decode_fwd_static_scratch(const t5b_decode_args* args, void* stream);
 

@@ -40,7 +40,9 @@ def _args(nat, q, k, v, out, table, N, splits, causal):
 
 
 @pytest.mark.parametrize("B,H,M,N,causal,splits", [(3, 4, 1, 2000, True, 6), (2, 2, 3, 1500, True, 0),
-                                                    (4, 16, 1, 8192, False, 0)])
+                                                    (4, 16, 1, 8192, False, 0),
+                                                    (2, 3, 7, 1800, True, 5),      # more rows than one launch takes:
+                                                    (1, 2, 8, 3000, False, 0)])    # the counters serve several launches
 def test_static_scratch_matches_workspace_entry_point(B, H, M, N, causal, splits):
     from turbot5_b200 import _native as nat
     L = nat.lib()
@@ -85,3 +87,25 @@ def test_static_scratch_refuses_oversized_problems():
     status = L.t5b_decode_fwd_static_scratch(a, torch.cuda.current_stream(dev).cuda_stream)
     assert status == 8                            # T5B_ERR_WORKSPACE
     assert b"workspace" in L.t5b_status_string(status)
+
+
+def test_static_scratch_checks_arguments_before_touching_the_array():
+    """A call that is refused for its arguments reports that reason (not a scratch problem) and
+    queues nothing on the shared array."""
+    from turbot5_b200 import _native as nat
+    L = nat.lib()
+    dt = torch.bfloat16
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    q = torch.zeros((2, 2, 1, 64), dtype=dt, device=dev)
+    k = torch.zeros((2, 2, 4096, 64), dtype=dt, device=dev)
+    out = torch.zeros_like(q)
+    a = _args(nat, q, k, k, out, None, 4096, 300, False)          # more than 256 splits
+    assert L.t5b_decode_fwd_static_scratch(a, stream) == 5        # T5B_ERR_ARG, as t5b_decode_fwd answers
+    a = _args(nat, q, k, k, out, None, 4096, 4, False)
+    a.k = None
+    assert L.t5b_decode_fwd_static_scratch(a, stream) == 5
+    a = _args(nat, q, k, k, out, None, 4096, 4, False)
+    a.D = 48
+    assert L.t5b_decode_fwd_static_scratch(a, stream) == 4        # T5B_ERR_HEAD_DIM
+    torch.cuda.synchronize()

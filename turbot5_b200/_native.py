@@ -13,6 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libturbot5_b200.so")
 
 OK = 0
+ERR_DEVICE_TIMEOUT = 7
 ERR_UNSUPPORTED = 10
 F32, F16, BF16 = 0, 1, 2
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMT, KERNEL_TCGEN05_POLYEXP, KERNEL_TCGEN05_2TILE = 0, 1, 2, 3, 4
@@ -25,7 +26,8 @@ SYMBOLS = ("t5b_status_string", "t5b_abi_version", "t5b_bucket_table_host", "t5b
            "t5b_attention_fwd", "t5b_attention_workspace_bytes", "t5b_attention_bwd", "t5b_attention_bwd_workspace_bytes", "t5b_decode_workspace_bytes", "t5b_decode_num_splits",
            "t5b_decode_fwd", "t5b_decode_static_scratch_bytes", "t5b_decode_fwd_static_scratch",
            "t5b_rmsnorm_fwd", "t5b_rmsnorm_bwd", "t5b_unpad_plan", "t5b_gather_rows",
-           "t5b_scatter_rows", "t5b_attention_merge", "t5b_add_rmsnorm_fwd", "t5b_gated_gelu_fwd")
+           "t5b_scatter_rows", "t5b_attention_merge", "t5b_add_rmsnorm_fwd", "t5b_gated_gelu_fwd",
+           "t5b_check_status", "t5b_selftest_bounded_wait")
 
 
 class AttnArgs(C.Structure):
@@ -136,6 +138,10 @@ def lib():
     L.t5b_unpad_plan.restype = C.c_int
     L.t5b_unpad_plan.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                  C.c_void_p, C.c_void_p]
+    L.t5b_check_status.restype = C.c_int
+    L.t5b_check_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]
+    L.t5b_selftest_bounded_wait.restype = C.c_int
+    L.t5b_selftest_bounded_wait.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     L.t5b_attention_merge.restype = C.c_int
     L.t5b_attention_merge.argtypes = [C.POINTER(MergeArgs), C.c_void_p]
     L.t5b_add_rmsnorm_fwd.restype = C.c_int

@@ -33,12 +33,15 @@ def device_status(device) -> torch.Tensor:
 
 
 def check_device_status(device="cuda") -> None:
-    """Synchronising check of the status word (tests / debugging)."""
+    """Synchronising check of the status word through the library's `t5b_check_status`: raises
+    if a kernel's bounded wait ran out since the last check (and clears the word)."""
     word = device_status(device)
-    code = int(word.item())
-    if code != 0:
-        word.zero_()
-        raise RuntimeError(f"turbot5_b200 kernel gave up waiting on the device (code {code})")
+    code = nat.C.c_int32(0)
+    with torch.cuda.device(word.device):
+        st = nat.lib().t5b_check_status(word.data_ptr(), nat.C.byref(code), nat.stream_ptr(word.device))
+    if st == nat.ERR_DEVICE_TIMEOUT:
+        raise RuntimeError(f"turbot5_b200 kernel gave up waiting on the device (code {code.value})")
+    nat.check(st, "check_device_status")
 
 
 def _check_qkv(q, k, v):

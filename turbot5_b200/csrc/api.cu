@@ -100,3 +100,60 @@ extern "C" int64_t t5b_attention_workspace_bytes(const t5b_attn_args* a) {
   const TailPlan plan = sm100_tail_plan(*a);
   return plan.parts > 1 ? plan.bytes() : 0;
 }
+
+// ---------------------------------------------------------------------------
+// Device-side waits that run out: reading the status word, and a self-test of the mechanism.
+//
+// Every wait in the tensor-core kernels is bounded (mbar_wait_bounded): when it runs out the
+// thread raises its block's abort flag, stores a non-zero code in the caller's device_status
+// word, and the block still frees its tensor memory and returns.  t5b_check_status is how a C
+// caller reads that word; t5b_selftest_bounded_wait makes a wait run out on purpose -- a barrier
+// nobody arrives at, with a short limit -- so that the path is exercised without any fault.
+namespace {
+
+__global__ void bounded_wait_selftest_kernel(int32_t* status, long long limit_cycles) {
+  __shared__ unsigned long long bar_word;
+  __shared__ int abort_flag;
+  const uint32_t bar = smem_u32(&bar_word);
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(bar, 1);            // one arrival expected; none will come
+    fence_barrier_init();
+  }
+  __syncthreads();
+  volatile int* flag = &abort_flag;
+  int fail = 0;
+  if (threadIdx.x == 0) {
+    // a single waiting thread, as the issuing threads of the attention kernels wait
+    if (!mbar_wait_bounded(bar, 0, flag, limit_cycles)) fail = 1;
+  } else if (threadIdx.x >= 32) {
+    // a whole warp, as the softmax warps wait: it leaves together once the flag is up
+    if (!mbar_wait_bounded_warp(bar, 0, flag)) fail = 2;
+  }
+  if (fail != 0 && status != nullptr) atomicCAS(status, 0, 9000 + fail);
+  __syncthreads();                // every thread gets here: nothing is left waiting
+}
+
+}  // namespace
+
+extern "C" int t5b_selftest_bounded_wait(int32_t* device_status, int64_t limit_cycles, void* stream) {
+  if (!device_status) return T5B_ERR_ARG;
+  if (limit_cycles <= 0 || limit_cycles > 2000000000LL) return T5B_ERR_ARG;     // at most about a second
+  bounded_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(device_status, (long long)limit_cycles);
+  return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;
+}
+
+extern "C" int t5b_check_status(int32_t* device_status, int32_t* code_out, void* stream) {
+  if (!device_status) return T5B_ERR_ARG;
+  int32_t code = 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemcpyAsync(&code, device_status, sizeof(code), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
+    cudaGetLastError();
+    return T5B_ERR_LAUNCH;
+  }
+  if (code_out) *code_out = code;
+  if (code == 0) return T5B_OK;
+  if (cudaMemsetAsync(device_status, 0, sizeof(code), st) != cudaSuccess) { cudaGetLastError(); return T5B_ERR_LAUNCH; }
+  return T5B_ERR_DEVICE_TIMEOUT;
+}

@@ -5,12 +5,13 @@
 // sequence -- as two 128-row tiles A and B that share every K/V tile brought into shared
 // memory (half the L2 -> SM traffic of one tile per block):
 //
-//   warps 8-11  a warpgroup of its own whose first thread loads (Q twice, then K/V tiles into a ring; cp.async.bulk.tensor,
-//               128-byte swizzle, completion on mbarriers) and issues all matrix products
+//   warps 8-11  a warpgroup of its own.  Lane 0 of warp 8 loads (Q twice, then K/V tiles into a
+//               ring; cp.async.bulk.tensor, 128-byte swizzle, completion on mbarriers) and issues
+//               the matrix products of tile A; lane 0 of warp 9 issues those of tile B
 //               (tcgen05.mma, S = Q K^T from shared memory, O += P V with P read from tensor
-//               memory; tcgen05.commit -> mbarriers), for both tiles.  The warpgroup gives its
-//               registers away (setmaxnreg): with 12 warps every scheduler holds three, and
-//               56 + 2 x 224 registers per thread fill a scheduler's 16384
+//               memory; tcgen05.commit -> mbarriers).  The warpgroup gives its registers away
+//               (setmaxnreg): with 12 warps every scheduler holds three, and 88 + 2 x 208
+//               registers per thread fill a scheduler's 16384
 //   warps 0-3   softmax of tile A, warps 4-7 softmax of tile B: ONE thread per query row.  A
 //               thread copies the 128 scores of its row from tensor memory to registers
 //               (tcgen05.ld) and hands the S buffer back at once, so the next Q K^T of its tile
@@ -22,7 +23,7 @@
 // thread handles twice the columns per tile, so the per-tile bookkeeping (barrier waits,
 // fences, tile classification, maximum update) is paid once per 128 exponentials instead of
 // once per 64, the two threads of a row no longer have to agree on the running maximum, and
-// 224 registers per thread leave nothing to spill.  With the instruction stream that lean
+// 208 registers per thread leave nothing to spill.  With the instruction stream that lean
 // the exponential unit (16 ex2 per clock per SM) becomes the real limit, and moving a share
 // of the exponentials to the FMA pipe (PolyExp) pays; see kPoly.
 //
@@ -84,7 +85,7 @@ constexpr int BLOCK_M = BM * TILES;  // query rows per block
 constexpr int BN = 128;              // keys per tile
 constexpr int STAGES = 3;            // K/V ring depth
 constexpr int NUM_THREADS = 384;
-constexpr int REGS_IO = 56, REGS_SOFTMAX = 224;   // per thread after setmaxnreg: (56 + 2 * 224) * 32 = 16128 per scheduler
+constexpr int REGS_IO = 88, REGS_SOFTMAX = 208;   // per thread after setmaxnreg: (88 + 2 * 208) * 32 = 16128 per scheduler
 constexpr int WARP_IO = 8;
 constexpr int TMEM_COLS = 512;
 constexpr int TILE_COLS = 256;       // tensor-memory columns per query tile
@@ -221,8 +222,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar(BAR_K_FULL + s), 1);
       mbar_init(bar(BAR_V_FULL + s), 1);
-      mbar_init(bar(BAR_K_EMPTY + s), 1);
-      mbar_init(bar(BAR_V_EMPTY + s), 1);
+      mbar_init(bar(BAR_K_EMPTY + s), TILES);    // one arrival per issuing thread
+      mbar_init(bar(BAR_V_EMPTY + s), TILES);
     }
     for (int t = 0; t < TILES; ++t) {
       mbar_init(bar(BAR_S_FULL + t), 1);
@@ -268,18 +269,27 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q,
   int fail_code = 0;
 
   if (warp >= WARP_IO) {
-    // ============================================================ loads and matrix products, one thread
+    // ============================================================ loads and matrix products
+    // Two issuing threads, one per query tile (lane 0 of warps 8 and 9); the first also refills the
+    // K/V ring.  A tcgen05.mma costs its issuing thread tens of cycles (descriptors travel through
+    // the uniform registers), and a tile step is twelve of them: one thread for both tiles was
+    // busy four fifths of the time and the softmax warps waited for their scores.
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_IO));
-    if (warp == WARP_IO && lane == 0 && n_max > 0) {
+    const int t = warp - WARP_IO;                 // query tile of this issuing thread
+    if (t < TILES && lane == 0 && n_max > 0) {
       constexpr uint32_t IDESC_QK = make_idesc_f16(kBf16, kBf16, BM, BN, false, false);
       constexpr uint32_t IDESC_PV = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);
-      auto issue_qk = [&](int t, int j) {
-        const int s = j % STAGES;
+      const int n_t = t == 0 ? n_tile[0] : n_tile[1];
+      const uint32_t tm = tmem + t * TILE_COLS;
+      // One ring slot per instantiation: the shared-memory descriptors of a step are then constants
+      // of the loop (kept in uniform registers), not values recomputed from j % STAGES per product.
+      auto issue_qk = [&](auto slot) {
+        constexpr int s = decltype(slot)::value;
         const uint64_t da = make_smem_desc_sw128(sQ + t * Q_BYTES, 16, 1024);
         const uint64_t db = make_smem_desc_sw128(sK + s * KV_BYTES, 16, 1024);
         #pragma unroll
         for (int k = 0; k < 4; ++k)   // 32 bytes of the 128-byte swizzle row per step
-          umma_ss(tmem + t * TILE_COLS + COL_S, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC_QK, k > 0);
+          umma_ss(tm + COL_S, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC_QK, k > 0);
         tc_commit(bar(BAR_S_FULL + t));
       };
       bool ok = mbar_wait_bounded(bar(BAR_Q_FULL), 0, abort_flag);
@@ -287,62 +297,60 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (ok && !mbar_wait_bounded(bar(BAR_K_FULL), 0, abort_flag)) { ok = false; fail_code = 21; }
       if (ok) {
         tc_fence_after();
-        if (n_tile[0] > 0) issue_qk(0, 0);
-        if (n_tile[1] > 0) issue_qk(1, 0);
-        tc_commit(bar(BAR_K_EMPTY));
+        if (n_t > 0) issue_qk(std::integral_constant<int, 0>{});
+        tc_commit(bar(BAR_K_EMPTY));          // (arrives at once when this thread issued nothing)
       }
-      for (int j = 0; ok && j < n_max; ++j) {
-        const int s = j % STAGES;
+      // step j with j % STAGES == slot; returns false when a wait gave up
+      auto step = [&](int j, auto slot) -> bool {
+        constexpr int s = decltype(slot)::value;
+        constexpr int s1 = (s + 1) % STAGES;
+        constexpr int sp = (s + STAGES - 1) % STAGES;       // slot of step j - 1
         const uint32_t ph = (uint32_t)((j / STAGES) & 1);
         if (j + 1 < n_max) {
-          // S of a tile has been copied to registers: its next Q K^T overlaps this tile's softmax
-          const int s1 = (j + 1) % STAGES;
-          if (!mbar_wait_bounded(bar(BAR_K_FULL + s1), (uint32_t)(((j + 1) / STAGES) & 1), abort_flag)) { fail_code = 23; break; }
+          // S of the tile has been copied to registers: its next Q K^T overlaps this step's softmax
+          if (!mbar_wait_bounded(bar(BAR_K_FULL + s1), (uint32_t)(((j + 1) / STAGES) & 1), abort_flag)) { fail_code = 23; return false; }
           tc_fence_after();
-          bool fine = true;
-          #pragma unroll
-          for (int t = 0; t < TILES; ++t) {
-            if (fine && j + 1 < n_tile[t]) {
-              if (!mbar_wait_bounded(bar(BAR_S_FREE + t), (uint32_t)(j & 1), abort_flag)) { fail_code = 25; fine = false; }
-              else { tc_fence_after(); issue_qk(t, j + 1); }
-            }
+          if (j + 1 < n_t) {
+            if (!mbar_wait_bounded(bar(BAR_S_FREE + t), (uint32_t)(j & 1), abort_flag)) { fail_code = 25; return false; }
+            tc_fence_after();
+            issue_qk(std::integral_constant<int, s1>{});
           }
-          if (!fine) break;
           tc_commit(bar(BAR_K_EMPTY + s1));
         }
-        // refill the ring: K(j+STAGES) into the slot of K(j) (both Q K^T of tile j were issued a
-        // tile ago), V(j-1+STAGES) into the slot of V(j-1) (its products were issued a tile ago)
-        if (j + STAGES < n_max) {
-          if (!mbar_wait_bounded(bar(BAR_K_EMPTY + s), ph, abort_flag)) { fail_code = 10; break; }
-          load_k(j + STAGES);
-        }
-        if (j >= 1 && j - 1 + STAGES < n_max) {
-          if (!mbar_wait_bounded(bar(BAR_V_EMPTY + ((j - 1) % STAGES)), (uint32_t)(((j - 1) / STAGES) & 1), abort_flag)) { fail_code = 11; break; }
-          load_v(j - 1 + STAGES);
-        }
-        if (!mbar_wait_bounded(bar(BAR_V_FULL + s), ph, abort_flag)) { fail_code = 24; break; }
-        tc_fence_after();
-        bool fine = true;
-        #pragma unroll
-        for (int t = 0; t < TILES; ++t) {
-          if (fine && j < n_tile[t]) {
-            if (!mbar_wait_bounded(bar(BAR_P_FULL + t), (uint32_t)(j & 1), abort_flag)) { fail_code = 22; fine = false; }
-            else {
-              tc_fence_after();
-              // V tile is [BN keys][64 dims], dims contiguous: an MN-major B operand.  8 keys x 128 B
-              // per swizzle group (1024 B, the stride byte offset); each K=16 step covers two groups.
-              #pragma unroll
-              for (int k = 0; k < BN / 16; ++k) {
-                const uint64_t dv = make_smem_desc_sw128(sV + s * KV_BYTES + k * 2048, 16, 1024);
-                umma_ts(tmem + t * TILE_COLS + COL_O, tmem + t * TILE_COLS + COL_P + k * 8, dv, IDESC_PV,
-                        (j > 0 || k > 0) ? 1u : 0u);
-              }
-              tc_commit(bar(BAR_O_DONE + t));
-            }
+        if (t == 0) {
+          // refill the ring: K(j+STAGES) into the slot of K(j) (the Q K^T of step j were issued a
+          // step ago), V(j-1+STAGES) into the slot of V(j-1) (its products were issued a step ago)
+          if (j + STAGES < n_max) {
+            if (!mbar_wait_bounded(bar(BAR_K_EMPTY + s), ph, abort_flag)) { fail_code = 10; return false; }
+            load_k(j + STAGES);
+          }
+          if (j >= 1 && j - 1 + STAGES < n_max) {
+            if (!mbar_wait_bounded(bar(BAR_V_EMPTY + sp), (uint32_t)(((j - 1) / STAGES) & 1), abort_flag)) { fail_code = 11; return false; }
+            load_v(j - 1 + STAGES);
           }
         }
-        if (!fine) break;
+        if (!mbar_wait_bounded(bar(BAR_V_FULL + s), ph, abort_flag)) { fail_code = 24; return false; }
+        tc_fence_after();
+        if (j < n_t) {
+          if (!mbar_wait_bounded(bar(BAR_P_FULL + t), (uint32_t)(j & 1), abort_flag)) { fail_code = 22; return false; }
+          tc_fence_after();
+          // V tile is [BN keys][64 dims], dims contiguous: an MN-major B operand.  8 keys x 128 B
+          // per swizzle group (1024 B, the stride byte offset); each K=16 step covers two groups.
+          #pragma unroll
+          for (int k = 0; k < BN / 16; ++k) {
+            const uint64_t dv = make_smem_desc_sw128(sV + s * KV_BYTES + k * 2048, 16, 1024);
+            umma_ts(tm + COL_O, tm + COL_P + k * 8, dv, IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(bar(BAR_O_DONE + t));
+        }
         tc_commit(bar(BAR_V_EMPTY + s));
+        return true;
+      };
+      static_assert(STAGES == 3, "the loop below is written out for three ring slots");
+      for (int j = 0; ok && j < n_max; j += STAGES) {
+        ok = step(j, std::integral_constant<int, 0>{});
+        if (ok && j + 1 < n_max) ok = step(j + 1, std::integral_constant<int, 1>{});
+        if (ok && j + 2 < n_max) ok = step(j + 2, std::integral_constant<int, 2>{});
       }
     }
   } else {

@@ -334,12 +334,15 @@ extern "C" int64_t t5b_decode_workspace_bytes(int B, int H, int M, int D, int nu
          decode::align256(bh * num_splits * M * (int64_t)D * 4);
 }
 
-extern "C" int t5b_decode_fwd(const t5b_decode_args* a, void* stream) {
+// Argument checks shared by both entry points; on T5B_OK `*splits` holds the split count and
+// `*empty` says that there is nothing to launch.
+static int decode_validate(const t5b_decode_args* a, BucketSpec* spec, int* splits, bool* empty) {
+  *empty = false;
   if (!a || !a->q || !a->k || !a->v || !a->out) return T5B_ERR_ARG;
   if (a->B < 0 || a->H < 0 || a->M < 0 || a->N < 0) return T5B_ERR_SHAPE;
   if (a->D != 16 && a->D != 32 && a->D != 64 && a->D != 128) return T5B_ERR_HEAD_DIM;
   if (a->dtype != T5B_F32 && a->dtype != T5B_F16 && a->dtype != T5B_BF16) return T5B_ERR_DTYPE;
-  if (a->B == 0 || a->H == 0 || a->M == 0) return T5B_OK;
+  if (a->B == 0 || a->H == 0 || a->M == 0) { *empty = true; return T5B_OK; }
   if (a->H > 65535 || a->B > 65535) return T5B_ERR_SHAPE;
   const int es = dtype_bytes(a->dtype);
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
@@ -347,18 +350,26 @@ extern "C" int t5b_decode_fwd(const t5b_decode_args* a, void* stream) {
   const int64_t strides[] = {a->k_stride_b, a->k_stride_h, a->k_stride_n,
                              a->v_stride_b, a->v_stride_h, a->v_stride_n};
   for (int64_t s : strides) if ((s * es) % 16 != 0) return T5B_ERR_ALIGN;
-
-  BucketSpec spec;
-  spec.n_side = 2; spec.bidirectional = 0; spec.max_distance = 1; spec.n_first = 0;
+  spec->n_side = 2; spec->bidirectional = 0; spec->max_distance = 1; spec->n_first = 0;
   if (a->table) {
     if (a->table_dtype != T5B_F32 && a->table_dtype != T5B_F16 && a->table_dtype != T5B_BF16) return T5B_ERR_DTYPE;
-    int st = make_bucket_spec(a->num_buckets, a->max_distance, a->causal ? 0 : 1, &spec);
+    int st = make_bucket_spec(a->num_buckets, a->max_distance, a->causal ? 0 : 1, spec);
     if (st != T5B_OK) return st;
-    if (spec.max_distance > 2048) return T5B_ERR_UNSUPPORTED;
+    if (spec->max_distance > 2048) return T5B_ERR_UNSUPPORTED;
   }
-  int splits = a->num_splits > 0 ? a->num_splits : t5b_decode_num_splits(a->B, a->H, a->N);
-  if (splits > 256) return T5B_ERR_ARG;
-  if (a->N == 0) splits = 1;
+  int n = a->num_splits > 0 ? a->num_splits : t5b_decode_num_splits(a->B, a->H, a->N);
+  if (n > 256) return T5B_ERR_ARG;
+  if (a->N == 0) n = 1;
+  *splits = n;
+  return T5B_OK;
+}
+
+extern "C" int t5b_decode_fwd(const t5b_decode_args* a, void* stream) {
+  BucketSpec spec;
+  int splits = 1;
+  bool empty = false;
+  const int vst = decode_validate(a, &spec, &splits, &empty);
+  if (vst != T5B_OK || empty) return vst;
 
   decode::Params p;
   p.q = a->q; p.k = a->k; p.v = a->v; p.out = a->out; p.table = a->table; p.seqlens_k = a->seqlens_k;
@@ -407,7 +418,9 @@ extern "C" int t5b_decode_fwd(const t5b_decode_args* a, void* stream) {
 // current) on the first call made on that device; make that first call before
 // starting any stream capture.  All calls share the one array: the split counters
 // at its front are cleared on the stream before every launch, and two calls
-// whose kernels overlap on the GPU (different streams) would race on it.
+// whose kernels overlap on the GPU (different streams) would race on it.  The
+// looked-up address is kept for the life of the process: after cudaDeviceReset
+// it is stale, and this entry point must not be used again in that process.
 constexpr long long kStaticScratchBytes = 4ll << 20;   // 4 MiB
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
@@ -435,10 +448,12 @@ static void* static_scratch_address(int* status) {
 extern "C" int64_t t5b_decode_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
 extern "C" int t5b_decode_fwd_static_scratch(const t5b_decode_args* a, void* stream) {
-  if (!a) return T5B_ERR_ARG;
-  if (a->B < 0 || a->H < 0 || a->M < 0 || a->N < 0) return T5B_ERR_SHAPE;
-  int splits = a->num_splits > 0 ? a->num_splits : t5b_decode_num_splits(a->B, a->H, a->N);
-  if (a->N == 0) splits = 1;
+  // every argument check comes first: a refused call leaves the shared array untouched
+  BucketSpec spec;
+  int splits = 1;
+  bool empty = false;
+  const int vst = decode_validate(a, &spec, &splits, &empty);
+  if (vst != T5B_OK || empty) return vst;
   t5b_decode_args b = *a;
   b.num_splits = splits;
   b.workspace = nullptr;
