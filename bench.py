@@ -228,6 +228,13 @@ def main():
     ap.add_argument("--train", action="store_true",
                     help="time forward + backward of the same workload (the training step of the attention core) "
                          "instead of the forward: a second workload, used for the backward kernels' profile")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "tcgen05", "tcgen05_2tile", "tcgen05_polyexp", "simt"],
+                    help="kernel of the attention step (default: the library's choice); the others exist for "
+                         "comparisons and profiles")
+    ap.add_argument("--workload", default="attention", choices=["attention", "encoder", "token_kernels"],
+                    help="attention: the headline step.  encoder / token_kernels: second workloads on one GPU, used "
+                         "for profiles -- a fused T5-base encoder pass over 2 x 8192 tokens per step, or one launch "
+                         "each of the token-wise kernels (RMSNorm, residual add + RMSNorm, gated GELU, merge) per step")
     ap.add_argument("--head-dim", type=int, default=64, choices=[64, 128],
                     help="64: the headline workload; 128: the same workload at the T5-3B/11B head size "
                          "(a second tile geometry of the kernel; used for its profile)")
@@ -254,7 +261,13 @@ def main():
         _keep_stdout_for_json()
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.workload != "attention":
+        side_workload(args, t5b, dev)
+        return
+
     w = dict(WORKLOAD)
+    if args.kernel != "auto":
+        w["name"] += f" (kernel={args.kernel})"
     if args.head_dim != w["D"]:
         w.update(D=args.head_dim, name=f"fused-bias attention fwd, 12 heads of dim {args.head_dim} @8k")
     B, H, L, D = w["B"], w["H"], w["L"], w["D"]
@@ -281,7 +294,8 @@ def main():
     def step(i):
         q, k, v = sets[i % n_sets]
         o_ = t5b.flash_attention_with_fusing_bias(q, k, v, table, causal=False, sm_scale=1.0,
-                                                  NUM_BUCKETS=w["num_buckets"], MAX_DISTANCE=w["max_distance"])
+                                                  NUM_BUCKETS=w["num_buckets"], MAX_DISTANCE=w["max_distance"],
+                                                  kernel=args.kernel)
         if args.train:
             torch.autograd.grad(o_, (q, k, v, table), dout)     # gradients only: no accumulation kernels in the step
         return o_
@@ -419,6 +433,60 @@ def main():
         _emit(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+def token_kernel_measurements(t5b, dev, iters=30):
+    """HBM-bound token-wise kernels at T5-base sizes (100 000 tokens: every operand larger than L2 or
+    rotated out by the others): algorithmic bytes / device time."""
+    from turbot5_b200.attention import merge_attention_partials
+    peaks = measured_peaks()
+    dt = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(11)
+    rows, d, f = 100000, 768, 2048
+    out = {}
+    x = torch.randn((rows, d), generator=g, device=dev).to(dt)
+    br = torch.randn((rows, d), generator=g, device=dev).to(dt)
+    wgt = torch.rand((d,), generator=g, device=dev).to(dt)
+    steps = {}
+    steps["rmsnorm_100000x768_bf16"] = (lambda: t5b.rms_layer_norm(x, wgt, 1e-6), 2 * rows * d * 2 + d * 2)
+    steps["add_rmsnorm_100000x768_bf16"] = (lambda: t5b.add_rms_layer_norm(x, br, wgt, 1e-6), 4 * rows * d * 2 + d * 2)
+    h = torch.randn((rows, 2 * f), generator=g, device=dev).to(dt)
+    steps["gated_gelu_100000x2048_bf16"] = (lambda: t5b.gated_gelu(h), 3 * rows * f * 2)
+    M = 12500
+    parts = [(torch.randn((1, M, 12, 64), generator=g, device=dev).transpose(1, 2),
+              torch.randn((1, 12, M), generator=g, device=dev) + 20.0) for _ in range(3)]
+    steps["merge_3_partials_12500x12x64"] = (lambda: merge_attention_partials(parts, dt),
+                                             3 * M * 12 * 64 * 4 + 3 * M * 12 * 4 + M * 12 * 64 * 2)
+    for name, (fn, nbytes) in steps.items():
+        ms = _time(fn, iters)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"], "algorithmic_bytes": nbytes}
+    return out, steps
+
+
+def side_workload(args, t5b, dev):
+    """Second workloads for profiles (one GPU): see --workload."""
+    peaks = measured_peaks()
+    dt = torch.bfloat16
+    if args.workload == "encoder":
+        from turbot5_b200.t5 import T5Stack, T5StackConfig
+        cfg = T5StackConfig()
+        torch.manual_seed(0)
+        enc = T5Stack(cfg, torch.nn.Embedding(cfg.vocab_size, cfg.d_model), is_decoder=False).to(dev).to(dt).eval()
+        ids = torch.randint(0, cfg.vocab_size, (2, 8192), generator=torch.Generator().manual_seed(0)).to(dev)
+        ms = _time(lambda: enc.forward_fused(ids), args.steps, warm=args.warmup)
+        _emit({"metric": "t5_base_encoder_fwd_tokens_per_s", "value": 2 * 8192 / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+               "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16",
+               "data": "synthetic", "config": {"workload": "fused T5-base encoder pass, 2 x 8192 tokens, 12 layers"}})
+    else:
+        res, _ = token_kernel_measurements(t5b, dev, iters=args.steps)
+        _emit({"metric": "token_kernels_GBps", "value": res["add_rmsnorm_100000x768_bf16"]["GB/s"], "unit": "GB/s",
+               "n_gpus": 1, "steps": args.steps, "warmup": 3, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+               "config": {"workload": "token-wise kernels at 100 000 x 768 (T5-base) bf16"},
+               "roofline": {"bound": "hbm", "achieved": res["add_rmsnorm_100000x768_bf16"]["GB/s"], "peak": peaks["hbm"],
+                            "unit": "GB/s", "frac": res["add_rmsnorm_100000x768_bf16"]["frac_of_hbm_peak"],
+                            "kernel": "add_rmsnorm_kernel"},
+               "kernels": res})
 
 
 def _time(fn, iters, warm=3):
@@ -617,13 +685,9 @@ def secondary_measurements(t5b, dev):
     dt = torch.bfloat16
     peaks = measured_peaks()
     g = torch.Generator(device=dev).manual_seed(7)
-    # RMSNorm, 100000 x 768 bf16 rows (2 x 154 MB traffic > L2)
-    x = torch.randn((100000, 768), generator=g, device=dev).to(dt)
-    wgt = torch.rand((768,), generator=g, device=dev).to(dt)
-    ms = _time(lambda: t5b.rms_layer_norm(x, wgt, 1e-6), 50)
-    gbs = (2 * x.numel() * 2 + 768 * 2) / (ms * 1e-3) / 1e9
-    out["rmsnorm_100000x768_bf16"] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"]}
-    del x
+    # token-wise kernels at 100000 x 768 bf16 (operands larger than L2)
+    tk, _ = token_kernel_measurements(t5b, dev)
+    out.update(tk)
     # split-KV decoding, one cross-attention layer of the T5-large decode shape: B 64, H 16, N 8192
     Bd, Hd, Nd = 64, 16, 8192
     kc = torch.randn((Bd, Hd, Nd, 64), generator=g, device=dev, dtype=torch.float32).to(dt)
@@ -645,8 +709,17 @@ def secondary_measurements(t5b, dev):
     ms = _time(lambda: t5b.flash_attention_with_fusing_bias_varlen(qkv[0], qkv[1], qkv[2], table, cu_d, cu_d, mx, mx,
                                                                    sm_scale=1.0), 20)
     fl = float((4 * 12 * 64 * lens.double() ** 2).sum())
+    # host time of one call (Python wrapper + launch, no synchronisation): the reference builds its
+    # work list in a Python loop with a device read per sequence on every call
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(50):
+        t5b.flash_attention_with_fusing_bias_varlen(qkv[0], qkv[1], qkv[2], table, cu_d, cu_d, mx, mx, sm_scale=1.0)
+    host_us = (time.perf_counter() - t0) / 50 * 1e6
+    torch.cuda.synchronize()
     out["varlen_32seq_128to4096"] = {"ms": ms, "TFLOP/s": fl / (ms * 1e-3) / 1e12, "tokens": T,
-                                     "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"]}
+                                     "frac_of_bf16_peak": fl / (ms * 1e-3) / 1e12 / peaks["tflops"],
+                                     "host_us_per_call": host_us}
     del qkv
     # training step of the attention core at the headline shape: forward + backward (dQ, dK, dV and the
     # bias-table gradient).  FLOPs counted as the 5 matrix products a backward needs (2.5 x forward) plus

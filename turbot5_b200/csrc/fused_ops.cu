@@ -45,6 +45,15 @@ static int sm_count() {
   return n;
 }
 
+// Grid for a grid-stride kernel with `work` block-sized pieces when the GPU holds `cap` blocks at
+// once: every block makes the same number of rounds (no thin last round).
+static int64_t balanced_blocks(int64_t work, int64_t cap) {
+  if (work < 1) return 1;
+  if (work <= cap) return work;
+  const int64_t rounds = (work + cap - 1) / cap;
+  return (work + rounds - 1) / rounds;
+}
+
 // ---------------------------------------------------------------- residual add + RMSNorm
 // A warp owns a row at a time (grid stride) and keeps the summed row in registers between the
 // sum of squares and the scaling.  T: 16-bit element type of hidden, branch and both outputs;
@@ -111,10 +120,8 @@ static int launch_add_rmsnorm(const void* hidden, const void* branch, const void
                               int64_t rows, int d, int64_t hs, int64_t bs, int64_t hos, int64_t ns, float eps,
                               cudaStream_t stream) {
   const int vpl = (d / 8 + 31) / 32;
-  int64_t blocks = (rows + 7) / 8;                       // 8 warps per block, a row per warp
-  const int64_t cap = (int64_t)sm_count() * 8;           // then grid-stride
-  if (blocks > cap) blocks = cap;
-  if (blocks < 1) blocks = 1;
+  // 8 warps per block, a row per warp; 8 blocks per SM at once, then grid-stride
+  const int64_t blocks = balanced_blocks((rows + 7) / 8, (int64_t)sm_count() * 8);
 #define T5B_AR_LAUNCH(V) add_rmsnorm_kernel<T, TW, V><<<(unsigned)blocks, 256, 0, stream>>>( \
       (const T*)hidden, (const T*)branch, (const TW*)w, (T*)hidden_out, (T*)normed, rows, d, hs, bs, hos, ns, eps)
   if (vpl <= 1) T5B_AR_LAUNCH(1);
@@ -256,9 +263,7 @@ extern "C" int t5b_gated_gelu_fwd(const void* x, void* out, int64_t rows, int32_
   if (d_ff % 8 != 0) return T5B_ERR_SHAPE;
   if ((((uintptr_t)x | (uintptr_t)out) & 15) != 0 || ((x_stride | out_stride) % 8) != 0) return T5B_ERR_ALIGN;
   const int64_t total = rows * (d_ff / 8);
-  int64_t blocks = (total + 255) / 256;
-  const int64_t cap = (int64_t)t5b::fused::sm_count() * 16;
-  if (blocks > cap) blocks = cap;
+  const int64_t blocks = t5b::fused::balanced_blocks((total + 255) / 256, (int64_t)t5b::fused::sm_count() * 8);
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == T5B_BF16)
     t5b::fused::gated_gelu_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out,
@@ -290,9 +295,7 @@ extern "C" int t5b_attention_merge(const t5b_merge_args* a, void* stream) {
   p.o_stride_b = a->o_stride_b; p.o_stride_h = a->o_stride_h; p.o_stride_m = a->o_stride_m;
   p.n_parts = a->n_parts; p.B = a->B; p.H = a->H; p.M = a->M; p.D = a->D;
   const int64_t total = (int64_t)a->B * a->H * a->M * (a->D / 4);
-  int64_t blocks = (total + 255) / 256;
-  const int64_t cap = (int64_t)t5b::fused::sm_count() * 16;
-  if (blocks > cap) blocks = cap;
+  const int64_t blocks = t5b::fused::balanced_blocks((total + 255) / 256, (int64_t)t5b::fused::sm_count() * 8);
   cudaStream_t st = (cudaStream_t)stream;
   if (a->out_dtype == T5B_BF16) t5b::fused::merge_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(p);
   else if (a->out_dtype == T5B_F16) t5b::fused::merge_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(p);
