@@ -45,6 +45,19 @@ static int sm_count() {
   return n;
 }
 
+// Blocks of `threads` threads of kernel `fn` that the current GPU holds at once; the answer depends
+// on the registers the compiler gave the kernel and is kept in `per_sm`, a static of the call site
+// (one per kernel instantiation).
+template <typename Fn>
+static int64_t resident_blocks(Fn fn, int threads, std::atomic<int>& per_sm) {
+  int n = per_sm.load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, threads, 0) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 1; }
+    per_sm.store(n, std::memory_order_relaxed);
+  }
+  return (int64_t)n * sm_count();
+}
+
 // Grid for a grid-stride kernel with `work` block-sized pieces when the GPU holds `cap` blocks at
 // once: every block makes the same number of rounds (no thin last round).
 static int64_t balanced_blocks(int64_t work, int64_t cap) {
@@ -120,10 +133,13 @@ static int launch_add_rmsnorm(const void* hidden, const void* branch, const void
                               int64_t rows, int d, int64_t hs, int64_t bs, int64_t hos, int64_t ns, float eps,
                               cudaStream_t stream) {
   const int vpl = (d / 8 + 31) / 32;
-  // 8 warps per block, a row per warp; 8 blocks per SM at once, then grid-stride
-  const int64_t blocks = balanced_blocks((rows + 7) / 8, (int64_t)sm_count() * 8);
-#define T5B_AR_LAUNCH(V) add_rmsnorm_kernel<T, TW, V><<<(unsigned)blocks, 256, 0, stream>>>( \
-      (const T*)hidden, (const T*)branch, (const TW*)w, (T*)hidden_out, (T*)normed, rows, d, hs, bs, hos, ns, eps)
+  // 8 warps per block, a row per warp; as many blocks as the GPU holds at once, then grid-stride
+#define T5B_AR_LAUNCH(V) do { \
+    auto kern = add_rmsnorm_kernel<T, TW, V>; \
+    static std::atomic<int> per_sm{0}; \
+    const int64_t blocks = balanced_blocks((rows + 7) / 8, resident_blocks(kern, 256, per_sm)); \
+    kern<<<(unsigned)blocks, 256, 0, stream>>>((const T*)hidden, (const T*)branch, (const TW*)w, (T*)hidden_out, \
+                                               (T*)normed, rows, d, hs, bs, hos, ns, eps); } while (0)
   if (vpl <= 1) T5B_AR_LAUNCH(1);
   else if (vpl == 2) T5B_AR_LAUNCH(2);
   else if (vpl == 3) T5B_AR_LAUNCH(3);
@@ -142,26 +158,46 @@ __device__ __forceinline__ float gelu_tanh(float a) {
   return a * __frcp_rn(1.f + fast_exp2(-u2 * kLog2e));
 }
 
+// A warp walks whole rows (grid stride), its lanes the 16-byte vectors of a row, two vectors of each
+// half in flight per lane.
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_gelu_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, int f, int64_t xs, int64_t os) {
-  const int vec_per_row = f / 8;
-  const int64_t total = rows * vec_per_row;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / vec_per_row;
-    const int v = (int)(i - row * vec_per_row);
-    const uint4 a4 = ld16(x + row * xs + v * 8);
-    const uint4 b4 = ld16(x + row * xs + f + v * 8);
-    const T* ea = reinterpret_cast<const T*>(&a4);
-    const T* eb = reinterpret_cast<const T*>(&b4);
-    uint4 o4;
-    T* eo = reinterpret_cast<T*>(&o4);
-    #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float g = to_float<T>(from_float<T>(gelu_tanh(to_float<T>(ea[k]))));   // the activation, rounded
-      eo[k] = from_float<T>(g * to_float<T>(eb[k]));
+  const int lane = threadIdx.x & 31;
+  const int nvec = f / 8;
+  const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t row = warp_id; row < rows; row += n_warps) {
+    const T* xr = x + row * xs;
+    T* orow = out + row * os;
+    for (int v0 = lane; v0 < nvec; v0 += 64) {
+      const int v1 = v0 + 32;
+      const bool two = v1 < nvec;
+      const uint4 a0 = ld16(xr + v0 * 8), b0 = ld16(xr + f + v0 * 8);
+      uint4 a1 = make_uint4(0, 0, 0, 0), b1 = make_uint4(0, 0, 0, 0);
+      if (two) { a1 = ld16(xr + v1 * 8); b1 = ld16(xr + f + v1 * 8); }
+      uint4 o0, o1;
+      const T* ea = reinterpret_cast<const T*>(&a0);
+      const T* eb = reinterpret_cast<const T*>(&b0);
+      T* eo = reinterpret_cast<T*>(&o0);
+      #pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float g = to_float<T>(from_float<T>(gelu_tanh(to_float<T>(ea[k]))));   // the activation, rounded
+        eo[k] = from_float<T>(g * to_float<T>(eb[k]));
+      }
+      st16(orow + v0 * 8, o0);
+      if (two) {
+        ea = reinterpret_cast<const T*>(&a1);
+        eb = reinterpret_cast<const T*>(&b1);
+        eo = reinterpret_cast<T*>(&o1);
+        #pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float g = to_float<T>(from_float<T>(gelu_tanh(to_float<T>(ea[k]))));
+          eo[k] = from_float<T>(g * to_float<T>(eb[k]));
+        }
+        st16(orow + v1 * 8, o1);
+      }
     }
-    st16(out + row * os + v * 8, o4);
   }
 }
 
@@ -178,19 +214,19 @@ struct MergeParams {
   int32_t n_parts, B, H, M, D;
 };
 
-// One thread per (batch, head, row, 4 dims).
+// One thread per (row, 4 dims); blockIdx.y = batch * H + head, blockIdx.x walks the rows in pieces
+// of 256 / (D / 4) (D / 4 is a power of two).
 template <typename TO>
 __global__ void __launch_bounds__(256)
-merge_kernel(const __grid_constant__ MergeParams p) {
-  const int vec = p.D / 4;
-  const int64_t total = (int64_t)p.B * p.H * p.M * vec;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int c = (int)(i % vec);
-    const int64_t r = i / vec;                 // (b * H + h) * M + m
-    const int m = (int)(r % p.M);
-    const int64_t bh = r / p.M;
-    const int h = (int)(bh % p.H);
-    const int64_t b = bh / p.H;
+merge_kernel(const __grid_constant__ MergeParams p, int vec_shift) {
+  const int vec = 1 << vec_shift;
+  const int c = threadIdx.x & (vec - 1);
+  const int rows_per_block = 256 >> vec_shift;
+  const int bh = blockIdx.y;
+  const int h = bh % p.H;
+  const int64_t b = bh / p.H;
+  for (int m = blockIdx.x * rows_per_block + (threadIdx.x >> vec_shift); m < p.M; m += gridDim.x * rows_per_block) {
+    const int64_t r = (int64_t)bh * p.M + m;
     float lse[kMaxParts];
     float mx = -INFINITY;
     #pragma unroll
@@ -216,7 +252,14 @@ merge_kernel(const __grid_constant__ MergeParams p) {
       acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
     }
     TO* o = reinterpret_cast<TO*>(p.out) + b * p.o_stride_b + h * p.o_stride_h + (int64_t)m * p.o_stride_m + c * 4;
-    o[0] = from_float<TO>(acc.x); o[1] = from_float<TO>(acc.y); o[2] = from_float<TO>(acc.z); o[3] = from_float<TO>(acc.w);
+    if (sizeof(TO) == 2) {
+      uint2 w2;
+      TO* e = reinterpret_cast<TO*>(&w2);
+      e[0] = from_float<TO>(acc.x); e[1] = from_float<TO>(acc.y); e[2] = from_float<TO>(acc.z); e[3] = from_float<TO>(acc.w);
+      *reinterpret_cast<uint2*>(o) = w2;
+    } else {
+      o[0] = from_float<TO>(acc.x); o[1] = from_float<TO>(acc.y); o[2] = from_float<TO>(acc.z); o[3] = from_float<TO>(acc.w);
+    }
     if (p.lse_out != nullptr && c == 0) p.lse_out[r] = mx > -INFINITY ? mx + __logf(wsum) : -INFINITY;
   }
 }
@@ -262,15 +305,19 @@ extern "C" int t5b_gated_gelu_fwd(const void* x, void* out, int64_t rows, int32_
   if (dtype != T5B_BF16 && dtype != T5B_F16) return T5B_ERR_DTYPE;
   if (d_ff % 8 != 0) return T5B_ERR_SHAPE;
   if ((((uintptr_t)x | (uintptr_t)out) & 15) != 0 || ((x_stride | out_stride) % 8) != 0) return T5B_ERR_ALIGN;
-  const int64_t total = rows * (d_ff / 8);
-  const int64_t blocks = t5b::fused::balanced_blocks((total + 255) / 256, (int64_t)t5b::fused::sm_count() * 8);
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == T5B_BF16)
-    t5b::fused::gated_gelu_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out,
-                                                                                    rows, d_ff, x_stride, out_stride);
-  else
-    t5b::fused::gated_gelu_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>((const __half*)x, (__half*)out, rows, d_ff,
-                                                                            x_stride, out_stride);
+  using namespace t5b::fused;
+  if (dtype == T5B_BF16) {
+    auto kern = gated_gelu_kernel<__nv_bfloat16>;
+    static std::atomic<int> per_sm{0};
+    const int64_t blocks = balanced_blocks((rows + 7) / 8, resident_blocks(kern, 256, per_sm));
+    kern<<<(unsigned)blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, d_ff, x_stride, out_stride);
+  } else {
+    auto kern = gated_gelu_kernel<__half>;
+    static std::atomic<int> per_sm{0};
+    const int64_t blocks = balanced_blocks((rows + 7) / 8, resident_blocks(kern, 256, per_sm));
+    kern<<<(unsigned)blocks, 256, 0, st>>>((const __half*)x, (__half*)out, rows, d_ff, x_stride, out_stride);
+  }
   return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;
 }
 
@@ -294,11 +341,21 @@ extern "C" int t5b_attention_merge(const t5b_merge_args* a, void* stream) {
   p.po_stride_b = a->part_stride_b; p.po_stride_h = a->part_stride_h; p.po_stride_m = a->part_stride_m;
   p.o_stride_b = a->o_stride_b; p.o_stride_h = a->o_stride_h; p.o_stride_m = a->o_stride_m;
   p.n_parts = a->n_parts; p.B = a->B; p.H = a->H; p.M = a->M; p.D = a->D;
-  const int64_t total = (int64_t)a->B * a->H * a->M * (a->D / 4);
-  const int64_t blocks = t5b::fused::balanced_blocks((total + 255) / 256, (int64_t)t5b::fused::sm_count() * 8);
+  const int vec = a->D / 4;
+  if ((vec & (vec - 1)) != 0 || vec > 256) return T5B_ERR_HEAD_DIM;        // D / 4 a power of two
+  int vec_shift = 0;
+  while ((1 << vec_shift) < vec) ++vec_shift;
+  if (((a->o_stride_b | a->o_stride_h | a->o_stride_m) % 4) != 0 || ((uintptr_t)a->out & 7) != 0) return T5B_ERR_ALIGN;
+  const int64_t bh = (int64_t)a->B * a->H;
+  if (bh > 65535) return T5B_ERR_SHAPE;
+  const int rows_per_block = 256 >> vec_shift;
+  int64_t gx = ((int64_t)a->M + rows_per_block - 1) / rows_per_block;
+  const int64_t per_bh = (8LL * t5b::fused::sm_count() + bh - 1) / bh;     // about eight blocks per SM in all
+  if (gx > per_bh) gx = t5b::fused::balanced_blocks(gx, per_bh);
+  dim3 grid((unsigned)gx, (unsigned)bh, 1);
   cudaStream_t st = (cudaStream_t)stream;
-  if (a->out_dtype == T5B_BF16) t5b::fused::merge_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, st>>>(p);
-  else if (a->out_dtype == T5B_F16) t5b::fused::merge_kernel<__half><<<(unsigned)blocks, 256, 0, st>>>(p);
-  else t5b::fused::merge_kernel<float><<<(unsigned)blocks, 256, 0, st>>>(p);
+  if (a->out_dtype == T5B_BF16) t5b::fused::merge_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, vec_shift);
+  else if (a->out_dtype == T5B_F16) t5b::fused::merge_kernel<__half><<<grid, 256, 0, st>>>(p, vec_shift);
+  else t5b::fused::merge_kernel<float><<<grid, 256, 0, st>>>(p, vec_shift);
   return cudaGetLastError() == cudaSuccess ? T5B_OK : T5B_ERR_LAUNCH;
 }

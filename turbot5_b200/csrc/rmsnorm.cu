@@ -10,6 +10,7 @@
 // result stays float32.
 #include "t5b_common.cuh"
 
+#include <atomic>
 #include <type_traits>
 
 namespace t5b {
@@ -123,17 +124,24 @@ static int launch(const void* x, const void* w, void* y, float* rstd, int64_t ro
   if (vec) {
     const int vpl = (d / VX + 31) / 32;
     constexpr int ROWS = 2;
-    int64_t blocks = (rows + WARPS * ROWS - 1) / (WARPS * ROWS);
-    // Beyond what the GPU holds at once (16 blocks of 4 warps per SM) the warps walk the rows with a
-    // grid stride.  The grid is then shrunk so that every block makes the SAME number of rounds: with
-    // the plain cap 100 000 rows were 5.28 rounds, i.e. a sixth round at a quarter of the bandwidth.
-    const int64_t cap = 148 * 16;
-    if (blocks > cap) {
-      const int64_t rounds = (blocks + cap - 1) / cap;
-      blocks = (blocks + rounds - 1) / rounds;
-    }
-#define T5B_RMS_LAUNCH(V) rmsnorm_vec_kernel<TX, TW, TY, V, ROWS><<<(unsigned)blocks, WARPS * 32, 0, stream>>>( \
-        xp, wp, yp, rstd, rows, d, xs, ys, eps)
+    // Beyond what the GPU holds at once the warps walk the rows with a grid stride, and the grid is
+    // shrunk so that every block makes the SAME number of rounds (no thin last round: with a fixed
+    // cap 100 000 rows ran a last round at a fraction of the bandwidth).  How many blocks fit is
+    // asked per kernel instantiation: it depends on the registers the compiler used.
+#define T5B_RMS_LAUNCH(V) do { \
+      auto kern = rmsnorm_vec_kernel<TX, TW, TY, V, ROWS>; \
+      static std::atomic<int> per_sm{0}; \
+      int n_res = per_sm.load(std::memory_order_relaxed); \
+      if (n_res == 0) { \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n_res, kern, WARPS * 32, 0) != cudaSuccess || n_res <= 0) { cudaGetLastError(); n_res = 1; } \
+        per_sm.store(n_res, std::memory_order_relaxed); \
+      } \
+      int n_sm = 148, dev_ = 0; \
+      if (cudaGetDevice(&dev_) != cudaSuccess || cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev_) != cudaSuccess) { cudaGetLastError(); n_sm = 148; } \
+      int64_t blocks = (rows + WARPS * ROWS - 1) / (WARPS * ROWS); \
+      const int64_t cap = (int64_t)n_res * n_sm; \
+      if (blocks > cap) { const int64_t rounds = (blocks + cap - 1) / cap; blocks = (blocks + rounds - 1) / rounds; } \
+      kern<<<(unsigned)blocks, WARPS * 32, 0, stream>>>(xp, wp, yp, rstd, rows, d, xs, ys, eps); } while (0)
     if (vpl <= 1) T5B_RMS_LAUNCH(1);
     else if (vpl == 2) T5B_RMS_LAUNCH(2);
     else if (vpl == 3) T5B_RMS_LAUNCH(3);
