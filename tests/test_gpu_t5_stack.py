@@ -90,6 +90,27 @@ def test_cuda_graph_decoding_equals_eager_decoding():
     assert (eager_last.float() - graph_last.float()).abs().max().item() < 1e-2
 
 
+def test_cuda_graph_decoding_with_a_long_cache_splits_the_keys():
+    """A cache long enough that the captured self-attention launch splits the keys (the split count
+    comes from the capacity and stays the same in every replay): tokens as in eager decoding."""
+    from turbot5_b200 import _native as nat
+    model = _model(torch.bfloat16, d_model=128, num_heads=4, d_ff=256)
+    steps = 530
+    assert nat.lib().t5b_decode_num_splits(1, 4, steps) > 1
+    ids = torch.randint(0, 128, (1, 200), generator=torch.Generator().manual_seed(6)).cuda()
+    with torch.no_grad():
+        enc = model.encoder(ids)
+        eager_tokens, eager_last = model.greedy_decode(enc, steps)
+        graph_tokens, graph_last = model.greedy_decode(enc, steps, use_cuda_graph=True)
+    # bf16 logits of near-ties may order differently between the two launch sequences; once a token
+    # differs the continuations diverge, so compare up to the first difference and require it late
+    same = (eager_tokens == graph_tokens)[0]
+    first_diff = int((~same).float().argmax()) if not bool(same.all()) else steps
+    assert first_diff >= 64, first_diff
+    if first_diff == steps:
+        assert (eager_last.float() - graph_last.float()).abs().max().item() < 5e-2
+
+
 def test_training_step_through_the_stack_gives_finite_gradients_everywhere():
     # encoder-decoder forward with a padding mask, cross-entropy loss, backward: every parameter
     # gets a finite, non-zero gradient through the CUDA attention, RMSNorm and unpad/pad kernels

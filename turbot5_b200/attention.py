@@ -110,9 +110,14 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
     q, k, v = _unit_stride_last(q), _unit_stride_last(k), _unit_stride_last(v)
     table, tdt, ts0 = _table_args(bias, H)
     out_dtype = torch.float32 if out_f32 else q.dtype
-    out = torch.empty_like(q, dtype=out_dtype)   # preserves q's layout (BHLD view of a BLHD buffer stays free to unshape)
-    if out.stride(-1) != 1:
-        out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
+    if q.stride(3) == 1 and q.stride(1) == D and q.stride(2) >= H * D:
+        # q is a (B,H,M,D) view of token-major rows (a projection output, possibly one slice of a stacked
+        # q|k|v projection): the result is laid out (B,M,H,D) so that merging the heads afterwards is free
+        out = torch.empty((B, M, H, D), dtype=out_dtype, device=q.device).transpose(1, 2)
+    else:
+        out = torch.empty_like(q, dtype=out_dtype)
+        if out.stride(-1) != 1:
+            out = torch.empty(q.shape, dtype=out_dtype, device=q.device)
     lse = torch.empty((B, H, M), dtype=torch.float32, device=q.device) if return_lse else None
     a = nat.AttnArgs()
     a.out_f32 = int(bool(out_f32))

@@ -121,11 +121,14 @@ class T5Block(nn.Module):
 
 class DecoderCache:
     """Preallocated K/V cache of one generation: self-attention keys/values grow in place,
-    cross-attention keys/values are projected once from the encoder output."""
+    cross-attention keys/values are projected once from the encoder output.  Keys and values of a
+    layer's self-attention live in ONE tensor (2, B, H, max_len, D), so that a decoding step appends
+    both with one copy; `self_k[i]` / `self_v[i]` are its two halves."""
 
     def __init__(self, n_layers, batch, heads, d_kv, max_len, dtype, device):
-        self.self_k = [torch.empty((batch, heads, max_len, d_kv), dtype=dtype, device=device) for _ in range(n_layers)]
-        self.self_v = [torch.empty((batch, heads, max_len, d_kv), dtype=dtype, device=device) for _ in range(n_layers)]
+        self.self_kv = [torch.empty((2, batch, heads, max_len, d_kv), dtype=dtype, device=device) for _ in range(n_layers)]
+        self.self_k = [kv[0] for kv in self.self_kv]
+        self.self_v = [kv[1] for kv in self.self_kv]
         self.cross_k: List[Optional[torch.Tensor]] = [None] * n_layers
         self.cross_v: List[Optional[torch.Tensor]] = [None] * n_layers
         self.length = 0
@@ -282,33 +285,70 @@ class T5Stack(nn.Module):
         shape (B,)) the number of cached keys including it; nothing in the launch sequence
         depends on their values, so the step can be captured once in a CUDA graph and replayed
         (the caller advances both tensors between replays).  Returns (B, 1, d_model).
+
+        For 16-bit weights the step is fused like `forward_fused`: one stacked q|k|v projection, one
+        copy that appends the new key and value to the cache, the split-KV kernel, the output
+        projection, residual add + RMSNorm in one kernel -- thirteen launches per layer instead of
+        twenty.
         """
         cfg = self.cfg
         B = input_ids.shape[0]
         H, D = cfg.num_heads, cfg.d_kv
+        HD = H * D
+        nb, md = cfg.relative_attention_num_buckets, cfg.relative_attention_max_distance
+        eps = cfg.layer_norm_epsilon
         hidden = self.embed_tokens(input_ids)
         table = self._table()
+        fused = hidden.dtype in (torch.bfloat16, torch.float16) and cfg.d_model % 8 == 0
         shape = lambda x: x.view(B, 1, H, D).transpose(1, 2)
+        # The split count of the self-attention launch comes from the cache CAPACITY, not from the
+        # current length, so it is the same in every replay (a split beyond the cached keys is empty
+        # and merges as such); a small batch then still fills the GPU late in a long generation.
+        from . import _native as nat
+        self_splits = max(1, nat.lib().t5b_decode_num_splits(B, H, cache.max_len))
+        if fused:
+            hidden = hidden.contiguous()
+            normed = rms_layer_norm(hidden, self.block[0].layer[0].layer_norm.weight, eps)
         for i, blk in enumerate(self.block):
-            sa, ca = blk.layer[0], blk.layer[1]
-            att = sa.SelfAttention
-            normed = sa.layer_norm(hidden).to(hidden.dtype)
-            q = shape(att.q(normed))
-            cache.self_k[i].index_copy_(2, pos, shape(att.k(normed)))
-            cache.self_v[i].index_copy_(2, pos, shape(att.v(normed)))
+            sa, ca, ffl = blk.layer[0], blk.layer[1], blk.layer[-1]
+            att, catt = sa.SelfAttention, ca.EncDecAttention
+            if fused:
+                w = self._stacked_weights(i)
+                qkv = nn.functional.linear(normed, w["qkv"])                       # (B, 1, 3*H*D)
+                q = shape(qkv[..., :HD])
+                # new key and value -> slot `pos` of the stacked cache, one copy: (2, B, H, 1, D)
+                cache.self_kv[i].index_copy_(3, pos, qkv[..., HD:].view(B, 1, 2, H, D).permute(2, 0, 3, 1, 4))
+            else:
+                normed = sa.layer_norm(hidden).to(hidden.dtype)
+                q = shape(att.q(normed))
+                cache.self_k[i].index_copy_(2, pos, shape(att.k(normed)))
+                cache.self_v[i].index_copy_(2, pos, shape(att.v(normed)))
             o = flash_decoding_with_fusing_bias(q, cache.self_k[i], cache.self_v[i], table, causal=True, sm_scale=1.0,
-                                                NUM_BUCKETS=cfg.relative_attention_num_buckets,
-                                                MAX_DISTANCE=cfg.relative_attention_max_distance, seqlens_k=seqlens,
-                                                num_splits=1)
-            hidden = hidden + att.o(o.transpose(1, 2).reshape(B, 1, H * D))
-            catt = ca.EncDecAttention
-            normed = ca.layer_norm(hidden).to(hidden.dtype)
+                                                NUM_BUCKETS=nb, MAX_DISTANCE=md, seqlens_k=seqlens,
+                                                num_splits=self_splits)
+            o = att.o(o.transpose(1, 2).reshape(B, 1, HD))
+            if fused:
+                hidden, normed = add_rms_layer_norm(hidden, o, ca.layer_norm.weight, eps, inplace=True)
+            else:
+                hidden = hidden + o
+                normed = ca.layer_norm(hidden).to(hidden.dtype)
             q = shape(catt.q(normed))
             o = flash_decoding_with_fusing_bias(q, cache.cross_k[i], cache.cross_v[i], None, causal=False,
                                                 sm_scale=1.0, seqlens_k=encoder_seqlens, q_pos_offset=0)
-            hidden = hidden + catt.o(o.transpose(1, 2).reshape(B, 1, H * D))
-            hidden = blk.layer[-1](hidden)
-        return self.final_layer_norm(hidden).to(hidden.dtype)
+            o = catt.o(o.transpose(1, 2).reshape(B, 1, HD))
+            if fused:
+                hidden, normed = add_rms_layer_norm(hidden, o, ffl.layer_norm.weight, eps, inplace=True)
+                ff = ffl.DenseReluDense
+                if "wi" in w:
+                    f = nn.functional.linear(gated_gelu(nn.functional.linear(normed, w["wi"])), ff.wo.weight)
+                else:
+                    f = ff(normed)
+                nxt = self.block[i + 1].layer[0].layer_norm if i + 1 < len(self.block) else self.final_layer_norm
+                hidden, normed = add_rms_layer_norm(hidden, f, nxt.weight, eps, inplace=True)
+            else:
+                hidden = hidden + o
+                hidden = ffl(hidden)
+        return normed if fused else self.final_layer_norm(hidden).to(hidden.dtype)
 
     def decode_step(self, input_ids, cache: DecoderCache, encoder_seqlens=None):
         """One cached step for `input_ids` (B, M) (M new tokens, usually 1); returns (B, M, d_model)."""
@@ -357,8 +397,10 @@ class GraphedDecoding:
     """Greedy generation whose single-token step is one CUDA graph.
 
     The step (all decoder layers, LM head, argmax, token write-back, position update) is run
-    once eagerly on a side stream (so scratch buffers and library workspaces exist), rewound,
-    captured, and rewound again; `step()` then replays it.  The token position and the cached
+    once eagerly on a side stream (cuBLAS handles and stacked weights then exist), rewound,
+    captured, and rewound again; `step()` then replays it.  The library's split scratch is kept
+    per stream: the capture stream gets its own, allocated and zeroed inside the graph's memory
+    pool during capture.  The token position and the cached
     length live in device tensors that the graph itself advances, so no launch argument
     changes between replays.
     """
