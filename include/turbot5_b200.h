@@ -148,6 +148,13 @@ typedef struct {
    * to the element type.  Tensor-core forward kernels only (T5B_ERR_UNSUPPORTED otherwise); pass
    * lse as well, the merge needs it. */
   int32_t out_f32;
+  /* > 0: sliding window -- query at position p sees the keys n with |n - p| < window (and below the
+   * sequence's length).  This is what T5LocalAttention computes when it is given its padding mask
+   * (src/turbot5/model/utils.py:149-155,174-188: the 3-block mask ANDed with |n - m| < block_len):
+   * pack the valid tokens (cu_seqlens) and pass window = block_len.  Dense or packed, not causal,
+   * not combined with local_block; forward only, the one-tile tensor-core kernel
+   * (T5B_ERR_UNSUPPORTED otherwise).  0: off. */
+  int32_t window;
 } t5b_attn_args;
 
 T5B_API int t5b_attention_fwd(const t5b_attn_args* args, void* stream);

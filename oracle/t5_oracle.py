@@ -158,7 +158,8 @@ def attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
 
 
 def local_attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, table: Optional[torch.Tensor],
-                          block_len: int, num_buckets: int = 32, max_distance: int = 128) -> torch.Tensor:
+                          block_len: int, num_buckets: int = 32, max_distance: int = 128,
+                          key_padding_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Block-local attention core of `T5LocalAttention.forward`
     (src/turbot5/model/attentions.py:553-650, helpers src/turbot5/model/utils.py:99-140).
 
@@ -168,6 +169,13 @@ def local_attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tab
     are all-zero blocks that are NOT masked (score = bias only), exactly as the reference
     concatenates them.  Bias: bidirectional buckets of (key position - query position) inside the
     3-block window (`compute_bias(block_len)`, attentions.py:529-551).
+
+    With `key_padding_mask` (raw 0/1 (B, L)) the mask `T5Stack` builds for this module is applied
+    (`_get_local_attention_mask`, src/turbot5/model/utils.py:149-155,174-188; added as -1e10,
+    attentions.py:600-603,619-621): a pair is visible when query and key are both valid AND
+    |key - query| < block_len -- with a mask the three blocks shrink to a sliding window, and the
+    zero blocks beyond the ends are masked.  Rows of padded queries see nothing but -1e10 and come
+    out as the mean of all values in the window (callers compare valid rows only).
     """
     B, H, L, D = q.shape
     bl = block_len if L >= block_len else L
@@ -190,6 +198,14 @@ def local_attention_basic(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tab
         bucket = relative_position_bucket(mem[None, :] - ctx[:, None], True, num_buckets, max_distance)
         bias = table.float()[torch.as_tensor(bucket, dtype=torch.long)]     # (bl, 3bl, H)
         scores = scores + bias.permute(2, 0, 1)[None, :, None]
+    if key_padding_mask is not None:
+        mp = torch.nn.functional.pad(key_padding_mask.float(), (0, pad)).view(B, nblk, bl)
+        z = torch.zeros_like(mp[:, :1])
+        ext = torch.cat([z, mp, z], dim=1)
+        m3 = torch.cat([ext[:, 0:nblk], ext[:, 1:nblk + 1], ext[:, 2:nblk + 2]], dim=2)         # (B, nblk, 3bl)
+        rel = torch.arange(3 * bl)[None, :] - torch.arange(bl, 2 * bl)[:, None]
+        vis = (mp[:, :, :, None] > 0) & (m3[:, :, None, :] > 0) & (rel.abs() < bl)[None, None]   # (B, nblk, bl, 3bl)
+        scores = scores + torch.where(vis, 0.0, -1e10)[:, None]
     out = torch.einsum("bhnqk,bhnkd->bhnqd", torch.softmax(scores, dim=-1), vc)
     return out.reshape(B, H, nblk * bl, D)[:, :, :L]
 

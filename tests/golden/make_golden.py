@@ -16,6 +16,8 @@ Fixtures written:
                    `T5Attention._relative_position_bucket`.
   attention_grad.npz  the same two functions under autograd: gradients of q, k, v and the table
   local.npz        `T5LocalAttention.forward` (block-local attention) with permutation projections
+  local_masked.npz the same module with the padding mask `T5Stack` builds for it
+                   (`_get_local_attention_mask`): right-padded batches
   attention.npz    small seeded q/k/v/table cases through `compute_bias` +
                    `naive_torch_attention_with_bias` (float32 math on bf16-representable
                    inputs, stored as bf16 bit patterns), incl. cached
@@ -75,11 +77,59 @@ def bf16_bits(t):
     return t.bfloat16().view(torch.int16).numpy().view(np.uint16)
 
 
-def main(ref_root: str):
+def make_local_masked(here):
+    """T5LocalAttention.forward with the 5-D mask of T5Stack (src/turbot5/model/modeling.py:488-489,
+    src/turbot5/model/utils.py:174-188) on right-padded batches; permutation projections as in
+    local.npz.  Rows of padded queries are whatever the reference computes there (not compared)."""
+    from turbot5.model.attentions import T5LocalAttention
+    from turbot5.model.config import T5Config
+    from turbot5.model.utils import _get_local_attention_mask
+    local = {}
+    # one sequence per case: the reference module itself fails on batches of several sequences with
+    # several blocks (`shape_blocks` views a transposed tensor, attentions.py:575-576,596)
+    specs = [("locm_ragged", 300, 128, [170]), ("locm_short", 100, 512, [37]), ("locm_even", 512, 256, [300]),
+             ("locm_long", 1100, 384, [650]), ("locm_full", 700, 256, [700])]
+    H, D = 2, 64
+    for name, L, bl, lens in specs:
+        B = len(lens)
+        cfg = T5Config(d_model=H * D, d_kv=D, num_heads=H, relative_attention_num_buckets=32,
+                       relative_attention_max_distance=128, is_decoder=False, dropout_rate=0.0,
+                       tie_word_embeddings=False, sliding_window=bl)
+        cfg.use_triton = False
+        att = T5LocalAttention(cfg, has_relative_attention_bias=True).eval()
+        gperm = torch.Generator().manual_seed(1600 + L)
+        eye = torch.eye(H * D)
+        pk_, pv_ = torch.randperm(H * D, generator=gperm), torch.randperm(H * D, generator=gperm)
+        table = seeded((32, H), 1700 + L, 0.1).bfloat16().float()
+        hidden = seeded((B, L, H * D), 1800 + L).bfloat16().float()
+        mask2d = torch.zeros((B, L))
+        for b, n in enumerate(lens):
+            mask2d[b, :n] = 1
+        mask5d = _get_local_attention_mask(mask2d, bl, hidden.device)
+        with torch.no_grad():
+            att.q.weight.copy_(eye); att.k.weight.copy_(eye[pk_]); att.v.weight.copy_(eye[pv_]); att.o.weight.copy_(eye)
+            att.relative_attention_bias.weight.copy_(table)
+            out = att(hidden, mask=mask5d)[0]
+        local[name + "_hidden"] = bf16_bits(hidden)
+        local[name + "_table"] = bf16_bits(table)
+        local[name + "_kperm"] = pk_.numpy()
+        local[name + "_vperm"] = pv_.numpy()
+        local[name + "_out"] = out.numpy()
+        local[name + "_lens"] = np.asarray(lens, dtype=np.int64)
+        local[name + "_meta"] = np.asarray([B, H, L, D, bl], dtype=np.int64)
+    local["names"] = np.asarray([s_[0] for s_ in specs])
+    np.savez_compressed(os.path.join(here, "local_masked.npz"), **local)
+
+
+def main(ref_root: str, only=None):
     here = os.path.dirname(os.path.abspath(__file__))
     sys.path.insert(0, os.path.join(ref_root, "src"))
     _install_shim()
     torch.manual_seed(0)
+    if only == "local_masked":
+        make_local_masked(here)
+        print("local_masked.npz written to", here)
+        return
     from turbot5.model.attentions import T5Attention
     from turbot5.model.config import T5Config
     from turbot5.model.modules import T5LayerNorm
@@ -250,6 +300,7 @@ def main(ref_root: str):
         local[name + "_meta"] = np.asarray([B, H, L, D, bl], dtype=np.int64)
     local["names"] = np.asarray([s_[0] for s_ in lspecs])
     np.savez_compressed(os.path.join(here, "local.npz"), **local)
+    make_local_masked(here)
 
     rn = {}
     for tag, xdt, wdt in (("f32", torch.float32, torch.float32),
@@ -327,5 +378,5 @@ def main(ref_root: str):
 
 if __name__ == "__main__":
     if len(sys.argv) < 2:
-        raise SystemExit("usage: make_golden.py /path/to/reference")
-    main(sys.argv[1])
+        raise SystemExit("usage: make_golden.py /path/to/reference [local_masked]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) > 2 else None)

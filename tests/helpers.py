@@ -101,3 +101,9 @@ def local_case(z, name):
     v = shape(hidden[..., torch.from_numpy(z[name + "_vperm"])])
     want = torch.from_numpy(z[name + "_out"]).view(B, L, H, D).transpose(1, 2)
     return q, k, v, from_bf16_bits(z[name + "_table"]), bl, want
+
+
+def local_masked_case(z, name):
+    """As `local_case`, plus the valid lengths of the right-padded batch."""
+    q, k, v, table, bl, want = local_case(z, name)
+    return q, k, v, table, bl, want, [int(x) for x in z[name + "_lens"]]

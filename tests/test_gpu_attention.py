@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import t5_oracle as orc
-from tests.helpers import attention_case, check_close, load, local_case, seeded
+from tests.helpers import attention_case, check_close, load, local_case, local_masked_case, seeded
 
 pytestmark = pytest.mark.gpu
 
@@ -464,3 +464,79 @@ def test_block_local_attention_refuses_what_it_cannot_do():
         t5b.flash_attention_with_fusing_bias(q, q, q, None, sm_scale=1.0, local_block=100)
     with pytest.raises(RuntimeError):
         t5b.flash_attention_with_fusing_bias(q.float(), q.float(), q.float(), None, sm_scale=1.0, local_block=128)
+
+
+# ---- T5LocalAttention with its padding mask: a sliding window |n - m| < block over the valid keys
+def _window_oracle(q, k, v, table, bl, lens):
+    mask = torch.zeros((q.shape[0], q.shape[2]))
+    for b, n in enumerate(lens):
+        mask[b, :n] = 1
+    return orc.local_attention_basic(q, k, v, table, bl, key_padding_mask=mask)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("name", ["locm_ragged", "locm_short", "locm_even", "locm_long", "locm_full"])
+def test_sliding_window_vs_masked_reference_fixture(name, dt):
+    """The valid prefix of the fixture's sequence as a dense call with window = block length."""
+    t5b = _ops()
+    q, k, v, table, bl, want, lens = local_masked_case(load("local_masked.npz"), name)
+    n = lens[0]
+    out = t5b.flash_attention_with_fusing_bias(q[:, :, :n].to("cuda", dt), k[:, :, :n].to("cuda", dt),
+                                               v[:, :, :n].to("cuda", dt), table.to("cuda", dt), sm_scale=1.0, window=bl)
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    check_close(out, want[:, :, :n], dt, name)
+
+
+@pytest.mark.parametrize("D,L,bl,lens", [(64, 3000, 512, [3000, 1717, 1]), (128, 1500, 256, [900, 1500]),
+                                         (64, 700, 128, [700, 129, 128]), (64, 300, 1024, [300, 77])])
+def test_local_module_with_padding_mask_vs_oracle(D, L, bl, lens):
+    """T5LocalFlashAttention with the raw mask: unpad, packed kernel with the window, pad."""
+    t5b = _ops()
+    dt = torch.bfloat16
+    H, B = 2, len(lens)
+
+    class Cfg:
+        is_decoder = False
+        relative_attention_num_buckets = 32
+        relative_attention_max_distance = 128
+        d_model = H * D
+        d_kv = D
+        num_heads = H
+        dropout_rate = 0.0
+        sliding_window = bl
+    mod = t5b.T5ATTENTION_TYPES["local"](Cfg(), has_relative_attention_bias=True)
+    eye = torch.eye(H * D)
+    g = torch.Generator().manual_seed(3)
+    pk_, pv_ = torch.randperm(H * D, generator=g), torch.randperm(H * D, generator=g)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    with torch.no_grad():
+        mod.q.weight.copy_(eye); mod.k.weight.copy_(eye[pk_]); mod.v.weight.copy_(eye[pv_]); mod.o.weight.copy_(eye)
+        mod.relative_attention_bias.weight.copy_(table.float())
+    mod = mod.cuda().to(dt).eval()
+    hidden = seeded((B, L, H * D), 5, 0.5 if D == 128 else 1.0, dtype=dt)
+    mask = torch.zeros((B, L), dtype=torch.int64)
+    for b, n in enumerate(lens):
+        mask[b, :n] = 1
+    with torch.no_grad():
+        out = mod(hidden.cuda(), mask=mask.cuda())[0]
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    shape = lambda x: x.view(B, L, H, D).transpose(1, 2)
+    hf = hidden.float()
+    want = _window_oracle(shape(hf), shape(hf[..., pk_]), shape(hf[..., pv_]), table.float(), bl, lens)
+    want = want.transpose(1, 2).reshape(B, L, H * D)
+    for b, n in enumerate(lens):
+        check_close(out[b, :n], want[b, :n], dt, f"masked local row {b}")
+        assert torch.count_nonzero(out[b, n:]) == 0          # padded rows come back as zeros
+
+
+def test_sliding_window_refuses_what_it_cannot_do():
+    t5b = _ops()
+    q = torch.randn(1, 2, 600, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError):       # no CUDA-core kernel for it
+        t5b.flash_attention_with_fusing_bias(q.float(), q.float(), q.float(), None, sm_scale=1.0, window=128)
+    with pytest.raises(NotImplementedError):       # no backward
+        t5b.flash_attention_with_fusing_bias(q.clone().requires_grad_(True), q, q, None, sm_scale=1.0, window=128)
+    with pytest.raises(NotImplementedError):       # not together with the causal mask
+        t5b.flash_attention_with_fusing_bias(q, q, q, None, causal=True, sm_scale=1.0, window=128)

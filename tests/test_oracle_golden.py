@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle import t5_oracle as orc
-from tests.helpers import attention_case, from_bf16_bits, load, local_case, seeded
+from tests.helpers import attention_case, from_bf16_bits, load, local_case, local_masked_case, seeded
 
 
 def test_bucket_tables_bit_exact():
@@ -183,3 +183,16 @@ def test_block_local_attention_oracle(name):
     q, k, v, table, bl, want = local_case(load("local.npz"), name)
     got = orc.local_attention_basic(q, k, v, table, bl)
     assert (got - want).abs().max().item() <= 2e-5
+
+
+@pytest.mark.parametrize("name", ["locm_ragged", "locm_short", "locm_even", "locm_long", "locm_full"])
+def test_block_local_attention_with_padding_mask_oracle(name):
+    """The masked form (a sliding window over the valid keys) against the reference module driven
+    with the mask its stack builds."""
+    q, k, v, table, bl, want, lens = local_masked_case(load("local_masked.npz"), name)
+    mask = torch.zeros((q.shape[0], q.shape[2]))
+    for b, n in enumerate(lens):
+        mask[b, :n] = 1
+    got = orc.local_attention_basic(q, k, v, table, bl, key_padding_mask=mask)
+    for b, n in enumerate(lens):
+        assert (got[b, :, :n] - want[b, :, :n]).abs().max().item() < 2e-5, name

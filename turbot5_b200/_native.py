@@ -46,7 +46,7 @@ class AttnArgs(C.Structure):
         ("causal", C.c_int32), ("num_buckets", C.c_int32), ("max_distance", C.c_int32),
         ("q_pos_offset", C.c_int32), ("kernel", C.c_int32), ("sm_scale", C.c_float),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
-        ("local_block", C.c_int32), ("out_f32", C.c_int32),
+        ("local_block", C.c_int32), ("out_f32", C.c_int32), ("window", C.c_int32),
     ]
 
 

@@ -70,12 +70,19 @@ def _unit_stride_last(t):
 
 def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
                                      NUM_BUCKETS=32, MAX_DISTANCE=128, *, q_pos_offset=None,
-                                     return_lse=False, kernel="auto", balance_last_wave=True, local_block=None):
+                                     return_lse=False, kernel="auto", balance_last_wave=True, local_block=None,
+                                     window=None):
     """See `_dense_forward`; differentiable in q, k, v and the bias table.  `local_block` turns the
-    call into block-local attention (T5LocalAttention: the keys of the three neighbouring blocks)."""
+    call into block-local attention (T5LocalAttention: the keys of the three neighbouring blocks);
+    `window` into a sliding window |n - query position| < window (forward only)."""
     local_block = int(local_block or 0)
     if local_block:
         q_pos_offset, balance_last_wave = 0, False
+    if window:
+        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
+            raise NotImplementedError("sliding-window attention has no backward kernel")
+        return _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset=q_pos_offset,
+                              return_lse=return_lse, kernel=kernel, balance_last_wave=False, window=int(window))
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _DenseAttention.apply(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset,
                                          kernel, balance_last_wave, local_block)
@@ -87,7 +94,7 @@ def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
 
 def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *,
                    q_pos_offset=None, return_lse=False, kernel="auto", balance_last_wave=True, _keep=None,
-                   local_block=0, out_f32=False):
+                   local_block=0, out_f32=False, window=0):
     """softmax(sm_scale * Q K^T + T5 bias(n - m) [+ causal mask]) V without an L x L tensor.
 
     q (B,H,M,D), k/v (B,H,N,D), any batch/head/row strides (last dim contiguous);
@@ -140,6 +147,7 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
     a.sm_scale = float(sm_scale)
     a.workspace, a.workspace_bytes = None, 0
     a.local_block = int(local_block)
+    a.window = int(window)
     with torch.cuda.device(q.device):
         if balance_last_wave:
             need = nat.lib().t5b_attention_workspace_bytes(a)
@@ -147,8 +155,9 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
                 ws = _scratch(q.device, "attn", need)
                 a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
         st = nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device))
-        if st == nat.ERR_UNSUPPORTED and out_f32:
-            raise NotImplementedError("float32 partial outputs need the tensor-core forward kernels")
+        if st == nat.ERR_UNSUPPORTED and (out_f32 or window):
+            raise NotImplementedError("float32 partial outputs and sliding windows need the tensor-core forward "
+                                      "kernel (bf16/fp16, head dim 64 or 128, 16-byte aligned rows)")
         nat.check(st, "flash_attention_with_fusing_bias")
     if _keep is not None:
         _keep.update(args=a, q=q, k=k, v=v, table=table)
@@ -205,8 +214,14 @@ def merge_attention_partials(parts, dtype, return_lse=False):
 def flash_attention_with_fusing_bias_varlen(q, k, v, bias, cu_seqlens_q, cu_seqlens_k,
                                             max_seqlen_q, max_seqlen_k, causal=False, sm_scale=None,
                                             NUM_BUCKETS=32, MAX_DISTANCE=128, *, return_lse=False,
-                                            kernel="auto"):
-    """See `_varlen_forward`; differentiable in q, k, v and the bias table."""
+                                            kernel="auto", window=None):
+    """See `_varlen_forward`; differentiable in q, k, v and the bias table.  `window`: sliding window
+    |n - query position| < window inside every sequence (forward only)."""
+    if window:
+        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
+            raise NotImplementedError("sliding-window attention has no backward kernel")
+        return _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, sm_scale,
+                               NUM_BUCKETS, MAX_DISTANCE, return_lse=return_lse, kernel=kernel, window=int(window))
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _VarlenAttention.apply(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                                           causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, kernel)
@@ -216,7 +231,8 @@ def flash_attention_with_fusing_bias_varlen(q, k, v, bias, cu_seqlens_q, cu_seql
 
 
 def _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=False,
-                    sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *, return_lse=False, kernel="auto", _keep=None):
+                    sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *, return_lse=False, kernel="auto", _keep=None,
+                    window=0):
     """Packed-sequence variant: q (Tq,H,D), k/v (Tk,H,D), int32 cu_seqlens on the device.
 
     Positions are relative to each sequence.  Tiles are scheduled on the device
@@ -263,9 +279,13 @@ def _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max
     a.sm_scale = float(sm_scale)
     a.workspace, a.workspace_bytes = None, 0
     a.local_block = 0
+    a.window = int(window)
     with torch.cuda.device(q.device):
-        nat.check(nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device)),
-                  "flash_attention_with_fusing_bias_varlen")
+        st = nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device))
+        if st == nat.ERR_UNSUPPORTED and window:
+            raise NotImplementedError("sliding windows need the tensor-core forward kernel (bf16/fp16, head dim 64 "
+                                      "or 128, 16-byte aligned rows)")
+        nat.check(st, "flash_attention_with_fusing_bias_varlen")
     if _keep is not None:
         _keep.update(args=a, q=q, k=k, v=v, table=table, cu_q=cu_seqlens_q, cu_k=cu_seqlens_k)
     return (out, lse) if return_lse else out

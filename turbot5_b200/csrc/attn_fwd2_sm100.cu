@@ -645,7 +645,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q,
 // True when the two-tile kernel was asked for and applies: head dim 64, full (not block-local)
 // attention, and more than one 128-row query tile per sequence.
 bool sm100w_prefers(const t5b_attn_args& a) {
-  if (a.kernel != T5B_KERNEL_TCGEN05_2TILE || a.D != 64 || a.local_block != 0) return false;
+  if (a.kernel != T5B_KERNEL_TCGEN05_2TILE || a.D != 64 || a.local_block != 0 || a.window != 0) return false;
   return a.M > sm100w::BM;      // packed calls: M is the caller's max_seqlen_q
 }
 

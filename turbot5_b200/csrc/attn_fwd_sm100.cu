@@ -196,6 +196,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
   // keys this tile can see
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
+  // Sliding window (T5LocalAttention with its padding mask: |n - query| < window over the valid keys):
+  // the tile walks the key tiles that hold a visible key for any of its rows.
+  if (p.window > 0) {
+    n_base = max(0, qpos0 - p.window + 1) / BN * BN;
+    kv_end = min(kv_end, qpos0 + rows_in_tile - 1 + p.window);
+  }
   const int n_kv_all = kv_end > n_base ? (kv_end - n_base + BN - 1) / BN : 0;
   // this block's share of the key tiles: [kv_first, kv_first + n_kv)
   const int kv_per = (n_kv_all + parts - 1) / parts;
@@ -439,7 +445,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       if (lane == 0) mbar_arrive(bar(BAR_S_FREE));
 
       // tile classification (uniform over the block)
-      const bool need_mask = (n0 + BN > len_k) || (p.causal && (n0 + BN - 1 > qpos0));
+      const bool need_mask = (n0 + BN > len_k) || (p.causal && (n0 + BN - 1 > qpos0)) ||
+                             (p.window > 0 && (n0 <= qpos0 + BM - 1 - p.window || n0 + BN - 1 >= qpos0 + p.window));
       int bias_mode = 0;            // 0 none, 1 constant over the tile, 2 per element
       float bias_const = 0.f;
       if (has_bias) {
@@ -474,14 +481,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
         } else {
           // per-row window into the padded table: column c of this tile reads brow[c]
           const float* brow = lut + (n0 + c0 - qpos + md + LUT_PAD);
-          const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;   // columns < n_valid are visible
+          int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;   // columns < n_valid are visible
+          int n_lo = -(1 << 30);                                               // ... from column n_lo on
+          if (p.window > 0) {
+            n_valid = min(n_valid, qpos + p.window - n0 - c0);
+            n_lo = qpos - p.window + 1 - n0 - c0;
+          }
           #pragma unroll
           for (int c = 0; c < NCH; ++c) {
             #pragma unroll
             for (int i = 0; i < 32; ++i) {
               const float bias = bias_mode == 2 ? brow[c * 32 + i] : bias_const;
               float x = fmaf(__uint_as_float(sv[c][i]), scale, bias);
-              if (need_mask && (c * 32 + i >= n_valid)) x = -INFINITY;
+              if (need_mask && (c * 32 + i >= n_valid || c * 32 + i < n_lo)) x = -INFINITY;
               sv[c][i] = __float_as_uint(x);
               if ((i & 3) == 0) m0 = fmaxf(m0, x); else if ((i & 3) == 1) m1 = fmaxf(m1, x);
               else if ((i & 3) == 2) m2 = fmaxf(m2, x); else m3 = fmaxf(m3, x);
@@ -730,7 +742,8 @@ bool sm100_supports(const t5b_attn_args& a) {
   if (a.dtype != T5B_BF16 && a.dtype != T5B_F16) return false;
   if (a.D != 64 && a.D != 128) return false;
   if (a.max_distance > 2048 && a.table) return false;
-  if (a.local_block < 0) return false;
+  if (a.local_block < 0 || a.window < 0) return false;
+  if (a.window > 0 && (a.causal || a.local_block > 0)) return false;
   if (a.local_block > 0) {
     // block-local attention: dense self-attention without a causal mask; a 128-row query tile
     // must lie inside one block
@@ -759,7 +772,7 @@ TailPlan sm100_tail_plan(const t5b_attn_args& a) {
   t.tail_first = t.n_total;
   t.parts = 1;
   t.counters_bytes = t.ml_bytes = t.o_bytes = 0;
-  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || n_total > 0x3fffffffLL) return t;
+  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || a.window > 0 || n_total > 0x3fffffffLL) return t;
   static std::atomic<int> sms[64];     // SM count per device, 0 = not asked yet (any thread may get here first)
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return t; }

@@ -22,6 +22,7 @@ struct AttnParams {
   int32_t q_pos_offset;
   int32_t local_block;   // > 0: block-local attention (tensor-core forward only)
   int32_t out_f32;       // != 0: out is float32 (a partial result for the merge kernel)
+  int32_t window;        // > 0: keys with |n - query position| < window only (one-tile tensor-core forward)
   float scale_log2;   // sm_scale * log2(e): softmax runs in the base-2 domain
   // Dense tensor-core launches use a 1-D grid over (query tile, head, batch).  Blocks at or
   // beyond `tail_first` share a query tile `tail_parts` ways along the keys and merge through
@@ -57,6 +58,7 @@ inline AttnParams make_attn_params(const t5b_attn_args& a) {
   p.q_pos_offset = a.q_pos_offset;
   p.local_block = a.local_block;
   p.out_f32 = a.out_f32;
+  p.window = a.window;
   p.scale_log2 = a.sm_scale * kLog2e;
   p.tiles_x = 0; p.tail_first = 0x7fffffff; p.tail_parts = 1;
   p.ws_counters = nullptr; p.ws_ml = nullptr; p.ws_o = nullptr;

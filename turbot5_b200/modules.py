@@ -271,8 +271,15 @@ class T5LocalFlashAttention(T5FlashAttention):
     block's two neighbours (zero blocks at the ends) and materialises a (block, 3 x block) bias; here
     the same kernel that serves full attention walks only the three blocks of keys a query tile
     can see, the zero blocks come from the TMA's out-of-bounds fill, and the bias is looked up
-    per element as always.  Encoder self-attention without a padding mask (the reference adds
-    -1e10 at masked keys: not expressed here yet), no cache; differentiable.
+    per element as always.  Encoder self-attention, no cache; differentiable without a mask.
+
+    With the raw 0/1 (batch, length) padding mask the reference's mask for this module
+    (`_get_local_attention_mask`, src/turbot5/model/utils.py:149-155,174-188, added as -1e10 at
+    attentions.py:600-603,619-621) makes a pair visible when both tokens are valid and
+    |key - query| < block length: a sliding window over the valid keys.  Here the valid tokens are
+    packed (no host synchronisation), the packed-sequence kernel runs with that window, and the
+    rows of padded queries come back as zeros; forward only.  As in the full-attention module the
+    mask is taken to be right-padded (positions are counted inside the packed sequences).
     """
 
     def __init__(self, config, has_relative_attention_bias=False, **kwargs):
@@ -281,8 +288,6 @@ class T5LocalFlashAttention(T5FlashAttention):
 
     def forward(self, hidden_states, mask=None, position_bias=None, layer_head_mask=None, past_key_value=None,
                 use_cache=None, output_attentions=False, **kwargs):
-        if mask is not None:
-            raise NotImplementedError("T5LocalFlashAttention does not take a padding mask yet")
         if self.is_decoder:
             raise NotImplementedError("T5LocalFlashAttention covers encoder self-attention only")
         batch_size, seq_length = hidden_states.shape[:2]
@@ -294,10 +299,19 @@ class T5LocalFlashAttention(T5FlashAttention):
             table = position_bias
         elif self.has_relative_attention_bias:
             table = self.relative_attention_bias.weight
-        attn = flash_attention_with_fusing_bias(q, k, v, table, causal=False, sm_scale=1.0,
-                                                NUM_BUCKETS=self.relative_attention_num_buckets,
-                                                MAX_DISTANCE=self.relative_attention_max_distance,
-                                                local_block=self.block_len)
+        nb, md = self.relative_attention_num_buckets, self.relative_attention_max_distance
+        if mask is None:
+            attn = flash_attention_with_fusing_bias(q, k, v, table, causal=False, sm_scale=1.0, NUM_BUCKETS=nb,
+                                                    MAX_DISTANCE=md, local_block=self.block_len)
+        else:
+            if mask.dim() != 2:
+                raise ValueError("T5LocalFlashAttention takes the raw 0/1 (batch, length) mask")
+            plan = get_unpad_plan(mask)
+            q_p, k_p, v_p = (unpad_rows(t.transpose(1, 2), plan) for t in (q, k, v))
+            out_p = flash_attention_with_fusing_bias_varlen(q_p, k_p, v_p, table, plan.cu_seqlens, plan.cu_seqlens,
+                                                            seq_length, seq_length, causal=False, sm_scale=1.0,
+                                                            NUM_BUCKETS=nb, MAX_DISTANCE=md, window=self.block_len)
+            attn = pad_rows(out_p, plan).transpose(1, 2)
         out = self.o(attn.transpose(1, 2).contiguous().view(batch_size, -1, self.inner_dim))
         outputs = (out, None, table)
         if output_attentions:
