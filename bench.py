@@ -102,11 +102,14 @@ class ClockSampler:
 def _reference_functions():
     """The reference's own `basic` pieces (T5Attention._relative_position_bucket,
     naive_torch_attention_with_bias) when its source tree can be imported on this machine
-    (an install under baseline/_ref, or the reference checkout), else None.  The three
-    symbols the installed `transformers` no longer has are stubbed first; none is on this path."""
+    (an install under baseline/_ref, a checkout named by TURBOT5_REFERENCE_SRC, or a `reference`
+    checkout beside this repository), else None.  The three symbols the installed `transformers` no
+    longer has are stubbed first; none is on this path."""
     import types
-    for root in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference/src"):
-        if not os.path.isdir(os.path.join(root, "turbot5")):
+    roots = [os.path.join(ROOT, "baseline", "_ref"), os.environ.get("TURBOT5_REFERENCE_SRC", ""),
+             os.path.join(os.path.dirname(ROOT), "reference", "src")]
+    for root in roots:
+        if not root or not os.path.isdir(os.path.join(root, "turbot5")):
             continue
         try:
             import transformers.pytorch_utils as pu

@@ -84,10 +84,52 @@ __device__ __forceinline__ TileWork find_varlen_tile(const AttnParams& p, int bl
   const int lane = threadIdx.x & 31;
   int found_b = -1, tile_in_seq = 0, acc = 0;
   // Longest sequences first: a tile's work grows with its sequence's key count, and a long tile
-  // scheduled last leaves the GPU mostly idle while it finishes.  Without sorting anything, the
-  // sequences are taken in four classes by key count (quarters of max_seqlen_k = p.N, the
-  // caller's upper bound; 0 or a too small bound just puts everything into the first class),
-  // each class in index order.
+  // scheduled last leaves the GPU mostly idle while it finishes.
+  if (p.B <= 128) {
+    // Exact order (key count descending, index ascending) without sorting anything: a lane owns up
+    // to four sequences and counts, for each, the tiles of all sequences that precede it in that
+    // order -- B^2 / 32 comparisons per block, a few hundred instructions for a batch of 32.
+    const int chunks = (p.B + 31) >> 5;
+    int lk[4], nt[4], start[4];
+    #pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int bb = lane + 32 * u;
+      lk[u] = -1; nt[u] = 0; start[u] = 0;
+      if (u < chunks && bb < p.B) {
+        lk[u] = p.cu_k[bb + 1] - p.cu_k[bb];
+        nt[u] = (p.cu_q[bb + 1] - p.cu_q[bb] + TILE_M - 1) / TILE_M;
+      }
+    }
+    #pragma unroll
+    for (int u2 = 0; u2 < 4; ++u2) {
+      if (u2 < chunks) {
+        for (int src = 0; src < 32; ++src) {
+          const int olk = __shfl_sync(0xffffffffu, lk[u2], src);
+          const int ont = __shfl_sync(0xffffffffu, nt[u2], src);
+          const int ob = src + 32 * u2;
+          #pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int bb = lane + 32 * u;
+            const bool precedes = olk > lk[u] || (olk == lk[u] && ob < bb);
+            start[u] += precedes ? ont : 0;
+          }
+        }
+      }
+    }
+    #pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const bool mine = u < chunks && nt[u] > 0 && blk >= start[u] && blk < start[u] + nt[u];
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (m && found_b < 0) {
+        const int src = __ffs(m) - 1;
+        found_b = src + 32 * u;
+        tile_in_seq = blk - __shfl_sync(0xffffffffu, start[u], src);
+      }
+    }
+  } else {
+  // Larger batches: the sequences are taken in four classes by key count (quarters of
+  // max_seqlen_k = p.N, the caller's upper bound; 0 or a too small bound just puts everything
+  // into the first class), each class in index order.
   const int t1 = (int)(((long long)p.N * 3) >> 2), t2 = p.N >> 1, t3 = p.N >> 2;
   for (int cls = 0; cls < 4 && found_b < 0; ++cls) {
     for (int b0 = 0; b0 < p.B && found_b < 0; b0 += 32) {
@@ -114,6 +156,7 @@ __device__ __forceinline__ TileWork find_varlen_tile(const AttnParams& p, int bl
       }
       acc += __shfl_sync(0xffffffffu, incl, 31);
     }
+  }
   }
   TileWork w;
   w.b = -1; w.q_row0 = 0; w.rows_in_tile = 0; w.k_row0 = 0; w.len_k = 0; w.qpos0 = 0;
