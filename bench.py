@@ -418,6 +418,10 @@ def main():
             "gpu_launches": args.steps * (4 if args.train else 1),
             "clocks": clocks,
         }
+        if clocks and clocks.get("sm_mhz"):
+            # clock-independent form of the step time: SM cycles (in millions) per step at the median clock seen
+            line["mcycles_per_step"] = ms_step * clocks["sm_mhz"] / 1e3
+            line["timed_region_s"] = ms_total / 1e3
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             pairs = B * H
