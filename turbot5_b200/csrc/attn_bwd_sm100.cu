@@ -1155,6 +1155,483 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
   }
 }
 
+// ======================================================================== dK and dV, head dim 64
+// One block per SM owns a 128-key tile and streams 128-query tiles.  Tensor memory (all 512
+// columns): S^T and dP^T (128 float32 columns each), P^T and dS^T (64 columns each: 128 queries in
+// 16 bits) in columns of their OWN, dV and dK (64 each).  Because P^T and dS^T do not overwrite
+// S^T and dP^T, the products of the next query tile are queued as soon as the softmax warps have
+// READ the current ones into registers; sixteen softmax warps (lane quarter x 32-column group)
+// then never wait for the tensor core in steady state, and the 128-wide products run at the full
+// tensor rate instead of the shared-memory rate of the 64-wide ones.  Two issuing threads: one
+// for the products with both operands in shared memory (S^T, dP^T), one for those that read
+// P^T / dS^T from tensor memory (dV, dK).
+namespace wide {
+constexpr int BQ = 128;                 // rows of a streamed query tile
+constexpr int ST = 4;                   // stages of the Q / dO ring
+constexpr int TILE = BM * 128;          // bytes of a 128-row x 64-dim tile
+constexpr int SOFTMAX_WARPS = 16;
+constexpr int WARP_LOAD = 16, WARP_SS = 17, WARP_TS = 18;
+constexpr int THREADS = 19 * 32;
+constexpr int PAD = 2 * BM;             // table padding: |key - query| of a near-diagonal tile stays below max_distance + 255
+constexpr int COL_ST = 0, COL_DPT = 128, COL_PT = 256, COL_DST = 320, COL_DV = 384, COL_DK = 448;
+enum {
+  W_RES_FULL = 0,
+  W_Q_FULL = 1,                         // [ST] Q tile (TMA) + its lse / delta vectors (loading warp)
+  W_DO_FULL = W_Q_FULL + ST,            // [ST]
+  W_EMPTY = W_DO_FULL + ST,             // [ST] both tiles of a stage: after dK of that step
+  W_FULL = W_EMPTY + ST,                // S^T and dP^T of a tile are complete
+  W_FREE,                               // ... and read into registers by all softmax warps
+  W_PDS_FULL,                           // P^T and dS^T of a tile are stored
+  W_TS_DONE,                            // ... and read by the dV and dK products
+  W_O_DONE,
+  W_NUM
+};
+static_assert(W_NUM <= 24, "barrier slots");
+struct __align__(16) WControl {
+  unsigned long long bars[24];
+  uint32_t tmem_base;
+  int abort_flag;
+  int work[6];
+  float vec[ST][2][BQ];                 // (bias of a far tile) - lse in the log2 domain, and -delta
+};
+__host__ __device__ inline size_t smem_bytes(int lut_entries) {
+  return 1024 + (size_t)(2 + 2 * ST) * TILE + sizeof(WControl) + 16 + (size_t)lut_entries * 4 + 16;
+}
+}  // namespace wide
+
+template <bool kBf16>
+__global__ void __launch_bounds__(wide::THREADS, 1)
+attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                         const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+                         const __grid_constant__ AttnParams p, const __grid_constant__ BwdExtra e,
+                         const __grid_constant__ BucketSpec spec) {
+  using namespace wide;
+  constexpr int HD = 64;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t sK = base, sV = base + TILE, sQ = base + 2 * TILE, sDO = sQ + ST * TILE;
+  WControl* ctl = reinterpret_cast<WControl*>(smem + (2 + 2 * ST) * TILE);
+  float* lut = reinterpret_cast<float*>(smem + (2 + 2 * ST) * TILE + ((sizeof(WControl) + 15) / 16) * 16);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- work item: a 128-key tile of one (batch, head) or packed sequence
+  int h, b = 0, batch_idx = 0, part = 0, parts = 1, tail_slot = 0;
+  int key0, k_row0 = 0, len_k, q_row0 = 0, len_q, q_off;
+  if (p.cu_k == nullptr) {
+    const int tiles_k = (p.N + BM - 1) / BM;
+    int tile_lin = (int)blockIdx.x;
+    if (tile_lin >= e.k_tail_first) {
+      const int ee = tile_lin - e.k_tail_first;
+      parts = e.k_parts;
+      tail_slot = ee / parts;
+      part = ee - tail_slot * parts;
+      tile_lin = e.k_tail_first + tail_slot;
+    }
+    const int tx = tile_lin % tiles_k;
+    const int hb = tile_lin / tiles_k;
+    h = hb % p.H;
+    batch_idx = b = hb / p.H;
+    key0 = tx * BM;
+    len_k = p.N; len_q = p.M; q_off = p.q_pos_offset;
+  } else {
+    h = blockIdx.y;
+    if (warp == 0) {
+      int seq = -1, t = 0;
+      const bool found = find_seq_tile(p.cu_k, p.B, BM, (int)blockIdx.x, seq, t);
+      if (lane == 0) { ctl->work[0] = found ? seq : -1; ctl->work[1] = t; }
+    }
+    __syncthreads();
+    const int seq = ctl->work[0];
+    if (seq < 0) return;
+    key0 = ctl->work[1] * BM;
+    k_row0 = p.cu_k[seq]; len_k = p.cu_k[seq + 1] - k_row0;
+    q_row0 = p.cu_q[seq]; len_q = p.cu_q[seq + 1] - q_row0;
+    q_off = len_k - len_q;
+  }
+  const int keys_in_tile = min(BM, len_k - key0);
+  // query tiles that can see a key of this tile: causal keeps q_off + m >= key
+  int i_first = 0;
+  if (p.causal) i_first = max(0, key0 - q_off) / BQ;
+  int n_qt_all = (len_q + BQ - 1) / BQ;
+  if (p.local_block > 0) {
+    // block-local attention: only the queries of the three neighbouring blocks see this key tile
+    const int bl = p.M < p.local_block ? p.M : p.local_block;
+    const int kb = key0 / bl;
+    i_first = max(0, (kb - 1) * bl) / BQ;
+    n_qt_all = (min(len_q, (kb + 2) * bl) + BQ - 1) / BQ;
+  }
+  int n_qt = max(0, n_qt_all - i_first);
+  if (parts > 1) {       // this block's share of the query tiles
+    const int per = (n_qt + parts - 1) / parts;
+    const int first = min(part * per, n_qt);
+    n_qt = min(n_qt, first + per) - first;
+    i_first += first;
+  }
+
+  const uint32_t bar0 = smem_u32(&ctl->bars[0]);
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  const int md = spec.max_distance;
+  const bool has_bias = p.table != nullptr;
+  auto stat_index = [&](int m) -> int64_t {
+    return p.cu_q == nullptr ? ((int64_t)batch_idx * p.H + h) * p.M + m : ((int64_t)q_row0 + m) * p.H + h;
+  };
+  // loading warp: lse / delta of the first query tile, requested before the set-up below
+  float pre_l[4] = {0.f, 0.f, 0.f, 0.f}, pre_d[4] = {0.f, 0.f, 0.f, 0.f};
+  if (warp == WARP_LOAD && n_qt > 0) {
+    #pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int m = i_first * BQ + lane + 32 * u;
+      if (m < len_q) { pre_l[u] = p.lse[stat_index(m)]; pre_d[u] = e.delta[stat_index(m)]; }
+    }
+  }
+  auto load_q_tile = [&](int i) {
+    const int s = i % ST;
+    const int m0 = (i_first + i) * BQ;
+    mbar_expect_tx(bar(W_Q_FULL + s), TILE);
+    tma_load_4d(sQ + s * TILE, &tmap_q, bar(W_Q_FULL + s), 0, q_row0 + m0, h, b);
+    mbar_expect_tx(bar(W_DO_FULL + s), TILE);
+    tma_load_4d(sDO + s * TILE, &tmap_do, bar(W_DO_FULL + s), 0, q_row0 + m0, h, b);
+  };
+  if (warp == WARP_LOAD && lane == 0) {
+    ctl->abort_flag = 0;
+    mbar_init(bar(W_RES_FULL), 1);
+    for (int s = 0; s < ST; ++s) {
+      mbar_init(bar(W_Q_FULL + s), 2);       // TMA transaction + the vectors written by the loading warp
+      mbar_init(bar(W_DO_FULL + s), 1);
+      mbar_init(bar(W_EMPTY + s), 1);
+    }
+    mbar_init(bar(W_FULL), 1);
+    mbar_init(bar(W_FREE), SOFTMAX_WARPS);
+    mbar_init(bar(W_PDS_FULL), SOFTMAX_WARPS);
+    mbar_init(bar(W_TS_DONE), 1);
+    mbar_init(bar(W_O_DONE), 1);
+    fence_barrier_init();
+    fence_proxy_async();
+    if (n_qt > 0) {
+      mbar_expect_tx(bar(W_RES_FULL), 2 * TILE);
+      tma_load_4d(sK, &tmap_k, bar(W_RES_FULL), 0, k_row0 + key0, h, b);
+      tma_load_4d(sV, &tmap_v, bar(W_RES_FULL), 0, k_row0 + key0, h, b);
+      for (int i = 0; i < ST && i < n_qt; ++i) load_q_tile(i);
+    }
+  }
+  if (warp == WARP_SS) {
+    tmem_alloc(smem_u32(&ctl->tmem_base), 512);
+    tmem_relinquish();
+  }
+  if (has_bias) {
+    for (int i = tid; i <= 2 * md; i += THREADS) {
+      const int bucket = bucket_of_delta_counted(spec, i - md);
+      lut[PAD + i] = load_table(p.table, p.table_dtype, (int64_t)bucket * p.table_stride0 + h) * kLog2e;
+    }
+    __syncthreads();
+    const float lo_v = lut[PAD], hi_v = lut[PAD + 2 * md];
+    for (int i = tid; i < PAD; i += THREADS) {
+      lut[i] = lo_v;
+      lut[PAD + 2 * md + 1 + i] = hi_v;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+  int fail_code = 0;
+  // bias of a query tile that lies entirely beyond +-max_distance of this key tile (one value for
+  // the whole 128 x 128 tile): the loading warp folds it into the lse vector
+  auto far_tile_bias = [&](int q_lo, bool& is_far) -> float {
+    is_far = false;
+    if (!has_bias) { is_far = true; return 0.f; }
+    const int dmin = key0 - (q_lo + BQ - 1), dmax = key0 + BM - 1 - q_lo;
+    if (dmin >= md) { is_far = true; return lut[2 * md + PAD]; }
+    if (dmax <= -md) { is_far = true; return lut[PAD]; }
+    return 0.f;
+  };
+
+  if (warp == WARP_LOAD) {
+    // whole warp: lane 0 drives the TMA, all lanes fetch the lse / delta of the query tile
+    bool okp = true;
+    for (int i = 0; i < n_qt; ++i) {
+      const int s = i % ST;
+      const uint32_t ph = (uint32_t)((i / ST) & 1);
+      const int m0 = (i_first + i) * BQ;
+      // the statistics of the next tile are requested a whole iteration before they are used
+      float cur_l[4], cur_d[4];
+      #pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        cur_l[u] = pre_l[u]; cur_d[u] = pre_d[u];
+        const int m = m0 + BQ + lane + 32 * u;
+        if (i + 1 < n_qt && m < len_q) { pre_l[u] = p.lse[stat_index(m)]; pre_d[u] = e.delta[stat_index(m)]; }
+      }
+      if (i >= ST) {
+        // every lane waits: the vectors of this stage are rewritten below
+        if (!mbar_wait_bounded(bar(W_EMPTY + s), ph ^ 1u, abort_flag)) okp = false;
+        if (!__all_sync(0xffffffffu, okp)) { fail_code = 10; break; }
+        if (lane == 0) load_q_tile(i);        // the first ST tiles were requested above
+      }
+      bool is_far;
+      const float fold = far_tile_bias(q_off + m0, is_far);
+      #pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = lane + 32 * u;
+        const int m = m0 + c;
+        const bool valid = m < len_q;
+        const float l_ = valid ? cur_l[u] : 0.f;
+        const float d_ = valid ? cur_d[u] : 0.f;
+        // stored negated: the softmax warps add them with packed operations
+        ctl->vec[s][0][c] = fold - lse_to_log2(l_, valid);
+        ctl->vec[s][1][c] = valid ? -d_ : 0.f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(W_Q_FULL + s));
+    }
+  } else if (warp == WARP_SS) {
+    if (lane == 0 && n_qt > 0) {
+      constexpr uint32_t IDESC = make_idesc_f16(kBf16, kBf16, BM, BQ, false, false);   // 128 keys x 128 queries
+      bool ok = mbar_wait_bounded(bar(W_RES_FULL), 0, abort_flag);
+      if (!ok) fail_code = 20;
+      for (int i = 0; ok && i < n_qt; ++i) {
+        const int s = i % ST;
+        const uint32_t ph = (uint32_t)((i / ST) & 1);
+        // S^T(i) = K Q^T and dP^T(i) = V dO^T once the softmax warps hold those of tile i-1 in registers
+        if (!mbar_wait_bounded(bar(W_Q_FULL + s), ph, abort_flag)) { fail_code = 21; break; }
+        if (!mbar_wait_bounded(bar(W_DO_FULL + s), ph, abort_flag)) { fail_code = 23; break; }
+        if (i > 0 && !mbar_wait_bounded(bar(W_FREE), (uint32_t)((i - 1) & 1), abort_flag)) { fail_code = 22; break; }
+        tc_fence_after();
+        {
+          const uint64_t da = make_smem_desc_sw128(sK, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sQ + s * TILE, 16, 1024);
+          #pragma unroll
+          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_ST, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, k > 0);
+        }
+        {
+          const uint64_t da = make_smem_desc_sw128(sV, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sDO + s * TILE, 16, 1024);
+          #pragma unroll
+          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_DPT, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, k > 0);
+        }
+        tc_commit(bar(W_FULL));
+      }
+    }
+  } else if (warp == WARP_TS) {
+    if (lane == 0 && n_qt > 0) {
+      constexpr uint32_t IDESC = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);    // dO / Q as MN-major B
+      for (int i = 0; i < n_qt; ++i) {
+        const int s = i % ST;
+        // P^T(i) and dS^T(i) are stored.  (Their stage was loaded long ago: S^T(i) needed it, and
+        // the softmax warps saw S^T(i) before they arrived here.)
+        if (!mbar_wait_bounded(bar(W_PDS_FULL), (uint32_t)(i & 1), abort_flag)) { fail_code = 25; break; }
+        tc_fence_after();
+        // dV += P^T(i) dO, dK += dS^T(i) Q: 16 queries per step, the first operand from tensor memory
+        #pragma unroll
+        for (int k = 0; k < BQ / 16; ++k) {
+          const uint64_t db = make_smem_desc_sw128(sDO + s * TILE + k * 2048, 16, 1024);
+          umma_ts(tmem + COL_DV, tmem + COL_PT + 8 * k, db, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        #pragma unroll
+        for (int k = 0; k < BQ / 16; ++k) {
+          const uint64_t db = make_smem_desc_sw128(sQ + s * TILE + k * 2048, 16, 1024);
+          umma_ts(tmem + COL_DK, tmem + COL_DST + 8 * k, db, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(W_TS_DONE));          // P^T and dS^T may be overwritten
+        // S^T(i) and dP^T(i), the other readers of this stage, completed before P^T(i) could be formed
+        tc_commit(bar(W_EMPTY + s));
+        if (i + 1 == n_qt) tc_commit(bar(W_O_DONE));
+      }
+    }
+  } else {
+    const int quarter = warp & 3, cg = warp >> 2;      // tensor-memory lane quarter, 32-column group
+    const int r = quarter * 32 + lane;                 // key row inside the tile
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tST = tmem + lane_base + COL_ST + cg * 32;
+    const uint32_t tDPT = tmem + lane_base + COL_DPT + cg * 32;
+    const uint32_t tPT = tmem + lane_base + COL_PT + cg * 16;
+    const uint32_t tDST = tmem + lane_base + COL_DST + cg * 16;
+    const float scale = p.scale_log2;
+    const int key = key0 + r;
+    const bool key_ok = r < keys_in_tile;
+    const int wkey0 = key0 + quarter * 32;             // first key of this warp
+    bool ok = true;
+
+    // One probe per wait in the common case: the vote makes the branch uniform.  A wait that ran
+    // out leaves `ok` false for the whole warp; the tile is finished with whatever the registers
+    // hold (nothing below can fault) and the loop ends at the bottom of the tile.
+    auto wait = [&](int which, uint32_t parity, int code) {
+      if (__all_sync(0xffffffffu, mbar_try_wait(bar(which), parity))) return;
+      if (!mbar_wait_bounded_warp(bar(which), parity, abort_flag) && ok) { ok = false; fail_code = code; }
+    };
+    // every arrival follows a warp-wide tcgen05.wait: all lanes' accesses are complete, no __syncwarp
+    auto arrive = [&](int which) {
+      tc_fence_before();
+      if (lane == 0) mbar_arrive(bar(which));
+    };
+    const bool warp_beyond_keys = wkey0 + 32 > len_k;
+    // One pass per tile, as in the dQ kernel: S^T and dP^T are read together, P^T and dS^T stored
+    // together: two probes, one load and one store round trip, two arrivals per tile.  The lse /
+    // delta vectors of a stage are ordered by the chain loading warp -> Q_FULL -> issuing thread
+    // -> FULL (commit) -> here.
+    for (int i = 0; i < n_qt; ++i) {
+      const int s = i % ST;
+      const int q_lo = q_off + (i_first + i) * BQ;       // key-coordinate position of the tile's first query
+      const int qp0 = q_lo + cg * 32;                    // ... of this warp's column 0
+      // a tile entirely beyond +-max_distance has one bias value, folded into the vector by the
+      // loading warp; otherwise the bias is looked up per element (the table is padded with its
+      // end values, so any key - query of such a tile is inside it)
+      const bool per_element = has_bias && !(key0 - (q_lo + BQ - 1) >= md || key0 + BM - 1 - q_lo <= -md);
+      const bool masked = warp_beyond_keys || (p.causal && wkey0 + 31 > qp0);
+      const float* vl = &ctl->vec[s][0][cg * 32];
+      const float* vd = &ctl->vec[s][1][cg * 32];
+      // column c has delta = key - (qp0 + c): the table index falls as c grows
+      const float* lrow = lut + (key - qp0 + md + PAD);
+      wait(W_FULL, (uint32_t)(i & 1), 30);
+      tc_fence_after();
+      uint32_t sv[32], dp[32];
+      tmem_ld_x32(tST, sv);
+      tmem_ld_x32(tDPT, dp);
+      tmem_ld_wait();
+      arrive(W_FREE);                                    // S^T(i+1) and dP^T(i+1) may be formed now
+
+      // P^T = exp2(S^T scale + bias - lse), dS^T = P^T o (dP^T - delta); both rounded to 16 bits as
+      // the first operands of the dV and dK products
+      // (all 32 columns before the first store: a version that stored each half of 16 as soon as it
+      // was packed had fewer live registers and was 9 % slower over the whole backward)
+      uint32_t pp[16], pd[16];
+      if (!masked && !per_element) {
+        #pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const int c = 4 * g;
+          const float4 l4 = *reinterpret_cast<const float4*>(vl + c);
+          const float4 d4 = *reinterpret_cast<const float4*>(vd + c);
+          float x0, x1, x2, x3;
+          fma2v(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, l4.x, l4.y);
+          fma2v(x2, x3, __uint_as_float(sv[c + 2]), __uint_as_float(sv[c + 3]), scale, l4.z, l4.w);
+          float g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]);
+          float g2 = __uint_as_float(dp[c + 2]), g3 = __uint_as_float(dp[c + 3]), e0, e1, e2, e3;
+          add2(g0, g1, d4.x, d4.y);          // dP - delta
+          add2(g2, g3, d4.z, d4.w);
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+          mul2(e0, e1, p0, p1, g0, g1);
+          mul2(e2, e3, p2, p3, g2, g3);
+          pp[2 * g] = pack2<kBf16>(p0, p1);
+          pp[2 * g + 1] = pack2<kBf16>(p2, p3);
+          pd[2 * g] = pack2<kBf16>(e0, e1);
+          pd[2 * g + 1] = pack2<kBf16>(e2, e3);
+        }
+      } else if (!masked) {
+        #pragma unroll
+        for (int g = 0; g < 16; ++g) {
+          const int c = 2 * g;
+          const float2 l2 = *reinterpret_cast<const float2*>(vl + c);
+          const float2 d2 = *reinterpret_cast<const float2*>(vd + c);
+          float x0 = lrow[-c], x1 = lrow[-c - 1], g0 = __uint_as_float(dp[c]), g1 = __uint_as_float(dp[c + 1]), e0, e1;
+          add2(x0, x1, l2.x, l2.y);          // bias - lse
+          fma2v(x0, x1, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), scale, x0, x1);
+          add2(g0, g1, d2.x, d2.y);          // dP - delta
+          const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+          mul2(e0, e1, p0, p1, g0, g1);
+          pp[g] = pack2<kBf16>(p0, p1);
+          pd[g] = pack2<kBf16>(e0, e1);
+        }
+      } else {
+        #pragma unroll
+        for (int g = 0; g < 16; ++g) {
+          float pv[2], dv2[2];
+          #pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int c = 2 * g + u;
+            const float bias = per_element ? lrow[-c] : 0.f;
+            float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
+            // masked: key outside the sequence, or (causal) after the query
+            if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
+            pv[u] = fast_exp2(x);
+            dv2[u] = pv[u] * (__uint_as_float(dp[c]) + vd[c]);
+          }
+          pp[g] = pack2<kBf16>(pv[0], pv[1]);
+          pd[g] = pack2<kBf16>(dv2[0], dv2[1]);
+        }
+      }
+      if (i > 0) {
+        wait(W_TS_DONE, (uint32_t)((i - 1) & 1), 32);    // dV(i-1) and dK(i-1) have read P^T(i-1) and dS^T(i-1)
+        tc_fence_after();
+      }
+      tmem_st_x16(tPT, pp);
+      tmem_st_x16(tDST, pd);
+      tmem_st_wait();
+      arrive(W_PDS_FULL);
+      if (!ok) break;                                    // warp-uniform: every wait ends in a vote
+    }
+
+
+    if (ok && n_qt > 0) {
+      if (!mbar_wait_bounded_warp(bar(W_O_DONE), 0, abort_flag)) { ok = false; fail_code = 35; }
+      tc_fence_after();
+    }
+    if (ok) {          // warp-uniform; only the stores depend on the key row
+      const int64_t krow = (int64_t)k_row0 + key;
+      uint8_t* dvrow = reinterpret_cast<uint8_t*>(e.dv) + cg * 32 +
+                       2 * ((int64_t)b * p.v_stride_b + (int64_t)h * p.v_stride_h + krow * p.v_stride_n);
+      uint8_t* dkrow = reinterpret_cast<uint8_t*>(e.dk) + cg * 32 +
+                       2 * ((int64_t)b * p.k_stride_b + (int64_t)h * p.k_stride_h + krow * p.k_stride_n);
+      #pragma unroll 1
+      for (int t = 0; t < 2; ++t) {
+        const float sc = t == 0 ? 1.f : e.sm_scale;
+        uint8_t* dst = t == 0 ? dvrow : dkrow;
+        float o[16];
+        uint32_t v[16];
+        if (n_qt > 0) {
+          tmem_ld_x16(tmem + lane_base + (t == 0 ? COL_DV : COL_DK) + cg * 16, v);
+          tmem_ld_wait();
+        } else {
+          #pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0u;
+        }
+        #pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = __uint_as_float(v[i]) * sc;
+        bool write_out = key_ok;
+        if (parts > 1 && key_ok) {
+          float* acc = (t == 0 ? e.ws_dv : e.ws_dk) + ((int64_t)tail_slot * BM + r) * HD + cg * 16;
+          #pragma unroll
+          for (int i = 0; i < 16; ++i) atomicAdd(acc + i, o[i]);
+          __threadfence();
+          int* counter = e.ws_cnt_k + (((int64_t)tail_slot * BM + r) * 4 + cg) * 2 + t;
+          write_out = (atomicAdd(counter, 1) == parts - 1);
+          if (write_out) {
+            __threadfence();
+            #pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 t4 = __ldcg(reinterpret_cast<const float4*>(acc) + i);
+              o[4 * i] = t4.x; o[4 * i + 1] = t4.y; o[4 * i + 2] = t4.z; o[4 * i + 3] = t4.w;
+              reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            *counter = 0;
+          }
+        }
+        if (write_out) {
+          #pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            uint4 w4;
+            w4.x = pack2<kBf16>(o[8 * i + 0], o[8 * i + 1]);
+            w4.y = pack2<kBf16>(o[8 * i + 2], o[8 * i + 3]);
+            w4.z = pack2<kBf16>(o[8 * i + 4], o[8 * i + 5]);
+            w4.w = pack2<kBf16>(o[8 * i + 6], o[8 * i + 7]);
+            *reinterpret_cast<uint4*>(dst + i * 16) = w4;
+          }
+        }
+      }
+    }
+  }
+
+  if (fail_code != 0 && p.status != nullptr) atomicCAS(p.status, 0, 3100 + fail_code);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_SS) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 }  // namespace sm100b
 
 // Last-wave plan of the two backward kernels (see BwdExtra).  The counter areas have a fixed
@@ -1164,6 +1641,13 @@ struct BwdPlan {
   int64_t cnt_bytes, dq_bytes, dk_bytes;
   int64_t bytes() const { return (q_parts > 1 || k_parts > 1) ? 2 * cnt_bytes + dq_bytes + 2 * dk_bytes : 0; }
 };
+
+// Head dim 64 takes the 128-query dK/dV kernel (one block per SM); T5B_BWD_DKV_WIDE=0 builds
+// the library with the 64-query kernel (two blocks per SM) for every head dim.
+#ifndef T5B_BWD_DKV_WIDE
+#define T5B_BWD_DKV_WIDE 1
+#endif
+static bool dkv_wide(const t5b_attn_args& a) { return T5B_BWD_DKV_WIDE != 0 && a.D == 64; }
 
 static BwdPlan sm100_bwd_plan(const t5b_attn_args& a) {
   using namespace sm100b;
@@ -1196,8 +1680,25 @@ static BwdPlan sm100_bwd_plan(const t5b_attn_args& a) {
     tail_first = (int)(n_total - rem);
   };
   split(nq, (a.N + BT - 1) / BT, t.q_tail_first, t.q_parts, t.q_rem);
-  split(nk, (a.M + BT - 1) / BT, t.k_tail_first, t.k_parts, t.k_rem);
-  t.cnt_bytes = al((int64_t)slots * BM * 2 * 2 * 4);
+  if (dkv_wide(a)) {
+    // one block per SM, 128-query steps: at least 8 of them (1024 rows) per part
+    auto split_wide = [&](long long n_total, int n_stream, int& tail_first, int& parts, int& rem) {
+      rem = (int)(n_total % sms);
+      if (rem == 0) return;
+      int pp = sms / rem;
+      if (pp > n_stream / 8) pp = n_stream / 8;
+      if (pp > 8) pp = 8;
+      if (pp < 2) { rem = 0; return; }
+      parts = pp;
+      tail_first = (int)(n_total - rem);
+    };
+    split_wide(nk, (a.M + wide::BQ - 1) / wide::BQ, t.k_tail_first, t.k_parts, t.k_rem);
+  } else {
+    split(nk, (a.M + BT - 1) / BT, t.k_tail_first, t.k_parts, t.k_rem);
+  }
+  // counters: (row, half, tensor) per slot of the 64-query kernels = (row, 16-column group, tensor)
+  // per SM of the 128-query kernel: the same size
+  t.cnt_bytes = al((int64_t)(HD == 64 ? 2 : 1) * sms * BM * 2 * 2 * 4);
   t.dq_bytes = al((int64_t)t.q_rem * BM * HD * 4);
   t.dk_bytes = al((int64_t)t.k_rem * BM * HD * 4);
   return t;
@@ -1327,7 +1828,21 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
     kq<<<gq, NUM_THREADS, smem, stream>>>(q128, do128, k64, v64, p, e, spec);
     if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
   }
-  if (gk.x > 0) {
+  if (gk.x > 0 && dkv_wide(a)) {
+    auto kw = bf16 ? attn_bwd_dkv_wide_kernel<true> : attn_bwd_dkv_wide_kernel<false>;
+    static std::atomic<bool> wide_attr_set[64][2];
+    if (dev < 0 || dev >= 64 || !wide_attr_set[dev][bf16 ? 1 : 0].load(std::memory_order_acquire)) {
+      const int smem_max = (int)wide::smem_bytes(2 * 2048 + 1 + 2 * wide::PAD);
+      if (cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) != cudaSuccess) {
+        cudaGetLastError();
+        return T5B_ERR_LAUNCH;
+      }
+      if (dev >= 0 && dev < 64) wide_attr_set[dev][bf16 ? 1 : 0].store(true, std::memory_order_release);
+    }
+    const size_t smem_w = wide::smem_bytes(a.table ? 2 * spec.max_distance + 1 + 2 * wide::PAD : 0);
+    kw<<<gk, wide::THREADS, smem_w, stream>>>(k128, v128, q128, do128, p, e, spec);
+    if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
+  } else if (gk.x > 0) {
     kkv<<<gk, NUM_THREADS, smem, stream>>>(k128, v128, q64, do64, p, e, spec);
     if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
   }
