@@ -1179,11 +1179,12 @@ enum {
   W_Q_FULL = 1,                         // [ST] Q tile (TMA) + its lse / delta vectors (loading warp)
   W_DO_FULL = W_Q_FULL + ST,            // [ST]
   W_EMPTY = W_DO_FULL + ST,             // [ST] both tiles of a stage: after dK of that step
-  W_FULL = W_EMPTY + ST,                // S^T and dP^T of a tile are complete
-  W_FREE,                               // ... and read into registers by all softmax warps
-  W_PDS_FULL,                           // P^T and dS^T of a tile are stored
-  W_TS_DONE,                            // ... and read by the dV and dK products
-  W_O_DONE,
+  // per half of a query tile (queries 0-63 | 64-127; two barriers each):
+  W_FULL = W_EMPTY + ST,                // S^T and dP^T of the half are complete
+  W_FREE = W_FULL + 2,                  // ... and read into registers by its eight softmax warps
+  W_PDS_FULL = W_FREE + 2,              // P^T and dS^T of the half are stored
+  W_TS_DONE = W_PDS_FULL + 2,           // ... and read by the dV and dK products
+  W_O_DONE = W_TS_DONE + 2,
   W_NUM
 };
 static_assert(W_NUM <= 24, "barrier slots");
@@ -1303,10 +1304,12 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
       mbar_init(bar(W_DO_FULL + s), 1);
       mbar_init(bar(W_EMPTY + s), 1);
     }
-    mbar_init(bar(W_FULL), 1);
-    mbar_init(bar(W_FREE), SOFTMAX_WARPS);
-    mbar_init(bar(W_PDS_FULL), SOFTMAX_WARPS);
-    mbar_init(bar(W_TS_DONE), 1);
+    for (int hf = 0; hf < 2; ++hf) {
+      mbar_init(bar(W_FULL + hf), 1);
+      mbar_init(bar(W_FREE + hf), SOFTMAX_WARPS / 2);
+      mbar_init(bar(W_PDS_FULL + hf), SOFTMAX_WARPS / 2);
+      mbar_init(bar(W_TS_DONE + hf), 1);
+    }
     mbar_init(bar(W_O_DONE), 1);
     fence_barrier_init();
     fence_proxy_async();
@@ -1389,53 +1392,61 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     }
   } else if (warp == WARP_SS) {
     if (lane == 0 && n_qt > 0) {
-      constexpr uint32_t IDESC = make_idesc_f16(kBf16, kBf16, BM, BQ, false, false);   // 128 keys x 128 queries
+      constexpr uint32_t IDESC = make_idesc_f16(kBf16, kBf16, BM, BQ / 2, false, false);   // 128 keys x 64 queries
       bool ok = mbar_wait_bounded(bar(W_RES_FULL), 0, abort_flag);
       if (!ok) fail_code = 20;
       for (int i = 0; ok && i < n_qt; ++i) {
         const int s = i % ST;
         const uint32_t ph = (uint32_t)((i / ST) & 1);
-        // S^T(i) = K Q^T and dP^T(i) = V dO^T once the softmax warps hold those of tile i-1 in registers
         if (!mbar_wait_bounded(bar(W_Q_FULL + s), ph, abort_flag)) { fail_code = 21; break; }
         if (!mbar_wait_bounded(bar(W_DO_FULL + s), ph, abort_flag)) { fail_code = 23; break; }
-        if (i > 0 && !mbar_wait_bounded(bar(W_FREE), (uint32_t)((i - 1) & 1), abort_flag)) { fail_code = 22; break; }
-        tc_fence_after();
-        {
-          const uint64_t da = make_smem_desc_sw128(sK, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(sQ + s * TILE, 16, 1024);
-          #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_ST, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, k > 0);
+        #pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          // S^T(i) = K Q^T and dP^T(i) = V dO^T of this half once its warps hold those of tile i-1 in registers
+          if (i > 0 && !mbar_wait_bounded(bar(W_FREE + hf), (uint32_t)((i - 1) & 1), abort_flag)) { ok = false; fail_code = 22; break; }
+          tc_fence_after();
+          {
+            const uint64_t da = make_smem_desc_sw128(sK, 16, 1024);
+            const uint64_t db = make_smem_desc_sw128(sQ + s * TILE + hf * (TILE / 2), 16, 1024);
+            #pragma unroll
+            for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_ST + 64 * hf, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, k > 0);
+          }
+          {
+            const uint64_t da = make_smem_desc_sw128(sV, 16, 1024);
+            const uint64_t db = make_smem_desc_sw128(sDO + s * TILE + hf * (TILE / 2), 16, 1024);
+            #pragma unroll
+            for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_DPT + 64 * hf, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, k > 0);
+          }
+          tc_commit(bar(W_FULL + hf));
         }
-        {
-          const uint64_t da = make_smem_desc_sw128(sV, 16, 1024);
-          const uint64_t db = make_smem_desc_sw128(sDO + s * TILE, 16, 1024);
-          #pragma unroll
-          for (int k = 0; k < 4; ++k) umma_ss(tmem + COL_DPT, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), IDESC, k > 0);
-        }
-        tc_commit(bar(W_FULL));
       }
     }
   } else if (warp == WARP_TS) {
     if (lane == 0 && n_qt > 0) {
       constexpr uint32_t IDESC = make_idesc_f16(kBf16, kBf16, BM, HD, false, true);    // dO / Q as MN-major B
-      for (int i = 0; i < n_qt; ++i) {
+      bool ok = true;
+      for (int i = 0; ok && i < n_qt; ++i) {
         const int s = i % ST;
-        // P^T(i) and dS^T(i) are stored.  (Their stage was loaded long ago: S^T(i) needed it, and
-        // the softmax warps saw S^T(i) before they arrived here.)
-        if (!mbar_wait_bounded(bar(W_PDS_FULL), (uint32_t)(i & 1), abort_flag)) { fail_code = 25; break; }
-        tc_fence_after();
-        // dV += P^T(i) dO, dK += dS^T(i) Q: 16 queries per step, the first operand from tensor memory
         #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {
-          const uint64_t db = make_smem_desc_sw128(sDO + s * TILE + k * 2048, 16, 1024);
-          umma_ts(tmem + COL_DV, tmem + COL_PT + 8 * k, db, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+        for (int hf = 0; hf < 2; ++hf) {
+          // P^T(i) and dS^T(i) of this half are stored.  (Their stage was loaded long ago: S^T(i)
+          // needed it, and the softmax warps saw S^T(i) before they arrived here.)
+          if (!mbar_wait_bounded(bar(W_PDS_FULL + hf), (uint32_t)(i & 1), abort_flag)) { ok = false; fail_code = 25; break; }
+          tc_fence_after();
+          // dV += P^T(i) dO, dK += dS^T(i) Q: 16 queries per step, the first operand from tensor memory
+          #pragma unroll
+          for (int k = 4 * hf; k < 4 * hf + 4; ++k) {
+            const uint64_t db = make_smem_desc_sw128(sDO + s * TILE + k * 2048, 16, 1024);
+            umma_ts(tmem + COL_DV, tmem + COL_PT + 8 * k, db, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          #pragma unroll
+          for (int k = 4 * hf; k < 4 * hf + 4; ++k) {
+            const uint64_t db = make_smem_desc_sw128(sQ + s * TILE + k * 2048, 16, 1024);
+            umma_ts(tmem + COL_DK, tmem + COL_DST + 8 * k, db, IDESC, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(bar(W_TS_DONE + hf));   // P^T and dS^T of the half may be overwritten
         }
-        #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {
-          const uint64_t db = make_smem_desc_sw128(sQ + s * TILE + k * 2048, 16, 1024);
-          umma_ts(tmem + COL_DK, tmem + COL_DST + 8 * k, db, IDESC, (i > 0 || k > 0) ? 1u : 0u);
-        }
-        tc_commit(bar(W_TS_DONE));          // P^T and dS^T may be overwritten
+        if (!ok) break;
         // S^T(i) and dP^T(i), the other readers of this stage, completed before P^T(i) could be formed
         tc_commit(bar(W_EMPTY + s));
         if (i + 1 == n_qt) tc_commit(bar(W_O_DONE));
@@ -1468,6 +1479,7 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
       if (lane == 0) mbar_arrive(bar(which));
     };
     const bool warp_beyond_keys = wkey0 + 32 > len_k;
+    const int hf = cg >> 1;                            // half of the query tile this warp works on
     // One pass per tile, as in the dQ kernel: S^T and dP^T are read together, P^T and dS^T stored
     // together: two probes, one load and one store round trip, two arrivals per tile.  The lse /
     // delta vectors of a stage are ordered by the chain loading warp -> Q_FULL -> issuing thread
@@ -1485,13 +1497,13 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
       const float* vd = &ctl->vec[s][1][cg * 32];
       // column c has delta = key - (qp0 + c): the table index falls as c grows
       const float* lrow = lut + (key - qp0 + md + PAD);
-      wait(W_FULL, (uint32_t)(i & 1), 30);
+      wait(W_FULL + hf, (uint32_t)(i & 1), 30);
       tc_fence_after();
       uint32_t sv[32], dp[32];
       tmem_ld_x32(tST, sv);
       tmem_ld_x32(tDPT, dp);
       tmem_ld_wait();
-      arrive(W_FREE);                                    // S^T(i+1) and dP^T(i+1) may be formed now
+      arrive(W_FREE + hf);                                   // S^T(i+1) and dP^T(i+1) may be formed now
 
       // P^T = exp2(S^T scale + bias - lse), dS^T = P^T o (dP^T - delta); both rounded to 16 bits as
       // the first operands of the dV and dK products
@@ -1553,13 +1565,13 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
         }
       }
       if (i > 0) {
-        wait(W_TS_DONE, (uint32_t)((i - 1) & 1), 32);    // dV(i-1) and dK(i-1) have read P^T(i-1) and dS^T(i-1)
+        wait(W_TS_DONE + hf, (uint32_t)((i - 1) & 1), 32);    // dV(i-1) and dK(i-1) have read P^T(i-1) and dS^T(i-1)
         tc_fence_after();
       }
       tmem_st_x16(tPT, pp);
       tmem_st_x16(tDST, pd);
       tmem_st_wait();
-      arrive(W_PDS_FULL);
+      arrive(W_PDS_FULL + hf);
       if (!ok) break;                                    // warp-uniform: every wait ends in a vote
     }
 
