@@ -411,7 +411,7 @@ def main():
                                            "(profiles/attn_fwd_sm100_8k.md); algorithmic Q+K+V+O = "
                                            f"{4 * B * H * L * D * 2 / 1e6:.1f} MB",
                          "peak_source": peaks["source"],
-                         "kernel": "attn_fwd_kernel + attn_bwd_dq_kernel + attn_bwd_dkv_kernel" if args.train
+                         "kernel": "attn_fwd_kernel + attn_bwd_dq_kernel + attn_bwd_dkv_wide_kernel" if args.train
                                    else "attn_fwd_kernel<bf16>"},
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": set_bytes,
                     "d2h_bytes_per_step": B * H * L * D * 2, "ms_per_step": e2e_ms, "steps": e2e_steps},

@@ -13,6 +13,10 @@
 //                           S^T = K Q^T, dP^T = V dO^T
 //                           P^T, dS^T written over S^T, dP^T in place (16-bit)
 //                           dV += P^T dO,  dK += dS^T Q                                  (:440-632)
+//                         (head dim 128; head dim 64 when built with T5B_BWD_DKV_WIDE=0)
+//   attn_bwd_dkv_wide_kernel   head dim 64: the same products over 128-query steps, one block per SM,
+//                         P^T and dS^T in tensor-memory columns of their own, the two 64-query halves
+//                         of a step as independent pipelines
 //
 // S and dP are recomputed in both kernels (7 matrix products per tile pair instead of 5): no
 // atomics on dQ, every output tile has one owner, results are deterministic except the few
