@@ -152,8 +152,8 @@ typedef struct {
    * sequence's length).  This is what T5LocalAttention computes when it is given its padding mask
    * (src/turbot5/model/utils.py:149-155,174-188: the 3-block mask ANDed with |n - m| < block_len):
    * pack the valid tokens (cu_seqlens) and pass window = block_len.  Dense or packed, not causal,
-   * not combined with local_block; forward only, the one-tile tensor-core kernel
-   * (T5B_ERR_UNSUPPORTED otherwise).  0: off. */
+   * not combined with local_block; the tensor-core kernels only, forward (one-tile kernel) and
+   * backward (T5B_ERR_UNSUPPORTED otherwise).  0: off. */
   int32_t window;
 } t5b_attn_args;
 

@@ -319,6 +319,105 @@ def test_block_local_attention_gradients_vs_oracle(D, L, bl):
         check_grad_close(g.grad, w.grad, f"local d{D} L{L} block {bl} {nm}", floor=2.0 if nm == "dtable" else 1e-6)
 
 
+@pytest.mark.parametrize("D,bl,lens", [(64, 256, [1500, 700, 1]), (64, 128, [700, 129, 128]), (128, 256, [900, 300]),
+                                       (64, 1024, [300, 77]), (64, 512, [3000])])
+def test_sliding_window_gradients_vs_oracle(D, bl, lens):
+    """Packed sequences with the sliding window |key - query| < window (T5LocalAttention with its
+    padding mask): dq, dk, dv and the bias-table gradient against float32 autograd of the oracle."""
+    t5b = _ops()
+    dt = torch.bfloat16
+    H, T = 2, sum(lens)
+    q, k, v = (seeded((T, H, D), s, 0.5 if D == 64 else 0.35, dtype=dt) for s in (1, 2, 3))
+    dout = seeded((T, H, D), 5, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    ref = [t.float().clone().requires_grad_(True) for t in (q, k, v, table)]
+    outs, lo = [], 0
+    for n in lens:
+        seq = [t[lo:lo + n].transpose(0, 1).unsqueeze(0) for t in ref[:3]]          # (1, H, n, D)
+        outs.append(orc.local_attention_basic(*seq, ref[3], bl, key_padding_mask=torch.ones((1, n)))[0].transpose(0, 1))
+        lo += n
+    want = torch.cat(outs)
+    (want * dout.float()).sum().backward()
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    leaves = [t.cuda().requires_grad_(True) for t in (q, k, v, table)]
+    out = t5b.flash_attention_with_fusing_bias_varlen(*leaves, cu, cu, max(lens), max(lens), sm_scale=1.0, window=bl)
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    check_close(out.detach(), want.detach(), dt, "window out")
+    for g, w, nm in zip(leaves, ref, ("dq", "dk", "dv", "dtable")):
+        check_grad_close(g.grad, w.grad, f"window d{D} block {bl} {nm}", floor=2.0 if nm == "dtable" else 1e-6)
+
+
+@pytest.mark.parametrize("D,L,bl", [(64, 1100, 256), (128, 640, 128)])
+def test_dense_sliding_window_gradients_vs_oracle(D, L, bl):
+    t5b = _ops()
+    dt = torch.bfloat16
+    q, k, v = (seeded((2, 2, L, D), s, 0.5 if D == 64 else 0.35, dtype=dt) for s in (1, 2, 3))
+    dout = seeded((2, 2, L, D), 5, dtype=dt)
+    table = seeded((32, 2), 4, 0.1, dtype=dt)
+    ref = [t.float().clone().requires_grad_(True) for t in (q, k, v, table)]
+    want = orc.local_attention_basic(*ref, bl, key_padding_mask=torch.ones((2, L)))
+    (want * dout.float()).sum().backward()
+    leaves = [t.cuda().requires_grad_(True) for t in (q, k, v, table)]
+    out = t5b.flash_attention_with_fusing_bias(*leaves, sm_scale=1.0, window=bl)
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    check_close(out.detach(), want.detach(), dt, "window out")
+    for g, w, nm in zip(leaves, ref, ("dq", "dk", "dv", "dtable")):
+        check_grad_close(g.grad, w.grad, f"dense window d{D} L{L} block {bl} {nm}", floor=2.0 if nm == "dtable" else 1e-6)
+
+
+def test_local_module_with_padding_mask_trains():
+    """T5LocalFlashAttention with the raw mask under autograd: unpad, packed kernel with the window, pad;
+    gradient of the hidden states against float32 autograd of the oracle (valid rows; padded rows get none)."""
+    t5b = _ops()
+    dt = torch.bfloat16
+    H, D, L, bl, lens = 2, 64, 900, 256, [900, 411]
+    B = len(lens)
+
+    class Cfg:
+        is_decoder = False
+        relative_attention_num_buckets = 32
+        relative_attention_max_distance = 128
+        d_model = H * D
+        d_kv = D
+        num_heads = H
+        dropout_rate = 0.0
+        sliding_window = bl
+    mod = t5b.T5ATTENTION_TYPES["local"](Cfg(), has_relative_attention_bias=True)
+    eye = torch.eye(H * D)
+    g = torch.Generator().manual_seed(3)
+    pk_, pv_ = torch.randperm(H * D, generator=g), torch.randperm(H * D, generator=g)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    with torch.no_grad():
+        mod.q.weight.copy_(eye); mod.k.weight.copy_(eye[pk_]); mod.v.weight.copy_(eye[pv_]); mod.o.weight.copy_(eye)
+        mod.relative_attention_bias.weight.copy_(table.float())
+    mod = mod.cuda().to(dt).train()
+    hidden = seeded((B, L, H * D), 5, 0.5, dtype=dt)
+    dout = seeded((B, L, H * D), 6, dtype=dt)
+    mask = torch.zeros((B, L), dtype=torch.int64)
+    for b, n in enumerate(lens):
+        mask[b, :n] = 1
+    hid = hidden.cuda().requires_grad_(True)
+    out = mod(hid, mask=mask.cuda())[0]
+    (out.float() * (dout.cuda().float() * mask.cuda()[..., None])).sum().backward()
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    href = hidden.float().clone().requires_grad_(True)
+    tref = table.float().clone().requires_grad_(True)
+    shape = lambda x: x.view(B, L, H, D).transpose(1, 2)
+    want = orc.local_attention_basic(shape(href), shape(href[..., pk_]), shape(href[..., pv_]), tref, bl,
+                                     key_padding_mask=mask.float())
+    want = want.transpose(1, 2).reshape(B, L, H * D)
+    (want * (dout.float() * mask[..., None])).sum().backward()
+    for b, n in enumerate(lens):
+        check_grad_close(hid.grad[b, :n], href.grad[b, :n], f"masked local hidden grad row {b}", rel=3e-2)
+        assert torch.count_nonzero(hid.grad[b, n:]) == 0
+    check_grad_close(mod.relative_attention_bias.weight.grad, tref.grad, "masked local dtable", floor=2.0)
+
+
 def test_gradients_at_a_long_sequence():
     # 4096 x 4096 keys, two heads: every tile class of the backward kernels (far tiles with one bias
     # bucket, diagonal tiles with per-element bias, the split last wave) in one call, against float32

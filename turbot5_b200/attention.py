@@ -74,22 +74,21 @@ def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
                                      window=None):
     """See `_dense_forward`; differentiable in q, k, v and the bias table.  `local_block` turns the
     call into block-local attention (T5LocalAttention: the keys of the three neighbouring blocks);
-    `window` into a sliding window |n - query position| < window (forward only)."""
+    `window` into a sliding window |n - query position| < window (tensor-core kernels only:
+    bf16/fp16, head dim 64 or 128, not causal)."""
     local_block = int(local_block or 0)
+    window = int(window or 0)
+    if local_block or window:
+        balance_last_wave = False
     if local_block:
-        q_pos_offset, balance_last_wave = 0, False
-    if window:
-        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
-            raise NotImplementedError("sliding-window attention has no backward kernel")
-        return _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset=q_pos_offset,
-                              return_lse=return_lse, kernel=kernel, balance_last_wave=False, window=int(window))
+        q_pos_offset = 0
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _DenseAttention.apply(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset,
-                                         kernel, balance_last_wave, local_block)
+                                         kernel, balance_last_wave, local_block, window)
         return (out, lse) if return_lse else out
     return _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset=q_pos_offset,
                           return_lse=return_lse, kernel=kernel, balance_last_wave=balance_last_wave,
-                          local_block=local_block)
+                          local_block=local_block, window=window)
 
 
 def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, MAX_DISTANCE=128, *,
@@ -216,18 +215,14 @@ def flash_attention_with_fusing_bias_varlen(q, k, v, bias, cu_seqlens_q, cu_seql
                                             NUM_BUCKETS=32, MAX_DISTANCE=128, *, return_lse=False,
                                             kernel="auto", window=None):
     """See `_varlen_forward`; differentiable in q, k, v and the bias table.  `window`: sliding window
-    |n - query position| < window inside every sequence (forward only)."""
-    if window:
-        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
-            raise NotImplementedError("sliding-window attention has no backward kernel")
-        return _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, sm_scale,
-                               NUM_BUCKETS, MAX_DISTANCE, return_lse=return_lse, kernel=kernel, window=int(window))
+    |n - query position| < window inside every sequence (tensor-core kernels only)."""
+    window = int(window or 0)
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _VarlenAttention.apply(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
-                                          causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, kernel)
+                                          causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, kernel, window)
         return (out, lse) if return_lse else out
     return _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal, sm_scale,
-                           NUM_BUCKETS, MAX_DISTANCE, return_lse=return_lse, kernel=kernel)
+                           NUM_BUCKETS, MAX_DISTANCE, return_lse=return_lse, kernel=kernel, window=window)
 
 
 def _varlen_forward(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, causal=False,
@@ -333,8 +328,9 @@ def _attention_backward(keep, out, lse, dout, varlen):
             g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
         st = nat.lib().t5b_attention_bwd(g, nat.stream_ptr(q.device))
     if st == nat.ERR_UNSUPPORTED:
-        raise NotImplementedError("no backward kernel for this call (max_distance above 2048, or "
-                                  "kernel='tcgen05' on a shape its backward does not take: bf16/fp16, head dim 64)")
+        raise NotImplementedError("no backward kernel for this call (max_distance above 2048, a sliding window or "
+                                  "kernel='tcgen05' on a shape the tensor-core backward does not take: bf16/fp16, "
+                                  "head dim 64 or 128)")
     nat.check(st, "flash_attention_with_fusing_bias (backward)")
     if dtable is not None:
         dtable = dtable[: table.shape[0]].to(table.dtype)
@@ -347,11 +343,11 @@ class _DenseAttention(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, q_pos_offset, kernel, balance,
-                local_block=0):
+                local_block=0, window=0):
         keep = {}
         out, lse = _dense_forward(q, k, v, bias, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE,
                                   q_pos_offset=q_pos_offset, return_lse=True, kernel=kernel,
-                                  balance_last_wave=balance, _keep=keep, local_block=local_block)
+                                  balance_last_wave=balance, _keep=keep, local_block=local_block, window=window)
         ctx.keep = keep
         ctx.save_for_backward(out, lse)
         ctx.mark_non_differentiable(lse)
@@ -361,7 +357,7 @@ class _DenseAttention(torch.autograd.Function):
     def backward(ctx, dout, _dlse):
         out, lse = ctx.saved_tensors
         dq, dk, dv, dtable = _attention_backward(ctx.keep, out, lse, dout, varlen=False)
-        return dq, dk, dv, dtable, None, None, None, None, None, None, None, None
+        return dq, dk, dv, dtable, None, None, None, None, None, None, None, None, None
 
 
 class _VarlenAttention(torch.autograd.Function):
@@ -369,10 +365,11 @@ class _VarlenAttention(torch.autograd.Function):
     (src/turbot5/ops/varlen_fused_bias_attn.py: FlashAttentionBias of that file)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, bias, cu_q, cu_k, max_q, max_k, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, kernel):
+    def forward(ctx, q, k, v, bias, cu_q, cu_k, max_q, max_k, causal, sm_scale, NUM_BUCKETS, MAX_DISTANCE, kernel,
+                window=0):
         keep = {}
         out, lse = _varlen_forward(q, k, v, bias, cu_q, cu_k, max_q, max_k, causal, sm_scale, NUM_BUCKETS,
-                                   MAX_DISTANCE, return_lse=True, kernel=kernel, _keep=keep)
+                                   MAX_DISTANCE, return_lse=True, kernel=kernel, _keep=keep, window=window)
         ctx.keep = keep
         ctx.save_for_backward(out, lse)
         ctx.mark_non_differentiable(lse)
@@ -382,7 +379,7 @@ class _VarlenAttention(torch.autograd.Function):
     def backward(ctx, dout, _dlse):
         out, lse = ctx.saved_tensors
         dq, dk, dv, dtable = _attention_backward(ctx.keep, out, lse, dout, varlen=True)
-        return dq, dk, dv, dtable, None, None, None, None, None, None, None, None, None
+        return dq, dk, dv, dtable, None, None, None, None, None, None, None, None, None, None
 
 
 def _scratch(device, kind: str, nbytes: int) -> torch.Tensor:

@@ -74,7 +74,9 @@ extern "C" int t5b_attention_bwd(const t5b_attn_bwd_args* g, void* stream) {
   if (!a->q || !a->k || !a->v || !a->out || !a->lse) return T5B_ERR_ARG;
   if (!g->dout || !g->dq || !g->dk || !g->dv || !g->delta) return T5B_ERR_ARG;
   if (a->local_block != 0 && (!sm100_bwd_supports(*g) || a->kernel == T5B_KERNEL_SIMT)) return T5B_ERR_UNSUPPORTED;
-  if (a->window != 0 || a->out_f32 != 0) return T5B_ERR_UNSUPPORTED;       // forward-only modes
+  if (a->out_f32 != 0) return T5B_ERR_UNSUPPORTED;                        // a forward-only mode
+  if (a->window != 0 && (a->window < 0 || a->causal || a->local_block != 0 || !sm100_bwd_supports(*g) ||
+                         a->kernel == T5B_KERNEL_SIMT)) return T5B_ERR_UNSUPPORTED;
   if (a->table && !g->dtable) return T5B_ERR_ARG;
   if ((varlen ? a->total_k : a->N) == 0 || (varlen ? a->total_q : a->M) == 0) return T5B_ERR_UNSUPPORTED;
   BucketSpec spec;

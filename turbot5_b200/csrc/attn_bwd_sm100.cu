@@ -225,6 +225,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   }
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
+  if (p.window > 0) {
+    // sliding window |key - query position| < window: the key tiles that hold a visible key of any row
+    n_base = max(0, qpos0 - p.window + 1) / BT * BT;
+    kv_end = min(kv_end, qpos0 + rows_in_tile - 1 + p.window);
+  }
   const int n_kv_all = kv_end > n_base ? (kv_end - n_base + BT - 1) / BT : 0;
   const int kv_per = (n_kv_all + parts - 1) / parts;
   const int kv_first = min(part * kv_per, n_kv_all);      // this block's key tiles: [kv_first, kv_first + n_kv)
@@ -415,7 +420,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_S_FREE));
 
-      const bool need_mask = (n0 + BT > len_k) || (p.causal && (n0 + BT - 1 > qpos0));
+      const bool need_mask = (n0 + BT > len_k) || (p.causal && (n0 + BT - 1 > qpos0)) ||
+                             (p.window > 0 && (n0 <= qpos0 + BM - 1 - p.window || n0 + BT - 1 >= qpos0 + p.window));
       int bias_mode = 0;
       float bias_const = 0.f;
       if (has_bias) {
@@ -425,7 +431,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         else bias_mode = 2;
       }
       const int lut0 = n0 + c0 - qpos + md + LUT_PAD;      // table index of column 0 of this thread
-      const int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;
+      int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;     // columns < n_valid are visible
+      int n_lo = -(1 << 30);                                                 // ... from column n_lo on
+      if (p.window > 0) {
+        n_valid = min(n_valid, qpos + p.window - n0 - c0);
+        n_lo = qpos - p.window + 1 - n0 - c0;
+      }
       uint32_t pk[16];
       float ds_sum = 0.f;
       if (!need_mask && bias_mode != 2) {
@@ -466,7 +477,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             const int c = 2 * i + u;
             const float bias = bias_mode == 2 ? lut[lut0 + c] : bias_const;
             float x = fmaf(__uint_as_float(sv[c]), scale, bias) - lse2;
-            if (need_mask && c >= n_valid) x = -INFINITY;
+            if (need_mask && (c >= n_valid || c < n_lo)) x = -INFINITY;
             const float pr = fast_exp2(x);
             const float d = pr * (__uint_as_float(dp[c]) - delta_r);
             dsv[u] = d;
@@ -697,6 +708,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     const int kb = key0 / bl;
     i_first = max(0, (kb - 1) * bl) / BT;
     n_qt_all = (min(len_q, (kb + 2) * bl) + BT - 1) / BT;
+  }
+  if (p.window > 0) {
+    // sliding window: the queries within (key - window, key + window) of a key of this tile
+    i_first = max(0, key0 - p.window + 1 - q_off) / BT;
+    n_qt_all = (min(len_q, max(0, key0 + BM - 1 + p.window - q_off)) + BT - 1) / BT;
   }
   int n_qt = max(0, n_qt_all - i_first);
   if (parts > 1) {       // this block's share of the query tiles
@@ -941,7 +957,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       // causal boundary crosses the tile, one bias value.  Two halves of 16 columns: each is
       // stored as soon as it is packed, which keeps the live registers below the limit.
       const int q_lo = q_off + (i_first + i) * BT;      // position of the tile's first query
-      const bool tile_masked = (key0 + BM > len_k) || (p.causal && key0 + BM - 1 > q_lo);
+      const bool tile_masked = (key0 + BM > len_k) || (p.causal && key0 + BM - 1 > q_lo) ||
+                               (p.window > 0 && (key0 + BM - 1 - q_lo >= p.window || q_lo + BT - 1 - key0 >= p.window));
       if constexpr (NBUF == 1) {
         // pass 1: P^T = exp2(S^T scale + bias - lse), kept in sv as float32 and stored as the A
         // operand of the dV product.  Two halves of 16 columns, each stored as soon as it is packed.
@@ -984,7 +1001,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
                 float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
                 // masked: key outside the sequence, or (causal) after the query
-                if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
+                if (!key_ok || (p.causal && key > qp0 + c) ||
+                    (p.window > 0 && (key - (qp0 + c) >= p.window || (qp0 + c) - key >= p.window))) x = -INFINITY;
                 pv[u] = fast_exp2(x);
                 sv[c] = __float_as_uint(pv[u]);
               }
@@ -1069,7 +1087,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 const float bias = bias_mode == 2 ? lut[lut0 - c] : bias_const;
                 float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
                 // masked: key outside the sequence, or (causal) after the query
-                if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
+                if (!key_ok || (p.causal && key > qp0 + c) ||
+                    (p.window > 0 && (key - (qp0 + c) >= p.window || (qp0 + c) - key >= p.window))) x = -INFINITY;
                 const float pr = fast_exp2(x);
                 pv[u] = pr;
                 dv2[u] = pr * (__uint_as_float(dp[c]) + vd[c]);
@@ -1267,6 +1286,11 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     const int kb = key0 / bl;
     i_first = max(0, (kb - 1) * bl) / BQ;
     n_qt_all = (min(len_q, (kb + 2) * bl) + BQ - 1) / BQ;
+  }
+  if (p.window > 0) {
+    // sliding window: the queries within (key - window, key + window) of a key of this tile
+    i_first = max(0, key0 - p.window + 1 - q_off) / BQ;
+    n_qt_all = (min(len_q, max(0, key0 + BM - 1 + p.window - q_off)) + BQ - 1) / BQ;
   }
   int n_qt = max(0, n_qt_all - i_first);
   if (parts > 1) {       // this block's share of the query tiles
@@ -1496,7 +1520,8 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
       // loading warp; otherwise the bias is looked up per element (the table is padded with its
       // end values, so any key - query of such a tile is inside it)
       const bool per_element = has_bias && !(key0 - (q_lo + BQ - 1) >= md || key0 + BM - 1 - q_lo <= -md);
-      const bool masked = warp_beyond_keys || (p.causal && wkey0 + 31 > qp0);
+      const bool masked = warp_beyond_keys || (p.causal && wkey0 + 31 > qp0) ||
+                          (p.window > 0 && (wkey0 + 31 - qp0 >= p.window || qp0 + 31 - wkey0 >= p.window));
       const float* vl = &ctl->vec[s][0][cg * 32];
       const float* vd = &ctl->vec[s][1][cg * 32];
       // column c has delta = key - (qp0 + c): the table index falls as c grows
@@ -1560,7 +1585,8 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
             const float bias = per_element ? lrow[-c] : 0.f;
             float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
             // masked: key outside the sequence, or (causal) after the query
-            if (!key_ok || (p.causal && key > qp0 + c)) x = -INFINITY;
+            if (!key_ok || (p.causal && key > qp0 + c) ||
+                (p.window > 0 && (key - (qp0 + c) >= p.window || (qp0 + c) - key >= p.window))) x = -INFINITY;
             pv[u] = fast_exp2(x);
             dv2[u] = pv[u] * (__uint_as_float(dp[c]) + vd[c]);
           }
@@ -1676,7 +1702,7 @@ static BwdPlan sm100_bwd_plan(const t5b_attn_args& a) {
   t.q_parts = t.k_parts = 1;
   t.q_rem = t.k_rem = 0;
   t.cnt_bytes = t.dq_bytes = t.dk_bytes = 0;
-  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || nq > 0x3fffffffLL || nk > 0x3fffffffLL) return t;
+  if (a.cu_seqlens_q != nullptr || a.causal || a.local_block > 0 || a.window > 0 || nq > 0x3fffffffLL || nk > 0x3fffffffLL) return t;
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess ||
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {

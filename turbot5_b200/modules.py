@@ -278,7 +278,8 @@ class T5LocalFlashAttention(T5FlashAttention):
     attentions.py:600-603,619-621) makes a pair visible when both tokens are valid and
     |key - query| < block length: a sliding window over the valid keys.  Here the valid tokens are
     packed (no host synchronisation), the packed-sequence kernel runs with that window, and the
-    rows of padded queries come back as zeros; forward only.  As in the full-attention module the
+    rows of padded queries come back as zeros (differentiable: the packed kernel's backward takes
+    the same window).  As in the full-attention module the
     mask is taken to be right-padded (positions are counted inside the packed sequences).
     """
 
