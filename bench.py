@@ -677,13 +677,19 @@ def config2_measurement(t5b, dev, rank, world, dist):
         ms_enc = _time_ranks(lambda: model.encoder.forward_fused(ids_l), 10, dev, world, dist, warm=3)
         ms_enc_unfused = _time_ranks(lambda: model.encoder(ids_l), 10, dev, world, dist, warm=3)
         ms_full = _time_ranks(lambda: model(ids_l, dec_l), 10, dev, world, dist, warm=3)
+        # the same pass as one CUDA graph (token ids copied into the graph's buffers every call)
+        from turbot5_b200.t5 import GraphedForward
+        graphed = GraphedForward(model, per, Le, Ld, dev)
+        ms_graph = _time_ranks(lambda: graphed(ids_l, dec_l), 10, dev, world, dist, warm=3)
     n_b = per * world
     return {"workload": f"T5-base 12+12 layers bf16, {n_b} x {Le} encoder tokens + {n_b} x {Ld} decoder tokens, "
                         f"batch sharded {per} per GPU, no communication", "scaling": "strong",
             "encoder_ms": ms_enc, "encoder_tokens_per_s": n_b * Le / (ms_enc * 1e-3),
             "encoder_ms_without_fused_token_kernels": ms_enc_unfused,
             "encoder_decoder_forward_ms": ms_full,
-            "encoder_decoder_tokens_per_s": n_b * (Le + Ld) / (ms_full * 1e-3)}
+            "encoder_decoder_tokens_per_s": n_b * (Le + Ld) / (ms_full * 1e-3),
+            "encoder_decoder_forward_ms_cuda_graph": ms_graph,
+            "encoder_decoder_tokens_per_s_cuda_graph": n_b * (Le + Ld) / (ms_graph * 1e-3)}
 
 
 def secondary_measurements(t5b, dev):

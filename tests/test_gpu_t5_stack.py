@@ -90,6 +90,25 @@ def test_cuda_graph_decoding_equals_eager_decoding():
     assert (eager_last.float() - graph_last.float()).abs().max().item() < 1e-2
 
 
+def test_cuda_graph_forward_equals_eager_forward():
+    """The whole teacher-forced pass as one graph: same logits as the eager pass, for two different
+    inputs through the same graph (the ids are copied into the graph's buffers), wrong shapes refused."""
+    from turbot5_b200.t5 import GraphedForward
+    model = _model(torch.bfloat16, d_model=128, num_heads=4, d_ff=256)
+    g = torch.Generator().manual_seed(8)
+    graphed = GraphedForward(model, 3, 260, 24)
+    for _ in range(2):
+        ids = torch.randint(0, 128, (3, 260), generator=g).cuda()
+        dec = torch.randint(0, 128, (3, 24), generator=g).cuda()
+        with torch.no_grad():
+            want = model(ids, dec)
+        got = graphed(ids, dec)
+        torch.cuda.synchronize()
+        assert (got.float() - want.float()).abs().max().item() < 1e-2
+    with pytest.raises(ValueError):
+        graphed(ids[:2], dec[:2])
+
+
 def test_cuda_graph_decoding_with_a_long_cache_splits_the_keys():
     """A cache long enough that the captured self-attention launch splits the keys (the split count
     comes from the capacity and stays the same in every replay): tokens as in eager decoding."""

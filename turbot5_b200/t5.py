@@ -453,6 +453,41 @@ class GraphedDecoding:
         self.steps_done += 1
 
 
+class GraphedForward:
+    """A whole teacher-forced forward pass (encoder, decoder, LM head) of fixed shapes as one CUDA graph.
+
+    At small batches the pass is a few hundred short kernels and the host's launch rate, not the
+    GPU, sets its duration (twelve decoder layers over 4 x 128 tokens: 4.4 ms of launches for well
+    under 2 ms of work).  The pass is run once on a side stream (cuBLAS handles, stacked weights
+    and the library's per-stream scratch then exist), captured, and replayed by `__call__`, which
+    copies the token ids into the graph's input buffers and returns the graph's logits buffer (a
+    static tensor: it is overwritten by the next call).  Inference only, unpadded inputs.
+    """
+
+    def __init__(self, model, batch, enc_len, dec_len, device=None):
+        dev = torch.device(device) if device is not None else model.shared.weight.device
+        self.model = model
+        self.input_ids = torch.zeros((batch, enc_len), dtype=torch.long, device=dev)
+        self.decoder_input_ids = torch.zeros((batch, dec_len), dtype=torch.long, device=dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side), torch.no_grad():
+            model(self.input_ids, self.decoder_input_ids)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.logits = model(self.input_ids, self.decoder_input_ids)
+
+    def __call__(self, input_ids, decoder_input_ids):
+        if input_ids.shape != self.input_ids.shape or decoder_input_ids.shape != self.decoder_input_ids.shape:
+            raise ValueError("GraphedForward was captured for ids of shapes %s and %s" %
+                             (tuple(self.input_ids.shape), tuple(self.decoder_input_ids.shape)))
+        self.input_ids.copy_(input_ids, non_blocking=True)
+        self.decoder_input_ids.copy_(decoder_input_ids, non_blocking=True)
+        self.graph.replay()
+        return self.logits
+
+
 class T5ForConditionalGeneration(nn.Module):
     def __init__(self, cfg: T5StackConfig):
         super().__init__()
