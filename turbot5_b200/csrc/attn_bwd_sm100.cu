@@ -162,12 +162,15 @@ enum {
 static_assert(B_NUM <= 24, "barrier slots");
 
 // ======================================================================== dQ and dtable
-template <bool kBf16, int HD>
+// kWindow (all three kernels): the sliding-window mode is compiled into kernels of its own, so that
+// its extra per-row values do not cost the plain kernels registers.
+template <bool kBf16, int HD, bool kWindow>
 __global__ void __launch_bounds__(NUM_THREADS, (HD == 64 ? 2 : 1))
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                    const __grid_constant__ AttnParams p, const __grid_constant__ BwdExtra e,
                    const __grid_constant__ BucketSpec spec) {
+  const int window = kWindow ? p.window : 0;
   using G = BGeo<HD>;
   constexpr int NSUB = G::NSUB, SUB_BIG = G::SUB_BIG, SUB_SMALL = G::SUB_SMALL;
   constexpr int BIG_BYTES = G::BIG_BYTES, SMALL_BYTES = G::SMALL_BYTES, SMEM_TILES = G::SMEM_TILES;
@@ -225,10 +228,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   }
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
-  if (p.window > 0) {
+  if (window > 0) {
     // sliding window |key - query position| < window: the key tiles that hold a visible key of any row
-    n_base = max(0, qpos0 - p.window + 1) / BT * BT;
-    kv_end = min(kv_end, qpos0 + rows_in_tile - 1 + p.window);
+    n_base = max(0, qpos0 - window + 1) / BT * BT;
+    kv_end = min(kv_end, qpos0 + rows_in_tile - 1 + window);
   }
   const int n_kv_all = kv_end > n_base ? (kv_end - n_base + BT - 1) / BT : 0;
   const int kv_per = (n_kv_all + parts - 1) / parts;
@@ -421,7 +424,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       if (lane == 0) mbar_arrive(bar(B_S_FREE));
 
       const bool need_mask = (n0 + BT > len_k) || (p.causal && (n0 + BT - 1 > qpos0)) ||
-                             (p.window > 0 && (n0 <= qpos0 + BM - 1 - p.window || n0 + BT - 1 >= qpos0 + p.window));
+                             (window > 0 && (n0 <= qpos0 + BM - 1 - window || n0 + BT - 1 >= qpos0 + window));
       int bias_mode = 0;
       float bias_const = 0.f;
       if (has_bias) {
@@ -433,9 +436,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const int lut0 = n0 + c0 - qpos + md + LUT_PAD;      // table index of column 0 of this thread
       int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;     // columns < n_valid are visible
       int n_lo = -(1 << 30);                                                 // ... from column n_lo on
-      if (p.window > 0) {
-        n_valid = min(n_valid, qpos + p.window - n0 - c0);
-        n_lo = qpos - p.window + 1 - n0 - c0;
+      if (window > 0) {
+        n_valid = min(n_valid, qpos + window - n0 - c0);
+        n_lo = qpos - window + 1 - n0 - c0;
       }
       uint32_t pk[16];
       float ds_sum = 0.f;
@@ -633,12 +636,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 }
 
 // ======================================================================== dK and dV
-template <bool kBf16, int HD>
+template <bool kBf16, int HD, bool kWindow>
 __global__ void __launch_bounds__(NUM_THREADS, (HD == 64 ? 2 : 1))
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                     const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                     const __grid_constant__ AttnParams p, const __grid_constant__ BwdExtra e,
                     const __grid_constant__ BucketSpec spec) {
+  const int window = kWindow ? p.window : 0;
   // tensor memory: S^T and dP^T (64 fp32 columns each, keys in the lanes); P^T and dS^T are
   // written over them in place: the 32 query columns of row half q sit, packed, in the first
   // 16 columns of that half's own 32 (a K=16 step of the second MMA takes any column address)
@@ -709,10 +713,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     i_first = max(0, (kb - 1) * bl) / BT;
     n_qt_all = (min(len_q, (kb + 2) * bl) + BT - 1) / BT;
   }
-  if (p.window > 0) {
+  if (window > 0) {
     // sliding window: the queries within (key - window, key + window) of a key of this tile
-    i_first = max(0, key0 - p.window + 1 - q_off) / BT;
-    n_qt_all = (min(len_q, max(0, key0 + BM - 1 + p.window - q_off)) + BT - 1) / BT;
+    i_first = max(0, key0 - window + 1 - q_off) / BT;
+    n_qt_all = (min(len_q, max(0, key0 + BM - 1 + window - q_off)) + BT - 1) / BT;
   }
   int n_qt = max(0, n_qt_all - i_first);
   if (parts > 1) {       // this block's share of the query tiles
@@ -958,7 +962,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
       // stored as soon as it is packed, which keeps the live registers below the limit.
       const int q_lo = q_off + (i_first + i) * BT;      // position of the tile's first query
       const bool tile_masked = (key0 + BM > len_k) || (p.causal && key0 + BM - 1 > q_lo) ||
-                               (p.window > 0 && (key0 + BM - 1 - q_lo >= p.window || q_lo + BT - 1 - key0 >= p.window));
+                               (window > 0 && (key0 + BM - 1 - q_lo >= window || q_lo + BT - 1 - key0 >= window));
       if constexpr (NBUF == 1) {
         // pass 1: P^T = exp2(S^T scale + bias - lse), kept in sv as float32 and stored as the A
         // operand of the dV product.  Two halves of 16 columns, each stored as soon as it is packed.
@@ -1002,7 +1006,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
                 // masked: key outside the sequence, or (causal) after the query
                 if (!key_ok || (p.causal && key > qp0 + c) ||
-                    (p.window > 0 && (key - (qp0 + c) >= p.window || (qp0 + c) - key >= p.window))) x = -INFINITY;
+                    (window > 0 && (key - (qp0 + c) >= window || (qp0 + c) - key >= window))) x = -INFINITY;
                 pv[u] = fast_exp2(x);
                 sv[c] = __float_as_uint(pv[u]);
               }
@@ -1088,7 +1092,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
                 float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
                 // masked: key outside the sequence, or (causal) after the query
                 if (!key_ok || (p.causal && key > qp0 + c) ||
-                    (p.window > 0 && (key - (qp0 + c) >= p.window || (qp0 + c) - key >= p.window))) x = -INFINITY;
+                    (window > 0 && (key - (qp0 + c) >= window || (qp0 + c) - key >= window))) x = -INFINITY;
                 const float pr = fast_exp2(x);
                 pv[u] = pr;
                 dv2[u] = pr * (__uint_as_float(dp[c]) + vd[c]);
@@ -1223,12 +1227,13 @@ __host__ __device__ inline size_t smem_bytes(int lut_entries) {
 }
 }  // namespace wide
 
-template <bool kBf16>
+template <bool kBf16, bool kWindow>
 __global__ void __launch_bounds__(wide::THREADS, 1)
 attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                          const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                          const __grid_constant__ AttnParams p, const __grid_constant__ BwdExtra e,
                          const __grid_constant__ BucketSpec spec) {
+  const int window = kWindow ? p.window : 0;
   using namespace wide;
   constexpr int HD = 64;
   extern __shared__ uint8_t smem_raw[];
@@ -1287,10 +1292,10 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     i_first = max(0, (kb - 1) * bl) / BQ;
     n_qt_all = (min(len_q, (kb + 2) * bl) + BQ - 1) / BQ;
   }
-  if (p.window > 0) {
+  if (window > 0) {
     // sliding window: the queries within (key - window, key + window) of a key of this tile
-    i_first = max(0, key0 - p.window + 1 - q_off) / BQ;
-    n_qt_all = (min(len_q, max(0, key0 + BM - 1 + p.window - q_off)) + BQ - 1) / BQ;
+    i_first = max(0, key0 - window + 1 - q_off) / BQ;
+    n_qt_all = (min(len_q, max(0, key0 + BM - 1 + window - q_off)) + BQ - 1) / BQ;
   }
   int n_qt = max(0, n_qt_all - i_first);
   if (parts > 1) {       // this block's share of the query tiles
@@ -1521,7 +1526,7 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
       // end values, so any key - query of such a tile is inside it)
       const bool per_element = has_bias && !(key0 - (q_lo + BQ - 1) >= md || key0 + BM - 1 - q_lo <= -md);
       const bool masked = warp_beyond_keys || (p.causal && wkey0 + 31 > qp0) ||
-                          (p.window > 0 && (wkey0 + 31 - qp0 >= p.window || qp0 + 31 - wkey0 >= p.window));
+                          (window > 0 && (wkey0 + 31 - qp0 >= window || qp0 + 31 - wkey0 >= window));
       const float* vl = &ctl->vec[s][0][cg * 32];
       const float* vd = &ctl->vec[s][1][cg * 32];
       // column c has delta = key - (qp0 + c): the table index falls as c grows
@@ -1586,7 +1591,7 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
             float x = fmaf(__uint_as_float(sv[c]), scale, bias) + vl[c];
             // masked: key outside the sequence, or (causal) after the query
             if (!key_ok || (p.causal && key > qp0 + c) ||
-                (p.window > 0 && (key - (qp0 + c) >= p.window || (qp0 + c) - key >= p.window))) x = -INFINITY;
+                (window > 0 && (key - (qp0 + c) >= window || (qp0 + c) - key >= window))) x = -INFINITY;
             pv[u] = fast_exp2(x);
             dv2[u] = pv[u] * (__uint_as_float(dp[c]) + vd[c]);
           }
@@ -1834,14 +1839,24 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
 
   const int lut_n = a.table ? 2 * spec.max_distance + 1 + 2 * LUT_PAD : 0;
   const size_t smem = HD == 64 ? smem_bytes<64>(lut_n) : smem_bytes<128>(lut_n);
-  auto kq = HD == 64 ? (bf16 ? attn_bwd_dq_kernel<true, 64> : attn_bwd_dq_kernel<false, 64>)
-                     : (bf16 ? attn_bwd_dq_kernel<true, 128> : attn_bwd_dq_kernel<false, 128>);
-  auto kkv = HD == 64 ? (bf16 ? attn_bwd_dkv_kernel<true, 64> : attn_bwd_dkv_kernel<false, 64>)
-                      : (bf16 ? attn_bwd_dkv_kernel<true, 128> : attn_bwd_dkv_kernel<false, 128>);
-  static std::atomic<bool> attr_set[64][4];   // any thread may get here first
+  const bool win = a.window > 0;
+  using KernelFn = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, CUtensorMap, AttnParams, BwdExtra, BucketSpec);
+  static const KernelFn kq_all[2][2][2] = {
+      {{attn_bwd_dq_kernel<false, 64, false>, attn_bwd_dq_kernel<false, 64, true>},
+       {attn_bwd_dq_kernel<true, 64, false>, attn_bwd_dq_kernel<true, 64, true>}},
+      {{attn_bwd_dq_kernel<false, 128, false>, attn_bwd_dq_kernel<false, 128, true>},
+       {attn_bwd_dq_kernel<true, 128, false>, attn_bwd_dq_kernel<true, 128, true>}}};
+  static const KernelFn kkv_all[2][2][2] = {
+      {{attn_bwd_dkv_kernel<false, 64, false>, attn_bwd_dkv_kernel<false, 64, true>},
+       {attn_bwd_dkv_kernel<true, 64, false>, attn_bwd_dkv_kernel<true, 64, true>}},
+      {{attn_bwd_dkv_kernel<false, 128, false>, attn_bwd_dkv_kernel<false, 128, true>},
+       {attn_bwd_dkv_kernel<true, 128, false>, attn_bwd_dkv_kernel<true, 128, true>}}};
+  const KernelFn kq = kq_all[HD == 64 ? 0 : 1][bf16 ? 1 : 0][win ? 1 : 0];
+  const KernelFn kkv = kkv_all[HD == 64 ? 0 : 1][bf16 ? 1 : 0][win ? 1 : 0];
+  static std::atomic<bool> attr_set[64][8];   // any thread may get here first
   int dev = 0;
   cudaGetDevice(&dev);
-  const int which = (bf16 ? 1 : 0) + (HD == 64 ? 0 : 2);
+  const int which = (bf16 ? 1 : 0) + (HD == 64 ? 0 : 2) + (win ? 4 : 0);
   if (dev < 0 || dev >= 64 || !attr_set[dev][which].load(std::memory_order_acquire)) {
     const int lut_max = 2 * 2048 + 1 + 2 * LUT_PAD;
     const int smem_max = (int)(HD == 64 ? smem_bytes<64>(lut_max) : smem_bytes<128>(lut_max));
@@ -1871,15 +1886,17 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
     if (cudaGetLastError() != cudaSuccess) return T5B_ERR_LAUNCH;
   }
   if (gk.x > 0 && dkv_wide(a)) {
-    auto kw = bf16 ? attn_bwd_dkv_wide_kernel<true> : attn_bwd_dkv_wide_kernel<false>;
-    static std::atomic<bool> wide_attr_set[64][2];
-    if (dev < 0 || dev >= 64 || !wide_attr_set[dev][bf16 ? 1 : 0].load(std::memory_order_acquire)) {
+    const KernelFn kw = bf16 ? (win ? attn_bwd_dkv_wide_kernel<true, true> : attn_bwd_dkv_wide_kernel<true, false>)
+                             : (win ? attn_bwd_dkv_wide_kernel<false, true> : attn_bwd_dkv_wide_kernel<false, false>);
+    static std::atomic<bool> wide_attr_set[64][4];
+    const int which_w = (bf16 ? 1 : 0) + (win ? 2 : 0);
+    if (dev < 0 || dev >= 64 || !wide_attr_set[dev][which_w].load(std::memory_order_acquire)) {
       const int smem_max = (int)wide::smem_bytes(2 * 2048 + 1 + 2 * wide::PAD);
       if (cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) != cudaSuccess) {
         cudaGetLastError();
         return T5B_ERR_LAUNCH;
       }
-      if (dev >= 0 && dev < 64) wide_attr_set[dev][bf16 ? 1 : 0].store(true, std::memory_order_release);
+      if (dev >= 0 && dev < 64) wide_attr_set[dev][which_w].store(true, std::memory_order_release);
     }
     const size_t smem_w = wide::smem_bytes(a.table ? 2 * spec.max_distance + 1 + 2 * wide::PAD : 0);
     kw<<<gk, wide::THREADS, smem_w, stream>>>(k128, v128, q128, do128, p, e, spec);

@@ -115,7 +115,10 @@ __host__ __device__ inline size_t smem_bytes(int lut_entries) {
 
 // kPoly: of every 8 column pairs of an unmasked tile, this many take their exponentials on the FMA
 // pipe (PolyExp above) instead of the exponential unit; 8 = all of them (used by the parity tests).
-template <bool kBf16, int HD, int kPoly>
+// kWindow: the sliding-window mode is compiled into a kernel of its own (with it in the plain kernel
+// the two extra per-row values of the masked path raised the spills of the softmax loop from 108 to
+// 264 bytes and the 8k forward went from 0.577 to 0.67 ms).
+template <bool kBf16, int HD, int kPoly, bool kWindow = false>
 __global__ void __launch_bounds__(HD == 64 ? 288 : MAX_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k,
@@ -193,14 +196,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     len_k = (blk + 2) * bl;
   }
 
+  const int window = kWindow ? p.window : 0;
   // keys this tile can see
   int kv_end = len_k;
   if (p.causal) kv_end = min(len_k, qpos0 + rows_in_tile);
   // Sliding window (T5LocalAttention with its padding mask: |n - query| < window over the valid keys):
   // the tile walks the key tiles that hold a visible key for any of its rows.
-  if (p.window > 0) {
-    n_base = max(0, qpos0 - p.window + 1) / BN * BN;
-    kv_end = min(kv_end, qpos0 + rows_in_tile - 1 + p.window);
+  if (window > 0) {
+    n_base = max(0, qpos0 - window + 1) / BN * BN;
+    kv_end = min(kv_end, qpos0 + rows_in_tile - 1 + window);
   }
   const int n_kv_all = kv_end > n_base ? (kv_end - n_base + BN - 1) / BN : 0;
   // this block's share of the key tiles: [kv_first, kv_first + n_kv)
@@ -446,7 +450,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 
       // tile classification (uniform over the block)
       const bool need_mask = (n0 + BN > len_k) || (p.causal && (n0 + BN - 1 > qpos0)) ||
-                             (p.window > 0 && (n0 <= qpos0 + BM - 1 - p.window || n0 + BN - 1 >= qpos0 + p.window));
+                             (window > 0 && (n0 <= qpos0 + BM - 1 - window || n0 + BN - 1 >= qpos0 + window));
       int bias_mode = 0;            // 0 none, 1 constant over the tile, 2 per element
       float bias_const = 0.f;
       if (has_bias) {
@@ -483,9 +487,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           const float* brow = lut + (n0 + c0 - qpos + md + LUT_PAD);
           int n_valid = (p.causal ? min(len_k, qpos + 1) : len_k) - n0 - c0;   // columns < n_valid are visible
           int n_lo = -(1 << 30);                                               // ... from column n_lo on
-          if (p.window > 0) {
-            n_valid = min(n_valid, qpos + p.window - n0 - c0);
-            n_lo = qpos - p.window + 1 - n0 - c0;
+          if (window > 0) {
+            n_valid = min(n_valid, qpos + window - n0 - c0);
+            n_lo = qpos - window + 1 - n0 - c0;
           }
           #pragma unroll
           for (int c = 0; c < NCH; ++c) {
@@ -846,17 +850,17 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
     grid = dim3((unsigned)blocks, 1, 1);
   }
   if (grid.y > 65535 || grid.z > 65535) return T5B_ERR_SHAPE;
-  // kernel variant: [head dim 128][bf16][every exponential on the FMA pipe]
+  // kernel variant: [head dim 128][bf16][0: default, 1: every exponential on the FMA pipe, 2: sliding window]
   using KernelFn = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, AttnParams, BucketSpec);
-  static const KernelFn kernels[2][2][2] = {
-      {{attn_fwd_kernel<false, 64, T5B_FWD_POLY64>, attn_fwd_kernel<false, 64, 8>},
-       {attn_fwd_kernel<true, 64, T5B_FWD_POLY64>, attn_fwd_kernel<true, 64, 8>}},
-      {{attn_fwd_kernel<false, 128, 0>, attn_fwd_kernel<false, 128, 8>},
-       {attn_fwd_kernel<true, 128, 0>, attn_fwd_kernel<true, 128, 8>}}};
-  const int all_poly = a.kernel == T5B_KERNEL_TCGEN05_POLYEXP ? 1 : 0;
+  static const KernelFn kernels[2][2][3] = {
+      {{attn_fwd_kernel<false, 64, T5B_FWD_POLY64>, attn_fwd_kernel<false, 64, 8>, attn_fwd_kernel<false, 64, 0, true>},
+       {attn_fwd_kernel<true, 64, T5B_FWD_POLY64>, attn_fwd_kernel<true, 64, 8>, attn_fwd_kernel<true, 64, 0, true>}},
+      {{attn_fwd_kernel<false, 128, 0>, attn_fwd_kernel<false, 128, 8>, attn_fwd_kernel<false, 128, 0, true>},
+       {attn_fwd_kernel<true, 128, 0>, attn_fwd_kernel<true, 128, 8>, attn_fwd_kernel<true, 128, 0, true>}}};
+  const int all_poly = a.window > 0 ? 2 : (a.kernel == T5B_KERNEL_TCGEN05_POLYEXP ? 1 : 0);
   const KernelFn kern = kernels[HD == 64 ? 0 : 1][bf16 ? 1 : 0][all_poly];
   // opt in to > 48 KB of dynamic shared memory once per device and kernel (any thread may get here first)
-  static std::atomic<bool> attr_set[64][8];
+  static std::atomic<bool> attr_set[64][12];
   int dev = 0;
   cudaGetDevice(&dev);
   const int which = (bf16 ? 1 : 0) + (HD == 64 ? 0 : 2) + 4 * all_poly;

@@ -80,7 +80,7 @@ struct TileWork {
 // lists (ceil(len_q / TILE_M) tiles each).  Called by ONE full warp; the result
 // is valid in every lane.  No host-built work list, no host synchronisation.
 template <int TILE_M>
-__device__ __forceinline__ TileWork find_varlen_tile(const AttnParams& p, int blk) {
+__device__ __noinline__ TileWork find_varlen_tile(const AttnParams& p, int blk) {
   const int lane = threadIdx.x & 31;
   int found_b = -1, tile_in_seq = 0, acc = 0;
   // Longest sequences first: a tile's work grows with its sequence's key count, and a long tile
