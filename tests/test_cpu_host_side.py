@@ -181,3 +181,24 @@ def test_attention_workspace_query_is_zero_without_a_device_or_when_not_applicab
     assert L.t5b_attention_workspace_bytes(None) == 0
     a.dtype, a.D, a.B, a.H, a.M, a.N = nat.F32, 64, 1, 1, 4096, 4096
     assert L.t5b_attention_workspace_bytes(a) == 0        # float32 never takes the tensor-core kernel
+
+
+def test_hot_kernels_stay_within_their_register_and_spill_budget():
+    """ptxas's own report for the tensor-core kernels of the bench workload (bf16, head dim 64, no window):
+    two blocks per SM need <= 96 registers, and the softmax loops are written to (almost) fit in them.
+    Extra loop-live values show up here as spills long before any numerical test notices."""
+    from turbot5_b200 import build
+    fwd = build.resource_report("attn_fwd_sm100.cu")
+    bwd = build.resource_report("attn_bwd_sm100.cu")
+
+    def pick(report, *parts):
+        names = [n for n in report if all(p in n for p in parts)]
+        assert len(names) == 1, (parts, names)
+        return report[names[0]]
+    # mangled template arguments: Lb1 = bf16, Li64 = head dim, Li0 = no FMA-pipe exponentials, trailing Lb0 = no window
+    k = pick(fwd, "attn_fwd_kernel", "ILb1ELi64ELi0ELb0E")
+    assert k["registers"] <= 96 and k["spill_stores"] <= 128, k
+    k = pick(bwd, "attn_bwd_dq_kernel", "ILb1ELi64ELb0E")
+    assert k["registers"] <= 96 and k["spill_stores"] <= 16, k
+    k = pick(bwd, "attn_bwd_dkv_wide_kernel", "ILb1ELb0E")
+    assert k["registers"] <= 96 and k["spill_stores"] <= 64, k

@@ -42,9 +42,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     for src in SOURCES:
         obj = os.path.join(CSRC, src.replace(".cu", ".o"))
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
-        if verbose:
-            cmd.insert(1, "-Xptxas=-v")
+        cmd = [_nvcc(), "-Xptxas=-v", *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)))
         objs.append(obj)
     for src, pr in procs:
@@ -53,6 +51,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(out.decode())
         if pr.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{out.decode()}")
+        with open(_ptxas_log(src), "w") as f:      # registers and spills per kernel, see resource_report()
+            f.write(out.decode())
     tmp = LIB + ".tmp"
     link = [_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", tmp, *objs]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
@@ -60,6 +60,43 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("link failed:\n" + r.stdout.decode())
     os.replace(tmp, LIB)
     return LIB
+
+
+def _ptxas_log(src: str) -> str:
+    return os.path.join(CSRC, src.replace(".cu", ".ptxas.txt"))
+
+
+def resource_report(src: str) -> dict:
+    """{mangled kernel name: {"registers", "spill_stores", "spill_loads", "stack"}} from ptxas's own
+    report for one source file (written by `build`; compiled again here, without an object file, when
+    the library was built by an older copy of this script).  A few extra live values in a softmax loop
+    can turn into spills that cost a kernel 15 % without failing any test, so the tests hold the hot
+    kernels to a budget."""
+    import re
+    log = _ptxas_log(src)
+    if not os.path.exists(log) or os.path.getmtime(log) < os.path.getmtime(os.path.join(CSRC, src)):
+        cmd = [_nvcc(), "-Xptxas=-v", *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", os.devnull]
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n{r.stdout.decode()}")
+        with open(log, "w") as f:
+            f.write(r.stdout.decode())
+    report, name = {}, None
+    for line in open(log):
+        m = re.search(r"Compiling entry function '([^']+)'", line)
+        if m:
+            name = m.group(1)
+            report[name] = {"registers": 0, "spill_stores": 0, "spill_loads": 0, "stack": 0}
+            continue
+        if name is None:
+            continue
+        m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+        if m:
+            report[name].update(stack=int(m.group(1)), spill_stores=int(m.group(2)), spill_loads=int(m.group(3)))
+        m = re.search(r"Used (\d+) registers", line)
+        if m:
+            report[name]["registers"] = int(m.group(1))
+    return report
 
 
 if __name__ == "__main__":
