@@ -436,16 +436,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     for (int j = 0; j < n_kv; ++j) {
       const int n0 = n_first + j * BN;             // first key of the tile
       const int c0 = half * NH;                    // first column of this thread inside the tile
-      if (!mbar_wait_bounded_warp(bar(BAR_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
+      if (!mbar_wait_warp_fast(bar(BAR_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
 
       // this thread's scores -> registers, then give the S buffer back to the MMA warp
       uint32_t sv[NCH][32];
       #pragma unroll
       for (int c = 0; c < NCH; ++c) tmem_ld_x32(tS + 32 * c, sv[c]);
-      tmem_ld_wait();
+      tmem_ld_wait();                                // warp-wide: every lane's loads are complete
       tc_fence_before();
-      __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_S_FREE));
 
       // tile classification (uniform over the block)
@@ -587,7 +586,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // ---- partner's step; rescale O, l and (if the steps differ) this tile's P.  Rare.
       bool o_done_seen = (j == 0);
       if (j > 0) {
-        const bool met = mbar_wait_bounded_warp(pair_bar, pair_uses & 1u, abort_flag);
+        const bool met = mbar_wait_warp_fast(pair_bar, pair_uses & 1u, abort_flag);
         ++pair_uses;
         if (!met) { ok = false; fail_code = 33; break; }
         const float k_max = fmaxf(k_me, ctl->xchg[j & 1][half ^ 1][r]);
@@ -619,14 +618,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
       l_sum += t_sum;
       if (!o_done_seen) {
-        if (!mbar_wait_bounded_warp(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
+        if (!mbar_wait_warp_fast(bar(BAR_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
         tc_fence_after();
       }
       #pragma unroll
       for (int c = 0; c < NCH; ++c) tmem_st_x16(tP + 16 * c, pk[c]);
-      tmem_st_wait();
+      tmem_st_wait();                                // warp-wide: every lane's stores are complete
       tc_fence_before();
-      __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_P_FULL));
     }
 

@@ -138,6 +138,13 @@ __device__ __forceinline__ bool mbar_wait_bounded_warp(uint32_t bar, uint32_t pa
   return __all_sync(0xffffffffu, done);
 }
 
+// The same with one probe and one vote in the common case (the phase is already complete): the
+// vote makes the branch uniform, so no divergence bookkeeping surrounds the probe.
+__device__ __forceinline__ bool mbar_wait_warp_fast(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+  return mbar_wait_bounded_warp(bar, parity, abort_flag);
+}
+
 // 4-D tiled TMA load, global -> shared, completion on an mbarrier (no multicast).
 __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
