@@ -413,14 +413,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     for (int j = 0; j < n_kv; ++j) {
       const int n0 = n_first + j * BT;
       const int c0 = half * 32;
-      if (!mbar_wait_bounded_warp(bar(B_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
+      if (!mbar_wait_warp_fast(bar(B_S_FULL), (uint32_t)(j & 1), abort_flag)) { ok = false; fail_code = 30; break; }
       tc_fence_after();
       uint32_t sv[32], dp[32];
       tmem_ld_x32(tS, sv);
       tmem_ld_x32(tDP, dp);
       tmem_ld_wait();
       tc_fence_before();
-      __syncwarp();
+      // (tcgen05.wait is warp-wide: every lane's accesses are complete, no __syncwarp before the arrival)
       if (lane == 0) mbar_arrive(bar(B_S_FREE));
 
       const bool need_mask = (n0 + BT > len_k) || (p.causal && (n0 + BT - 1 > qpos0)) ||
@@ -493,13 +493,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       if (bias_mode == 1) far_pos += ds_sum;
       if (bias_mode == 3) far_neg += ds_sum;
       if (j > 0) {
-        if (!mbar_wait_bounded_warp(bar(B_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
+        if (!mbar_wait_warp_fast(bar(B_O_DONE), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; fail_code = 31; break; }
         tc_fence_after();
       }
       tmem_st_x16(tDS, pk);
       tmem_st_wait();
       tc_fence_before();
-      __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_P_FULL));
       // (after dS is published: the matrix product runs while the warp does its bookkeeping)
       if (bias_mode == 2) {
