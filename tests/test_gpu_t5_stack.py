@@ -107,6 +107,10 @@ def test_cuda_graph_forward_equals_eager_forward():
         assert (got.float() - want.float()).abs().max().item() < 1e-2
     with pytest.raises(ValueError):
         graphed(ids[:2], dec[:2])
+    got = model.forward_cuda_graph(ids, dec)          # the per-shape cache on the model
+    again = model.forward_cuda_graph(ids, dec)
+    torch.cuda.synchronize()
+    assert got is again and (got.float() - want.float()).abs().max().item() < 1e-2
 
 
 def test_cuda_graph_decoding_with_a_long_cache_splits_the_keys():

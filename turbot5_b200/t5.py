@@ -513,6 +513,17 @@ class T5ForConditionalGeneration(nn.Module):
         return self.logits(dec)
 
     @torch.no_grad()
+    def forward_cuda_graph(self, input_ids, decoder_input_ids):
+        """`forward` for unpadded inference inputs through a CUDA graph kept per input shape (captured on
+        first use; the returned logits live in the graph's buffer until the next call with that shape)."""
+        key = (tuple(input_ids.shape), tuple(decoder_input_ids.shape), input_ids.device)
+        graphs = self.__dict__.setdefault("_forward_graphs", {})
+        if key not in graphs:
+            graphs[key] = GraphedForward(self, input_ids.shape[0], input_ids.shape[1], decoder_input_ids.shape[1],
+                                         input_ids.device)
+        return graphs[key](input_ids, decoder_input_ids)
+
+    @torch.no_grad()
     def greedy_decode(self, encoder_hidden_states, steps, encoder_seqlens=None, use_cuda_graph=False):
         """Greedy generation from `decoder_start_token_id` with the preallocated cache.
 
