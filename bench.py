@@ -34,7 +34,7 @@ WORKLOAD = dict(name="fused-bias attention fwd, T5-base heads @8k", B=2, H=12, L
 L2_BYTES = 126 * 1024 * 1024
 # DRAM traffic (read + write) of one launch of the forward kernel on the workload above,
 # from an ncu capture of that launch (dram__bytes_read.sum + dram__bytes_write.sum).
-NCU_DRAM_BYTES_PER_LAUNCH = 75.6e6 + 13.5e6
+NCU_DRAM_BYTES_PER_LAUNCH = 75.6e6 + 10.7e6
 
 
 def flops_per_step(w):
