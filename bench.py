@@ -262,7 +262,15 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         _keep_stdout_for_json()
-        dist.init_process_group("nccl", device_id=dev)
+        # The collectives of the sequence-parallel leg run on a high-priority stream: their few blocks are then
+        # scheduled ahead of the attention blocks still waiting for an SM, so the gather really starts while the
+        # attention over the local keys runs.
+        opts = None
+        if os.environ.get("T5B_BENCH_NCCL_PRIORITY", "1") != "0":
+            from torch.distributed import ProcessGroupNCCL
+            opts = ProcessGroupNCCL.Options()
+            opts.is_high_priority_stream = True
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
 
     if args.workload != "attention":
         side_workload(args, t5b, dev)

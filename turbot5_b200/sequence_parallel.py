@@ -104,6 +104,18 @@ class _DeviceOps:
         return merge_attention_partials(parts, dtype)
 
 
+def high_priority_group(ranks=None):
+    """An NCCL process group whose collectives run on a high-priority stream.  The all-gather of
+    `sequence_parallel_attention_overlapped` is a kernel of a few blocks that has to start while the
+    attention over the local keys already fills every SM; on a stream of normal priority its blocks
+    queue behind the attention blocks that are still waiting for an SM and most of the gather ends
+    up exposed (4 GPUs, one layer over 100 000 tokens: 0.25 ms exposed, against 0.03 ms with this)."""
+    from torch.distributed import ProcessGroupNCCL
+    opts = ProcessGroupNCCL.Options()
+    opts.is_high_priority_stream = True
+    return dist.new_group(ranks=ranks, pg_options=opts)
+
+
 def sequence_parallel_attention_overlapped(q_local: torch.Tensor, kv_local: torch.Tensor,
                                            bias: Optional[torch.Tensor], seq_len: int, causal: bool = False,
                                            sm_scale: Optional[float] = None, NUM_BUCKETS: int = 32,
@@ -119,7 +131,9 @@ def sequence_parallel_attention_overlapped(q_local: torch.Tensor, kv_local: torc
     landed in this rank's memory, the keys before and after the local shard are attended and the
     (up to three) partials are merged -- softmax over disjoint key sets combines exactly through
     the log-sum-exps, in any order.  Returns (B, S, H, D) in q's dtype; rows of the last shard
-    beyond `seq_len` are unspecified.
+    beyond `seq_len` are unspecified.  Give it a `group` whose collectives run on a high-priority
+    stream (`high_priority_group()`, or `init_process_group(..., pg_options=...)`), otherwise the
+    gather starts late.
     """
     ops = ops or _DeviceOps
     world = dist.get_world_size(group) if dist.is_initialized() else 1
