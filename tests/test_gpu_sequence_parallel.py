@@ -64,7 +64,9 @@ def _worker(rank, world, port, L, q_out):
         # keys and over the gathered keys on either side, merged; checked against the CPU oracle
         from oracle import t5_oracle as orc
         kv = torch.cat([shard(k).reshape(1, S, H * 64), shard(v).reshape(1, S, H * 64)], dim=-1).contiguous()
-        o2 = t5b.sequence_parallel_attention_overlapped(shard(q), kv, table, L, sm_scale=1.0)
+        from turbot5_b200.sequence_parallel import high_priority_group
+        o2 = t5b.sequence_parallel_attention_overlapped(shard(q), kv, table, L, sm_scale=1.0,
+                                                        group=high_priority_group())
         torch.cuda.synchronize()
         t5b.check_device_status()
         want = orc.attention_basic(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), table.cpu(),
