@@ -37,6 +37,31 @@ L2_BYTES = 126 * 1024 * 1024
 NCU_DRAM_BYTES_PER_LAUNCH = 75.6e6 + 10.7e6
 
 
+def _bind_to_gpu_numa_node(index):
+    """Run this process on the CPUs of the NUMA node its GPU hangs off, before any pinned host buffer is
+    allocated: the end-to-end leg copies 100 MB per step over PCIe, and with several ranks on one host the
+    copies of all of them otherwise share whichever node the buffers happened to land on.  Returns the
+    node, or None when the machine does not say (then nothing is changed)."""
+    try:
+        pr = torch.cuda.get_device_properties(index)
+        bdf = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        node = int(open("/sys/bus/pci/devices/" + bdf + "/numa_node").read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)          # never widen what the launcher allowed
+        if not cpus:
+            return None
+        _bind_to_gpu_numa_node.before = os.sched_getaffinity(0)
+        os.sched_setaffinity(0, cpus)
+        return node
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None
+
+
 def flops_per_step(w):
     return 4.0 * w["B"] * w["H"] * w["L"] * w["L"] * w["D"]
 
@@ -260,6 +285,7 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: turbot5_b200 has no CPU path")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = _bind_to_gpu_numa_node(local)
     if world > 1:
         _keep_stdout_for_json()
         # The collectives of the sequence-parallel leg run on a high-priority stream: their few blocks are then
@@ -422,7 +448,8 @@ def main():
                          "kernel": "attn_fwd_kernel + attn_bwd_dq_kernel + attn_bwd_dkv_wide_kernel" if args.train
                                    else "attn_fwd_kernel<bf16>"},
             "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": set_bytes,
-                    "d2h_bytes_per_step": B * H * L * D * 2, "ms_per_step": e2e_ms, "steps": e2e_steps},
+                    "d2h_bytes_per_step": B * H * L * D * 2, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "host_numa_node_rank0": numa},
             "gpu_launches": args.steps * (4 if args.train else 1),
             "clocks": clocks,
         }
@@ -431,6 +458,9 @@ def main():
             line["mcycles_per_step"] = ms_step * clocks["sm_mhz"] / 1e3
             line["timed_region_s"] = ms_total / 1e3
         if world == 1 and not args.no_cpu_baseline:
+            before = getattr(_bind_to_gpu_numa_node, "before", None)
+            if before:                                  # the CPU baseline takes every core the launcher allowed
+                os.sched_setaffinity(0, before)
             cores = os.cpu_count() or 1
             pairs = B * H
             ref = _reference_functions()
