@@ -844,6 +844,18 @@ def secondary_measurements(t5b, dev):
             ms_mod = _time(lambda: enc(ids), 5, warm=2)
         out[f"t5_base_encoder_fwd_{Bt}x{Lt}"] = {"ms": ms, "tokens_per_s": Bt * Lt / (ms * 1e-3),
                                                  "ms_without_fused_token_kernels": ms_mod}
+    # a padded batch: 16 x 1024 with lengths uniform in [128, 1024].  The module path unpads and pads around every
+    # attention call and runs everything else on the padded batch; the fused pass packs the valid tokens once.
+    lens = torch.randint(128, 1025, (16,), generator=torch.Generator().manual_seed(1))
+    mask = (torch.arange(1024)[None, :] < lens[:, None]).to(torch.int64).to(dev)
+    n_tok = int(lens.sum())
+    with torch.no_grad():
+        ms_mod = _time(lambda: enc(ids, attention_mask=mask), 5, warm=2)
+        ms_packed = _time(lambda: enc.forward_fused(ids, attention_mask=mask), 5, warm=2)
+        ms_packed_known = _time(lambda: enc.forward_fused(ids, attention_mask=mask, packed_rows=n_tok), 5, warm=2)
+    out["t5_base_encoder_fwd_16x1024_padded"] = {
+        "valid_tokens": n_tok, "ms_module_path": ms_mod, "ms_packed_once": ms_packed,
+        "ms_packed_once_token_count_known": ms_packed_known, "valid_tokens_per_s": n_tok / (ms_packed * 1e-3)}
     del enc
     # the same encoder with block-local self-attention (blocks of 512) over one 65 536-token sequence
     cfg_l = T5StackConfig(attention_type="local", sliding_window=512)

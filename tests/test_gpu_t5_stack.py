@@ -90,6 +90,31 @@ def test_cuda_graph_decoding_equals_eager_decoding():
     assert (eager_last.float() - graph_last.float()).abs().max().item() < 1e-2
 
 
+def test_fused_encoder_packs_a_padded_batch_once():
+    """forward_fused with the padding mask: the valid tokens are packed after the embedding, every layer runs
+    on the packed rows, the result is scattered back -- same hidden states as the module path with the mask on
+    the valid rows, zeros on the padded ones; with and without the caller's bound on the token count."""
+    model = _model(torch.bfloat16, d_model=128, num_heads=4, d_ff=256)
+    g = torch.Generator().manual_seed(11)
+    B, L = 4, 300
+    lens = [300, 171, 1, 64]
+    ids = torch.randint(0, 128, (B, L), generator=g).cuda()
+    mask = torch.zeros((B, L), dtype=torch.int64)
+    for b, n in enumerate(lens):
+        mask[b, :n] = 1
+    mask = mask.cuda()
+    with torch.no_grad():
+        want = model.encoder(ids, attention_mask=mask)
+        got = model.encoder.forward_fused(ids, attention_mask=mask)
+        got2 = model.encoder.forward_fused(ids, attention_mask=mask, packed_rows=sum(lens) + 5)
+    torch.cuda.synchronize()
+    for b, n in enumerate(lens):
+        assert (got[b, :n].float() - want[b, :n].float()).abs().max().item() < 6e-2, b
+        assert (got[b, :n].float() - want[b, :n].float()).abs().mean().item() < 6e-3, b
+        assert torch.count_nonzero(got[b, n:]) == 0
+        assert torch.equal(got[b, :n], got2[b, :n])
+
+
 def test_cuda_graph_forward_equals_eager_forward():
     """The whole teacher-forced pass as one graph: same logits as the eager pass, for two different
     inputs through the same graph (the ids are copied into the graph's buffers), wrong shapes refused."""

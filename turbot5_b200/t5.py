@@ -24,7 +24,8 @@ from typing import List, Optional
 import torch
 from torch import nn
 
-from .attention import flash_attention_with_fusing_bias, flash_decoding_with_fusing_bias
+from .attention import (flash_attention_with_fusing_bias, flash_attention_with_fusing_bias_varlen,
+                        flash_decoding_with_fusing_bias)
 from .modules import (T5ATTENTION_TYPES, T5FlashAttention, T5LayerNorm, add_rms_layer_norm, gated_gelu,
                       rms_layer_norm)
 
@@ -191,7 +192,7 @@ class T5Stack(nn.Module):
 
     @torch.no_grad()
     def forward_fused(self, input_ids=None, inputs_embeds=None, seq_len=None, group=None, overlap=True, ops=None,
-                      encoder_hidden_states=None):
+                      encoder_hidden_states=None, attention_mask=None, packed_rows=None):
         """Forward pass without padding masks and without gradients, with the token-wise work fused
         around the attention path: per encoder block eight launches -- stacked q/k/v projection,
         attention, output projection, residual add fused with the next RMSNorm, stacked wi_0|wi_1
@@ -205,6 +206,15 @@ class T5Stack(nn.Module):
         token-wise operation runs on the shard, and each attention layer gathers the other ranks'
         keys and values (see `sequence_parallel_attention_overlapped`; `overlap=False` gathers first
         and attends once).  Returns the normed hidden states of the rows this call was given.
+        With `attention_mask` (encoder stacks; the raw 0/1 (B, L) mask, right-padded) the valid tokens
+        are packed ONCE, after the embedding: every projection, norm and feed-forward layer then runs
+        on the packed rows only, the attention layers use the packed-sequence kernel, and the result is
+        scattered back at the end (zeros at padded positions) -- where the reference unpads and pads
+        around every attention call and does everything else on the padded batch
+        (src/turbot5/model/attentions.py:405-470, model/padding.py:113-150).  `packed_rows` is an
+        upper bound on the number of valid tokens known to the caller (e.g. from the tokenizer; it must not
+        be smaller than the true count); without it the count is read back from the device once per call.
+
         `ops` replaces the library operators (an object with rms_layer_norm, add_rms_layer_norm,
         gated_gelu, attention and the partial / merge pair of the sequence-parallel path): tests of
         the sharding logic on CPU ranks pass reference implementations.
@@ -214,6 +224,18 @@ class T5Stack(nn.Module):
         if self.is_decoder and (encoder_hidden_states is None or seq_len is not None):
             raise ValueError("a decoder stack needs encoder_hidden_states and is not sequence parallel")
         x = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+        plan = None
+        if attention_mask is not None:
+            if self.is_decoder or seq_len is not None:
+                raise ValueError("attention_mask is taken by unsharded encoder stacks")
+            from .padding import get_unpad_plan, pad_rows, unpad_rows
+            plan = get_unpad_plan(attention_mask)
+            pad_shape = x.shape
+            n_valid = int(plan.cu_seqlens[-1]) if packed_rows is None else int(packed_rows)
+            n_valid = min(max(n_valid, 1), pad_shape[0] * pad_shape[1])
+            n_valid = -(-n_valid // 8) * 8                                  # whole 16-byte groups of rows for the views
+            n_valid = min(n_valid, pad_shape[0] * pad_shape[1])
+            x = unpad_rows(x, plan)[:n_valid].unsqueeze(0)                  # (1, T, d_model): kept tokens, zero tail
         B, S, _ = x.shape
         H, D = cfg.num_heads, cfg.d_kv
         HD = H * D
@@ -221,7 +243,7 @@ class T5Stack(nn.Module):
         eps = cfg.layer_norm_epsilon
         table = self._table()
         heads = lambda t: t.unflatten(-1, (H, D)).transpose(1, 2)        # (B, L, H*D) -> (B, H, L, D) view
-        x = x.contiguous() if inputs_embeds is None else x.clone(memory_format=torch.contiguous_format)
+        x = x.contiguous() if (inputs_embeds is None or plan is not None) else x.clone(memory_format=torch.contiguous_format)
         normed = ops.rms_layer_norm(x, self.block[0].layer[0].layer_norm.weight, eps).to(x.dtype)
         if seq_len is not None:
             from . import sequence_parallel as sp
@@ -230,7 +252,13 @@ class T5Stack(nn.Module):
             if type(att) is not T5FlashAttention:
                 raise ValueError("forward_fused covers full attention (attention_type='flash')")
             w = self._stacked_weights(i)
-            if seq_len is None:
+            if plan is not None:
+                qkv = nn.functional.linear(normed, w["qkv"])[0]                           # (T, 3*H*D)
+                q, k, v = (qkv[:, j * HD:(j + 1) * HD].unflatten(-1, (H, D)) for j in range(3))
+                attn = flash_attention_with_fusing_bias_varlen(q, k, v, table, plan.cu_seqlens, plan.cu_seqlens,
+                                                               plan.seqlen, plan.seqlen, causal=False, sm_scale=1.0,
+                                                               NUM_BUCKETS=nb, MAX_DISTANCE=md)
+            elif seq_len is None:
                 qkv = nn.functional.linear(normed, w["qkv"])
                 q, k, v = (heads(qkv[..., j * HD:(j + 1) * HD]) for j in range(3))
                 attn = ops.attention(q, k, v, table, self.is_decoder, 1.0, nb, md, 0).transpose(1, 2)
@@ -263,6 +291,8 @@ class T5Stack(nn.Module):
                 f = ff(normed)
             nxt = self.block[i + 1].layer[0].layer_norm if i + 1 < len(self.block) else self.final_layer_norm
             x, normed = ops.add_rms_layer_norm(x, f, nxt.weight, eps, inplace=True)
+        if plan is not None:
+            return pad_rows(normed[0], plan)          # (B, L, d_model), zeros at padded positions
         return normed
 
     # ---- generation with a preallocated cache (decoder only)
