@@ -115,6 +115,28 @@ def test_fused_encoder_packs_a_padded_batch_once():
         assert torch.equal(got[b, :n], got2[b, :n])
 
 
+def test_masked_inference_runs_packed_end_to_end():
+    """A padded batch through the model in inference mode: the encoder packs the valid tokens once and the
+    decoder's cross attention reads the packed states; same logits as the module path with the masks."""
+    model = _model(torch.bfloat16, d_model=128, num_heads=4, d_ff=256)
+    g = torch.Generator().manual_seed(12)
+    B, L, Ld = 3, 260, 24
+    lens = [260, 97, 5]
+    ids = torch.randint(0, 128, (B, L), generator=g).cuda()
+    dec = torch.randint(0, 128, (B, Ld), generator=g).cuda()
+    mask = torch.zeros((B, L), dtype=torch.int64)
+    for b, n in enumerate(lens):
+        mask[b, :n] = 1
+    mask = mask.cuda()
+    with torch.no_grad():
+        enc = model.encoder(ids, attention_mask=mask)
+        want = model.logits(model.decoder(dec, encoder_hidden_states=enc, encoder_attention_mask=mask))
+        got = model(ids, dec, attention_mask=mask)
+    torch.cuda.synchronize()
+    diff = (got.float() - want.float()).abs()
+    assert diff.max().item() < 0.15 and diff.mean().item() < 1.5e-2, (diff.max().item(), diff.mean().item())
+
+
 def test_cuda_graph_forward_equals_eager_forward():
     """The whole teacher-forced pass as one graph: same logits as the eager pass, for two different
     inputs through the same graph (the ids are copied into the graph's buffers), wrong shapes refused."""

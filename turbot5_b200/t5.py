@@ -192,7 +192,8 @@ class T5Stack(nn.Module):
 
     @torch.no_grad()
     def forward_fused(self, input_ids=None, inputs_embeds=None, seq_len=None, group=None, overlap=True, ops=None,
-                      encoder_hidden_states=None, attention_mask=None, packed_rows=None):
+                      encoder_hidden_states=None, attention_mask=None, packed_rows=None, return_packed=False,
+                      encoder_plan=None):
         """Forward pass without padding masks and without gradients, with the token-wise work fused
         around the attention path: per encoder block eight launches -- stacked q/k/v projection,
         attention, output projection, residual add fused with the next RMSNorm, stacked wi_0|wi_1
@@ -214,6 +215,10 @@ class T5Stack(nn.Module):
         (src/turbot5/model/attentions.py:405-470, model/padding.py:113-150).  `packed_rows` is an
         upper bound on the number of valid tokens known to the caller (e.g. from the tokenizer; it must not
         be smaller than the true count); without it the count is read back from the device once per call.
+        `return_packed=True` skips the final scatter and returns (packed states (T, d_model), plan): a
+        decoder stack takes them as `encoder_hidden_states` (2-D) with `encoder_plan=plan` and its cross
+        attention then reads the packed keys directly (packed-sequence kernel, no bias), so the encoder
+        output is never padded again.
 
         `ops` replaces the library operators (an object with rms_layer_norm, add_rms_layer_norm,
         gated_gelu, attention and the partial / merge pair of the sequence-parallel path): tests of
@@ -223,6 +228,8 @@ class T5Stack(nn.Module):
         cfg = self.cfg
         if self.is_decoder and (encoder_hidden_states is None or seq_len is not None):
             raise ValueError("a decoder stack needs encoder_hidden_states and is not sequence parallel")
+        if (encoder_plan is not None) != (encoder_hidden_states is not None and encoder_hidden_states.dim() == 2):
+            raise ValueError("packed encoder states (T, d_model) go together with encoder_plan")
         x = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
         plan = None
         if attention_mask is not None:
@@ -233,9 +240,13 @@ class T5Stack(nn.Module):
             pad_shape = x.shape
             n_valid = int(plan.cu_seqlens[-1]) if packed_rows is None else int(packed_rows)
             n_valid = min(max(n_valid, 1), pad_shape[0] * pad_shape[1])
-            n_valid = -(-n_valid // 8) * 8                                  # whole 16-byte groups of rows for the views
-            n_valid = min(n_valid, pad_shape[0] * pad_shape[1])
             x = unpad_rows(x, plan)[:n_valid].unsqueeze(0)                  # (1, T, d_model): kept tokens, zero tail
+            # With a caller's bound there may be rows past the last token.  The attention kernel does not
+            # write them, and whatever the allocation held there must not reach a later matrix product
+            # as the value row of a masked key (0 x NaN): those rows are zeroed after every attention call.
+            tail_rows = None
+            if packed_rows is not None:
+                tail_rows = (torch.arange(n_valid, device=x.device) >= plan.cu_seqlens[-1])[:, None, None]
         B, S, _ = x.shape
         H, D = cfg.num_heads, cfg.d_kv
         HD = H * D
@@ -247,6 +258,10 @@ class T5Stack(nn.Module):
         normed = ops.rms_layer_norm(x, self.block[0].layer[0].layer_norm.weight, eps).to(x.dtype)
         if seq_len is not None:
             from . import sequence_parallel as sp
+        if encoder_plan is not None:
+            if encoder_plan.batch != B:
+                raise ValueError("encoder_plan was made for another batch size")
+            cu_dec = torch.arange(B + 1, dtype=torch.int32, device=x.device) * S
         for i, blk in enumerate(self.block):
             att, ffl = blk.layer[0].SelfAttention, blk.layer[-1]
             if type(att) is not T5FlashAttention:
@@ -258,6 +273,8 @@ class T5Stack(nn.Module):
                 attn = flash_attention_with_fusing_bias_varlen(q, k, v, table, plan.cu_seqlens, plan.cu_seqlens,
                                                                plan.seqlen, plan.seqlen, causal=False, sm_scale=1.0,
                                                                NUM_BUCKETS=nb, MAX_DISTANCE=md)
+                if tail_rows is not None:
+                    attn = attn.masked_fill(tail_rows, 0)
             elif seq_len is None:
                 qkv = nn.functional.linear(normed, w["qkv"])
                 q, k, v = (heads(qkv[..., j * HD:(j + 1) * HD]) for j in range(3))
@@ -279,10 +296,19 @@ class T5Stack(nn.Module):
                 ca = blk.layer[1]
                 x, normed = ops.add_rms_layer_norm(x, o, ca.layer_norm.weight, eps, inplace=True)
                 catt = ca.EncDecAttention
-                q = heads(nn.functional.linear(normed, catt.q.weight))
                 ckv = nn.functional.linear(encoder_hidden_states, w["ckv"])
-                attn = ops.attention(q, heads(ckv[..., :HD]), heads(ckv[..., HD:]), None, False, 1.0, nb, md, 0)
-                o = nn.functional.linear(attn.transpose(1, 2).reshape(B, S, HD), catt.o.weight)
+                if encoder_plan is None:
+                    q = heads(nn.functional.linear(normed, catt.q.weight))
+                    attn = ops.attention(q, heads(ckv[..., :HD]), heads(ckv[..., HD:]), None, False, 1.0, nb, md, 0)
+                    attn = attn.transpose(1, 2)
+                else:
+                    # packed encoder states: every decoder sequence has S query rows, its keys are the valid
+                    # encoder tokens of the same batch row
+                    q = nn.functional.linear(normed, catt.q.weight).view(B * S, H, D)
+                    attn = flash_attention_with_fusing_bias_varlen(
+                        q, ckv[:, :HD].unflatten(-1, (H, D)), ckv[:, HD:].unflatten(-1, (H, D)), None, cu_dec,
+                        encoder_plan.cu_seqlens, S, encoder_plan.seqlen, causal=False, sm_scale=1.0)
+                o = nn.functional.linear(attn.reshape(B, S, HD), catt.o.weight)
             x, normed = ops.add_rms_layer_norm(x, o, ffl.layer_norm.weight, eps, inplace=True)
             ff = ffl.DenseReluDense
             if "wi" in w:
@@ -292,6 +318,8 @@ class T5Stack(nn.Module):
             nxt = self.block[i + 1].layer[0].layer_norm if i + 1 < len(self.block) else self.final_layer_norm
             x, normed = ops.add_rms_layer_norm(x, f, nxt.weight, eps, inplace=True)
         if plan is not None:
+            if return_packed:
+                return normed[0], plan
             return pad_rows(normed[0], plan)          # (B, L, d_model), zeros at padded positions
         return normed
 
@@ -533,11 +561,16 @@ class T5ForConditionalGeneration(nn.Module):
         return self.lm_head(decoder_hidden)
 
     def forward(self, input_ids, decoder_input_ids, attention_mask=None):
-        if attention_mask is None and not torch.is_grad_enabled() and self.cfg.attention_type == "flash" and \
+        if not torch.is_grad_enabled() and self.cfg.attention_type == "flash" and \
                 input_ids.is_cuda and self.shared.weight.dtype in (torch.bfloat16, torch.float16):
-            # inference without padding: fused token-wise kernels in both stacks
-            enc = self.encoder.forward_fused(input_ids)
-            return self.logits(self.decoder.forward_fused(decoder_input_ids, encoder_hidden_states=enc))
+            # inference: fused token-wise kernels in both stacks; a padded batch is packed once and the
+            # decoder's cross attention reads the packed encoder states
+            if attention_mask is None:
+                enc = self.encoder.forward_fused(input_ids)
+                return self.logits(self.decoder.forward_fused(decoder_input_ids, encoder_hidden_states=enc))
+            enc, plan = self.encoder.forward_fused(input_ids, attention_mask=attention_mask, return_packed=True)
+            return self.logits(self.decoder.forward_fused(decoder_input_ids, encoder_hidden_states=enc,
+                                                          encoder_plan=plan))
         enc = self.encoder(input_ids, attention_mask=attention_mask)
         dec = self.decoder(decoder_input_ids, encoder_hidden_states=enc, encoder_attention_mask=attention_mask)
         return self.logits(dec)
