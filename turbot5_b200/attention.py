@@ -215,7 +215,12 @@ def flash_attention_with_fusing_bias_varlen(q, k, v, bias, cu_seqlens_q, cu_seql
                                             NUM_BUCKETS=32, MAX_DISTANCE=128, *, return_lse=False,
                                             kernel="auto", window=None):
     """See `_varlen_forward`; differentiable in q, k, v and the bias table.  `window`: sliding window
-    |n - query position| < window inside every sequence (tensor-core kernels only)."""
+    |n - query position| < window inside every sequence (tensor-core kernels only).
+
+    q, k and v may have more rows than `cu_seqlens[-1]` (buffers sized for the worst case): those rows
+    are never attended and the matching output rows are not written, but the rows of k and v must
+    hold finite numbers -- the last tile of the last sequence can load them, a masked key has
+    probability 0, and 0 x NaN is NaN."""
     window = int(window or 0)
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, bias)):
         out, lse = _VarlenAttention.apply(q, k, v, bias, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
