@@ -137,6 +137,26 @@ def test_masked_inference_runs_packed_end_to_end():
     assert diff.max().item() < 0.15 and diff.mean().item() < 1.5e-2, (diff.max().item(), diff.mean().item())
 
 
+def test_generate_on_a_padded_batch_equals_the_step_by_step_module_path():
+    """`generate`: packed encoder pass, cache, graph-captured steps -- the same tokens as the encoder module
+    with the mask followed by eager cached decoding with the key lengths."""
+    model = _model(torch.bfloat16, d_model=128, num_heads=4, d_ff=256)
+    g = torch.Generator().manual_seed(13)
+    B, L = 3, 200
+    lens = [200, 61, 9]
+    ids = torch.randint(0, 128, (B, L), generator=g).cuda()
+    mask = torch.zeros((B, L), dtype=torch.int64)
+    for b, n in enumerate(lens):
+        mask[b, :n] = 1
+    mask = mask.cuda()
+    with torch.no_grad():
+        enc = model.encoder(ids, attention_mask=mask)
+        want, _ = model.greedy_decode(enc, 6, encoder_seqlens=torch.tensor(lens, dtype=torch.int32, device="cuda"))
+    got = model.generate(ids, attention_mask=mask, max_new_tokens=6)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+
+
 def test_cuda_graph_forward_equals_eager_forward():
     """The whole teacher-forced pass as one graph: same logits as the eager pass, for two different
     inputs through the same graph (the ids are copied into the graph's buffers), wrong shapes refused."""

@@ -587,6 +587,23 @@ class T5ForConditionalGeneration(nn.Module):
         return graphs[key](input_ids, decoder_input_ids)
 
     @torch.no_grad()
+    def generate(self, input_ids, attention_mask=None, max_new_tokens=32, use_cuda_graph=True):
+        """Greedy generation for a (padded) batch of prompts: the encoder pass on the packed valid tokens
+        (`forward_fused`), the cross-attention keys and values projected once into the preallocated cache,
+        then one captured single-token step per new token.  Returns the generated ids (B, max_new_tokens)."""
+        fused = self.cfg.attention_type == "flash" and input_ids.is_cuda and \
+            self.shared.weight.dtype in (torch.bfloat16, torch.float16)
+        seqlens = None
+        if attention_mask is not None:
+            seqlens = attention_mask.to(torch.int32).sum(-1).to(torch.int32)
+        if fused:
+            enc = self.encoder.forward_fused(input_ids, attention_mask=attention_mask)
+        else:
+            enc = self.encoder(input_ids, attention_mask=attention_mask)
+        tokens, _ = self.greedy_decode(enc, max_new_tokens, encoder_seqlens=seqlens, use_cuda_graph=use_cuda_graph)
+        return tokens
+
+    @torch.no_grad()
     def greedy_decode(self, encoder_hidden_states, steps, encoder_seqlens=None, use_cuda_graph=False):
         """Greedy generation from `decoder_start_token_id` with the preallocated cache.
 
