@@ -113,6 +113,9 @@ def test_fused_encoder_packs_a_padded_batch_once():
         assert (got[b, :n].float() - want[b, :n].float()).abs().mean().item() < 6e-3, b
         assert torch.count_nonzero(got[b, n:]) == 0
         assert torch.equal(got[b, :n], got2[b, :n])
+    with torch.no_grad():          # a bound below the true count does not drop tokens silently
+        bad = model.encoder.forward_fused(ids, attention_mask=mask, packed_rows=sum(lens) - 1)
+    assert torch.isnan(bad[0, 0]).all()
 
 
 def test_masked_inference_runs_packed_end_to_end():

@@ -213,8 +213,9 @@ class T5Stack(nn.Module):
         scattered back at the end (zeros at padded positions) -- where the reference unpads and pads
         around every attention call and does everything else on the padded batch
         (src/turbot5/model/attentions.py:405-470, model/padding.py:113-150).  `packed_rows` is an
-        upper bound on the number of valid tokens known to the caller (e.g. from the tokenizer; it must not
-        be smaller than the true count); without it the count is read back from the device once per call.
+        upper bound on the number of valid tokens known to the caller (e.g. from the tokenizer; with a bound
+        below the true count the result is all NaN); without it the count is read back from the device once
+        per call.
         `return_packed=True` skips the final scatter and returns (packed states (T, d_model), plan): a
         decoder stack takes them as `encoder_hidden_states` (2-D) with `encoder_plan=plan` and its cross
         attention then reads the packed keys directly (packed-sequence kernel, no bias), so the encoder
@@ -245,8 +246,12 @@ class T5Stack(nn.Module):
             # write them, and whatever the allocation held there must not reach a later matrix product
             # as the value row of a masked key (0 x NaN): those rows are zeroed after every attention call.
             tail_rows = None
+            cu_att = plan.cu_seqlens
             if packed_rows is not None:
                 tail_rows = (torch.arange(n_valid, device=x.device) >= plan.cu_seqlens[-1])[:, None, None]
+                # no row past the buffers is ever touched, whatever the bound: the attention calls see the
+                # sequences cut at it (the result is then marked below)
+                cu_att = plan.cu_seqlens.clamp(max=n_valid)
         B, S, _ = x.shape
         H, D = cfg.num_heads, cfg.d_kv
         HD = H * D
@@ -270,7 +275,7 @@ class T5Stack(nn.Module):
             if plan is not None:
                 qkv = nn.functional.linear(normed, w["qkv"])[0]                           # (T, 3*H*D)
                 q, k, v = (qkv[:, j * HD:(j + 1) * HD].unflatten(-1, (H, D)) for j in range(3))
-                attn = flash_attention_with_fusing_bias_varlen(q, k, v, table, plan.cu_seqlens, plan.cu_seqlens,
+                attn = flash_attention_with_fusing_bias_varlen(q, k, v, table, cu_att, cu_att,
                                                                plan.seqlen, plan.seqlen, causal=False, sm_scale=1.0,
                                                                NUM_BUCKETS=nb, MAX_DISTANCE=md)
                 if tail_rows is not None:
@@ -318,8 +323,17 @@ class T5Stack(nn.Module):
             nxt = self.block[i + 1].layer[0].layer_norm if i + 1 < len(self.block) else self.final_layer_norm
             x, normed = ops.add_rms_layer_norm(x, f, nxt.weight, eps, inplace=True)
         if plan is not None:
+            if packed_rows is not None:
+                # a bound below the true token count would silently drop tokens: make that loud (NaN
+                # everywhere) without reading anything back
+                normed = normed.masked_fill(plan.cu_seqlens[-1] > S, float("nan"))
             if return_packed:
                 return normed[0], plan
+            if packed_rows is not None and S < pad_shape[0] * pad_shape[1]:
+                # the scatter reads the packed row of every valid token: give it all of them
+                full = normed.new_full((pad_shape[0] * pad_shape[1], normed.shape[-1]), float("nan"))
+                full[:S] = normed[0]
+                return pad_rows(full, plan)
             return pad_rows(normed[0], plan)          # (B, L, d_model), zeros at padded positions
         return normed
 
