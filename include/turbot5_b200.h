@@ -122,7 +122,8 @@ typedef struct {
   int32_t dtype;          /* t5b_dtype of q, k, v, out */
   int32_t table_dtype;    /* t5b_dtype of table        */
   int32_t B, H, M, N, D;
-  int32_t total_q, total_k;   /* varlen only */
+  int32_t total_q, total_k;   /* varlen only: rows of q / of k and v; a cu_seqlens entry beyond them is cut there
+                               * (the kernels never touch a row past a tensor) */
   int32_t causal;
   int32_t num_buckets, max_distance;
   int32_t q_pos_offset;       /* dense only; the reference's P_SEQ = N - M for cached decoding */

@@ -43,3 +43,33 @@ def test_bounded_wait_runs_out_and_is_reported():
     torch.cuda.synchronize()
     t5b.check_device_status(dev)
     check_close(out, orc.attention_basic(q, k, v, table), dt, "launch after a reported give-up")
+
+
+def test_cu_seqlens_past_the_tensors_touch_nothing_beyond_them():
+    """A cumulative-length array that runs past the row count of the packed tensors (a caller's mistake)
+    is cut at the tensors: rows that exist are computed, nothing after them is read as data or written.
+    The tensors are views into larger buffers whose remaining rows hold a sentinel (so even a wrong
+    kernel would stay inside an allocation)."""
+    import turbot5_b200 as t5b
+    dt = torch.bfloat16
+    H, D, rows, spare = 2, 64, 300, 200
+    g = torch.Generator(device="cuda").manual_seed(3)
+    bufs = [torch.randn((rows + spare, H, D), generator=g, device="cuda").to(dt) for _ in range(3)]
+    for b in bufs:
+        b[rows:] = 777.0
+    q, k, v = (b[:rows] for b in bufs)
+    table = (torch.randn((32, H), generator=g, device="cuda") * 0.1).to(dt)
+    cu = torch.tensor([0, 200, 450], dtype=torch.int32, device="cuda")       # second sequence claims 250 rows, 100 exist
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+    out = t5b.flash_attention_with_fusing_bias_varlen(*leaves, table, cu, cu, 256, 256, sm_scale=1.0)
+    dout = torch.randn((rows, H, D), generator=g, device="cuda").to(dt)
+    grads = torch.autograd.grad(out, leaves, dout)
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    # the same call with the lengths as they really are gives the same rows
+    cu_ok = torch.tensor([0, 200, 300], dtype=torch.int32, device="cuda")
+    want = t5b.flash_attention_with_fusing_bias_varlen(q, k, v, table, cu_ok, cu_ok, 256, 256, sm_scale=1.0)
+    assert torch.equal(out.detach(), want)
+    assert all(torch.isfinite(x).all() for x in grads)
+    for b in bufs:
+        assert (b[rows:] == 777.0).all()

@@ -216,8 +216,8 @@ dkv_kernel(const __grid_constant__ AttnParams p, const __grid_constant__ Extra e
     const int seq = shared_seq[0];
     if (seq < 0) return;
     key0 = shared_seq[1] * TM;
-    k_row0 = p.cu_k[seq]; len_k = p.cu_k[seq + 1] - k_row0;
-    q_row0 = p.cu_q[seq]; len_q = p.cu_q[seq + 1] - q_row0;
+    k_row0 = min(p.cu_k[seq], p.total_k); len_k = min(p.cu_k[seq + 1], p.total_k) - k_row0;
+    q_row0 = min(p.cu_q[seq], p.total_q); len_q = min(p.cu_q[seq + 1], p.total_q) - q_row0;
     q_off = len_k - len_q;
   }
   const int md = spec.max_distance;

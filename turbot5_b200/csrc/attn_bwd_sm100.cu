@@ -696,8 +696,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     const int seq = ctl->work[0];
     if (seq < 0) return;
     key0 = ctl->work[1] * BM;
-    k_row0 = p.cu_k[seq]; len_k = p.cu_k[seq + 1] - k_row0;
-    q_row0 = p.cu_q[seq]; len_q = p.cu_q[seq + 1] - q_row0;
+    k_row0 = min(p.cu_k[seq], p.total_k); len_k = min(p.cu_k[seq + 1], p.total_k) - k_row0;
+    q_row0 = min(p.cu_q[seq], p.total_q); len_q = min(p.cu_q[seq + 1], p.total_q) - q_row0;
     q_off = len_k - len_q;
   }
   const int keys_in_tile = min(BM, len_k - key0);
@@ -1275,8 +1275,8 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
     const int seq = ctl->work[0];
     if (seq < 0) return;
     key0 = ctl->work[1] * BM;
-    k_row0 = p.cu_k[seq]; len_k = p.cu_k[seq + 1] - k_row0;
-    q_row0 = p.cu_q[seq]; len_q = p.cu_q[seq + 1] - q_row0;
+    k_row0 = min(p.cu_k[seq], p.total_k); len_k = min(p.cu_k[seq + 1], p.total_k) - k_row0;
+    q_row0 = min(p.cu_q[seq], p.total_q); len_q = min(p.cu_q[seq + 1], p.total_q) - q_row0;
     q_off = len_k - len_q;
   }
   const int keys_in_tile = min(BM, len_k - key0);

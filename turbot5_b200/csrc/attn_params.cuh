@@ -18,6 +18,7 @@ struct AttnParams {
   int64_t table_stride0;
   int32_t table_dtype;
   int32_t B, H, M, N, D;
+  int32_t total_q, total_k;   // packed tensors: rows of q / of k and v (cu_seqlens beyond them are cut: nothing past a tensor is touched)
   int32_t causal;
   int32_t q_pos_offset;
   int32_t local_block;   // > 0: block-local attention (tensor-core forward only)
@@ -54,6 +55,7 @@ inline AttnParams make_attn_params(const t5b_attn_args& a) {
   p.table_stride0 = a.table_stride0;
   p.table_dtype = a.table_dtype;
   p.B = a.B; p.H = a.H; p.M = a.M; p.N = a.N; p.D = a.D;
+  p.total_q = (int32_t)a.total_q; p.total_k = (int32_t)a.total_k;
   p.causal = a.causal;
   p.q_pos_offset = a.q_pos_offset;
   p.local_block = a.local_block;
@@ -161,8 +163,11 @@ __device__ __noinline__ TileWork find_varlen_tile(const AttnParams& p, int blk) 
   TileWork w;
   w.b = -1; w.q_row0 = 0; w.rows_in_tile = 0; w.k_row0 = 0; w.len_k = 0; w.qpos0 = 0;
   if (found_b >= 0) {
-    const int q0 = p.cu_q[found_b], q1 = p.cu_q[found_b + 1];
-    const int k0 = p.cu_k[found_b], k1 = p.cu_k[found_b + 1];
+    // (lengths cut at the tensors' row counts: a cu_seqlens that runs past a tensor must not turn into
+    // an access past it)
+    const int q0 = min(p.cu_q[found_b], p.total_q), q1 = min(p.cu_q[found_b + 1], p.total_q);
+    const int k0 = min(p.cu_k[found_b], p.total_k), k1 = min(p.cu_k[found_b + 1], p.total_k);
+    if ((q1 - q0) - tile_in_seq * TILE_M <= 0) return w;
     w.b = 0;
     w.q_row0 = q0 + tile_in_seq * TILE_M;
     w.rows_in_tile = min(TILE_M, (q1 - q0) - tile_in_seq * TILE_M);
