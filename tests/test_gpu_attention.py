@@ -76,6 +76,57 @@ def test_golden_other_head_dims_bf16(name):
     check_close(out, c["out"], torch.bfloat16, name)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [16, 32])
+@pytest.mark.parametrize("B,H,M,N,causal,off", [(2, 3, 300, 300, False, None), (1, 2, 128, 1024, False, 0),
+                                                 (1, 2, 640, 640, True, None), (1, 1, 1, 300, True, None),
+                                                 (1, 16, 2048, 2048, False, None)])
+def test_narrow_head_dims_on_the_tensor_core_kernel(B, H, M, N, causal, off, D, dtype):
+    # head dims 16 and 32 run as head dim 64 with zero-filled columns; forced onto the
+    # tensor-core kernel, non-contiguous (B, L, H, D) storage as the modules produce it
+    q = seeded((B, M, H, D), 1, dtype=dtype).transpose(1, 2)
+    k = seeded((B, N, H, D), 2, dtype=dtype).transpose(1, 2)
+    v = seeded((B, N, H, D), 3, dtype=dtype).transpose(1, 2)
+    table = seeded((32, H), 4, 0.1, dtype=dtype)
+    out = _run_dense(q, k, v, table, dtype, "tcgen05", causal=causal, q_pos_offset=off)
+    assert out.shape == (B, H, M, D)
+    if M * N > 1024 * 1024:
+        rows = [0, 777, M - 1]
+        want = orc.attention_basic(q[:, :2, rows] if off is not None else q[:, :2], k[:, :2], v[:, :2], table[:, :2],
+                                   causal=causal, q_pos_offset=off)[:, :, rows]
+        check_close(out[:, :2, rows], want, dtype)
+    else:
+        want = orc.attention_basic(q, k, v, table, causal=causal, q_pos_offset=off)
+        check_close(out, want, dtype, f"{(B, H, M, N, causal, off, D)}")
+
+
+@pytest.mark.parametrize("D", [16, 32])
+def test_narrow_head_dims_packed_and_token_major(D):
+    t5b = _ops()
+    dt = torch.bfloat16
+    lens = [5, 128, 0, 129, 300, 1]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    T, H = int(cu[-1]), 3
+    q, k, v = seeded((T, H, D), 1, dtype=dt), seeded((T, H, D), 2, dtype=dt), seeded((T, H, D), 3, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    want = orc.attention_basic_varlen(q, k, v, table, cu, cu, causal=False)
+    out = t5b.flash_attention_with_fusing_bias_varlen(
+        q.cuda(), k.cuda(), v.cuda(), table.cuda(), cu.cuda(), cu.cuda(), max(lens), max(lens),
+        sm_scale=1.0, kernel="tcgen05")
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    check_close(out, want, dt)
+    # token-major storage: the heads of one token are neighbours in the output, so a store wider
+    # than the head would land in the next head
+    B, L = 2, 200
+    qd, kd, vd = (seeded((B, L, H, D), s, dtype=dt).cuda().transpose(1, 2) for s in (5, 6, 7))
+    got = t5b.flash_attention_with_fusing_bias(qd, kd, vd, table.cuda(), sm_scale=1.0, kernel="tcgen05")
+    ref = t5b.flash_attention_with_fusing_bias(qd, kd, vd, table.cuda(), sm_scale=1.0, kernel="simt")
+    torch.cuda.synchronize()
+    assert got.transpose(1, 2).is_contiguous()
+    assert (got.float() - ref.float()).abs().max().item() < 2e-2
+
+
 @pytest.mark.parametrize("kernel", KERNELS_16BIT)
 def test_golden_cached_decode_rows(kernel):
     # unidirectional bias, query rows at the end of the keys.  The fixture has no

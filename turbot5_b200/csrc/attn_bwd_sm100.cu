@@ -1758,7 +1758,8 @@ int64_t sm100_bwd_workspace_bytes(const t5b_attn_bwd_args& g) {
 // True when the tensor-core backward can take this problem.
 bool sm100_bwd_supports(const t5b_attn_bwd_args& g) {
   const t5b_attn_args& a = g.fwd;
-  if (!sm100_supports(a)) return false;       // bf16/fp16, head dim 64 or 128, aligned
+  if (!sm100_supports(a)) return false;       // bf16/fp16, aligned
+  if (a.D != 64 && a.D != 128) return false;
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   if (!al16(g.dout) || !al16(g.dq) || !al16(g.dk) || !al16(g.dv)) return false;
   const int64_t s[] = {g.do_stride_b, g.do_stride_h, g.do_stride_m};

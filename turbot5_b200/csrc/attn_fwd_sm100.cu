@@ -638,7 +638,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     ctl->xchg[slot][half][r] = l_sum;
     if (ok && !pair_sync()) { ok = false; fail_code = 33; }
     l_sum += ctl->xchg[slot][half ^ 1][r];
-    if (ok) {
+    // Head dims 16 and 32 run as head dim 64: the tensor maps fill the missing columns of Q, K and
+    // V with zeros, so S is unchanged and the extra columns of O are zero; only the real ones
+    // (p.D) are written.
+    const int d_cols = p.D - half * OH;
+    if (ok && d_cols > 0) {
       const bool row_ok = r < rows_in_tile;
       const int64_t row = (int64_t)q_row0 + r;
       const int64_t o_off = (int64_t)b * p.o_stride_b + (int64_t)h * p.o_stride_h + row * p.o_stride_m + half * OH;
@@ -706,7 +710,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           float4* of = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o_off);
           #pragma unroll
           for (int i = 0; i < OH / 4; ++i)
-            of[i] = make_float4(o[4 * i] * inv_l, o[4 * i + 1] * inv_l, o[4 * i + 2] * inv_l, o[4 * i + 3] * inv_l);
+            if (4 * i < d_cols)
+              of[i] = make_float4(o[4 * i] * inv_l, o[4 * i + 1] * inv_l, o[4 * i + 2] * inv_l, o[4 * i + 3] * inv_l);
         } else
         #pragma unroll
         for (int i = 0; i < OH / 8; ++i) {
@@ -715,7 +720,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           w4.y = pack2<kBf16>(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
           w4.z = pack2<kBf16>(o[8 * i + 4] * inv_l, o[8 * i + 5] * inv_l);
           w4.w = pack2<kBf16>(o[8 * i + 6] * inv_l, o[8 * i + 7] * inv_l);
-          *reinterpret_cast<uint4*>(orow + i * 16) = w4;
+          if (8 * i < d_cols) *reinterpret_cast<uint4*>(orow + i * 16) = w4;
         }
         if (p.lse != nullptr && half == 0) {
           const float lse = l_sum > 0.f ? (m_use + log2f(l_sum)) * kLn2 : -INFINITY;
@@ -742,7 +747,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
 // True when the tcgen05 kernel can take this problem.
 bool sm100_supports(const t5b_attn_args& a) {
   if (a.dtype != T5B_BF16 && a.dtype != T5B_F16) return false;
-  if (a.D != 64 && a.D != 128) return false;
+  if (a.D != 16 && a.D != 32 && a.D != 64 && a.D != 128) return false;    // 16 and 32 run zero-padded to 64
   if (a.max_distance > 2048 && a.table) return false;
   if (a.local_block < 0 || a.window < 0) return false;
   if (a.window > 0 && (a.causal || a.local_block > 0)) return false;
@@ -766,7 +771,7 @@ bool sm100_supports(const t5b_attn_args& a) {
 TailPlan sm100_tail_plan(const t5b_attn_args& a) {
   using namespace sm100;
   if (sm100w_prefers(a)) return sm100w_tail_plan(a);
-  const int HD = a.D, BN = a.D == 64 ? Geo<64>::BN : Geo<128>::BN;
+  const int HD = a.D <= 64 ? 64 : 128, BN = HD == 64 ? Geo<64>::BN : Geo<128>::BN;
   TailPlan t;
   t.tiles_x = (a.M + BM - 1) / BM;
   const long long n_total = (long long)t.tiles_x * a.H * a.B;
@@ -807,19 +812,19 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
   if (sm100w_prefers(a)) return sm100w_attention_fwd(a, spec, stream);
   const bool varlen = a.cu_seqlens_q != nullptr;
   const bool bf16 = a.dtype == T5B_BF16;
-  const int HD = a.D;
+  const int HD = a.D <= 64 ? 64 : 128;    // width the kernel computes in; the tensor maps zero-fill columns past a.D
   const int BN = HD == 64 ? Geo<64>::BN : Geo<128>::BN;
   const int LUT_PAD = BM + BN;
   CUtensorMap mq, mk, mv;
   int st;
   if (varlen) {
-    if ((st = make_tmap(&mq, a.q, bf16, HD, BM, a.total_q, a.H, 1, a.q_stride_m, a.q_stride_h, 0)) != T5B_OK) return st;
-    if ((st = make_tmap(&mk, a.k, bf16, HD, BN, a.total_k, a.H, 1, a.k_stride_n, a.k_stride_h, 0)) != T5B_OK) return st;
-    if ((st = make_tmap(&mv, a.v, bf16, HD, BN, a.total_k, a.H, 1, a.v_stride_n, a.v_stride_h, 0)) != T5B_OK) return st;
+    if ((st = make_tmap(&mq, a.q, bf16, a.D, BM, a.total_q, a.H, 1, a.q_stride_m, a.q_stride_h, 0)) != T5B_OK) return st;
+    if ((st = make_tmap(&mk, a.k, bf16, a.D, BN, a.total_k, a.H, 1, a.k_stride_n, a.k_stride_h, 0)) != T5B_OK) return st;
+    if ((st = make_tmap(&mv, a.v, bf16, a.D, BN, a.total_k, a.H, 1, a.v_stride_n, a.v_stride_h, 0)) != T5B_OK) return st;
   } else {
-    if ((st = make_tmap(&mq, a.q, bf16, HD, BM, a.M, a.H, a.B, a.q_stride_m, a.q_stride_h, a.q_stride_b)) != T5B_OK) return st;
-    if ((st = make_tmap(&mk, a.k, bf16, HD, BN, a.N, a.H, a.B, a.k_stride_n, a.k_stride_h, a.k_stride_b)) != T5B_OK) return st;
-    if ((st = make_tmap(&mv, a.v, bf16, HD, BN, a.N, a.H, a.B, a.v_stride_n, a.v_stride_h, a.v_stride_b)) != T5B_OK) return st;
+    if ((st = make_tmap(&mq, a.q, bf16, a.D, BM, a.M, a.H, a.B, a.q_stride_m, a.q_stride_h, a.q_stride_b)) != T5B_OK) return st;
+    if ((st = make_tmap(&mk, a.k, bf16, a.D, BN, a.N, a.H, a.B, a.k_stride_n, a.k_stride_h, a.k_stride_b)) != T5B_OK) return st;
+    if ((st = make_tmap(&mv, a.v, bf16, a.D, BN, a.N, a.H, a.B, a.v_stride_n, a.v_stride_h, a.v_stride_b)) != T5B_OK) return st;
   }
   AttnParams p = make_attn_params(a);
   const int lut_n = a.table ? 2 * spec.max_distance + 1 + 2 * LUT_PAD : 0;

@@ -125,7 +125,8 @@ inline EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// (D, rows, H, B) view with element strides; box = one [box_rows][64 dims] sub-tile.
+// (D, rows, H, B) view with element strides; box = one [box_rows][64 dims] sub-tile.  With
+// D < 64 the box reaches past the tensor's inner extent and those columns arrive as zeros.
 inline int make_tmap(CUtensorMap* map, const void* ptr, bool bf16, int HD, int box_rows, int64_t rows, int H, int B,
                      int64_t stride_row, int64_t stride_h, int64_t stride_b) {
   EncodeTiledFn enc = get_encode_fn();
