@@ -41,8 +41,9 @@ typedef enum {
 typedef enum { T5B_F32 = 0, T5B_F16 = 1, T5B_BF16 = 2 } t5b_dtype;
 
 /* Which kernel family a forward call should use.  AUTO picks the tcgen05/TMA
- * kernel whenever dtype/shape/alignment allow (bf16 or fp16, head dim 64 or 128,
- * 16-byte aligned pointers and strides) and the CUDA-core kernel otherwise.
+ * kernel whenever dtype/shape/alignment allow (bf16 or fp16, 16-byte aligned pointers and
+ * strides; head dims 16 and 32 run as head dim 64 with the missing columns read as zeros and
+ * only the real ones written) and the CUDA-core kernel otherwise.
  * TCGEN05_POLYEXP is the tcgen05 kernel with EVERY exponential of an unmasked tile
  * evaluated by its FMA-pipe polynomial (the default kernel sends only a share of
  * them that way); it exists so that tests can pin that code path on its own.
@@ -176,8 +177,8 @@ T5B_API int64_t t5b_attention_workspace_bytes(const t5b_attn_args* args);
  *   dtable  float32 [num_buckets, H], contiguous; the gradient of the bias table is ADDED to
  *           it (the caller zeroes it); NULL when fwd.table is NULL.
  *   delta   float32 scratch of the shape of lse.
- * bf16/fp16 with head dim 64 or 128 and 16-byte aligned rows run on the tensor-core kernels;
- * everything else the forward accepts (float32, head dims 16/32) on CUDA-core kernels; fwd.kernel
+ * bf16/fp16 with 16-byte aligned rows run on the tensor-core kernels (head dims 16 and 32 as head
+ * dim 64, zero-filled); everything else the forward accepts (float32, other alignments) on CUDA-core kernels; fwd.kernel
  * selects as in the forward.  M > 0 and N > 0 (T5B_ERR_UNSUPPORTED otherwise: the gradients are
  * zero and the caller writes them).
  */

@@ -162,14 +162,15 @@ SIMT_CASES = [
 
 @pytest.mark.parametrize("dt,D,B,H,M,N,causal,off", SIMT_CASES)
 def test_cuda_core_backward_vs_oracle(dt, D, B, H, M, N, causal, off):
-    # float32 tensors and head dims other than 64 take the CUDA-core backward (float32 arithmetic)
+    # float32 tensors, rows that are not 16-byte aligned and kernel="simt" take the CUDA-core backward
+    # (float32 arithmetic)
     q = seeded((B, H, M, D), 1, 0.5, dtype=dt)
     k = seeded((B, H, N, D), 2, 0.5, dtype=dt)
     v = seeded((B, H, N, D), 3, dtype=dt)
     dout = seeded((B, H, M, D), 5, dtype=dt)
     table = seeded((32, H), 4, 0.1, dtype=dt)
     want = _oracle_grads(q, k, v, table, dout, causal=causal, q_pos_offset=off)
-    kw = dict(kernel="simt") if (dt != torch.float32 and D in (64, 128)) else {}
+    kw = dict(kernel="simt") if dt != torch.float32 else {}
     got = _cuda_grads(q, k, v, table, dout, dt, causal=causal, q_pos_offset=off, **kw)
     rel = 2e-4 if dt == torch.float32 else 1e-2
     check_close(got[0], want[0], dt, "out")
@@ -201,6 +202,59 @@ def test_head_dim_128_tensor_core_backward_vs_oracle(B, H, M, N, causal, off, dt
     check_close(got[0], want[0], dt, what + " out")
     for g, w, nm in zip(got[1:], want[1:], ("dq", "dk", "dv", "dtable")):
         check_grad_close(g, w, what + " " + nm, floor=2.0 if nm == "dtable" else 1e-6)
+
+
+CASES_NARROW = [
+    (2, 3, 512, 512, False, None),
+    (1, 2, 777, 777, True, None),
+    (2, 2, 128, 1024, False, 0),
+    (1, 2, 300, 300, False, 4000),
+    (1, 5, 2048, 2048, False, None),     # last wave split
+]
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [16, 32])
+@pytest.mark.parametrize("B,H,M,N,causal,off", CASES_NARROW)
+def test_narrow_head_dims_tensor_core_backward_vs_oracle(B, H, M, N, causal, off, D, dt):
+    # head dims 16 and 32 run as head dim 64 with zero-filled columns; token-major storage, so a
+    # gradient store wider than the head would land in the next head
+    q = seeded((B, M, H, D), 1, 0.5, dtype=dt).transpose(1, 2)
+    k = seeded((B, N, H, D), 2, 0.5, dtype=dt).transpose(1, 2)
+    v = seeded((B, N, H, D), 3, dtype=dt).transpose(1, 2)
+    dout = seeded((B, M, H, D), 5, dtype=dt).transpose(1, 2)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    want = _oracle_grads(q, k, v, table, dout, causal=causal, q_pos_offset=off)
+    got = _cuda_grads(q, k, v, table, dout, dt, causal=causal, q_pos_offset=off, kernel="tcgen05")
+    what = f"d{D} {(B, H, M, N, causal, off)}"
+    check_close(got[0], want[0], dt, what + " out")
+    for g, w, nm in zip(got[1:], want[1:], ("dq", "dk", "dv", "dtable")):
+        assert g.shape == w.shape
+        check_grad_close(g, w, what + " " + nm, floor=2.0 if nm == "dtable" else 1e-6)
+
+
+@pytest.mark.parametrize("D", [16, 32])
+def test_narrow_head_dims_backward_packed_sequences(D):
+    t5b = _ops()
+    dt = torch.bfloat16
+    lens = [5, 128, 0, 129, 300, 1, 257, 64]
+    cu = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int32)
+    T, H = int(cu[-1]), 3
+    q, k, v = seeded((T, H, D), 1, 0.7, dtype=dt), seeded((T, H, D), 2, 0.7, dtype=dt), seeded((T, H, D), 3, dtype=dt)
+    dout = seeded((T, H, D), 5, dtype=dt)
+    table = seeded((32, H), 4, 0.1, dtype=dt)
+    qf, kf, vf, tf = (t.float().clone().requires_grad_(True) for t in (q, k, v, table))
+    want = orc.attention_basic_varlen(qf, kf, vf, tf, cu, cu, causal=False)
+    (want * dout.float()).sum().backward()
+    qc, kc, vc, tc = (t.cuda().requires_grad_(True) for t in (q, k, v, table))
+    out = t5b.flash_attention_with_fusing_bias_varlen(qc, kc, vc, tc, cu.cuda(), cu.cuda(), max(lens), max(lens),
+                                                      sm_scale=1.0, kernel="tcgen05")
+    out.backward(dout.cuda())
+    torch.cuda.synchronize()
+    t5b.check_device_status()
+    for g, w, nm in ((qc.grad, qf.grad, "dq"), (kc.grad, kf.grad, "dk"), (vc.grad, vf.grad, "dv"),
+                     (tc.grad, tf.grad, "dtable")):
+        check_grad_close(g, w, f"d{D} packed " + nm, floor=2.0 if nm == "dtable" else 1e-6)
 
 
 def test_head_dim_128_backward_packed_sequences():

@@ -75,7 +75,7 @@ def flash_attention_with_fusing_bias(q, k, v, bias, causal=False, sm_scale=None,
     """See `_dense_forward`; differentiable in q, k, v and the bias table.  `local_block` turns the
     call into block-local attention (T5LocalAttention: the keys of the three neighbouring blocks);
     `window` into a sliding window |n - query position| < window (tensor-core kernels only:
-    bf16/fp16, head dim 64 or 128, not causal)."""
+    bf16/fp16, not causal)."""
     local_block = int(local_block or 0)
     window = int(window or 0)
     if local_block or window:
@@ -156,7 +156,7 @@ def _dense_forward(q, k, v, bias, causal=False, sm_scale=None, NUM_BUCKETS=32, M
         st = nat.lib().t5b_attention_fwd(a, nat.stream_ptr(q.device))
         if st == nat.ERR_UNSUPPORTED and (out_f32 or window):
             raise NotImplementedError("float32 partial outputs and sliding windows need the tensor-core forward "
-                                      "kernel (bf16/fp16, head dim 64 or 128, 16-byte aligned rows)")
+                                      "kernel (bf16/fp16, 16-byte aligned rows)")
         nat.check(st, "flash_attention_with_fusing_bias")
     if _keep is not None:
         _keep.update(args=a, q=q, k=k, v=v, table=table)
@@ -335,7 +335,7 @@ def _attention_backward(keep, out, lse, dout, varlen):
     if st == nat.ERR_UNSUPPORTED:
         raise NotImplementedError("no backward kernel for this call (max_distance above 2048, a sliding window or "
                                   "kernel='tcgen05' on a shape the tensor-core backward does not take: bf16/fp16, "
-                                  "head dim 64 or 128)")
+                                  "16-byte aligned rows)")
     nat.check(st, "flash_attention_with_fusing_bias (backward)")
     if dtable is not None:
         dtable = dtable[: table.shape[0]].to(table.dtype)

@@ -1,5 +1,5 @@
 // CUDA-core backward of the fused-bias attention for what the tensor-core backward does not
-// take: float32 tensors (all arithmetic in float32), head dims 16/32, rows that are not
+// take: float32 tensors (all arithmetic in float32) and 16-bit rows that are not
 // 16-byte aligned.  Same three steps and the same ownership as attn_bwd_sm100.cu (delta; one
 // block per 32 query rows for dQ and the bias-table gradient; one block per 32 keys for dK and
 // dV; nothing but the small table gradient is accumulated with atomics); same semantics as

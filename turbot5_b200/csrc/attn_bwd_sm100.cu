@@ -1,4 +1,5 @@
-// Backward of the fused relative-position-bias attention for sm_100a (bf16/fp16, head dim 64 or 128).
+// Backward of the fused relative-position-bias attention for sm_100a (bf16/fp16, head dim 64 or 128;
+// head dims 16 and 32 run as 64 with the missing columns zero-filled by the tensor maps).
 //
 // Three launches, as the reference's backward (src/turbot5/ops/fused_bias_attention.py:62-147):
 //
@@ -554,8 +555,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       }
       uint8_t* drow = reinterpret_cast<uint8_t*>(e.dq) + half * OH * 2 +
                       2 * ((int64_t)b * p.q_stride_b + (int64_t)h * p.q_stride_h + row * p.q_stride_m);
-      bool write_out = row_ok;
-      if (parts > 1 && row_ok) {
+      // head dims 16 and 32 run zero-filled to 64 (see the tensor maps): only the real columns are written
+      const int d_cols = p.D - half * OH;
+      bool write_out = row_ok && d_cols > 0;
+      if (parts > 1 && write_out) {
         float* acc = e.ws_dq + ((int64_t)tail_slot * BM + r) * HD + half * OH;
         #pragma unroll
         for (int i = 0; i < OH; ++i) atomicAdd(acc + i, o[i]);
@@ -581,7 +584,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           w4.y = pack2<kBf16>(o[8 * i + 2], o[8 * i + 3]);
           w4.z = pack2<kBf16>(o[8 * i + 4], o[8 * i + 5]);
           w4.w = pack2<kBf16>(o[8 * i + 6], o[8 * i + 7]);
-          *reinterpret_cast<uint4*>(drow + i * 16) = w4;
+          if (8 * i < d_cols) *reinterpret_cast<uint4*>(drow + i * 16) = w4;
         }
       }
     }
@@ -1138,8 +1141,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
           #pragma unroll
           for (int i = 0; i < 32; ++i) o[32 * c + i] = __uint_as_float(v[i]) * sc;
         }
-        bool write_out = key_ok;
-        if (parts > 1 && key_ok) {
+        const int d_cols = p.D - half * OH;      // head dims 16 and 32: only the real columns are written
+        bool write_out = key_ok && d_cols > 0;
+        if (parts > 1 && write_out) {
           float* acc = (t == 0 ? e.ws_dv : e.ws_dk) + ((int64_t)tail_slot * BM + r) * HD + half * OH;
           #pragma unroll
           for (int i = 0; i < OH; ++i) atomicAdd(acc + i, o[i]);
@@ -1165,7 +1169,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
             w4.y = pack2<kBf16>(o[8 * i + 2], o[8 * i + 3]);
             w4.z = pack2<kBf16>(o[8 * i + 4], o[8 * i + 5]);
             w4.w = pack2<kBf16>(o[8 * i + 6], o[8 * i + 7]);
-            *reinterpret_cast<uint4*>(dst + i * 16) = w4;
+            if (8 * i < d_cols) *reinterpret_cast<uint4*>(dst + i * 16) = w4;
           }
         }
       }
@@ -1635,8 +1639,8 @@ attn_bwd_dkv_wide_kernel(const __grid_constant__ CUtensorMap tmap_k, const __gri
         }
         #pragma unroll
         for (int i = 0; i < 16; ++i) o[i] = __uint_as_float(v[i]) * sc;
-        bool write_out = key_ok;
-        if (parts > 1 && key_ok) {
+        bool write_out = key_ok && cg * 16 < p.D;   // head dims 16 and 32: only the real columns are written
+        if (parts > 1 && write_out) {
           float* acc = (t == 0 ? e.ws_dv : e.ws_dk) + ((int64_t)tail_slot * BM + r) * HD + cg * 16;
           #pragma unroll
           for (int i = 0; i < 16; ++i) atomicAdd(acc + i, o[i]);
@@ -1693,11 +1697,11 @@ struct BwdPlan {
 #ifndef T5B_BWD_DKV_WIDE
 #define T5B_BWD_DKV_WIDE 1
 #endif
-static bool dkv_wide(const t5b_attn_args& a) { return T5B_BWD_DKV_WIDE != 0 && a.D == 64; }
+static bool dkv_wide(const t5b_attn_args& a) { return T5B_BWD_DKV_WIDE != 0 && a.D <= 64; }
 
 static BwdPlan sm100_bwd_plan(const t5b_attn_args& a) {
   using namespace sm100b;
-  const int HD = a.D;
+  const int HD = a.D <= 64 ? 64 : 128;      // width the kernels compute in
   BwdPlan t;
   const long long nq = (long long)((a.M + BM - 1) / BM) * a.H * a.B;
   const long long nk = (long long)((a.N + BM - 1) / BM) * a.H * a.B;
@@ -1758,8 +1762,7 @@ int64_t sm100_bwd_workspace_bytes(const t5b_attn_bwd_args& g) {
 // True when the tensor-core backward can take this problem.
 bool sm100_bwd_supports(const t5b_attn_bwd_args& g) {
   const t5b_attn_args& a = g.fwd;
-  if (!sm100_supports(a)) return false;       // bf16/fp16, aligned
-  if (a.D != 64 && a.D != 128) return false;
+  if (!sm100_supports(a)) return false;       // bf16/fp16, aligned; head dims 16 and 32 run zero-filled to 64
   auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
   if (!al16(g.dout) || !al16(g.dq) || !al16(g.dk) || !al16(g.dv)) return false;
   const int64_t s[] = {g.do_stride_b, g.do_stride_h, g.do_stride_m};
@@ -1772,7 +1775,7 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
   const t5b_attn_args& a = g.fwd;
   const bool varlen = a.cu_seqlens_q != nullptr;
   const bool bf16 = a.dtype == T5B_BF16;
-  const int HD = a.D;
+  const int HD = a.D <= 64 ? 64 : 128;      // width the kernels compute in; the tensor maps zero-fill columns past a.D
   AttnParams p = make_attn_params(a);
   p.tiles_x = (a.M + BM - 1) / BM;
   BwdExtra e;
@@ -1806,12 +1809,18 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
   // 1. delta
   {
     const long long n_rows = rows_q * a.H;
-    const int rows_per_block = 8 * (32 / (HD / 8));
+    const int rows_per_block = 8 * (32 / (a.D / 8));
     long long blocks = (n_rows + rows_per_block - 1) / rows_per_block;
     if (blocks > 148LL * 16) blocks = 148LL * 16;
     if (blocks > 0) {
       const unsigned nb = (unsigned)blocks;
-      if (HD == 64) {
+      if (a.D == 16) {
+        if (bf16) bwd_delta_kernel<__nv_bfloat16, 16><<<nb, 256, 0, stream>>>(p, e, n_rows);
+        else bwd_delta_kernel<__half, 16><<<nb, 256, 0, stream>>>(p, e, n_rows);
+      } else if (a.D == 32) {
+        if (bf16) bwd_delta_kernel<__nv_bfloat16, 32><<<nb, 256, 0, stream>>>(p, e, n_rows);
+        else bwd_delta_kernel<__half, 32><<<nb, 256, 0, stream>>>(p, e, n_rows);
+      } else if (a.D == 64) {
         if (bf16) bwd_delta_kernel<__nv_bfloat16, 64><<<nb, 256, 0, stream>>>(p, e, n_rows);
         else bwd_delta_kernel<__half, 64><<<nb, 256, 0, stream>>>(p, e, n_rows);
       } else {
@@ -1828,14 +1837,14 @@ int sm100_attention_bwd(const t5b_attn_bwd_args& g, const BucketSpec& spec, cuda
   const int Bm = varlen ? 1 : a.B;
   const int64_t qsb = varlen ? 0 : a.q_stride_b, ksb = varlen ? 0 : a.k_stride_b, vsb = varlen ? 0 : a.v_stride_b;
   const int64_t dsb = varlen ? 0 : g.do_stride_b;
-  if ((st = make_tmap(&q128, a.q, bf16, HD, BM, Mr, a.H, Bm, a.q_stride_m, a.q_stride_h, qsb)) != T5B_OK) return st;
-  if ((st = make_tmap(&do128, g.dout, bf16, HD, BM, Mr, a.H, Bm, g.do_stride_m, g.do_stride_h, dsb)) != T5B_OK) return st;
-  if ((st = make_tmap(&k64, a.k, bf16, HD, BT, Nr, a.H, Bm, a.k_stride_n, a.k_stride_h, ksb)) != T5B_OK) return st;
-  if ((st = make_tmap(&v64, a.v, bf16, HD, BT, Nr, a.H, Bm, a.v_stride_n, a.v_stride_h, vsb)) != T5B_OK) return st;
-  if ((st = make_tmap(&k128, a.k, bf16, HD, BM, Nr, a.H, Bm, a.k_stride_n, a.k_stride_h, ksb)) != T5B_OK) return st;
-  if ((st = make_tmap(&v128, a.v, bf16, HD, BM, Nr, a.H, Bm, a.v_stride_n, a.v_stride_h, vsb)) != T5B_OK) return st;
-  if ((st = make_tmap(&q64, a.q, bf16, HD, BT, Mr, a.H, Bm, a.q_stride_m, a.q_stride_h, qsb)) != T5B_OK) return st;
-  if ((st = make_tmap(&do64, g.dout, bf16, HD, BT, Mr, a.H, Bm, g.do_stride_m, g.do_stride_h, dsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&q128, a.q, bf16, a.D, BM, Mr, a.H, Bm, a.q_stride_m, a.q_stride_h, qsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&do128, g.dout, bf16, a.D, BM, Mr, a.H, Bm, g.do_stride_m, g.do_stride_h, dsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&k64, a.k, bf16, a.D, BT, Nr, a.H, Bm, a.k_stride_n, a.k_stride_h, ksb)) != T5B_OK) return st;
+  if ((st = make_tmap(&v64, a.v, bf16, a.D, BT, Nr, a.H, Bm, a.v_stride_n, a.v_stride_h, vsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&k128, a.k, bf16, a.D, BM, Nr, a.H, Bm, a.k_stride_n, a.k_stride_h, ksb)) != T5B_OK) return st;
+  if ((st = make_tmap(&v128, a.v, bf16, a.D, BM, Nr, a.H, Bm, a.v_stride_n, a.v_stride_h, vsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&q64, a.q, bf16, a.D, BT, Mr, a.H, Bm, a.q_stride_m, a.q_stride_h, qsb)) != T5B_OK) return st;
+  if ((st = make_tmap(&do64, g.dout, bf16, a.D, BT, Mr, a.H, Bm, g.do_stride_m, g.do_stride_h, dsb)) != T5B_OK) return st;
 
   const int lut_n = a.table ? 2 * spec.max_distance + 1 + 2 * LUT_PAD : 0;
   const size_t smem = HD == 64 ? smem_bytes<64>(lut_n) : smem_bytes<128>(lut_n);

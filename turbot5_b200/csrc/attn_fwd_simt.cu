@@ -1,6 +1,6 @@
 // CUDA-core forward kernel for the cases the tcgen05 kernel does not take:
-// float32 inputs (all arithmetic in float32, for the 1e-4 parity bound), head
-// dims 16/32/128, and rows that are not 16-byte aligned.  Same semantics, same
+// float32 inputs (all arithmetic in float32, for the 1e-4 parity bound) at head
+// dims 16/32/64/128, and rows that are not 16-byte aligned.  Same semantics, same
 // bias lookup, same packed-sequence scheduling; no throughput target.
 //
 // A block owns 32 query rows; four threads share a row, each holding a quarter
