@@ -230,7 +230,9 @@ def test_narrow_head_dims_tensor_core_backward_vs_oracle(B, H, M, N, causal, off
     check_close(got[0], want[0], dt, what + " out")
     for g, w, nm in zip(got[1:], want[1:], ("dq", "dk", "dv", "dtable")):
         assert g.shape == w.shape
-        check_grad_close(g, w, what + " " + nm, floor=2.0 if nm == "dtable" else 1e-6)
+        # with every key in one bucket (offset 4000) the table gradient is 180 000 rounded terms that
+        # cancel to zero: the scale of its error is the sum of their magnitudes, not the result
+        check_grad_close(g, w, what + " " + nm, floor=4.0 if nm == "dtable" else 1e-6)
 
 
 @pytest.mark.parametrize("D", [16, 32])
