@@ -227,24 +227,32 @@ merge_kernel(const __grid_constant__ MergeParams p, int vec_shift) {
   const int64_t b = bh / p.H;
   for (int m = blockIdx.x * rows_per_block + (threadIdx.x >> vec_shift); m < p.M; m += gridDim.x * rows_per_block) {
     const int64_t r = (int64_t)bh * p.M + m;
+    // every load of the row is issued before the first value is used: the partial rows do not
+    // wait for the log-sum-exps (a partial that saw no keys holds zeros, and is skipped below)
+    const int64_t off = b * p.po_stride_b + h * p.po_stride_h + (int64_t)m * p.po_stride_m + c * 4;
     float lse[kMaxParts];
-    float mx = -INFINITY;
+    float4 v[kMaxParts];
     #pragma unroll
     for (int s = 0; s < kMaxParts; ++s) {
       lse[s] = -INFINITY;
-      if (s < p.n_parts) { lse[s] = p.pl[s][r]; mx = fmaxf(mx, lse[s]); }
+      v[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (s < p.n_parts) {
+        lse[s] = __ldg(p.pl[s] + r);
+        v[s] = __ldcs(reinterpret_cast<const float4*>(p.po[s] + off));
+      }
     }
+    float mx = -INFINITY;
+    #pragma unroll
+    for (int s = 0; s < kMaxParts; ++s) mx = fmaxf(mx, lse[s]);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float wsum = 0.f;
-    const int64_t off = b * p.po_stride_b + h * p.po_stride_h + (int64_t)m * p.po_stride_m + c * 4;
     if (mx > -INFINITY) {
       #pragma unroll
       for (int s = 0; s < kMaxParts; ++s) {
-        if (s < p.n_parts && lse[s] > -INFINITY) {
+        if (lse[s] > -INFINITY) {
           const float wgt = __expf(lse[s] - mx);
-          const float4 v = *reinterpret_cast<const float4*>(p.po[s] + off);
-          acc.x = fmaf(wgt, v.x, acc.x); acc.y = fmaf(wgt, v.y, acc.y);
-          acc.z = fmaf(wgt, v.z, acc.z); acc.w = fmaf(wgt, v.w, acc.w);
+          acc.x = fmaf(wgt, v[s].x, acc.x); acc.y = fmaf(wgt, v[s].y, acc.y);
+          acc.z = fmaf(wgt, v[s].z, acc.z); acc.w = fmaf(wgt, v[s].w, acc.w);
           wsum += wgt;
         }
       }

@@ -115,12 +115,15 @@ __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+#ifndef T5B_WAIT_LIMIT_CYCLES
+#define T5B_WAIT_LIMIT_CYCLES 2000000000LL      // about a second
+#endif
 // Bounded wait: polls the barrier; gives up after `limit_cycles` SM cycles or as
 // soon as another thread of the block has raised *abort_flag (shared memory).
 // Returns false when it gave up.  Nothing in this library waits without a bound.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag,
-                                                  long long limit_cycles = 2000000000LL) {
+                                                  long long limit_cycles = T5B_WAIT_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
