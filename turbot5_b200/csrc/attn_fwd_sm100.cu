@@ -118,7 +118,9 @@ __host__ __device__ inline size_t smem_bytes(int lut_entries) {
 // kWindow: the sliding-window mode is compiled into a kernel of its own (with it in the plain kernel
 // the two extra per-row values of the masked path raised the spills of the softmax loop from 108 to
 // 264 bytes and the 8k forward went from 0.577 to 0.67 ms).
-template <bool kBf16, int HD, int kPoly, bool kWindow = false>
+// kNarrow: head dims 16 and 32 (run as head dim 64, see the epilogue) have kernels of their own for the
+// same reason: the column test in the epilogue, outside every loop, cost the plain kernel 3 %.
+template <bool kBf16, int HD, int kPoly, bool kWindow = false, bool kNarrow = false>
 __global__ void __launch_bounds__(HD == 64 ? 288 : MAX_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
                 const __grid_constant__ CUtensorMap tmap_k,
@@ -641,7 +643,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
     // Head dims 16 and 32 run as head dim 64: the tensor maps fill the missing columns of Q, K and
     // V with zeros, so S is unchanged and the extra columns of O are zero; only the real ones
     // (p.D) are written.
-    const int d_cols = p.D - half * OH;
+    const int d_cols = kNarrow ? p.D - half * OH : OH;
     if (ok && d_cols > 0) {
       const bool row_ok = r < rows_in_tile;
       const int64_t row = (int64_t)q_row0 + r;
@@ -710,7 +712,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           float4* of = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o_off);
           #pragma unroll
           for (int i = 0; i < OH / 4; ++i)
-            if (4 * i < d_cols)
+            if (!kNarrow || 4 * i < d_cols)
               of[i] = make_float4(o[4 * i] * inv_l, o[4 * i + 1] * inv_l, o[4 * i + 2] * inv_l, o[4 * i + 3] * inv_l);
         } else
         #pragma unroll
@@ -720,7 +722,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q,
           w4.y = pack2<kBf16>(o[8 * i + 2] * inv_l, o[8 * i + 3] * inv_l);
           w4.z = pack2<kBf16>(o[8 * i + 4] * inv_l, o[8 * i + 5] * inv_l);
           w4.w = pack2<kBf16>(o[8 * i + 6] * inv_l, o[8 * i + 7] * inv_l);
-          if (8 * i < d_cols) *reinterpret_cast<uint4*>(orow + i * 16) = w4;
+          if (!kNarrow || 8 * i < d_cols) *reinterpret_cast<uint4*>(orow + i * 16) = w4;
         }
         if (p.lse != nullptr && half == 0) {
           const float lse = l_sum > 0.f ? (m_use + log2f(l_sum)) * kLn2 : -INFINITY;
@@ -853,17 +855,21 @@ int sm100_attention_fwd(const t5b_attn_args& a, const BucketSpec& spec, cudaStre
     grid = dim3((unsigned)blocks, 1, 1);
   }
   if (grid.y > 65535 || grid.z > 65535) return T5B_ERR_SHAPE;
-  // kernel variant: [head dim 128][bf16][0: default, 1: every exponential on the FMA pipe, 2: sliding window]
+  // kernel variant: [head dim 128][bf16][0: default, 1: every exponential on the FMA pipe, 2: sliding window,
+  // 3: default for head dims 16 and 32].  At head dim 64 the variants 1 and 2 also take the narrow heads.
   using KernelFn = void (*)(CUtensorMap, CUtensorMap, CUtensorMap, AttnParams, BucketSpec);
-  static const KernelFn kernels[2][2][3] = {
-      {{attn_fwd_kernel<false, 64, T5B_FWD_POLY64>, attn_fwd_kernel<false, 64, 8>, attn_fwd_kernel<false, 64, 0, true>},
-       {attn_fwd_kernel<true, 64, T5B_FWD_POLY64>, attn_fwd_kernel<true, 64, 8>, attn_fwd_kernel<true, 64, 0, true>}},
-      {{attn_fwd_kernel<false, 128, 0>, attn_fwd_kernel<false, 128, 8>, attn_fwd_kernel<false, 128, 0, true>},
-       {attn_fwd_kernel<true, 128, 0>, attn_fwd_kernel<true, 128, 8>, attn_fwd_kernel<true, 128, 0, true>}}};
-  const int all_poly = a.window > 0 ? 2 : (a.kernel == T5B_KERNEL_TCGEN05_POLYEXP ? 1 : 0);
+  static const KernelFn kernels[2][2][4] = {
+      {{attn_fwd_kernel<false, 64, T5B_FWD_POLY64>, attn_fwd_kernel<false, 64, 8, false, true>,
+        attn_fwd_kernel<false, 64, 0, true, true>, attn_fwd_kernel<false, 64, T5B_FWD_POLY64, false, true>},
+       {attn_fwd_kernel<true, 64, T5B_FWD_POLY64>, attn_fwd_kernel<true, 64, 8, false, true>,
+        attn_fwd_kernel<true, 64, 0, true, true>, attn_fwd_kernel<true, 64, T5B_FWD_POLY64, false, true>}},
+      {{attn_fwd_kernel<false, 128, 0>, attn_fwd_kernel<false, 128, 8>, attn_fwd_kernel<false, 128, 0, true>, nullptr},
+       {attn_fwd_kernel<true, 128, 0>, attn_fwd_kernel<true, 128, 8>, attn_fwd_kernel<true, 128, 0, true>, nullptr}}};
+  int all_poly = a.window > 0 ? 2 : (a.kernel == T5B_KERNEL_TCGEN05_POLYEXP ? 1 : 0);
+  if (all_poly == 0 && a.D < 64) all_poly = 3;
   const KernelFn kern = kernels[HD == 64 ? 0 : 1][bf16 ? 1 : 0][all_poly];
   // opt in to > 48 KB of dynamic shared memory once per device and kernel (any thread may get here first)
-  static std::atomic<bool> attr_set[64][12];
+  static std::atomic<bool> attr_set[64][16];
   int dev = 0;
   cudaGetDevice(&dev);
   const int which = (bf16 ? 1 : 0) + (HD == 64 ? 0 : 2) + 4 * all_poly;
