@@ -45,8 +45,9 @@ typedef enum { T5B_F32 = 0, T5B_F16 = 1, T5B_BF16 = 2 } t5b_dtype;
  * strides; head dims 16 and 32 run as head dim 64 with the missing columns read as zeros and
  * only the real ones written) and the CUDA-core kernel otherwise.
  * TCGEN05_POLYEXP is the tcgen05 kernel with EVERY exponential of an unmasked tile
- * evaluated by its FMA-pipe polynomial (the default kernel sends only a share of
- * them that way); it exists so that tests can pin that code path on its own.
+ * evaluated by its FMA-pipe polynomial (the default kernel sends a compile-time share of
+ * them that way, none as shipped: it measured no faster); it exists so that tests can pin that
+ * code path on its own.
  * The tcgen05 family has a second forward kernel at head dim 64 that gives a block two
  * 128-row query tiles and one thread per row; TCGEN05_2TILE selects it where it applies
  * (full attention, more than 128 query rows; the default kernel otherwise).  It is slower
