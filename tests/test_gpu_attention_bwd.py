@@ -355,7 +355,8 @@ def test_last_wave_split_leaves_its_scratch_clean():
             assert torch.count_nonzero(ws) == 0
 
 
-@pytest.mark.parametrize("D,L,bl", [(64, 1024, 256), (64, 300, 128), (64, 200, 512), (128, 768, 128)])
+@pytest.mark.parametrize("D,L,bl", [(64, 1024, 256), (64, 300, 128), (64, 200, 512), (128, 768, 128), (32, 640, 128),
+                                    (16, 300, 128)])
 def test_block_local_attention_gradients_vs_oracle(D, L, bl):
     t5b = _ops()
     dt = torch.bfloat16
@@ -376,7 +377,7 @@ def test_block_local_attention_gradients_vs_oracle(D, L, bl):
 
 
 @pytest.mark.parametrize("D,bl,lens", [(64, 256, [1500, 700, 1]), (64, 128, [700, 129, 128]), (128, 256, [900, 300]),
-                                       (64, 1024, [300, 77]), (64, 512, [3000])])
+                                       (64, 1024, [300, 77]), (64, 512, [3000]), (32, 128, [700, 129, 128]), (16, 256, [900, 300])])
 def test_sliding_window_gradients_vs_oracle(D, bl, lens):
     """Packed sequences with the sliding window |key - query| < window (T5LocalAttention with its
     padding mask): dq, dk, dv and the bias-table gradient against float32 autograd of the oracle."""
@@ -405,7 +406,7 @@ def test_sliding_window_gradients_vs_oracle(D, bl, lens):
         check_grad_close(g.grad, w.grad, f"window d{D} block {bl} {nm}", floor=2.0 if nm == "dtable" else 1e-6)
 
 
-@pytest.mark.parametrize("D,L,bl", [(64, 1100, 256), (128, 640, 128)])
+@pytest.mark.parametrize("D,L,bl", [(64, 1100, 256), (128, 640, 128), (32, 640, 128)])
 def test_dense_sliding_window_gradients_vs_oracle(D, L, bl):
     t5b = _ops()
     dt = torch.bfloat16

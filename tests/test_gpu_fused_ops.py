@@ -63,10 +63,12 @@ def test_gated_gelu_vs_torch(rows, f, dt):
                                                  (300, 1000, (0, 77, 600, 1000), 350, False),
                                                  (256, 900, (0, 500, 900), None, True),
                                                  (100, 400, (0, 130, 400), 150, False)])
-def test_partials_over_key_slices_merge_to_the_full_result(M, N, cuts, off, causal, dt):
+@pytest.mark.parametrize("D", [64, 32])
+def test_partials_over_key_slices_merge_to_the_full_result(M, N, cuts, off, causal, dt, D):
     from turbot5_b200.attention import flash_attention_partial, merge_attention_partials
     B, H = 2, 3
-    q, k, v = seeded((B, H, M, 64), 1, dtype=dt), seeded((B, H, N, 64), 2, dtype=dt), seeded((B, H, N, 64), 3, dtype=dt)
+    # token-major storage (the heads of a token side by side), as the sequence-parallel encoder has it
+    q, k, v = (seeded((B, L_, H, D), sd, dtype=dt).transpose(1, 2) for sd, L_ in ((1, M), (2, N), (3, N)))
     table = seeded((32, H), 4, 0.1, dtype=dt)
     qpos = (N - M) if off is None else off
     want = orc.attention_basic(q, k, v, table, causal=causal, q_pos_offset=qpos)
