@@ -507,6 +507,12 @@ def token_kernel_measurements(t5b, dev, iters=30):
         ms = _time(fn, iters)
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[name] = {"ms": ms, "GB/s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"], "algorithmic_bytes": nbytes}
+    # a plain device copy of the RMSNorm's bytes (153.6 MB in, 153.6 MB out), timed the same way: what a launch of
+    # this size reaches here (the peak in the fractions above is a copy of a much larger buffer)
+    y = torch.empty_like(x)
+    ms = _time(lambda: y.copy_(x), iters)
+    out["rmsnorm_100000x768_bf16"]["copy_of_the_same_bytes_ms"] = ms
+    out["rmsnorm_100000x768_bf16"]["frac_of_that_copy"] = ms / out["rmsnorm_100000x768_bf16"]["ms"]
     return out, steps
 
 
