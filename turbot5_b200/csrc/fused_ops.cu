@@ -75,12 +75,24 @@ template <typename T, typename TW, int VPL>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(const T* __restrict__ hidden, const T* __restrict__ branch, const TW* __restrict__ w,
                    T* __restrict__ hidden_out, T* __restrict__ normed, int64_t rows, int d,
-                   int64_t hs, int64_t bs, int64_t hos, int64_t ns, float eps) {
+                   int64_t hs, int64_t bs, int64_t hos, int64_t ns, float eps, int w_aligned) {
   const int lane = threadIdx.x & 31;
   const int nvec = d / 8;
   const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
   const float inv_d = 1.f / (float)d;
+  // this lane's weights, read once (vector loads when the weight is aligned for them) and kept for every row
+  struct alignas(8 * sizeof(TW)) WVec { TW v[8]; };
+  WVec wv[VPL];
+  #pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + i * 32;
+    if (v < nvec && w_aligned) wv[i] = *reinterpret_cast<const WVec*>(w + v * 8);
+    else {
+      #pragma unroll
+      for (int k = 0; k < 8; ++k) wv[i].v[k] = v < nvec ? w[v * 8 + k] : from_float<TW>(0.f);
+    }
+  }
   for (int64_t row = warp_id; row < rows; row += n_warps) {
     uint4 a[VPL], b[VPL];
     #pragma unroll
@@ -120,7 +132,7 @@ add_rmsnorm_kernel(const T* __restrict__ hidden, const T* __restrict__ branch, c
         for (int k = 0; k < 8; ++k) {
           float xn = to_float<T>(ea[k]) * rstd;
           if (sizeof(TW) == 2) xn = to_float<TW>(from_float<TW>(xn));   // first rounding, to the weight's type
-          eo[k] = from_float<T>(to_float<TW>(w[v * 8 + k]) * xn);
+          eo[k] = from_float<T>(to_float<TW>(wv[i].v[k]) * xn);
         }
         st16(normed + row * ns + v * 8, o4);
       }
@@ -139,7 +151,8 @@ static int launch_add_rmsnorm(const void* hidden, const void* branch, const void
     static std::atomic<int> per_sm{0}; \
     const int64_t blocks = balanced_blocks((rows + 7) / 8, resident_blocks(kern, 256, per_sm)); \
     kern<<<(unsigned)blocks, 256, 0, stream>>>((const T*)hidden, (const T*)branch, (const TW*)w, (T*)hidden_out, \
-                                               (T*)normed, rows, d, hs, bs, hos, ns, eps); } while (0)
+                                               (T*)normed, rows, d, hs, bs, hos, ns, eps, \
+                                               ((uintptr_t)w % (8 * sizeof(TW))) == 0 ? 1 : 0); } while (0)
   if (vpl <= 1) T5B_AR_LAUNCH(1);
   else if (vpl == 2) T5B_AR_LAUNCH(2);
   else if (vpl == 3) T5B_AR_LAUNCH(3);
